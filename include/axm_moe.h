@@ -1,0 +1,199 @@
+/*
+ * axm_moe.h — C ABI of the B200 (sm_100a) mixture-of-experts layer.
+ *
+ * One layer call is   router -> permute (dispatch) -> grouped SwiGLU expert FFN
+ * -> weighted combine (+ residual).  Every entry point takes plain device
+ * pointers and sizes, enqueues its kernels on the caller's stream, never
+ * synchronises and never allocates: scratch memory comes from the caller as one
+ * workspace whose size axm_moe_workspace_bytes() reports.
+ *
+ * The layer replaces the MoE branch of PROJECT-AXIOM's CUDA library.  Each
+ * declaration names the interface of that engine it stands in for, as
+ * file:line inside the engine's source tree.  Tensor layouts are the engine's:
+ *
+ *   x, out            [T][D]      bf16, row-major        (core/src/CUDA/kernel/moe_router.cu:205-220)
+ *   router weights    [D][E]      bf16 or fp32, E contiguous (core/src/CUDA/util/gpu_types.cuh:147-148)
+ *   gate, up weights  [E][D][F]   bf16, F contiguous     (core/src/CUDA/util/gpu_types.cuh:152-155)
+ *   down weights      [E][F][D]   bf16, D contiguous     (core/src/CUDA/util/gpu_types.cuh:156-157)
+ *   logits            [T][E]      fp32
+ *   expert indices    [T][k]      int32, slot 0 = largest probability
+ *   gate weights      [T][k]      fp32
+ *   histogram         [E]         int32
+ *
+ * All functions return AXM_OK (0) or a negative AxmStatus; axm_last_error()
+ * returns a thread-local description of the last failure.  There is no CPU
+ * fallback: on a machine without a usable sm_100 device every compute entry
+ * point fails with AXM_ERR_DEVICE.
+ */
+#ifndef AXM_MOE_H
+#define AXM_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define AXM_API __attribute__((visibility("default")))
+#else
+#define AXM_API
+#endif
+
+typedef enum AxmStatus {
+  AXM_OK = 0,
+  AXM_ERR_ARGUMENT = -1,  /* null pointer, zero or unsupported dimension */
+  AXM_ERR_WORKSPACE = -2, /* workspace missing, misaligned or too small */
+  AXM_ERR_DEVICE = -3,    /* no sm_100 device / driver entry point missing */
+  AXM_ERR_LAUNCH = -4,    /* cudaGetLastError() after an enqueue */
+  AXM_ERR_TIMEOUT = -5    /* a bounded device-side wait gave up (status word) */
+} AxmStatus;
+
+enum { AXM_ROUTER_BF16 = 0, AXM_ROUTER_FP32 = 1 };
+
+enum {
+  AXM_FLAG_RESIDUAL = 1,       /* out = bf16(x + y), else out = y            */
+  AXM_FLAG_HIST_ACCUMULATE = 2 /* histogram[e] += counts, else histogram = counts */
+};
+
+/* Problem shape.  D and F must be multiples of 8 (16-byte rows); E <= 256;
+ * 1 <= k <= min(E, 8); S <= 8. */
+typedef struct AxmMoeDesc {
+  int32_t tokens;       /* T */
+  int32_t d_model;      /* D */
+  int32_t d_ff;         /* F */
+  int32_t num_experts;  /* E, routed experts */
+  int32_t top_k;        /* k */
+  int32_t num_shared;   /* S, always-on experts added unweighted */
+  int32_t router_dtype; /* AXM_ROUTER_BF16 | AXM_ROUTER_FP32 */
+  int32_t flags;        /* AXM_FLAG_* */
+} AxmMoeDesc;
+
+/* Device pointers.  Inputs first; outputs the caller wants published may be
+ * NULL, in which case the layer keeps them in its workspace. */
+typedef struct AxmMoeTensors {
+  const void* x;             /* [T][D] bf16 */
+  const void* router_w;      /* [D][E] */
+  const float* router_bias;  /* [E] fp32 added to the logits, or NULL */
+  const void* w_gate;        /* [E][D][F] bf16 */
+  const void* w_up;          /* [E][D][F] bf16 */
+  const void* w_down;        /* [E][F][D] bf16 */
+  const void* shared_gate;   /* [S][D][F] bf16 or NULL when S == 0 */
+  const void* shared_up;     /* [S][D][F] */
+  const void* shared_down;   /* [S][F][D] */
+  float* logits;             /* [T][E] fp32, optional */
+  int32_t* topk_idx;         /* [T][k], optional */
+  float* topk_gate;          /* [T][k], optional */
+  int32_t* histogram;        /* [E], optional */
+  int32_t* offsets;          /* [E+1] exclusive scan of this call's counts, optional */
+  int32_t* row_src;          /* [T*k] permuted row r came from slot t*k+i, optional */
+  int32_t* slot_dst;         /* [T*k] slot t*k+i went to permuted row r, optional */
+  void* y;                   /* [T][D] bf16 weighted expert sum before the residual, optional */
+  void* out;                 /* [T][D] bf16, required; may alias x */
+} AxmMoeTensors;
+
+/* Thread-local text of the last error returned on this thread. */
+AXM_API const char* axm_last_error(void);
+
+/* Library / build identification: "axm_moe <version> sm_100a". */
+AXM_API const char* axm_version(void);
+
+/* Number of kernels one axm_moe_forward() call enqueues for this shape. */
+AXM_API int axm_moe_forward_launches(const AxmMoeDesc* desc);
+
+/* Bytes of scratch axm_moe_forward() needs for this shape (256-byte aligned
+ * base required).  Replaces the lazily allocated activation buffers of
+ * core/src/CUDA/kernel/moe_router.cu:222-261. */
+AXM_API int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes);
+
+/* The whole layer.  Replaces forward_mixture_experts
+ * (core/src/CUDA/kernel/moe_router.cuh:30-36, moe_router.cu:205-320). */
+AXM_API int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
+                            void* workspace, size_t workspace_bytes, void* stream);
+
+/* The same call for a caller whose activations live in host memory: copies x
+ * from (pinned) host memory, runs the layer, copies out back, all on `stream`,
+ * and synchronises the stream before returning.  Weights stay device pointers.
+ * Mirrors the host wrapper AI::forward_mixture_experts (core/src/ai.cpp:593-623).
+ * d_x / d_out are device staging buffers of T*D bf16 each (may be equal). */
+AXM_API int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
+                                 const void* h_x, void* h_out, void* d_x, void* d_out,
+                                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Device address of the int32 status word inside a workspace.  The GEMM kernels
+ * store a non-zero code there when one of their bounded waits gives up; a
+ * caller that synchronises can read it back.  No reference counterpart (the
+ * engine reports enqueue-time errors only, core/src/CUDA/kernel/moe_router.cu:319). */
+AXM_API int axm_moe_status_word(const AxmMoeDesc* desc, void* workspace, int32_t** status);
+
+/* ---- stages, callable on their own (tests, expert-parallel drivers) ---- */
+
+/* Fused router: logits (+bias), softmax, top-k, gates, per-block counts.
+ * Replaces top2_router_kernel (core/src/CUDA/kernel/moe_router.cu:27-111).
+ * block_counts: [AXM_ROUTE_BLOCKS][E] int32 scratch consumed by axm_moe_permute. */
+AXM_API int axm_moe_router(const AxmMoeDesc* desc, const void* x, const void* router_w,
+                           const float* router_bias, float* logits, int32_t* topk_idx,
+                           float* topk_gate, int32_t* block_counts, void* stream);
+
+/* Routing from caller-supplied fp32 logits: the part of the router whose
+ * results must equal the reference bit for bit
+ * (core/src/CUDA/kernel/moe_router.cu:59-110). */
+AXM_API int axm_moe_route_from_logits(const AxmMoeDesc* desc, const float* logits,
+                                      int32_t* topk_idx, float* topk_gate,
+                                      int32_t* block_counts, void* stream);
+
+/* Histogram, exclusive-scan offsets, stable expert-contiguous placement and the
+ * 16-byte row copies.  No counterpart kernel in the reference (its dispatch is
+ * per token, core/src/CUDA/kernel/moe_router.cu:113-191); the histogram follows
+ * moe_router.cu:107-110.  x_perm: [T*k][D] bf16 or NULL to skip the row copies. */
+AXM_API int axm_moe_permute(const AxmMoeDesc* desc, const void* x, const int32_t* topk_idx,
+                            const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                            int32_t* row_src, int32_t* slot_dst, void* x_perm, void* stream);
+
+/* One segment of rows that share an expert, for the grouped GEMMs.  Expert ids
+ * >= E address the shared experts. */
+typedef struct AxmSegment {
+  int32_t a_row0;   /* first row in the A operand */
+  int32_t out_row0; /* first row in the output */
+  int32_t rows;
+  int32_t expert;   /* bit 30 set: A rows come from the alternate A tensor */
+} AxmSegment;
+#define AXM_SEG_ALT_A (1 << 30)
+
+/* Builds the segment table of a single-GPU layer call on the device from the
+ * offsets array: one segment per routed expert, then one per shared expert. */
+AXM_API int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* offsets,
+                                   AxmSegment* segments, void* stream);
+
+/* Grouped SwiGLU expert FFN over `num_segments` segments read from device memory:
+ *   h   = SiLU(A . Wg[e]) * (A . Wu[e])     -> bf16 [rows_total][F]
+ *   o   = h . Wd[e]                         -> bf16 [rows_total][D]
+ * tcgen05 tensor-core kernels, bf16 in, fp32 accumulate in tensor memory.
+ * Replaces moe_top2_dispatch_kernel phases A and B
+ * (core/src/CUDA/kernel/moe_router.cu:155-190).
+ * a_rows / alt_rows are the row counts of x_perm and x_alt (tensor-map extents);
+ * rows_total is the row count of h and o. status is an int32 device word that
+ * receives a non-zero code if a bounded wait inside a kernel gave up. */
+AXM_API int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, int32_t a_rows,
+                               const void* x_alt, int32_t alt_rows, const AxmSegment* segments,
+                               int32_t num_segments, const void* w_gate, const void* w_up,
+                               const void* w_down, const void* shared_gate,
+                               const void* shared_up, const void* shared_down, void* h,
+                               void* o, int32_t rows_total, int32_t* status, void* stream);
+
+/* Weighted combine: y[t] = bf16(sum_i gate[t,i] * o[slot_dst[t,i]] + sum_s o_shared[s][t]),
+ * out[t] = bf16(x[t] + y[t]) with AXM_FLAG_RESIDUAL.  Replaces the gate-weighted
+ * sum and the residual add (core/src/CUDA/kernel/moe_router.cu:186-203,304-317).
+ * o_shared points at the first shared expert's rows ([S][T][D]) or NULL. */
+AXM_API int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void* o,
+                            const void* o_shared, const int32_t* slot_dst,
+                            const float* topk_gate, void* y, void* out, void* stream);
+
+/* Number of token blocks the router splits T into (rows of block_counts). */
+#define AXM_ROUTE_BLOCKS 296
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* AXM_MOE_H */

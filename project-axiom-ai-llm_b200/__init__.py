@@ -1,0 +1,183 @@
+"""Python host helper over the C ABI of the B200 MoE layer (include/axm_moe.h).
+
+The product is the shared library; this module only loads it with ctypes and
+offers the call shape of the reference engine's host wrapper
+AI::forward_mixture_experts (core/src/ai.cpp:593-623): give it activations, get
+the layer output and the per-expert histogram back.  PyTorch is used for device
+memory and streams, nothing else.  There is no fallback: if the library is not
+built, or no sm_100 device is present, calls raise.
+"""
+import ctypes
+import os
+
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libaxm_moe.so")
+DROPIN_PATH = os.path.join(HERE, "libaxm_moe_dropin.so")
+HEADER_PATH = os.path.join(HERE, "..", "include", "axm_moe.h")
+
+AXM_OK = 0
+AXM_ERR_ARGUMENT = -1
+AXM_ERR_WORKSPACE = -2
+AXM_ERR_DEVICE = -3
+AXM_ERR_LAUNCH = -4
+AXM_ERR_TIMEOUT = -5
+ROUTER_BF16 = 0
+ROUTER_FP32 = 1
+FLAG_RESIDUAL = 1
+FLAG_HIST_ACCUMULATE = 2
+ROUTE_BLOCKS = 296
+SEG_ALT_A = 1 << 30
+
+
+class AxmError(RuntimeError):
+    def __init__(self, status, text):
+        super().__init__(f"axm_moe status {status}: {text}")
+        self.status = status
+
+
+class MoeDesc(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in (
+        "tokens", "d_model", "d_ff", "num_experts", "top_k", "num_shared", "router_dtype", "flags")]
+
+
+class MoeTensors(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in (
+        "x", "router_w", "router_bias", "w_gate", "w_up", "w_down", "shared_gate", "shared_up",
+        "shared_down", "logits", "topk_idx", "topk_gate", "histogram", "offsets", "row_src",
+        "slot_dst", "y", "out")]
+
+
+class Segment(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_int32) for n in ("a_row0", "out_row0", "rows", "expert")]
+
+
+_lib = None
+
+
+def load():
+    """Loads libaxm_moe.so (once) and declares its prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise FileNotFoundError(
+            f"{LIB_PATH} is not built; run `python project-axiom-ai-llm_b200/build.py`")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, sz = ctypes.c_void_p, ctypes.c_int32, ctypes.c_size_t
+    dp = ctypes.POINTER(MoeDesc)
+    lib.axm_last_error.restype = ctypes.c_char_p
+    lib.axm_version.restype = ctypes.c_char_p
+    lib.axm_moe_forward_launches.argtypes = [dp]
+    lib.axm_moe_workspace_bytes.argtypes = [dp, ctypes.POINTER(sz)]
+    lib.axm_moe_forward.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, sz, vp]
+    lib.axm_moe_forward_host.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, vp, vp, vp, vp, sz, vp]
+    lib.axm_moe_status_word.argtypes = [dp, vp, ctypes.POINTER(vp)]
+    lib.axm_moe_router.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.axm_moe_route_from_logits.argtypes = [dp, vp, vp, vp, vp, vp]
+    lib.axm_moe_permute.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.axm_moe_build_segments.argtypes = [dp, vp, vp, vp]
+    lib.axm_moe_expert_ffn.argtypes = [dp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp,
+                                       vp, i32, vp, vp]
+    lib.axm_moe_combine.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    _lib = lib
+    return lib
+
+
+def check(status):
+    if status != AXM_OK:
+        raise AxmError(status, load().axm_last_error().decode())
+    return status
+
+
+def ptr(t):
+    return None if t is None else ctypes.c_void_p(t.data_ptr())
+
+
+def current_stream():
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def make_desc(tokens, d_model, d_ff, num_experts, top_k, num_shared=0, router_dtype=ROUTER_FP32,
+              flags=FLAG_RESIDUAL):
+    return MoeDesc(tokens, d_model, d_ff, num_experts, top_k, num_shared, router_dtype, flags)
+
+
+def workspace_bytes(desc):
+    n = ctypes.c_size_t(0)
+    check(load().axm_moe_workspace_bytes(ctypes.byref(desc), ctypes.byref(n)))
+    return n.value
+
+
+class MoeLayer:
+    """One MoE layer bound to its weights, with a workspace sized for `tokens`.
+
+    forward(x) returns (out, histogram) like the reference host wrapper; the
+    routing tensors of the last call stay readable as attributes.
+    """
+
+    def __init__(self, weights, tokens, top_k, residual=True, hist_accumulate=False,
+                 device="cuda"):
+        self.lib = load()
+        self.w = weights
+        wr = weights["router_w"]
+        D, E = wr.shape
+        F = weights["w_gate"].shape[2]
+        S = 0 if weights.get("shared_gate") is None else weights["shared_gate"].shape[0]
+        flags = (FLAG_RESIDUAL if residual else 0) | (FLAG_HIST_ACCUMULATE if hist_accumulate else 0)
+        rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
+        self.desc = make_desc(tokens, D, F, E, top_k, S, rdt, flags)
+        self.T, self.D, self.F, self.E, self.k, self.S = tokens, D, F, E, top_k, S
+        self.device = torch.device(device)
+        self.workspace = torch.empty(max(workspace_bytes(self.desc), 256), dtype=torch.uint8,
+                                     device=self.device)
+        dev = self.device
+        self.logits = torch.empty(tokens, E, dtype=torch.float32, device=dev)
+        self.topk_idx = torch.empty(tokens, top_k, dtype=torch.int32, device=dev)
+        self.topk_gate = torch.empty(tokens, top_k, dtype=torch.float32, device=dev)
+        self.histogram = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
+        self.row_src = torch.empty(tokens * top_k, dtype=torch.int32, device=dev)
+        self.slot_dst = torch.empty(tokens * top_k, dtype=torch.int32, device=dev)
+        self.y = torch.empty(tokens, D, dtype=torch.bfloat16, device=dev)
+
+    def tensors(self, x, out):
+        w = self.w
+        return MoeTensors(
+            x.data_ptr(), w["router_w"].data_ptr(),
+            None if w.get("router_bias") is None else w["router_bias"].data_ptr(),
+            w["w_gate"].data_ptr(), w["w_up"].data_ptr(), w["w_down"].data_ptr(),
+            None if self.S == 0 else w["shared_gate"].data_ptr(),
+            None if self.S == 0 else w["shared_up"].data_ptr(),
+            None if self.S == 0 else w["shared_down"].data_ptr(),
+            self.logits.data_ptr(), self.topk_idx.data_ptr(), self.topk_gate.data_ptr(),
+            self.histogram.data_ptr(), self.offsets.data_ptr(), self.row_src.data_ptr(),
+            self.slot_dst.data_ptr(), self.y.data_ptr(), out.data_ptr())
+
+    def forward(self, x, out=None):
+        assert x.is_cuda and x.dtype == torch.bfloat16 and x.shape == (self.T, self.D)
+        assert x.is_contiguous()
+        if out is None:
+            out = torch.empty_like(x)
+        t = self.tensors(x, out)
+        check(self.lib.axm_moe_forward(ctypes.byref(self.desc), ctypes.byref(t), ptr(self.workspace),
+                                       self.workspace.numel(), current_stream()))
+        return out, self.histogram
+
+    def forward_host(self, h_x, h_out, d_x, d_out):
+        """Activations in (pinned) host memory; synchronises before returning."""
+        t = self.tensors(d_x, d_out)
+        check(self.lib.axm_moe_forward_host(
+            ctypes.byref(self.desc), ctypes.byref(t), ptr(h_x), ptr(h_out), ptr(d_x), ptr(d_out),
+            ptr(self.workspace), self.workspace.numel(), current_stream()))
+        return h_out
+
+    def status(self):
+        """Reads the workspace status word (synchronises)."""
+        p = ctypes.c_void_p()
+        check(self.lib.axm_moe_status_word(ctypes.byref(self.desc), ptr(self.workspace),
+                                           ctypes.byref(p)))
+        off = p.value - self.workspace.data_ptr()
+        torch.cuda.synchronize()
+        return int(self.workspace[off:off + 4].view(torch.int32).item())

@@ -1,0 +1,64 @@
+"""Builds the CUDA libraries of this package in-tree with nvcc for sm_100a.
+
+  libaxm_moe.so         the layer behind include/axm_moe.h
+  libaxm_moe_dropin.so  the three symbols of the reference engine's MoE interface
+
+Run as a script or call build().  Nothing is installed outside this directory.
+"""
+import os
+import shutil
+import subprocess
+import sys
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+CSRC = os.path.join(HERE, "csrc")
+LIB = os.path.join(HERE, "libaxm_moe.so")
+DROPIN = os.path.join(HERE, "libaxm_moe_dropin.so")
+
+CORE_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_ffn.cu"]
+DROPIN_SOURCES = ["dropin.cu"]
+
+NVCC_FLAGS = [
+    "-gencode", "arch=compute_100a,code=sm_100a",
+    "-O3", "-std=c++17", "-lineinfo",
+    "-Xcompiler", "-fPIC,-fvisibility=hidden",
+    "--expt-relaxed-constexpr",
+]
+
+
+def _nvcc():
+    exe = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(exe):
+        raise RuntimeError("nvcc not found")
+    return exe
+
+
+def _stale(target, sources):
+    if not os.path.exists(target):
+        return True
+    t = os.path.getmtime(target)
+    deps = list(sources) + [os.path.join(CSRC, "common.cuh"),
+                            os.path.join(HERE, "..", "include", "axm_moe.h"), __file__]
+    return any(os.path.getmtime(s) > t for s in deps)
+
+
+def _run(cmd, verbose):
+    if verbose:
+        print(" ".join(cmd), flush=True)
+    subprocess.run(cmd, check=True)
+
+
+def build(force=False, verbose=True, ptxas_info=False):
+    core = [os.path.join(CSRC, s) for s in CORE_SOURCES]
+    extra = ["-Xptxas", "-v"] if ptxas_info else []
+    if force or _stale(LIB, core):
+        _run([_nvcc()] + NVCC_FLAGS + extra + ["-shared", "-o", LIB] + core + ["-lcudart"], verbose)
+    drop = [os.path.join(CSRC, s) for s in DROPIN_SOURCES]
+    if all(os.path.exists(s) for s in drop) and (force or _stale(DROPIN, drop + [LIB])):
+        _run([_nvcc()] + NVCC_FLAGS + ["-shared", "-o", DROPIN] + drop +
+             ["-L" + HERE, "-laxm_moe", "-Xlinker", "-rpath=$ORIGIN", "-lcudart", "-ldl"], verbose)
+    return LIB
+
+
+if __name__ == "__main__":
+    build(force="--force" in sys.argv, ptxas_info="--ptxas" in sys.argv)

@@ -1,0 +1,469 @@
+// Grouped SwiGLU expert GEMMs for sm_100a: tcgen05.mma with the accumulator in
+// tensor memory, operands staged in shared memory by TMA, one persistent CTA per
+// SM walking a tile list built from the segment table.
+//
+// Stands in for the two phases of the reference engine's per-token dispatch
+// kernel (core/src/CUDA/kernel/moe_router.cu:155-173 gate/up + SiLU*mul,
+// 177-190 down projection), which run on CUDA cores there.  The weight layouts
+// are consumed as the engine stores them ([E][D][F] and [E][F][D] with the
+// output dimension contiguous, core/src/CUDA/util/gpu_types.cuh:152-157): the B
+// operand is therefore "MN-major" and is described to the tensor core with the
+// transposed canonical shared-memory layout; no weight re-layout happens.
+//
+//   kernel<true>  : h[r, f]  = SiLU(x_r . Wg[e][:, f]) * (x_r . Wu[e][:, f])   (bf16)
+//   kernel<false> : o[r, d]  = h_r . Wd[e][:, d]                               (bf16)
+//
+// Tile: 128 rows x 256 accumulator columns x 64 reduction elements per stage.
+// In the SwiGLU kernel the 256 columns are 128 gate columns followed by the 128
+// up columns of the same f range, so one MMA produces both and the epilogue
+// needs nothing but its own thread's registers.
+//
+// Roles (192 threads): warp 0 = TMA producer (one lane), warp 1 = MMA issuer
+// (one lane) and TMEM owner, warps 2-5 = epilogue (TMEM -> registers -> global).
+// Two 256-column accumulators alternate so that the epilogue of tile i overlaps
+// the MMAs of tile i+1.
+#include <cuda.h>
+
+#include <cstdio>
+#include <cstdlib>
+#include <mutex>
+
+#include "common.cuh"
+
+namespace axm {
+
+constexpr int BM = 128;             // rows per tile
+constexpr int BK = 64;              // reduction elements per stage (128 bytes of bf16)
+constexpr int UMMA_N = 256;         // accumulator columns per tile
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kABytes = BM * BK * 2;          // 16 KiB
+constexpr int kBChunkBytes = 64 * BK * 2;     // 64 output columns x 64 k: 8 KiB
+constexpr int kBBytes = 4 * kBChunkBytes;     // 32 KiB
+constexpr int kStageBytes = kABytes + kBBytes;
+constexpr int kMaxSegments = 512;
+constexpr int kGemmThreads = 192;
+constexpr int kTmemCols = 512;
+
+struct __align__(8) GemmShared {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+  int total_tiles;
+  int tile_prefix[kMaxSegments + 1];  // m-tiles before segment s
+  AxmSegment seg[kMaxSegments];
+};
+
+constexpr size_t kGemmSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + sizeof(GemmShared);
+
+struct GemmArgs {
+  const AxmSegment* segments;
+  int num_segments;
+  int n_total;        // output columns: F (SwiGLU) or D (down)
+  int k_total;        // reduction length: D (SwiGLU) or F (down)
+  int routed_experts; // expert ids >= this address the shared-expert weights
+  __nv_bfloat16* out;
+  int* status;
+  int dbg[4];         // B leading / stride offsets, B and A k-advance (16-byte units)
+};
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading and
+// stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
+__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                   uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
+  d |= (uint64_t)1 << 46;  // version
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+
+// Instruction descriptor: fp32 accumulate, bf16 A and B, A K-major, B MN-major,
+// N = 256, M = 128.
+constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
+                                ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+struct TileCoord {
+  int seg;
+  int m_tile;
+  int n_tile;
+};
+
+__device__ __forceinline__ TileCoord decode_tile(const GemmShared* sh, int num_segments,
+                                                 int n_tiles, int linear) {
+  // largest s with tile_prefix[s] * n_tiles <= linear
+  int lo = 0, hi = num_segments - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (sh->tile_prefix[mid] * n_tiles <= linear) lo = mid; else hi = mid - 1;
+  }
+  TileCoord tc;
+  tc.seg = lo;
+  int local = linear - sh->tile_prefix[lo] * n_tiles;
+  int mt = sh->tile_prefix[lo + 1] - sh->tile_prefix[lo];
+  tc.n_tile = local / mt;
+  tc.m_tile = local - tc.n_tile * mt;
+  return tc;
+}
+
+template <bool kSwiGLU>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_alt,
+                    const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+                    const __grid_constant__ CUtensorMap tm_b0_sh, const __grid_constant__ CUtensorMap tm_b1_sh,
+                    GemmArgs args) {
+  extern __shared__ unsigned char smem_raw[];
+  // 128-byte-swizzled tiles need 1024-byte alignment.
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  GemmShared* sh = reinterpret_cast<GemmShared*>(tiles + (size_t)kStages * kStageBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  constexpr int BN_OUT = kSwiGLU ? 128 : 256;
+  const int n_tiles = (args.n_total + BN_OUT - 1) / BN_OUT;
+  const int k_blocks = (args.k_total + BK - 1) / BK;
+  const int nseg = args.num_segments;
+
+  // ---- set-up -------------------------------------------------------------------
+  for (int s = threadIdx.x; s < nseg; s += kGemmThreads) sh->seg[s] = args.segments[s];
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(&sh->full[i], 1);
+      mbar_init(&sh->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh->tmem_full[i], 1);
+      mbar_init(&sh->tmem_empty[i], 4);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b0);
+    if (kSwiGLU) tma_prefetch_desc(&tm_b1);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc(&sh->tmem_base, kTmemCols);
+    tmem_relinquish();
+  }
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int s = 0; s < nseg; ++s) {
+      sh->tile_prefix[s] = acc;
+      int rows = sh->seg[s].rows;
+      acc += rows > 0 ? (rows + BM - 1) / BM : 0;
+    }
+    sh->tile_prefix[nseg] = acc;
+    sh->total_tiles = acc * n_tiles;
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+
+  const int total_tiles = sh->total_tiles;
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (warp == 0) {
+    // ---- TMA producer ------------------------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        TileCoord tc = decode_tile(sh, nseg, n_tiles, tile);
+        const AxmSegment sg = sh->seg[tc.seg];
+        const int e_raw = sg.expert & 0xffff;
+        const bool shared_w = e_raw >= args.routed_experts;
+        const int e = shared_w ? e_raw - args.routed_experts : e_raw;
+        const bool alt_a = kSwiGLU && (sg.expert & AXM_SEG_ALT_A);
+        const int a_row = (kSwiGLU ? sg.a_row0 : sg.out_row0) + tc.m_tile * BM;
+        const CUtensorMap* ma = alt_a ? &tm_a_alt : &tm_a;
+        const CUtensorMap* mb0 = shared_w ? &tm_b0_sh : &tm_b0;
+        const CUtensorMap* mb1 = shared_w ? &tm_b1_sh : &tm_b1;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
+            ok = false;
+            break;
+          }
+          unsigned char* sa = tiles + (size_t)stage * kStageBytes;
+          unsigned char* sb = sa + kABytes;
+          mbar_expect_tx(&sh->full[stage], kStageBytes);
+          tma_load_2d(sa, ma, &sh->full[stage], kb * BK, a_row);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            if (kSwiGLU) {
+              const CUtensorMap* mb = c < 2 ? mb0 : mb1;
+              tma_load_3d(sb + c * kBChunkBytes, mb, &sh->full[stage],
+                          tc.n_tile * BN_OUT + (c & 1) * 64, kb * BK, e);
+            } else {
+              tma_load_3d(sb + c * kBChunkBytes, mb0, &sh->full[stage],
+                          tc.n_tile * BN_OUT + c * 64, kb * BK, e);
+            }
+          }
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer --------------------------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
+        if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * UMMA_N;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + (size_t)stage * kStageBytes);
+          const uint32_t sb = sa + kABytes;
+          // A: K-major, 8-row groups 1024 bytes apart.  B: MN-major, 64-column
+          // chunks 8192 bytes apart (leading), 8-k groups 1024 bytes apart (stride).
+          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t db = make_smem_desc(sb, (uint32_t)args.dbg[0] << 4, (uint32_t)args.dbg[1] << 4);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j) {
+            // +32 bytes along K for A; +16 k-rows x 128 bytes for B
+            tc_mma_bf16(d_tmem, da + (uint64_t)(j * args.dbg[3]), db + (uint64_t)(j * args.dbg[2]), kInstrDesc,
+                        (kb > 0 || j > 0) ? 1u : 0u);
+          }
+          tc_commit(&sh->empty[stage]);
+          if (++stage == kStages) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit(&sh->tmem_full[acc]);
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---- epilogue ------------------------------------------------------------------
+    const int quad = warp & 3;  // TMEM lane quadrant this warp may read
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
+      TileCoord tc = decode_tile(sh, nseg, n_tiles, tile);
+      const AxmSegment sg = sh->seg[tc.seg];
+      // warp-uniform outcome: the tcgen05.ld below needs the whole warp
+      if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag))) break;
+      tc_fence_after();
+      const int row_in_seg = tc.m_tile * BM + quad * 32 + lane;
+      const bool row_ok = row_in_seg < sg.rows;
+      const int n0 = tc.n_tile * BN_OUT;
+      __nv_bfloat16* out_row =
+          args.out + (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
+        uint32_t g[32];
+        tmem_ld32(t_addr + c0, g);
+        uint32_t packed[16];
+        if (kSwiGLU) {
+          uint32_t u[32];
+          tmem_ld32(t_addr + 128 + c0, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+            float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+            float h0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+            float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+            packed[j] = pack_bf16(h0, h1);
+          }
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j)
+            packed[j] = pack_bf16(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            if (n0 + c0 + q * 8 < args.n_total)
+              *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
+                  make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sh->tmem_empty[acc]);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ---- drain -----------------------------------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (sh->abort_flag != 0) {
+    // A wait gave up.  Give copies that are still in flight a bounded time to
+    // land in this CTA's shared memory before it is released, then report.
+    long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) {
+    }
+    if (threadIdx.x == 0 && args.status != nullptr) atomicExch(args.status, kSwiGLU ? 1 : 2);
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---- host side ------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qr;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qr) == cudaSuccess &&
+        qr == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Row-major bf16 matrix [rows][cols]; box = 64 columns x box_rows rows.
+static int make_map_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
+                       uint32_t box_rows) {
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {cols * 2};
+  cuuint32_t box[2] = {64, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AXM_ERR_ARGUMENT, "cuTensorMapEncodeTiled(2d) failed: %d", (int)r);
+  return AXM_OK;
+}
+
+// Weights [experts][k_rows][n_cols] bf16, n contiguous; box = 64 n x 64 k x 1 expert.
+static int make_map_3d(CUtensorMap* m, const void* base, uint64_t experts, uint64_t k_rows,
+                       uint64_t n_cols) {
+  cuuint64_t dims[3] = {n_cols, k_rows, experts};
+  cuuint64_t strides[2] = {n_cols * 2, n_cols * k_rows * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)BK, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AXM_ERR_ARGUMENT, "cuTensorMapEncodeTiled(3d) failed: %d", (int)r);
+  return AXM_OK;
+}
+
+int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
+                      int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
+                      const void* w_gate, const void* w_up, const void* w_down,
+                      const void* shared_gate, const void* shared_up, const void* shared_down,
+                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st) {
+  if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
+  const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
+  CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;
+  int rc;
+  if ((rc = make_map_2d(&a1, x_perm, (uint64_t)(a_rows > 0 ? a_rows : 1), D, BM))) return rc;
+  if (x_alt != nullptr && alt_rows > 0) {
+    if ((rc = make_map_2d(&a1_alt, x_alt, alt_rows, D, BM))) return rc;
+  } else {
+    a1_alt = a1;
+  }
+  if ((rc = make_map_3d(&g, w_gate, E, D, F))) return rc;
+  if ((rc = make_map_3d(&u, w_up, E, D, F))) return rc;
+  if ((rc = make_map_3d(&dn, w_down, E, F, D))) return rc;
+  if (S > 0) {
+    if ((rc = make_map_3d(&g_sh, shared_gate, S, D, F))) return rc;
+    if ((rc = make_map_3d(&u_sh, shared_up, S, D, F))) return rc;
+    if ((rc = make_map_3d(&dn_sh, shared_down, S, F, D))) return rc;
+  } else {
+    g_sh = g;
+    u_sh = u;
+    dn_sh = dn;
+  }
+  if ((rc = make_map_2d(&a2, h, rows_total, F, BM))) return rc;
+
+  static std::once_flag attr_once;
+  std::call_once(attr_once, [] {
+    cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+    cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
+  });
+  const int grid = sm_count();
+  GemmArgs ga;
+  ga.segments = segments;
+  ga.num_segments = num_segments;
+  ga.routed_experts = E;
+  ga.status = status;
+  ga.dbg[0] = kBChunkBytes >> 4;
+  ga.dbg[1] = 1024 >> 4;
+  ga.dbg[2] = 128;
+  ga.dbg[3] = 2;
+  if (const char* dbg = getenv("AXM_GEMM_DEBUG_DESC"))
+    sscanf(dbg, "%d,%d,%d,%d", &ga.dbg[0], &ga.dbg[1], &ga.dbg[2], &ga.dbg[3]);
+  ga.n_total = F;
+  ga.k_total = D;
+  ga.out = static_cast<__nv_bfloat16*>(h);
+  grouped_gemm_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
+  if ((rc = check_launch("grouped_gemm_kernel<swiglu>"))) return rc;
+  ga.n_total = D;
+  ga.k_total = F;
+  ga.out = static_cast<__nv_bfloat16*>(o);
+  grouped_gemm_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
+  return check_launch("grouped_gemm_kernel<down>");
+}
+
+}  // namespace axm
+
+using namespace axm;
+
+extern "C" int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, int32_t a_rows,
+                                  const void* x_alt, int32_t alt_rows,
+                                  const AxmSegment* segments, int32_t num_segments,
+                                  const void* w_gate, const void* w_up, const void* w_down,
+                                  const void* shared_gate, const void* shared_up,
+                                  const void* shared_down, void* h, void* o, int32_t rows_total,
+                                  int32_t* status, void* stream) {
+  if (desc == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
+  if (desc->d_model <= 0 || desc->d_ff <= 0 || desc->d_model % 8 || desc->d_ff % 8)
+    return fail(AXM_ERR_ARGUMENT, "d_model and d_ff must be positive multiples of 8");
+  if (desc->num_experts <= 0) return fail(AXM_ERR_ARGUMENT, "num_experts must be positive");
+  if (num_segments < 0 || num_segments > kMaxSegments)
+    return fail(AXM_ERR_ARGUMENT, "num_segments %d not in 0..%d", num_segments, kMaxSegments);
+  if (!x_perm || !segments || !w_gate || !w_up || !w_down || !h || !o)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_expert_ffn: null pointer");
+  if (desc->num_shared > 0 && (!shared_gate || !shared_up || !shared_down))
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_expert_ffn: shared experts without weights");
+  if (rows_total <= 0 || num_segments == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  return launch_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate,
+                           w_up, w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
+                           status, static_cast<cudaStream_t>(stream));
+}

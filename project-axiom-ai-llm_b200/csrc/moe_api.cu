@@ -1,0 +1,246 @@
+// Host side of the C ABI: error text, device checks, workspace carving and the
+// whole-layer call.  Mirrors the host logic of forward_mixture_experts in the
+// reference engine (core/src/CUDA/kernel/moe_router.cu:205-320): validate, then
+// enqueue router -> dispatch -> expert FFN -> combine on the caller's stream and
+// report only enqueue-time errors.  Unlike the engine it allocates nothing: all
+// scratch comes from the caller's workspace.
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+
+namespace axm {
+
+static thread_local char g_err[512] = "";
+
+void set_error(const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+}
+
+int fail(int status, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return status;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+  return AXM_OK;
+}
+
+struct DeviceInfo {
+  int checked_device = -1;
+  int major = 0;
+  int sms = 0;
+  cudaError_t err = cudaSuccess;
+};
+
+static DeviceInfo& device_info() {
+  static thread_local DeviceInfo info;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    info.err = e;
+    info.checked_device = -1;
+    cudaGetLastError();
+    return info;
+  }
+  if (dev != info.checked_device) {
+    cudaDeviceProp p;
+    info.err = cudaGetDeviceProperties(&p, dev);
+    if (info.err == cudaSuccess) {
+      info.major = p.major;
+      info.sms = p.multiProcessorCount;
+      info.checked_device = dev;
+    } else {
+      cudaGetLastError();
+    }
+  }
+  return info;
+}
+
+int require_device() {
+  DeviceInfo& i = device_info();
+  if (i.err != cudaSuccess)
+    return fail(AXM_ERR_DEVICE, "no usable CUDA device: %s", cudaGetErrorString(i.err));
+  if (i.major != 10)
+    return fail(AXM_ERR_DEVICE, "device has compute capability %d.x; this library is sm_100a only", i.major);
+  return AXM_OK;
+}
+
+int sm_count() { return device_info().sms > 0 ? device_info().sms : 148; }
+
+int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
+                   const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                   int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
+                   int32_t* status, cudaStream_t st);
+int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
+                      int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
+                      const void* w_gate, const void* w_up, const void* w_down,
+                      const void* shared_gate, const void* shared_up, const void* shared_down,
+                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st);
+
+static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
+
+// Carves the workspace.  With base == nullptr it only measures.
+struct Workspace {
+  float* logits;
+  int32_t* topk_idx;
+  float* topk_gate;
+  int32_t* block_counts;
+  int32_t* offsets;
+  int32_t* row_src;
+  int32_t* slot_dst;
+  AxmSegment* segments;
+  int32_t* status;
+  void* x_perm;
+  void* h;
+  void* o;
+  size_t bytes;
+};
+
+static Workspace carve(const AxmMoeDesc* d, void* base) {
+  Workspace w;
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    void* p = base ? static_cast<char*>(base) + off : nullptr;
+    off += align256(n);
+    return p;
+  };
+  const size_t T = d->tokens, D = d->d_model, F = d->d_ff, E = d->num_experts, k = d->top_k,
+               S = d->num_shared;
+  const size_t rows = T * k + T * S;
+  w.status = static_cast<int32_t*>(take(sizeof(int32_t)));
+  w.logits = static_cast<float*>(take(sizeof(float) * T * E));
+  w.topk_idx = static_cast<int32_t*>(take(sizeof(int32_t) * T * k));
+  w.topk_gate = static_cast<float*>(take(sizeof(float) * T * k));
+  w.block_counts = static_cast<int32_t*>(take(sizeof(int32_t) * AXM_ROUTE_BLOCKS * E));
+  w.offsets = static_cast<int32_t*>(take(sizeof(int32_t) * (E + 1)));
+  w.row_src = static_cast<int32_t*>(take(sizeof(int32_t) * T * k));
+  w.slot_dst = static_cast<int32_t*>(take(sizeof(int32_t) * T * k));
+  w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (E + S)));
+  w.x_perm = take(2 * T * k * D);
+  w.h = take(2 * rows * F);
+  w.o = take(2 * rows * D);
+  w.bytes = off;
+  return w;
+}
+
+static int validate_forward(const AxmMoeDesc* d) {
+  if (d == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
+  if (d->tokens < 0) return fail(AXM_ERR_ARGUMENT, "tokens %d negative", d->tokens);
+  if (d->d_model <= 0 || d->d_ff <= 0 || d->d_model % 8 || d->d_ff % 8)
+    return fail(AXM_ERR_ARGUMENT, "d_model %d and d_ff %d must be positive multiples of 8", d->d_model, d->d_ff);
+  if (d->num_experts <= 0 || d->num_experts > 256)
+    return fail(AXM_ERR_ARGUMENT, "num_experts %d not in 1..256", d->num_experts);
+  if (d->top_k <= 0 || d->top_k > 8 || d->top_k > d->num_experts)
+    return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..min(num_experts, 8)", d->top_k);
+  if (d->num_shared < 0 || d->num_shared > 8)
+    return fail(AXM_ERR_ARGUMENT, "num_shared %d not in 0..8", d->num_shared);
+  if (d->router_dtype != AXM_ROUTER_BF16 && d->router_dtype != AXM_ROUTER_FP32)
+    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", d->router_dtype);
+  if ((long long)d->tokens * (d->top_k + d->num_shared) > 0x7fffffffLL)
+    return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
+  return AXM_OK;
+}
+
+}  // namespace axm
+
+using namespace axm;
+
+extern "C" const char* axm_last_error(void) { return g_err; }
+
+extern "C" const char* axm_version(void) { return "axm_moe 0.1 sm_100a"; }
+
+extern "C" int axm_moe_forward_launches(const AxmMoeDesc* desc) {
+  if (validate_forward(desc) != AXM_OK) return AXM_ERR_ARGUMENT;
+  return desc->tokens == 0 ? 0 : 5;  // router, permute, gate/up GEMM, down GEMM, combine
+}
+
+extern "C" int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes) {
+  if (int rc = validate_forward(desc)) return rc;
+  if (bytes == nullptr) return fail(AXM_ERR_ARGUMENT, "bytes is null");
+  *bytes = carve(desc, nullptr).bytes;
+  return AXM_OK;
+}
+
+extern "C" int axm_moe_status_word(const AxmMoeDesc* desc, void* workspace, int32_t** status) {
+  if (int rc = validate_forward(desc)) return rc;
+  if (!workspace || !status) return fail(AXM_ERR_ARGUMENT, "axm_moe_status_word: null pointer");
+  *status = carve(desc, workspace).status;
+  return AXM_OK;
+}
+
+extern "C" int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  if (int rc = validate_forward(desc)) return rc;
+  if (t == nullptr) return fail(AXM_ERR_ARGUMENT, "tensors is null");
+  if (!t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->out)
+    return fail(AXM_ERR_ARGUMENT, "x, router_w, w_gate, w_up, w_down and out are required");
+  if (desc->num_shared > 0 && (!t->shared_gate || !t->shared_up || !t->shared_down))
+    return fail(AXM_ERR_ARGUMENT, "num_shared > 0 needs shared_gate, shared_up and shared_down");
+  if (desc->tokens == 0) return AXM_OK;
+  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
+    return fail(AXM_ERR_WORKSPACE, "workspace is null or not 256-byte aligned");
+  Workspace w = carve(desc, workspace);
+  if (workspace_bytes < w.bytes)
+    return fail(AXM_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", workspace_bytes, w.bytes);
+  if (int rc = require_device()) return rc;
+
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  float* logits = t->logits ? t->logits : w.logits;
+  int32_t* idx = t->topk_idx ? t->topk_idx : w.topk_idx;
+  float* gate = t->topk_gate ? t->topk_gate : w.topk_gate;
+  int32_t* offsets = t->offsets ? t->offsets : w.offsets;
+  int32_t* row_src = t->row_src ? t->row_src : w.row_src;
+  int32_t* slot_dst = t->slot_dst ? t->slot_dst : w.slot_dst;
+  const int T = desc->tokens, k = desc->top_k, S = desc->num_shared, E = desc->num_experts;
+
+  int rc = axm_moe_router(desc, t->x, t->router_w, t->router_bias, logits, idx, gate,
+                          w.block_counts, stream);
+  if (rc) return rc;
+  rc = launch_permute(desc, t->x, idx, w.block_counts, t->histogram, offsets, row_src, slot_dst,
+                      w.x_perm, w.segments, w.status, st);
+  if (rc) return rc;
+  rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
+                         t->w_down, t->shared_gate, t->shared_up, t->shared_down, w.h, w.o,
+                         T * k + T * S, w.status, st);
+  if (rc) return rc;
+  const __nv_bfloat16* o_shared =
+      S > 0 ? static_cast<const __nv_bfloat16*>(w.o) + (size_t)T * k * desc->d_model : nullptr;
+  return axm_moe_combine(desc, t->x, w.o, o_shared, slot_dst, gate, t->y, t->out, stream);
+}
+
+extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors* t,
+                                    const void* h_x, void* h_out, void* d_x, void* d_out,
+                                    void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = validate_forward(desc)) return rc;
+  if (!t || !h_x || !h_out || !d_x || !d_out)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_host: null pointer");
+  if (desc->tokens == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t bytes = (size_t)desc->tokens * desc->d_model * 2;
+  cudaError_t e = cudaMemcpyAsync(d_x, h_x, bytes, cudaMemcpyHostToDevice, st);
+  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "H2D copy: %s", cudaGetErrorString(e));
+  AxmMoeTensors tt = *t;
+  tt.x = d_x;
+  tt.out = d_out;
+  if (int rc = axm_moe_forward(desc, &tt, workspace, workspace_bytes, stream)) return rc;
+  e = cudaMemcpyAsync(h_out, d_out, bytes, cudaMemcpyDeviceToHost, st);
+  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "D2H copy: %s", cudaGetErrorString(e));
+  int32_t status = 0;
+  e = cudaMemcpyAsync(&status, carve(desc, workspace).status, sizeof(int32_t),
+                      cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "synchronise: %s", cudaGetErrorString(e));
+  if (status != 0) return fail(AXM_ERR_TIMEOUT, "a bounded wait in GEMM kernel %d gave up", status);
+  return AXM_OK;
+}

@@ -1,0 +1,320 @@
+// Dispatch (histogram -> exclusive scan -> stable expert-contiguous placement ->
+// 16-byte row copies) and the weighted combine with residual.
+//
+// The reference engine has no permutation: its dispatch kernel walks tokens one
+// CTA each (core/src/CUDA/kernel/moe_router.cu:113-191).  The placement rule
+// implemented here is the one that reproduces its routing in expert-contiguous
+// form: rows of an expert ordered by token index, then by slot.  The histogram
+// has the engine's meaning (one count per selection,
+// core/src/CUDA/kernel/moe_router.cu:107-110); accumulation across calls is the
+// caller's choice (AXM_FLAG_HIST_ACCUMULATE).  The combine kernel computes
+// bf16(sum_i gate_i * o_i) and then bf16(x + y), the two rounding points of
+// core/src/CUDA/kernel/moe_router.cu:186-203.
+#include "common.cuh"
+
+namespace axm {
+
+__host__ __device__ inline int route_block_begin2(int b, int T) {
+  return (int)(((long long)b * T) / AXM_ROUTE_BLOCKS);
+}
+
+constexpr int kPermThreads = 256;
+constexpr int kPermTokSub = 128;  // tokens placed per pass
+constexpr int kMaxE = 256;
+
+// One CTA per router block.  Shared memory: total[E], base[E], run[E], dst[kPermTokSub*k].
+__global__ void __launch_bounds__(kPermThreads)
+permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx,
+               const int32_t* __restrict__ block_counts, int32_t* __restrict__ histogram,
+               int32_t* __restrict__ offsets, int32_t* __restrict__ row_src,
+               int32_t* __restrict__ slot_dst, __nv_bfloat16* __restrict__ x_perm,
+               AxmSegment* __restrict__ segments, int32_t* __restrict__ status, int T, int D,
+               int E, int k, int S, int hist_accumulate) {
+  __shared__ int total_s[kMaxE];
+  __shared__ int run_s[kMaxE];   // next free row per expert for this block
+  __shared__ int scan_s[kMaxE + 1];
+  __shared__ int dst_s[kPermTokSub * 8];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.x;
+
+  for (int e = tid; e < E; e += kPermThreads) {
+    total_s[e] = 0;
+    run_s[e] = 0;
+  }
+  __syncthreads();
+  // Column sums of block_counts: all blocks -> total, blocks before this one -> run.
+  const int n_cells = AXM_ROUTE_BLOCKS * E;
+  for (int i = tid; i < n_cells; i += kPermThreads) {
+    int bb = i / E, e = i - bb * E;
+    int c = block_counts[i];
+    if (c != 0) {
+      atomicAdd(&total_s[e], c);
+      if (bb < b) atomicAdd(&run_s[e], c);
+    }
+  }
+  __syncthreads();
+  // Exclusive scan over experts (E <= 256: one warp walks it in chunks of 32).
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      int e = e0 + lane;
+      int v = e < E ? total_s[e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (e < E) scan_s[e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) scan_s[E] = carry;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += kPermThreads) run_s[e] += scan_s[e];
+  if (b == 0) {
+    for (int e = tid; e <= E; e += kPermThreads) {
+      if (offsets != nullptr) offsets[e] = scan_s[e];
+      if (e < E && histogram != nullptr)
+        histogram[e] = (hist_accumulate ? histogram[e] : 0) + total_s[e];
+    }
+    if (segments != nullptr) {
+      for (int e = tid; e < E + S; e += kPermThreads) {
+        AxmSegment sg;
+        if (e < E) {
+          sg.a_row0 = scan_s[e];
+          sg.out_row0 = scan_s[e];
+          sg.rows = total_s[e];
+          sg.expert = e;
+        } else {
+          sg.a_row0 = 0;
+          sg.out_row0 = T * k + (e - E) * T;
+          sg.rows = T;
+          sg.expert = e | AXM_SEG_ALT_A;
+        }
+        segments[e] = sg;
+      }
+    }
+    if (status != nullptr && tid == 0) *status = 0;
+  }
+  __syncthreads();
+
+  const int t_begin = route_block_begin2(b, T);
+  const int t_end = route_block_begin2(b + 1, T);
+  for (int ts = t_begin; ts < t_end; ts += kPermTokSub) {
+    const int nt = min(kPermTokSub, t_end - ts);
+    const int n_ent = nt * k;
+    // Stable placement: one warp walks the (token, slot) entries in order, 32 at
+    // a time; equal experts inside a chunk are ranked by a match + popcount.
+    if (warp == 0) {
+      for (int c0 = 0; c0 < n_ent; c0 += 32) {
+        int i = c0 + lane;
+        bool live = i < n_ent;
+        int e = live ? topk_idx[(size_t)ts * k + i] : -1;
+        unsigned peers = __match_any_sync(0xffffffffu, e);
+        int rank = __popc(peers & ((1u << lane) - 1u));
+        int dst = -1;
+        if (live) {
+          dst = run_s[e] + rank;
+          dst_s[i] = dst;
+        }
+        __syncwarp();
+        if (live && rank == __popc(peers) - 1) run_s[e] += rank + 1;  // last peer advances
+        __syncwarp();
+        if (live) {
+          size_t slot = (size_t)ts * k + i;
+          if (slot_dst != nullptr) slot_dst[slot] = dst;
+          if (row_src != nullptr) row_src[dst] = (int32_t)slot;
+        }
+      }
+    }
+    __syncthreads();
+    // Row copies: a warp takes a token, reads its row once in 16-byte pieces and
+    // stores it to each of its k destinations.
+    if (x_perm != nullptr) {
+      const int chunks = D / 8;
+      for (int tt = warp; tt < nt; tt += kPermThreads / 32) {
+        const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(ts + tt) * D);
+        for (int c0 = 0; c0 < chunks; c0 += 128) {
+          uint4 v[4];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            int c = c0 + j * 32 + lane;
+            if (c < chunks) v[j] = __ldg(src + c);
+          }
+          for (int i = 0; i < k; ++i) {
+            uint4* dstp = reinterpret_cast<uint4*>(x_perm + (size_t)dst_s[tt * k + i] * D);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              int c = c0 + j * 32 + lane;
+              if (c < chunks) dstp[c] = v[j];
+            }
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+}
+
+__global__ void build_segments_kernel(const int32_t* __restrict__ offsets,
+                                      AxmSegment* __restrict__ segments, int T, int E, int k,
+                                      int S) {
+  for (int e = threadIdx.x; e < E + S; e += blockDim.x) {
+    AxmSegment sg;
+    if (e < E) {
+      sg.a_row0 = offsets[e];
+      sg.out_row0 = offsets[e];
+      sg.rows = offsets[e + 1] - offsets[e];
+      sg.expert = e;
+    } else {
+      sg.a_row0 = 0;
+      sg.out_row0 = T * k + (e - E) * T;
+      sg.rows = T;
+      sg.expert = e | AXM_SEG_ALT_A;
+    }
+    segments[e] = sg;
+  }
+}
+
+// One thread per 16-byte piece of an output row.
+template <int K_MAX>
+__global__ void __launch_bounds__(256)
+combine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ o,
+               const __nv_bfloat16* __restrict__ o_shared, const int32_t* __restrict__ slot_dst,
+               const float* __restrict__ topk_gate, __nv_bfloat16* __restrict__ y,
+               __nv_bfloat16* __restrict__ out, int T, int D, int k, int S, int residual) {
+  const int chunks = D / 8;
+  const long long total = (long long)T * chunks;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
+       g += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(g / chunks);
+    const int c = (int)(g - (long long)t * chunks);
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
+    uint4 v[K_MAX];
+    float gw[K_MAX];
+#pragma unroll
+    for (int i = 0; i < K_MAX; ++i) {
+      if (i < k) {
+        int r = __ldg(slot_dst + (size_t)t * k + i);
+        gw[i] = __ldg(topk_gate + (size_t)t * k + i);
+        v[i] = __ldg(reinterpret_cast<const uint4*>(o + (size_t)r * D) + c);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < K_MAX; ++i) {
+      if (i < k) {
+        acc[0] = fmaf(gw[i], bf16_lo(v[i].x), acc[0]);
+        acc[1] = fmaf(gw[i], bf16_hi(v[i].x), acc[1]);
+        acc[2] = fmaf(gw[i], bf16_lo(v[i].y), acc[2]);
+        acc[3] = fmaf(gw[i], bf16_hi(v[i].y), acc[3]);
+        acc[4] = fmaf(gw[i], bf16_lo(v[i].z), acc[4]);
+        acc[5] = fmaf(gw[i], bf16_hi(v[i].z), acc[5]);
+        acc[6] = fmaf(gw[i], bf16_lo(v[i].w), acc[6]);
+        acc[7] = fmaf(gw[i], bf16_hi(v[i].w), acc[7]);
+      }
+    }
+    for (int s = 0; s < S; ++s) {
+      uint4 w = __ldg(reinterpret_cast<const uint4*>(o_shared + ((size_t)s * T + t) * D) + c);
+      acc[0] += bf16_lo(w.x);
+      acc[1] += bf16_hi(w.x);
+      acc[2] += bf16_lo(w.y);
+      acc[3] += bf16_hi(w.y);
+      acc[4] += bf16_lo(w.z);
+      acc[5] += bf16_hi(w.z);
+      acc[6] += bf16_lo(w.w);
+      acc[7] += bf16_hi(w.w);
+    }
+    uint4 yv;
+    yv.x = pack_bf16(acc[0], acc[1]);
+    yv.y = pack_bf16(acc[2], acc[3]);
+    yv.z = pack_bf16(acc[4], acc[5]);
+    yv.w = pack_bf16(acc[6], acc[7]);
+    if (y != nullptr) reinterpret_cast<uint4*>(y + (size_t)t * D)[c] = yv;
+    if (residual) {
+      uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)t * D) + c);
+      uint4 r;
+      r.x = pack_bf16(bf16_lo(xv.x) + bf16_lo(yv.x), bf16_hi(xv.x) + bf16_hi(yv.x));
+      r.y = pack_bf16(bf16_lo(xv.y) + bf16_lo(yv.y), bf16_hi(xv.y) + bf16_hi(yv.y));
+      r.z = pack_bf16(bf16_lo(xv.z) + bf16_lo(yv.z), bf16_hi(xv.z) + bf16_hi(yv.z));
+      r.w = pack_bf16(bf16_lo(xv.w) + bf16_lo(yv.w), bf16_hi(xv.w) + bf16_hi(yv.w));
+      reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = r;
+    } else {
+      reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = yv;
+    }
+  }
+}
+
+int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
+                   const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                   int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
+                   int32_t* status, cudaStream_t st) {
+  permute_kernel<<<AXM_ROUTE_BLOCKS, kPermThreads, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), topk_idx, block_counts, histogram, offsets, row_src,
+      slot_dst, static_cast<__nv_bfloat16*>(x_perm), segments, status, d->tokens, d->d_model,
+      d->num_experts, d->top_k, d->num_shared, (d->flags & AXM_FLAG_HIST_ACCUMULATE) ? 1 : 0);
+  return check_launch("permute_kernel");
+}
+
+}  // namespace axm
+
+using namespace axm;
+
+static int validate_perm(const AxmMoeDesc* d) {
+  if (d == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
+  if (d->tokens < 0 || d->d_model <= 0 || d->num_experts <= 0 || d->top_k <= 0)
+    return fail(AXM_ERR_ARGUMENT, "tokens/d_model/num_experts/top_k must be positive");
+  if (d->num_experts > kMaxE) return fail(AXM_ERR_ARGUMENT, "num_experts %d > %d", d->num_experts, kMaxE);
+  if (d->top_k > 8) return fail(AXM_ERR_ARGUMENT, "top_k %d > 8", d->top_k);
+  if (d->num_shared < 0 || d->num_shared > 8) return fail(AXM_ERR_ARGUMENT, "num_shared %d not in 0..8", d->num_shared);
+  if (d->d_model % 8 != 0) return fail(AXM_ERR_ARGUMENT, "d_model %d not a multiple of 8", d->d_model);
+  if ((long long)d->tokens * d->top_k + (long long)d->tokens * d->num_shared > 0x7fffffffLL)
+    return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
+  return AXM_OK;
+}
+
+extern "C" int axm_moe_permute(const AxmMoeDesc* desc, const void* x, const int32_t* topk_idx,
+                               const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                               int32_t* row_src, int32_t* slot_dst, void* x_perm, void* stream) {
+  if (int rc = validate_perm(desc)) return rc;
+  if (!topk_idx || !block_counts) return fail(AXM_ERR_ARGUMENT, "axm_moe_permute: null pointer");
+  if (x_perm != nullptr && x == nullptr) return fail(AXM_ERR_ARGUMENT, "axm_moe_permute: x_perm without x");
+  if (int rc = require_device()) return rc;
+  return launch_permute(desc, x, topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
+                        x_perm, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* offsets,
+                                      AxmSegment* segments, void* stream) {
+  if (int rc = validate_perm(desc)) return rc;
+  if (!offsets || !segments) return fail(AXM_ERR_ARGUMENT, "axm_moe_build_segments: null pointer");
+  if (int rc = require_device()) return rc;
+  build_segments_kernel<<<1, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      offsets, segments, desc->tokens, desc->num_experts, desc->top_k, desc->num_shared);
+  return check_launch("build_segments_kernel");
+}
+
+extern "C" int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void* o,
+                               const void* o_shared, const int32_t* slot_dst,
+                               const float* topk_gate, void* y, void* out, void* stream) {
+  if (int rc = validate_perm(desc)) return rc;
+  if (!o || !slot_dst || !topk_gate || !out) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: null pointer");
+  const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
+  if (residual && !x) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: residual without x");
+  if (desc->num_shared > 0 && !o_shared) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: shared experts without o_shared");
+  if (desc->tokens == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  long long total = (long long)desc->tokens * (desc->d_model / 8);
+  int blocks = (int)((total + 255) / 256);
+  int cap = sm_count() * 8;
+  if (blocks > cap) blocks = cap;
+  combine_kernel<8><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(o),
+      static_cast<const __nv_bfloat16*>(o_shared), slot_dst, topk_gate,
+      static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(out), desc->tokens,
+      desc->d_model, desc->top_k, desc->num_shared, residual);
+  return check_launch("combine_kernel");
+}

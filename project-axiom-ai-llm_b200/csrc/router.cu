@@ -1,0 +1,277 @@
+// Fused router: fp32 logits, softmax, top-k (lowest index wins ties),
+// renormalised gates and per-block expert counts.
+//
+// Stands in for top2_router_kernel of the reference engine
+// (core/src/CUDA/kernel/moe_router.cu:27-111), generalised to any k and E and
+// to fp32 router weights.  Everything after the logits follows that kernel's
+// fp32 operation order exactly, because expert indices and gates have to come
+// out bit-identical for identical logits:
+//     m = max_e z_e;  p_e = expf(z_e - m);  s = sum_e p_e (ascending e);
+//     p_e *= 1 / (s + 1e-9f);  k scans with strict '>' from e = 0;
+//     gate_i = p_i / (sum of the selected p + 1e-9f).
+// This file must be compiled without fast-math.
+//
+// Work split: the token range is cut into AXM_ROUTE_BLOCKS contiguous blocks,
+// one CTA each.  The permute kernel uses the same split, so the per-block
+// counts written here give it a stable placement without atomics on global
+// memory.
+#include "common.cuh"
+
+namespace axm {
+
+constexpr int kRouterThreads = 256;
+constexpr int kTokSub = 64;   // tokens handled per pass inside a block
+constexpr int kEC = 8;        // experts per register chunk
+constexpr int kMaxK = 8;
+
+__host__ __device__ inline int route_block_begin(int b, int T) {
+  return (int)(((long long)b * T) / AXM_ROUTE_BLOCKS);
+}
+
+template <typename WT>
+__device__ __forceinline__ float load_w(const WT* p);
+template <>
+__device__ __forceinline__ float load_w<float>(const float* p) {
+  return __ldg(p);
+}
+template <>
+__device__ __forceinline__ float load_w<__nv_bfloat16>(const __nv_bfloat16* p) {
+  return __bfloat162float(*p);
+}
+
+// Softmax / top-k / gates for one token whose logits sit in shared memory
+// (row `z`, overwritten with probabilities and then scratched).
+template <int K_MAX>
+__device__ __forceinline__ void route_one_token(float* z, int E, int k, int32_t* idx_out,
+                                                float* gate_out, int* hist_s) {
+  float m = z[0];
+  for (int e = 1; e < E; ++e) m = z[e] > m ? z[e] : m;
+  float s = 0.0f;
+  for (int e = 0; e < E; ++e) {
+    float p = expf(z[e] - m);
+    z[e] = p;
+    s += p;
+  }
+  float inv = 1.0f / (s + 1e-9f);
+  for (int e = 0; e < E; ++e) z[e] *= inv;
+
+  int sel[K_MAX];
+  float pv[K_MAX];
+  float sel_sum = 0.0f;
+#pragma unroll
+  for (int i = 0; i < K_MAX; ++i) {
+    if (i < k) {
+      int best = 0;
+      float bv = -1.0f;
+      for (int e = 0; e < E; ++e) {
+        float p = z[e];
+        if (p > bv) {
+          bv = p;
+          best = e;
+        }
+      }
+      z[best] = -2.0f;  // taken
+      sel[i] = best;
+      pv[i] = bv;
+      sel_sum += bv;
+    }
+  }
+  float denom = sel_sum + 1e-9f;
+#pragma unroll
+  for (int i = 0; i < K_MAX; ++i) {
+    if (i < k) {
+      idx_out[i] = sel[i];
+      gate_out[i] = pv[i] / denom;
+      atomicAdd(&hist_s[sel[i]], 1);
+    }
+  }
+}
+
+// kFromLogits: skip the GEMV and read z from `logits_in`.
+template <typename WT, bool kFromLogits>
+__global__ void __launch_bounds__(kRouterThreads)
+router_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ wr,
+              const float* __restrict__ bias, const float* __restrict__ logits_in,
+              float* __restrict__ logits_out, int32_t* __restrict__ topk_idx,
+              float* __restrict__ topk_gate, int32_t* __restrict__ block_counts, int T, int D,
+              int E, int k) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int EP = E + 1;  // padded row, so that threads walking rows hit distinct banks
+  float* z_s = reinterpret_cast<float*>(smem_raw);                 // [kTokSub][EP]
+  float* part_s = z_s + kTokSub * EP;                              // [8 warps][kTokSub][kEC]
+  int* hist_s = reinterpret_cast<int*>(part_s + 8 * kTokSub * kEC);  // [E]
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int t_begin = route_block_begin(blockIdx.x, T);
+  const int t_end = route_block_begin(blockIdx.x + 1, T);
+
+  for (int e = tid; e < E; e += kRouterThreads) hist_s[e] = 0;
+  __syncthreads();
+
+  for (int ts = t_begin; ts < t_end; ts += kTokSub) {
+    const int nt = min(kTokSub, t_end - ts);
+
+    if constexpr (kFromLogits) {
+      for (int i = tid; i < nt * E; i += kRouterThreads) {
+        int tt = i / E, e = i - tt * E;
+        z_s[tt * EP + e] = logits_in[(size_t)(ts + tt) * E + e];
+      }
+    } else {
+      for (int i = tid; i < nt * EP; i += kRouterThreads) z_s[i] = 0.0f;
+      __syncthreads();
+      // Each thread owns 8 consecutive d of every 2048-wide slab and keeps the
+      // matching 8 x kEC weights in registers while it walks the tokens.
+      for (int e0 = 0; e0 < E; e0 += kEC) {
+        for (int d0 = 0; d0 < D; d0 += kRouterThreads * 8) {
+          const int d = d0 + tid * 8;
+          float w[8][kEC];
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+#pragma unroll
+            for (int e = 0; e < kEC; ++e)
+              w[j][e] = (d + j < D && e0 + e < E) ? load_w<WT>(wr + (size_t)(d + j) * E + e0 + e)
+                                                  : 0.0f;
+          for (int tt = 0; tt < nt; ++tt) {
+            uint4 xv = make_uint4(0, 0, 0, 0);
+            if (d < D) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(ts + tt) * D + d));
+            float xf[8] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y),
+                           bf16_lo(xv.z), bf16_hi(xv.z), bf16_lo(xv.w), bf16_hi(xv.w)};
+            float acc[kEC];
+#pragma unroll
+            for (int e = 0; e < kEC; ++e) acc[e] = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+#pragma unroll
+              for (int e = 0; e < kEC; ++e) acc[e] = fmaf(xf[j], w[j][e], acc[e]);
+            // Transposed butterfly: 8 values on 32 lanes -> one value per lane
+            // after three exchange steps, then two plain steps.  Fixed tree, so
+            // the sum order (and the logits) are reproducible.
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              bool up = lane & 16;
+              float send = up ? acc[i] : acc[i + 4];
+              float keep = up ? acc[i + 4] : acc[i];
+              acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+              bool up = lane & 8;
+              float send = up ? acc[i] : acc[i + 2];
+              float keep = up ? acc[i + 2] : acc[i];
+              acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+            }
+            {
+              bool up = lane & 4;
+              float send = up ? acc[0] : acc[1];
+              float keep = up ? acc[1] : acc[0];
+              acc[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+            }
+            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
+            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+            if ((lane & 3) == 0) {
+              int e = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+              part_s[(warp * kTokSub + tt) * kEC + e] = acc[0];
+            }
+          }
+          __syncthreads();
+          for (int i = tid; i < nt * kEC; i += kRouterThreads) {
+            int tt = i / kEC, e = i - tt * kEC;
+            if (e0 + e < E) {
+              float sum = z_s[tt * EP + e0 + e];
+#pragma unroll
+              for (int wv = 0; wv < 8; ++wv) sum += part_s[(wv * kTokSub + tt) * kEC + e];
+              z_s[tt * EP + e0 + e] = sum;
+            }
+          }
+          __syncthreads();
+        }
+      }
+      if (bias != nullptr)
+        for (int i = tid; i < nt * E; i += kRouterThreads) {
+          int tt = i / E, e = i - tt * E;
+          z_s[tt * EP + e] += bias[e];
+        }
+    }
+    __syncthreads();
+    if (logits_out != nullptr)
+      for (int i = tid; i < nt * E; i += kRouterThreads) {
+        int tt = i / E, e = i - tt * E;
+        logits_out[(size_t)(ts + tt) * E + e] = z_s[tt * EP + e];
+      }
+    __syncthreads();
+    if (tid < nt) {
+      int t = ts + tid;
+      route_one_token<kMaxK>(z_s + tid * EP, E, k, topk_idx + (size_t)t * k,
+                             topk_gate + (size_t)t * k, hist_s);
+    }
+    __syncthreads();
+  }
+  for (int e = tid; e < E; e += kRouterThreads)
+    block_counts[(size_t)blockIdx.x * E + e] = hist_s[e];
+}
+
+static size_t router_smem_bytes(int E) {
+  return sizeof(float) * ((size_t)kTokSub * (E + 1) + 8 * kTokSub * kEC) + sizeof(int) * (size_t)E;
+}
+
+static int validate_route(const AxmMoeDesc* d) {
+  if (d == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
+  if (d->tokens < 0 || d->d_model <= 0 || d->num_experts <= 0 || d->top_k <= 0)
+    return fail(AXM_ERR_ARGUMENT, "tokens/d_model/num_experts/top_k must be positive");
+  if (d->num_experts > 256) return fail(AXM_ERR_ARGUMENT, "num_experts %d > 256", d->num_experts);
+  if (d->top_k > kMaxK || d->top_k > d->num_experts)
+    return fail(AXM_ERR_ARGUMENT, "top_k %d must be <= min(num_experts, %d)", d->top_k, kMaxK);
+  if (d->d_model % 8 != 0) return fail(AXM_ERR_ARGUMENT, "d_model %d not a multiple of 8", d->d_model);
+  return AXM_OK;
+}
+
+}  // namespace axm
+
+using namespace axm;
+
+extern "C" int axm_moe_router(const AxmMoeDesc* desc, const void* x, const void* router_w,
+                              const float* router_bias, float* logits, int32_t* topk_idx,
+                              float* topk_gate, int32_t* block_counts, void* stream) {
+  if (int rc = validate_route(desc)) return rc;
+  if (!x || !router_w || !topk_idx || !topk_gate || !block_counts)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_router: null pointer");
+  if (int rc = require_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t smem = router_smem_bytes(desc->num_experts);
+  const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+  if (desc->router_dtype == AXM_ROUTER_FP32) {
+    auto kern = router_kernel<float, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<AXM_ROUTE_BLOCKS, kRouterThreads, smem, st>>>(
+        xb, static_cast<const float*>(router_w), router_bias, nullptr, logits, topk_idx, topk_gate,
+        block_counts, desc->tokens, desc->d_model, desc->num_experts, desc->top_k);
+  } else if (desc->router_dtype == AXM_ROUTER_BF16) {
+    auto kern = router_kernel<__nv_bfloat16, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    kern<<<AXM_ROUTE_BLOCKS, kRouterThreads, smem, st>>>(
+        xb, static_cast<const __nv_bfloat16*>(router_w), router_bias, nullptr, logits, topk_idx,
+        topk_gate, block_counts, desc->tokens, desc->d_model, desc->num_experts, desc->top_k);
+  } else {
+    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", desc->router_dtype);
+  }
+  return check_launch("router_kernel");
+}
+
+extern "C" int axm_moe_route_from_logits(const AxmMoeDesc* desc, const float* logits,
+                                         int32_t* topk_idx, float* topk_gate,
+                                         int32_t* block_counts, void* stream) {
+  if (int rc = validate_route(desc)) return rc;
+  if (!logits || !topk_idx || !topk_gate || !block_counts)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_route_from_logits: null pointer");
+  if (int rc = require_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  size_t smem = router_smem_bytes(desc->num_experts);
+  auto kern = router_kernel<float, true>;
+  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  kern<<<AXM_ROUTE_BLOCKS, kRouterThreads, smem, st>>>(nullptr, nullptr, nullptr, logits, nullptr,
+                                                       topk_idx, topk_gate, block_counts,
+                                                       desc->tokens, desc->d_model,
+                                                       desc->num_experts, desc->top_k);
+  return check_launch("router_kernel(from logits)");
+}
