@@ -1,0 +1,354 @@
+"""Benchmark of the MoE-layer hot path on B200.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--config C3] [--impl reference]
+
+A step is one forward call of the layer over one batch of seeded synthetic
+tokens.  N = 1 runs the whole layer on one GPU; N > 1 (under torchrun) runs it
+expert-parallel: T/N tokens and E/N experts per rank, all-to-all dispatch and
+return.  Rank 0 prints one JSON line.  `--impl reference` times the CPU
+statement of the layer (the reference engine has no CPU implementation of its
+own and its GPU kernels are single-GPU CUDA-core code) on the host cores.
+"""
+import argparse
+import importlib
+import importlib.util
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+PKG_DIR = os.path.join(ROOT, "project-axiom-ai-llm_b200")
+
+# Fallback peaks, used only if MEASURED_PEAKS.json is absent.
+FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1590.0
+
+# DRAM bytes per launch of the gate/up GEMM from the committed ncu capture
+# (profiles/): {workload: bytes}.  None where no capture exists yet.
+NCU_TRAFFIC_BYTES = {}
+
+
+def load_package():
+    name = "project_axiom_ai_llm_b200"
+    if name in sys.modules:
+        return sys.modules[name]
+    spec = importlib.util.spec_from_file_location(
+        name, os.path.join(PKG_DIR, "__init__.py"), submodule_search_locations=[PKG_DIR])
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[name] = mod
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"],
+                "bf16_tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": FALLBACK_HBM_GBS, "bf16_tflops": FALLBACK_BF16_TFLOPS,
+            "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples while the timed region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+        self.file = None
+
+    def start(self):
+        try:
+            self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-lms", "50", "-i", str(self.index)], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.12)
+        self.proc.terminate()
+        self.proc.wait()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        self.file.close()
+        os.unlink(self.file.name)
+        busy = [v for v in sm if v > 0.5 * max(sm)] if sm else []
+        return {"sm_mhz": statistics.median(busy) if busy else None,
+                "sm_max_mhz": max(mx) if mx else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def cpu_baseline(cfg, x, w, sample_tokens, repeats=1):
+    """The CPU oracle timed on the first `sample_tokens` tokens of the batch."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_binding
+    orc = oracle_binding.load()
+    n = min(sample_tokens, cfg.tokens)
+    xs = x[:n].cpu()
+    wc = {k: (v.cpu() if v is not None else None) for k, v in w.items()}
+    best = None
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        z = orc.router_logits(xs, wc["router_w"], wc.get("router_bias"))
+        idx, gates, _, _, _ = orc.route(z, cfg.top_k)
+        orc.permutation(idx, cfg.num_experts)
+        orc.forward(xs, wc, idx, gates)
+        dt = time.perf_counter() - t0
+        best = dt if best is None else min(best, dt)
+    return {"value": n / best, "unit": "tokens/s", "cores": orc.threads(), "kind": "port",
+            "sample": f"first {n} tokens of the batch through router, permutation and expert FFN "
+                      f"(C, OpenMP, fp32 accumulate), {best:.2f} s"}
+
+
+def run_reference(args, wl):
+    """--impl reference: the CPU statement of the layer on the host cores, rank 0 only."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    import torch
+    cfg = wl.CONFIGS[args.config]
+    sample = args.reference_tokens
+    small = wl.scaled(cfg, tokens=sample)
+    x, w = wl.make_inputs(small)
+    times = []
+    info = None
+    for i in range(args.warmup + args.steps):
+        t0 = time.perf_counter()
+        info = cpu_baseline(small, x, w, sample)
+        if i >= args.warmup:
+            times.append(time.perf_counter() - t0)
+    ms = 1000.0 * sum(times) / len(times)
+    value = sample / (ms / 1000.0)
+    info["value"] = value
+    line = {
+        "impl": "reference", "metric": "MoE-layer tokens/s", "value": value, "unit": "tokens/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "gpu_launches": 0,
+        "config": workload_config(cfg, args.gpus, f"CPU sample of {sample} tokens per step"),
+        "cpu_baseline": info,
+        "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "note": "the reference engine has no CPU MoE path; this is the CPU port of its layer "
+                "semantics (oracle/), all host threads",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(cfg, n_gpus, l2_note):
+    return {
+        "workload": f"{cfg.name}: MoE layer forward, T={cfg.tokens} d_model={cfg.d_model} "
+                    f"E={cfg.num_experts}+{cfg.num_shared} shared top-{cfg.top_k} d_ff={cfg.d_ff}, "
+                    f"seed {cfg.seed}",
+        "tokens": cfg.tokens, "d_model": cfg.d_model, "num_experts": cfg.num_experts,
+        "top_k": cfg.top_k, "d_ff": cfg.d_ff, "num_shared": cfg.num_shared,
+        "parallelism": "single GPU" if n_gpus == 1 else f"expert-parallel ep{n_gpus} "
+                       f"({cfg.num_experts // n_gpus} experts and {cfg.tokens // n_gpus} tokens per GPU)",
+        "l2": l2_note,
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--config", default="C3", choices=["C1", "C2", "C3", "C4", "C5"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--cpu-tokens", type=int, default=256, help="tokens in the CPU baseline sample")
+    ap.add_argument("--reference-tokens", type=int, default=256)
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
+
+    axm = load_package()
+    wl = importlib.import_module("project_axiom_ai_llm_b200.workloads")
+    if args.impl == "reference":
+        run_reference(args, wl)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the MoE layer has no CPU fallback")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    cfg = wl.CONFIGS[args.config]
+    peaks = measured_peaks()
+    T, D, k = cfg.tokens, cfg.d_model, cfg.top_k
+    x, w = wl.make_inputs(cfg, device=dev)  # same seed on every rank -> same tensors
+    launches_per_step = 0
+
+    if world == 1:
+        layer = axm.MoeLayer(w, T, k)
+        out = torch.empty_like(x)
+        x_local = x
+        step = lambda: layer.forward(x_local, out)
+        launches_per_step = 5
+    else:
+        ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
+        assert T % world == 0 and cfg.num_experts % world == 0
+        tl = T // world
+        x_local = x[rank * tl:(rank + 1) * tl].contiguous()
+        wloc = ep.shard_weights(w, rank, world)
+        del w
+        layer = ep.ExpertParallelMoe(wloc, tl, cfg.num_experts, k)
+        out = torch.empty_like(x_local)
+        step = lambda: layer.forward(x_local, out)
+        launches_per_step = 5  # router, permute, two GEMMs, combine (exchanges are NCCL's)
+    del x
+    torch.cuda.empty_cache()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms_total], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_total = float(t.item())
+    ms_step = ms_total / args.steps
+    value = T / (ms_step / 1000.0)
+
+    # ---- end to end: host buffers, copies inside the timed region ----------------
+    h_x = x_local.cpu().pin_memory()
+    h_out = torch.empty_like(h_x).pin_memory()
+    d_x = torch.empty_like(x_local)
+    if world == 1:
+        e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out)
+    else:
+        def e2e_step():
+            d_x.copy_(h_x, non_blocking=True)
+            layer.forward(d_x, out)
+            h_out.copy_(out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record()
+    barrier()
+    e2e_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_ms /= args.steps
+    clocks = sampler.stop() if rank == 0 else None
+    copy_bytes = h_x.numel() * 2 * world
+
+    # ---- roofline of the dominant kernel (gate/up grouped GEMM) ---------------------
+    roofline = None
+    stages = None
+    if world == 1:
+        acc = [0.0] * 5
+        reps = 10
+        for _ in range(reps):
+            _, ms = layer.forward_profiled(x_local, out)
+            acc = [a + m for a, m in zip(acc, ms)]
+        stage_ms = [a / reps for a in acc]
+        names = ["router", "permute", "gate_up_gemm", "down_gemm", "combine"]
+        sb = cfg.stage_bytes(4)
+        rows = T * (k + cfg.num_shared)
+        flops_gu = 4.0 * rows * D * cfg.d_ff
+        flops_dn = 2.0 * rows * D * cfg.d_ff
+        stages = {n: {"ms": m} for n, m in zip(names, stage_ms)}
+        for n in ("router", "permute", "combine"):
+            gbs = sb[n] / (stages[n]["ms"] * 1e-3) / 1e9
+            stages[n].update({"bytes": sb[n], "gb_s": gbs, "frac_hbm": gbs / peaks["hbm_gbs"]})
+        for n, fl in (("gate_up_gemm", flops_gu), ("down_gemm", flops_dn)):
+            tf = fl / (stages[n]["ms"] * 1e-3) / 1e12
+            stages[n].update({"flops": fl, "tflop_s": tf, "frac_tensor": tf / peaks["bf16_tflops"]})
+        a = stages["gate_up_gemm"]["tflop_s"]
+        roofline = {"kernel": "grouped_gemm_kernel<SwiGLU> (gate/up)", "bound": "tensor",
+                    "achieved": a, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": a / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
+                    "frac_of_sustained": a / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
+                    "traffic": NCU_TRAFFIC_BYTES.get(cfg.name)}
+        status = layer.status()
+        if status != 0:
+            raise SystemExit(f"GEMM kernel reported a timed-out wait (status {status})")
+
+    cpu = None
+    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+        cpu = cpu_baseline(cfg, x_local, layer.w, args.cpu_tokens)
+
+    if rank == 0:
+        line = {
+            "metric": "MoE-layer tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": workload_config(cfg, world, "inputs larger than L2 (expert weights "
+                                      f"{cfg.weight_bytes / world / 1e9:.2f} GB per GPU); no flush"),
+            "e2e": {"value": T / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": copy_bytes, "d2h_bytes_per_step": copy_bytes},
+            "gpu_launches": launches_per_step * args.steps * world,
+            "clocks": clocks,
+            "gemm_tflops_layer": cfg.gemm_flops / (ms_step * 1e-3) / 1e12,
+            "gemm_frac_of_peak_layer": cfg.gemm_flops / (ms_step * 1e-3) / 1e12 / (peaks["bf16_tflops"] * world),
+        }
+        if roofline is not None:
+            line["roofline"] = roofline
+            line["stages"] = stages
+        if cpu is not None:
+            line["cpu_baseline"] = cpu
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -112,6 +112,14 @@ AXM_API int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes);
 AXM_API int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* axm_moe_forward with CUDA events between its five kernels; synchronises the
+ * stream and returns the device time of each stage in milliseconds:
+ * stage_ms[0..4] = router, permute, gate/up GEMM, down GEMM, combine.  A
+ * measuring aid with no reference counterpart. */
+AXM_API int axm_moe_forward_profiled(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
+                                     void* workspace, size_t workspace_bytes, void* stream,
+                                     float* stage_ms);
+
 /* The same call for a caller whose activations live in host memory: copies x
  * from (pinned) host memory, runs the layer, copies out back, all on `stream`,
  * and synchronises the stream before returning.  Weights stay device pointers.
@@ -168,7 +176,7 @@ AXM_API int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* offset
 
 /* Grouped SwiGLU expert FFN over `num_segments` segments read from device memory:
  *   h   = SiLU(A . Wg[e]) * (A . Wu[e])     -> bf16 [rows_total][F]
- *   o   = h . Wd[e]                         -> bf16 [rows_total][D]
+ *   o   = h . Wd[e]                         -> fp32 [rows_total][D]
  * tcgen05 tensor-core kernels, bf16 in, fp32 accumulate in tensor memory.
  * Replaces moe_top2_dispatch_kernel phases A and B
  * (core/src/CUDA/kernel/moe_router.cu:155-190).
@@ -182,10 +190,12 @@ AXM_API int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, int32
                                const void* shared_up, const void* shared_down, void* h,
                                void* o, int32_t rows_total, int32_t* status, void* stream);
 
-/* Weighted combine: y[t] = bf16(sum_i gate[t,i] * o[slot_dst[t,i]] + sum_s o_shared[s][t]),
+/* Weighted combine over fp32 expert rows:
+ * y[t] = bf16(sum_i gate[t,i] * o[slot_dst[t,i]] + sum_s o_shared[s][t]),
  * out[t] = bf16(x[t] + y[t]) with AXM_FLAG_RESIDUAL.  Replaces the gate-weighted
  * sum and the residual add (core/src/CUDA/kernel/moe_router.cu:186-203,304-317).
- * o_shared points at the first shared expert's rows ([S][T][D]) or NULL. */
+ * o is fp32 [T*k][D]; o_shared points at the first shared expert's fp32 rows
+ * ([S][T][D]) or NULL. */
 AXM_API int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void* o,
                             const void* o_shared, const int32_t* slot_dst,
                             const float* topk_gate, void* y, void* out, void* stream);

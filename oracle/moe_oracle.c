@@ -291,6 +291,15 @@ static void expert_ffn_rows(const uint16_t* x, const int32_t* rows, int n, int D
   }
 }
 
+/* One expert's FFN over n consecutive rows of x ([n][D] bf16): o[n][D] fp32. */
+ORC_API void orc_expert_ffn(const uint16_t* x, int n, int D, int F, const uint16_t* wg,
+                            const uint16_t* wu, const uint16_t* wd, int h_bf16, float* o) {
+  int32_t* rows = (int32_t*)malloc(sizeof(int32_t) * (size_t)(n > 0 ? n : 1));
+  for (int i = 0; i < n; ++i) rows[i] = i;
+  if (n > 0) expert_ffn_rows(x, rows, n, D, F, wg, wu, wd, h_bf16, o);
+  free(rows);
+}
+
 /*
  * Whole layer from given routing.
  *   x        [T][D] bf16

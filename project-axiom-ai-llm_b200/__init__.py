@@ -72,6 +72,8 @@ def load():
     lib.axm_moe_forward_launches.argtypes = [dp]
     lib.axm_moe_workspace_bytes.argtypes = [dp, ctypes.POINTER(sz)]
     lib.axm_moe_forward.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, sz, vp]
+    lib.axm_moe_forward_profiled.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, sz, vp,
+                                             ctypes.POINTER(ctypes.c_float)]
     lib.axm_moe_forward_host.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, vp, vp, vp, vp, sz, vp]
     lib.axm_moe_status_word.argtypes = [dp, vp, ctypes.POINTER(vp)]
     lib.axm_moe_router.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
@@ -164,6 +166,17 @@ class MoeLayer:
         check(self.lib.axm_moe_forward(ctypes.byref(self.desc), ctypes.byref(t), ptr(self.workspace),
                                        self.workspace.numel(), current_stream()))
         return out, self.histogram
+
+    def forward_profiled(self, x, out=None):
+        """forward() with per-stage device times: returns (out, [ms] * 5)."""
+        if out is None:
+            out = torch.empty_like(x)
+        t = self.tensors(x, out)
+        ms = (ctypes.c_float * 5)()
+        check(self.lib.axm_moe_forward_profiled(ctypes.byref(self.desc), ctypes.byref(t),
+                                                ptr(self.workspace), self.workspace.numel(),
+                                                current_stream(), ms))
+        return out, list(ms)
 
     def forward_host(self, h_x, h_out, d_x, d_out):
         """Activations in (pinned) host memory; synchronises before returning."""

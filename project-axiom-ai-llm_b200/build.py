@@ -52,11 +52,11 @@ def build(force=False, verbose=True, ptxas_info=False):
     core = [os.path.join(CSRC, s) for s in CORE_SOURCES]
     extra = ["-Xptxas", "-v"] if ptxas_info else []
     if force or _stale(LIB, core):
-        _run([_nvcc()] + NVCC_FLAGS + extra + ["-shared", "-o", LIB] + core + ["-lcudart"], verbose)
+        _run([_nvcc()] + NVCC_FLAGS + extra + ["-shared", "-o", LIB] + core + ["-cudart", "shared"], verbose)
     drop = [os.path.join(CSRC, s) for s in DROPIN_SOURCES]
     if all(os.path.exists(s) for s in drop) and (force or _stale(DROPIN, drop + [LIB])):
         _run([_nvcc()] + NVCC_FLAGS + ["-shared", "-o", DROPIN] + drop +
-             ["-L" + HERE, "-laxm_moe", "-Xlinker", "-rpath=$ORIGIN", "-lcudart", "-ldl"], verbose)
+             ["-L" + HERE, "-laxm_moe", "-Xlinker", "-rpath=$ORIGIN", "-cudart", "shared", "-ldl"], verbose)
     return LIB
 
 

@@ -11,7 +11,7 @@
 // transposed canonical shared-memory layout; no weight re-layout happens.
 //
 //   kernel<true>  : h[r, f]  = SiLU(x_r . Wg[e][:, f]) * (x_r . Wu[e][:, f])   (bf16)
-//   kernel<false> : o[r, d]  = h_r . Wd[e][:, d]                               (bf16)
+//   kernel<false> : o[r, d]  = h_r . Wd[e][:, d]                               (fp32)
 //
 // Tile: 128 rows x 256 accumulator columns x 64 reduction elements per stage.
 // In the SwiGLU kernel the 256 columns are 128 gate columns followed by the 128
@@ -65,7 +65,7 @@ struct GemmArgs {
   int n_total;        // output columns: F (SwiGLU) or D (down)
   int k_total;        // reduction length: D (SwiGLU) or F (down)
   int routed_experts; // expert ids >= this address the shared-expert weights
-  __nv_bfloat16* out;
+  void* out;          // bf16 rows (SwiGLU) or fp32 rows (down)
   int* status;
   int dbg[4];         // B leading / stride offsets, B and A k-advance (16-byte units)
 };
@@ -271,18 +271,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int row_in_seg = tc.m_tile * BM + quad * 32 + lane;
       const bool row_ok = row_in_seg < sg.rows;
       const int n0 = tc.n_tile * BN_OUT;
-      __nv_bfloat16* out_row =
-          args.out + (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+      const size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
         uint32_t g[32];
         tmem_ld32(t_addr + c0, g);
-        uint32_t packed[16];
-        if (kSwiGLU) {
+        if constexpr (kSwiGLU) {
           uint32_t u[32];
           tmem_ld32(t_addr + 128 + c0, u);
           tmem_ld_wait();
+          uint32_t packed[16];
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
@@ -291,18 +290,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
             packed[j] = pack_bf16(h0, h1);
           }
+          if (row_ok) {
+            __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(args.out) + out_elem;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              if (n0 + c0 + q * 8 < args.n_total)
+                *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
+                    make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+          }
         } else {
           tmem_ld_wait();
+          if (row_ok) {
+            float* out_row = static_cast<float*>(args.out) + out_elem;
 #pragma unroll
-          for (int j = 0; j < 16; ++j)
-            packed[j] = pack_bf16(__uint_as_float(g[2 * j]), __uint_as_float(g[2 * j + 1]));
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (n0 + c0 + q * 8 < args.n_total)
-              *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
-                  make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            for (int q = 0; q < 8; ++q)
+              if (n0 + c0 + q * 4 < args.n_total)
+                *reinterpret_cast<uint4*>(out_row + c0 + q * 4) =
+                    make_uint4(g[4 * q], g[4 * q + 1], g[4 * q + 2], g[4 * q + 3]);
           }
         }
       }
@@ -386,7 +390,8 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
                       const void* w_gate, const void* w_up, const void* w_down,
                       const void* shared_gate, const void* shared_up, const void* shared_down,
-                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st) {
+                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
+                      cudaEvent_t between) {
   if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
   CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;
@@ -430,12 +435,13 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
     sscanf(dbg, "%d,%d,%d,%d", &ga.dbg[0], &ga.dbg[1], &ga.dbg[2], &ga.dbg[3]);
   ga.n_total = F;
   ga.k_total = D;
-  ga.out = static_cast<__nv_bfloat16*>(h);
+  ga.out = h;
   grouped_gemm_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
   if ((rc = check_launch("grouped_gemm_kernel<swiglu>"))) return rc;
+  if (between != nullptr) cudaEventRecord(between, st);
   ga.n_total = D;
   ga.k_total = F;
-  ga.out = static_cast<__nv_bfloat16*>(o);
+  ga.out = o;
   grouped_gemm_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_kernel<down>");
 }
@@ -465,5 +471,5 @@ extern "C" int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, in
   if (int rc = require_device()) return rc;
   return launch_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate,
                            w_up, w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
-                           status, static_cast<cudaStream_t>(stream));
+                           status, static_cast<cudaStream_t>(stream), nullptr);
 }

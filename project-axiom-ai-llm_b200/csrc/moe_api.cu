@@ -85,7 +85,8 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
                       const void* w_gate, const void* w_up, const void* w_down,
                       const void* shared_gate, const void* shared_up, const void* shared_down,
-                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st);
+                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
+                      cudaEvent_t between);
 
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -128,7 +129,7 @@ static Workspace carve(const AxmMoeDesc* d, void* base) {
   w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (E + S)));
   w.x_perm = take(2 * T * k * D);
   w.h = take(2 * rows * F);
-  w.o = take(2 * rows * D);
+  w.o = take(4 * rows * D);
   w.bytes = off;
   return w;
 }
@@ -178,15 +179,15 @@ extern "C" int axm_moe_status_word(const AxmMoeDesc* desc, void* workspace, int3
   return AXM_OK;
 }
 
-extern "C" int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
-                               size_t workspace_bytes, void* stream) {
+static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
+                        size_t workspace_bytes, void* stream, cudaEvent_t* ev) {
   if (int rc = validate_forward(desc)) return rc;
   if (t == nullptr) return fail(AXM_ERR_ARGUMENT, "tensors is null");
+  if (desc->tokens == 0) return AXM_OK;  // empty input: nothing to enqueue
   if (!t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->out)
     return fail(AXM_ERR_ARGUMENT, "x, router_w, w_gate, w_up, w_down and out are required");
   if (desc->num_shared > 0 && (!t->shared_gate || !t->shared_up || !t->shared_down))
     return fail(AXM_ERR_ARGUMENT, "num_shared > 0 needs shared_gate, shared_up and shared_down");
-  if (desc->tokens == 0) return AXM_OK;
   if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0)
     return fail(AXM_ERR_WORKSPACE, "workspace is null or not 256-byte aligned");
   Workspace w = carve(desc, workspace);
@@ -203,19 +204,49 @@ extern "C" int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* t, v
   int32_t* slot_dst = t->slot_dst ? t->slot_dst : w.slot_dst;
   const int T = desc->tokens, k = desc->top_k, S = desc->num_shared, E = desc->num_experts;
 
+  if (ev) cudaEventRecord(ev[0], st);
   int rc = axm_moe_router(desc, t->x, t->router_w, t->router_bias, logits, idx, gate,
                           w.block_counts, stream);
   if (rc) return rc;
+  if (ev) cudaEventRecord(ev[1], st);
   rc = launch_permute(desc, t->x, idx, w.block_counts, t->histogram, offsets, row_src, slot_dst,
                       w.x_perm, w.segments, w.status, st);
   if (rc) return rc;
+  if (ev) cudaEventRecord(ev[2], st);
   rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
                          t->w_down, t->shared_gate, t->shared_up, t->shared_down, w.h, w.o,
-                         T * k + T * S, w.status, st);
+                         T * k + T * S, w.status, st, ev ? ev[3] : nullptr);
   if (rc) return rc;
-  const __nv_bfloat16* o_shared =
-      S > 0 ? static_cast<const __nv_bfloat16*>(w.o) + (size_t)T * k * desc->d_model : nullptr;
-  return axm_moe_combine(desc, t->x, w.o, o_shared, slot_dst, gate, t->y, t->out, stream);
+  if (ev) cudaEventRecord(ev[4], st);
+  const float* o_shared =
+      S > 0 ? static_cast<const float*>(w.o) + (size_t)T * k * desc->d_model : nullptr;
+  rc = axm_moe_combine(desc, t->x, w.o, o_shared, slot_dst, gate, t->y, t->out, stream);
+  if (ev) cudaEventRecord(ev[5], st);
+  return rc;
+}
+
+extern "C" int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+  return forward_impl(desc, t, workspace, workspace_bytes, stream, nullptr);
+}
+
+extern "C" int axm_moe_forward_profiled(const AxmMoeDesc* desc, const AxmMoeTensors* t,
+                                        void* workspace, size_t workspace_bytes, void* stream,
+                                        float* stage_ms) {
+  if (stage_ms == nullptr) return fail(AXM_ERR_ARGUMENT, "stage_ms is null");
+  for (int i = 0; i < 5; ++i) stage_ms[i] = 0.0f;
+  cudaEvent_t ev[6];
+  for (int i = 0; i < 6; ++i)
+    if (cudaEventCreate(&ev[i]) != cudaSuccess) return fail(AXM_ERR_LAUNCH, "cudaEventCreate failed");
+  int rc = forward_impl(desc, t, workspace, workspace_bytes, stream, ev);
+  if (rc == AXM_OK && desc->tokens > 0) {
+    cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
+    if (e != cudaSuccess) rc = fail(AXM_ERR_LAUNCH, "synchronise: %s", cudaGetErrorString(e));
+    else
+      for (int i = 0; i < 5; ++i) cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]);
+  }
+  for (int i = 0; i < 6; ++i) cudaEventDestroy(ev[i]);
+  return rc;
 }
 
 extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors* t,

@@ -7,8 +7,8 @@
 // form: rows of an expert ordered by token index, then by slot.  The histogram
 // has the engine's meaning (one count per selection,
 // core/src/CUDA/kernel/moe_router.cu:107-110); accumulation across calls is the
-// caller's choice (AXM_FLAG_HIST_ACCUMULATE).  The combine kernel computes
-// bf16(sum_i gate_i * o_i) and then bf16(x + y), the two rounding points of
+// caller's choice (AXM_FLAG_HIST_ACCUMULATE).  The combine kernel reads fp32 expert
+// rows, computes bf16(sum_i gate_i * o_i) and then bf16(x + y), the two rounding points of
 // core/src/CUDA/kernel/moe_router.cu:186-203.
 #include "common.cuh"
 
@@ -181,8 +181,8 @@ __global__ void build_segments_kernel(const int32_t* __restrict__ offsets,
 // One thread per 16-byte piece of an output row.
 template <int K_MAX>
 __global__ void __launch_bounds__(256)
-combine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ o,
-               const __nv_bfloat16* __restrict__ o_shared, const int32_t* __restrict__ slot_dst,
+combine_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ o,
+               const float* __restrict__ o_shared, const int32_t* __restrict__ slot_dst,
                const float* __restrict__ topk_gate, __nv_bfloat16* __restrict__ y,
                __nv_bfloat16* __restrict__ out, int T, int D, int k, int S, int residual) {
   const int chunks = D / 8;
@@ -194,39 +194,42 @@ combine_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restr
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-    uint4 v[K_MAX];
+    float4 va[K_MAX], vb[K_MAX];
     float gw[K_MAX];
 #pragma unroll
     for (int i = 0; i < K_MAX; ++i) {
       if (i < k) {
         int r = __ldg(slot_dst + (size_t)t * k + i);
         gw[i] = __ldg(topk_gate + (size_t)t * k + i);
-        v[i] = __ldg(reinterpret_cast<const uint4*>(o + (size_t)r * D) + c);
+        const float4* row = reinterpret_cast<const float4*>(o + (size_t)r * D) + 2 * c;
+        va[i] = __ldg(row);
+        vb[i] = __ldg(row + 1);
       }
     }
 #pragma unroll
     for (int i = 0; i < K_MAX; ++i) {
       if (i < k) {
-        acc[0] = fmaf(gw[i], bf16_lo(v[i].x), acc[0]);
-        acc[1] = fmaf(gw[i], bf16_hi(v[i].x), acc[1]);
-        acc[2] = fmaf(gw[i], bf16_lo(v[i].y), acc[2]);
-        acc[3] = fmaf(gw[i], bf16_hi(v[i].y), acc[3]);
-        acc[4] = fmaf(gw[i], bf16_lo(v[i].z), acc[4]);
-        acc[5] = fmaf(gw[i], bf16_hi(v[i].z), acc[5]);
-        acc[6] = fmaf(gw[i], bf16_lo(v[i].w), acc[6]);
-        acc[7] = fmaf(gw[i], bf16_hi(v[i].w), acc[7]);
+        acc[0] = fmaf(gw[i], va[i].x, acc[0]);
+        acc[1] = fmaf(gw[i], va[i].y, acc[1]);
+        acc[2] = fmaf(gw[i], va[i].z, acc[2]);
+        acc[3] = fmaf(gw[i], va[i].w, acc[3]);
+        acc[4] = fmaf(gw[i], vb[i].x, acc[4]);
+        acc[5] = fmaf(gw[i], vb[i].y, acc[5]);
+        acc[6] = fmaf(gw[i], vb[i].z, acc[6]);
+        acc[7] = fmaf(gw[i], vb[i].w, acc[7]);
       }
     }
     for (int s = 0; s < S; ++s) {
-      uint4 w = __ldg(reinterpret_cast<const uint4*>(o_shared + ((size_t)s * T + t) * D) + c);
-      acc[0] += bf16_lo(w.x);
-      acc[1] += bf16_hi(w.x);
-      acc[2] += bf16_lo(w.y);
-      acc[3] += bf16_hi(w.y);
-      acc[4] += bf16_lo(w.z);
-      acc[5] += bf16_hi(w.z);
-      acc[6] += bf16_lo(w.w);
-      acc[7] += bf16_hi(w.w);
+      const float4* row = reinterpret_cast<const float4*>(o_shared + ((size_t)s * T + t) * D) + 2 * c;
+      float4 a = __ldg(row), b = __ldg(row + 1);
+      acc[0] += a.x;
+      acc[1] += a.y;
+      acc[2] += a.z;
+      acc[3] += a.w;
+      acc[4] += b.x;
+      acc[5] += b.y;
+      acc[6] += b.z;
+      acc[7] += b.w;
     }
     uint4 yv;
     yv.x = pack_bf16(acc[0], acc[1]);
@@ -312,8 +315,8 @@ extern "C" int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void
   int cap = sm_count() * 8;
   if (blocks > cap) blocks = cap;
   combine_kernel<8><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const __nv_bfloat16*>(o),
-      static_cast<const __nv_bfloat16*>(o_shared), slot_dst, topk_gate,
+      static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(o),
+      static_cast<const float*>(o_shared), slot_dst, topk_gate,
       static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(out), desc->tokens,
       desc->d_model, desc->top_k, desc->num_shared, residual);
   return check_launch("combine_kernel");

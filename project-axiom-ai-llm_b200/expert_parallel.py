@@ -1,0 +1,156 @@
+"""Expert-parallel MoE layer: tokens and experts sharded over the ranks of one
+node, one process per GPU, two all-to-all exchanges per layer call.
+
+The reference engine is single-GPU (no NCCL anywhere in core/src); this module
+is the sharded form of its forward_mixture_experts call
+(core/src/CUDA/kernel/moe_router.cu:205-320):
+
+  rank r owns tokens [r*T/G, (r+1)*T/G) and experts [r*E/G, (r+1)*E/G);
+  router + permute run on the local tokens (router weights replicated);
+  counts all-to-all -> row all-to-all (dispatch) into local HBM, one segment per
+  (source rank, local expert) -> grouped SwiGLU GEMMs on local memory only ->
+  row all-to-all back -> weighted combine on the source rank (gates never move).
+  Shared experts are replicated and applied to the local tokens, no traffic.
+
+torch.distributed (NCCL over NVLink on GPUs, gloo in CPU tests) carries the
+exchanges.  The compute stages come from a `stages` object: CudaStages calls the
+C ABI; tests substitute a CPU stand-in to exercise the exchange logic with gloo.
+"""
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import (FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A, check,
+               current_stream, load, make_desc, ptr)
+
+
+class CudaStages:
+    """The four compute stages through the C ABI, on the current CUDA device."""
+
+    def __init__(self):
+        self.lib = load()
+
+    def router(self, desc, x, w, logits, idx, gate, block_counts):
+        check(self.lib.axm_moe_router(ctypes.byref(desc), ptr(x), ptr(w["router_w"]),
+                                      ptr(w.get("router_bias")), ptr(logits), ptr(idx), ptr(gate),
+                                      ptr(block_counts), current_stream()))
+
+    def permute(self, desc, x, idx, block_counts, histogram, offsets, row_src, slot_dst, x_perm):
+        check(self.lib.axm_moe_permute(ctypes.byref(desc), ptr(x), ptr(idx), ptr(block_counts),
+                                       ptr(histogram), ptr(offsets), ptr(row_src), ptr(slot_dst),
+                                       ptr(x_perm), current_stream()))
+
+    def expert_ffn(self, desc, a, a_rows, x_alt, alt_rows, segments, w, h, o, rows_total, status):
+        S = desc.num_shared
+        check(self.lib.axm_moe_expert_ffn(
+            ctypes.byref(desc), ptr(a), a_rows, ptr(x_alt), alt_rows, ptr(segments),
+            segments.shape[0], ptr(w["w_gate"]), ptr(w["w_up"]), ptr(w["w_down"]),
+            ptr(w["shared_gate"]) if S else None, ptr(w["shared_up"]) if S else None,
+            ptr(w["shared_down"]) if S else None, ptr(h), ptr(o), rows_total, ptr(status),
+            current_stream()))
+
+    def combine(self, desc, x, o, o_shared, slot_dst, gate, y, out):
+        check(self.lib.axm_moe_combine(ctypes.byref(desc), ptr(x), ptr(o), ptr(o_shared),
+                                       ptr(slot_dst), ptr(gate), ptr(y), ptr(out),
+                                       current_stream()))
+
+
+def shard_weights(w, rank, world):
+    """This rank's slice of the expert weights; router, bias and shared experts replicated."""
+    E = w["w_gate"].shape[0]
+    assert E % world == 0, "num_experts must divide by the number of ranks"
+    el = E // world
+    out = dict(w)
+    for n in ("w_gate", "w_up", "w_down"):
+        out[n] = w[n][rank * el:(rank + 1) * el].contiguous()
+    return out
+
+
+class ExpertParallelMoe:
+    """forward(x_local) -> out_local for this rank's T/G tokens."""
+
+    def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, stages=None,
+                 residual=True):
+        self.group = group
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.stages = stages if stages is not None else CudaStages()
+        self.w = local_weights
+        wr = local_weights["router_w"]
+        self.dev = wr.device
+        D = wr.shape[0]
+        F = local_weights["w_gate"].shape[2]
+        self.E, self.k, self.D, self.F = num_experts, top_k, D, F
+        self.El = num_experts // self.world
+        assert self.El * self.world == num_experts
+        assert local_weights["w_gate"].shape[0] == self.El
+        self.S = 0 if local_weights.get("shared_gate") is None else local_weights["shared_gate"].shape[0]
+        self.Tl = tokens_local
+        rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
+        flags = FLAG_RESIDUAL if residual else 0
+        # routing runs over the global expert set, the FFN over the local one
+        self.desc_route = make_desc(tokens_local, D, F, num_experts, top_k, 0, rdt, flags)
+        self.desc_ffn = make_desc(tokens_local, D, F, self.El, min(top_k, self.El), self.S, rdt, flags)
+        self.desc_comb = make_desc(tokens_local, D, F, num_experts, top_k, self.S, rdt, flags)
+        dev, i32, bf = self.dev, torch.int32, torch.bfloat16
+        n_slots = tokens_local * top_k
+        # worst case: every slot of every rank lands on this rank's experts
+        self.cap = n_slots * self.world
+        self.rows_total = self.cap + self.S * tokens_local
+        self.logits = torch.empty(tokens_local, num_experts, dtype=torch.float32, device=dev)
+        self.idx = torch.empty(tokens_local, top_k, dtype=i32, device=dev)
+        self.gate = torch.empty(tokens_local, top_k, dtype=torch.float32, device=dev)
+        self.block_counts = torch.empty(ROUTE_BLOCKS, num_experts, dtype=i32, device=dev)
+        self.histogram = torch.zeros(num_experts, dtype=i32, device=dev)
+        self.offsets = torch.empty(num_experts + 1, dtype=i32, device=dev)
+        self.row_src = torch.empty(n_slots, dtype=i32, device=dev)
+        self.slot_dst = torch.empty(n_slots, dtype=i32, device=dev)
+        self.x_perm = torch.empty(n_slots, D, dtype=bf, device=dev)
+        self.recv = torch.empty(self.cap, D, dtype=bf, device=dev)
+        self.h = torch.empty(self.rows_total, F, dtype=bf, device=dev)
+        self.o = torch.empty(self.rows_total, D, dtype=torch.float32, device=dev)
+        self.o_back = torch.empty(n_slots, D, dtype=torch.float32, device=dev)
+        self.y = torch.empty(tokens_local, D, dtype=bf, device=dev)
+        self.status = torch.zeros(1, dtype=i32, device=dev)
+        self.recv_counts = torch.empty(self.world, self.El, dtype=i32, device=dev)
+        self.last_rows_received = 0
+
+    def build_segments(self, recv_counts):
+        """Segment table for the rows received: one per (source rank, local expert),
+        in arrival order, then one per shared expert over the local tokens."""
+        flat = recv_counts.reshape(-1).to(torch.int64)
+        starts = torch.cumsum(flat, 0) - flat
+        expert = torch.arange(self.El, device=flat.device).repeat(self.world)
+        seg = torch.stack([starts, starts, flat, expert], dim=1)
+        if self.S:
+            s = torch.arange(self.S, device=flat.device)
+            shared = torch.stack([torch.zeros_like(s), self.cap + s * self.Tl,
+                                  torch.full_like(s, self.Tl), (self.El + s) | SEG_ALT_A], dim=1)
+            seg = torch.cat([seg, shared], 0)
+        return seg.to(torch.int32).contiguous()
+
+    def forward(self, x, out=None):
+        st, G, El = self.stages, self.world, self.El
+        if out is None:
+            out = torch.empty_like(x)
+        st.router(self.desc_route, x, self.w, self.logits, self.idx, self.gate, self.block_counts)
+        st.permute(self.desc_route, x, self.idx, self.block_counts, self.histogram, self.offsets,
+                   self.row_src, self.slot_dst, self.x_perm)
+        # counts: send[g][j] = my rows for expert g*El + j; recv[g][j] = rows rank g sends me
+        send_counts = (self.offsets[1:] - self.offsets[:-1]).reshape(G, El).contiguous()
+        dist.all_to_all_single(self.recv_counts, send_counts, group=self.group)
+        both = torch.stack([send_counts.sum(1), self.recv_counts.sum(1)]).cpu()  # one host sync
+        in_splits, out_splits = both[0].tolist(), both[1].tolist()
+        n_recv = sum(out_splits)
+        self.last_rows_received = n_recv
+        dist.all_to_all_single(self.recv[:n_recv], self.x_perm, out_splits, in_splits,
+                               group=self.group)
+        seg = self.build_segments(self.recv_counts)
+        st.expert_ffn(self.desc_ffn, self.recv, self.cap, x, self.Tl, seg, self.w, self.h, self.o,
+                      self.rows_total, self.status)
+        dist.all_to_all_single(self.o_back, self.o[:n_recv], in_splits, out_splits,
+                               group=self.group)
+        o_shared = self.o[self.cap:] if self.S else None
+        st.combine(self.desc_comb, x, self.o_back, o_shared, self.slot_dst, self.gate, self.y, out)
+        return out

@@ -67,7 +67,7 @@ def run_expert_ffn(axm, desc, xp, x_alt, seg, w, rows_total):
     lib = axm.load()
     dev = xp.device
     h = torch.zeros(rows_total, desc.d_ff, dtype=torch.bfloat16, device=dev)
-    o = torch.zeros(rows_total, desc.d_model, dtype=torch.bfloat16, device=dev)
+    o = torch.zeros(rows_total, desc.d_model, dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)
     S = desc.num_shared
     axm.check(lib.axm_moe_expert_ffn(
@@ -96,12 +96,42 @@ def to_dev(w, dev):
     return {k: (v.to(dev) if v is not None else None) for k, v in w.items()}
 
 
-def assert_close_layer(got, ref, rel=2e-2, abs_=1e-2, what="layer output"):
-    """|got - ref| <= abs_ + rel * |ref| element-wise (the layer tolerance)."""
+def _check(err, bound, what, detail, allow_frac, hard_factor):
+    bad = err > bound
+    n_bad = int(bad.sum())
+    worst = float((err / bound).max()) if err.numel() else 0.0
+    assert n_bad <= allow_frac * err.numel() and worst <= hard_factor, (
+        f"{what}: {n_bad} of {err.numel()} elements outside {detail} "
+        f"(allowed {allow_frac:g} of them), worst err/bound {worst:.3f} (limit {hard_factor}), "
+        f"max err {float(err.max()):.4g}")
+    return n_bad
+
+
+def assert_close_layer(got, ref, rel=2e-2, abs_=1e-2, what="layer output", allow_frac=0.0,
+                       hard_factor=1.0):
+    """|got - ref| <= abs_ + rel * |ref| element-wise (the layer tolerance).
+
+    allow_frac / hard_factor: against a reference that keeps the SwiGLU
+    intermediate in fp32, a pipeline that stores it as bf16 leaves a thin tail
+    (a few elements per million at d_model 4096, d_ff 14336, where two large
+    expert outputs cancel) just outside the bound; such a comparison allows that
+    fraction of elements to exceed the bound, and none by more than hard_factor."""
     g, r = got.float().cpu(), ref.float().cpu()
     err = (g - r).abs()
     bound = abs_ + rel * r.abs()
-    bad = err > bound
-    assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.numel()} elements outside "
-                           f"{abs_} + {rel}*|ref|; max err {float(err.max()):.4g}")
-    return float(err.max())
+    _check(err, bound, what, f"{abs_} + {rel}*|ref|", allow_frac, max(hard_factor, 1.0))
+    return float(err.max()) if err.numel() else 0.0
+
+
+def assert_close_out(got_out, ref_out, ref_y, rel=2e-2, abs_=1e-2, what="out", allow_frac=0.0,
+                     hard_factor=1.0):
+    """Tolerance for out = bf16(x + y).  The layer tolerance applies to y; the
+    residual add can cancel, so the same absolute error in y may be large
+    relative to a small |x + y|.  The bound is therefore the y tolerance plus one
+    bf16 step of the sum: |d| <= abs_ + rel * |y_ref| + 2^-7 * |out_ref|."""
+    g, r, y = got_out.float().cpu(), ref_out.float().cpu(), ref_y.float().cpu()
+    err = (g - r).abs()
+    bound = abs_ + rel * y.abs() + 2.0 ** -7 * r.abs()
+    _check(err, bound, what, f"{abs_} + {rel}*|y_ref| + 2^-7*|out_ref|", allow_frac,
+           max(hard_factor, 1.0))
+    return float(err.max()) if err.numel() else 0.0

@@ -30,6 +30,7 @@ class Oracle:
         lib.orc_build_permutation.argtypes = [vp, i32, i32, i32, vp, vp, vp]
         lib.orc_aux_loss.argtypes = [vp, vp, i32, i32, i32, ctypes.c_float]
         lib.orc_aux_loss.restype = ctypes.c_float
+        lib.orc_expert_ffn.argtypes = [vp, i32, i32, i32, vp, vp, vp, i32, vp]
         lib.orc_moe_forward.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp,
                                         vp, vp, i32, i32, i32, i32, vp, vp]
 
@@ -80,6 +81,17 @@ class Oracle:
         return float(self.lib.orc_aux_loss(self._p(np.ascontiguousarray(probs)),
                                            self._p(np.ascontiguousarray(idx)), T, E, idx.shape[1],
                                            alpha))
+
+    def expert_ffn(self, x_rows, wg, wu, wd, h_bf16=False):
+        """One expert over the given bf16 rows: fp32 [n][D] numpy."""
+        n, D = x_rows.shape
+        F = wg.shape[1]
+        o = np.zeros((n, D), dtype=np.float32)
+        if n:
+            self.lib.orc_expert_ffn(self._p(_bf16_np(x_rows)), n, D, F, self._p(_bf16_np(wg)),
+                                    self._p(_bf16_np(wu)), self._p(_bf16_np(wd)), int(h_bf16),
+                                    self._p(o))
+        return o
 
     def forward(self, x, w, idx, gates, h_bf16=False, o_bf16=False, tok_range=None):
         """Returns (y, out) as torch bf16 [T][D]; rows outside tok_range are zero."""

@@ -1,0 +1,92 @@
+"""The C-ABI library loads, exports every symbol its header declares, validates
+arguments, and refuses to compute without an sm_100 device (no CPU fallback)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+
+def declared_symbols(path):
+    text = open(path).read()
+    return sorted(set(re.findall(r"AXM_API\s+[\w\s\*]+?\b(axm_\w+)\s*\(", text)))
+
+
+def test_exports_every_declared_symbol(axm):
+    lib = axm.load()
+    names = declared_symbols(axm.HEADER_PATH)
+    assert len(names) >= 12
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/axm_moe.h but not exported"
+    assert b"sm_100a" in lib.axm_version()
+
+
+def test_struct_sizes_match_header(axm):
+    assert ctypes.sizeof(axm.MoeDesc) == 32
+    assert ctypes.sizeof(axm.MoeTensors) == 18 * 8
+    assert ctypes.sizeof(axm.Segment) == 16
+
+
+def test_workspace_size_and_launch_count(axm):
+    d = axm.make_desc(4096, 2048, 5632, 8, 2)
+    n = axm.workspace_bytes(d)
+    rows = 4096 * 2
+    assert n >= 2 * rows * (2048 + 5632 + 2048)
+    assert n % 256 == 0
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(d)) == 5
+    d0 = axm.make_desc(0, 2048, 5632, 8, 2)
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(d0)) == 0
+
+
+@pytest.mark.parametrize("kw", [
+    dict(d_model=2047), dict(d_ff=12), dict(num_experts=0), dict(num_experts=257), dict(top_k=0),
+    dict(top_k=9), dict(top_k=3, num_experts=2), dict(num_shared=9), dict(tokens=-1),
+    dict(router_dtype=7),
+])
+def test_bad_shapes_are_rejected(axm, kw):
+    base = dict(tokens=64, d_model=256, d_ff=512, num_experts=8, top_k=2)
+    base.update(kw)
+    d = axm.make_desc(**base)
+    n = ctypes.c_size_t(0)
+    rc = axm.load().axm_moe_workspace_bytes(ctypes.byref(d), ctypes.byref(n))
+    assert rc == axm.AXM_ERR_ARGUMENT
+    assert len(axm.load().axm_last_error()) > 0
+
+
+def test_null_pointers_are_rejected(axm):
+    lib = axm.load()
+    d = axm.make_desc(64, 256, 512, 8, 2)
+    t = axm.MoeTensors()
+    assert lib.axm_moe_forward(ctypes.byref(d), ctypes.byref(t), None, 0, None) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_forward(ctypes.byref(d), None, None, 0, None) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_router(ctypes.byref(d), None, None, None, None, None, None, None, None) \
+        == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_permute(ctypes.byref(d), None, None, None, None, None, None, None, None,
+                               None) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_combine(ctypes.byref(d), None, None, None, None, None, None, None, None) \
+        == axm.AXM_ERR_ARGUMENT
+
+
+def test_workspace_checks(axm):
+    lib = axm.load()
+    d = axm.make_desc(64, 256, 512, 8, 2)
+    fake = ctypes.c_void_p(0x1000)
+    t = axm.MoeTensors(*([0x1000] * 18))
+    assert lib.axm_moe_forward(ctypes.byref(d), ctypes.byref(t), None, 0, None) == axm.AXM_ERR_WORKSPACE
+    assert lib.axm_moe_forward(ctypes.byref(d), ctypes.byref(t), ctypes.c_void_p(0x1010), 1 << 30,
+                               None) == axm.AXM_ERR_WORKSPACE
+    assert lib.axm_moe_forward(ctypes.byref(d), ctypes.byref(t), fake, 16, None) == axm.AXM_ERR_WORKSPACE
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the behaviour without a GPU")
+def test_no_cpu_fallback(axm):
+    """With valid arguments but no sm_100 device the layer fails loudly."""
+    lib = axm.load()
+    d = axm.make_desc(64, 256, 512, 8, 2)
+    fake = ctypes.c_void_p(0x1000)
+    t = axm.MoeTensors(*([0x1000] * 18))
+    rc = lib.axm_moe_forward(ctypes.byref(d), ctypes.byref(t), fake, 1 << 30, None)
+    assert rc == axm.AXM_ERR_DEVICE
+    with pytest.raises(axm.AxmError):
+        axm.check(rc)

@@ -1,0 +1,165 @@
+"""Whole-layer parity through axm_moe_forward.
+
+Tolerance for the layer output y = MoE(x) (bf16 output, fp32 accumulate):
+|got - ref| <= 1e-2 + 2e-2 * |ref|; out = bf16(x + y) carries the same error in
+y plus one bf16 step of the sum (helpers.assert_close_out).
+ * Against the oracle run with the kernel's own rounding point (SwiGLU
+   intermediate stored as bf16, fp32 expert rows) every element must be inside
+   the bound, and y must agree to bf16 rounding: max |err| <= 2^-7 * max |y|.
+ * Against the oracle run the reference way (fp32 intermediate) the bf16
+   intermediate itself leaves a measured tail of about 3e-5 of the elements at
+   d_model 4096 / d_ff 14336 up to 1.5x the bound (the oracle's own bf16 mode
+   shows the same tail against its fp32 mode); that comparison allows 1e-4 of
+   the elements outside the bound and none beyond 2x.
+Full-size configurations are checked on token slices plus size-independent
+properties (determinism, histogram sum, permutation validity, residual identity,
+in-place equivalence)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def run_layer(axm, cfg, x, w, dev, **kw):
+    layer = axm.MoeLayer(helpers.to_dev(w, dev), cfg.tokens, cfg.top_k, **kw)
+    out, hist = layer.forward(x.to(dev))
+    assert layer.status() == 0
+    return layer, out
+
+
+def check_against_oracle(oracle, cfg, x, w, layer, out, tok_range=None):
+    idx = layer.topk_idx.cpu().numpy()
+    gate = layer.topk_gate.cpu().numpy()
+    lo, hi = (0, cfg.tokens) if tok_range is None else tok_range
+    y_ref, out_ref = oracle.forward(x, w, idx, gate, tok_range=tok_range)
+    helpers.assert_close_layer(layer.y[lo:hi], y_ref[lo:hi], what="y vs oracle (fp32 intermediates)",
+                               allow_frac=1e-4, hard_factor=2.0)
+    helpers.assert_close_out(out[lo:hi], out_ref[lo:hi], y_ref[lo:hi],
+                             what="out vs oracle (fp32 intermediates)", allow_frac=1e-4, hard_factor=2.0)
+    y_m, out_m = oracle.forward(x, w, idx, gate, h_bf16=True, tok_range=tok_range)
+    helpers.assert_close_layer(layer.y[lo:hi], y_m[lo:hi], what="y vs oracle (bf16 intermediate)")
+    helpers.assert_close_out(out[lo:hi], out_m[lo:hi], y_m[lo:hi], what="out vs oracle (bf16 intermediate)")
+    err = (layer.y[lo:hi].float().cpu() - y_m[lo:hi].float()).abs()
+    scale = float(y_m[lo:hi].float().abs().max())
+    assert float(err.max()) <= 2.0 ** -7 * max(scale, 1e-3), \
+        f"y vs oracle with matching rounding points: max err {float(err.max()):.4g}, max |y| {scale:.4g}"
+    # routing that fed the layer equals the oracle's from the layer's own logits
+    oi, og, _, oc, tie = oracle.route(layer.logits.cpu().numpy(), cfg.top_k)
+    mism = (oi != idx).any(axis=1)
+    assert not (mism & (tie == 0)).any()
+    ooff, ors, osd = oracle.permutation(idx, cfg.num_experts)
+    assert (layer.offsets.cpu().numpy() == ooff).all()
+    assert (layer.row_src.cpu().numpy() == ors).all()
+    assert (layer.slot_dst.cpu().numpy() == osd).all()
+    assert (layer.histogram.cpu().numpy() == np.bincount(idx.ravel(), minlength=cfg.num_experts)).all()
+
+
+def test_c1_full(axm, workloads, oracle, cuda_device):
+    cfg = workloads.CONFIGS["C1"]
+    x, w = workloads.make_inputs(cfg)
+    layer, out = run_layer(axm, cfg, x, w, cuda_device)
+    check_against_oracle(oracle, cfg, x, w, layer, out)
+
+
+def test_golden_small(axm, cuda_device):
+    """The committed vectors: routing bit-exact, output within the layer tolerance."""
+    g = np.load(os.path.join(GOLDEN, "moe_small.npz"))
+    bf = lambda a: torch.from_numpy(a.view(np.int16).copy()).view(torch.bfloat16)
+    x = bf(g["x_bits"])
+    w = {"router_w": torch.from_numpy(g["router_w"].copy()), "w_gate": bf(g["w_gate_bits"]),
+         "w_up": bf(g["w_up_bits"]), "w_down": bf(g["w_down_bits"])}
+    k = int(g["top_k"])
+    layer = axm.MoeLayer(helpers.to_dev(w, cuda_device), x.shape[0], k)
+    out, hist = layer.forward(x.to(cuda_device))
+    assert layer.status() == 0
+    assert (np.abs(layer.logits.cpu().numpy() - g["logits"]) <= 1e-4).all()
+    assert (layer.topk_idx.cpu().numpy() == g["topk_idx"]).all()
+    assert (hist.cpu().numpy() == g["histogram"]).all()
+    assert (layer.offsets.cpu().numpy() == g["offsets"]).all()
+    assert (layer.row_src.cpu().numpy() == g["row_src"]).all()
+    assert np.abs(layer.topk_gate.cpu().numpy() - g["topk_gate"]).max() <= 1e-6
+    helpers.assert_close_layer(layer.y, bf(g["y_bits"]), what="golden y")
+    helpers.assert_close_out(out, bf(g["out_bits"]), bf(g["y_bits"]), what="golden out")
+
+
+@pytest.mark.parametrize("name,tokens,slice_", [
+    ("C2", None, (1000, 1256)), ("C2", 777, None), ("C4", 2048, (0, 192)), ("C5", 1024, (512, 640)),
+    ("C3", 512, (100, 164)),
+])
+def test_configs_on_slices(axm, workloads, oracle, cuda_device, name, tokens, slice_):
+    cfg = workloads.scaled(workloads.CONFIGS[name], tokens=tokens)
+    x, w = workloads.make_inputs(cfg, device=cuda_device)
+    x, w = x.cpu(), {k: v.cpu() for k, v in w.items()}
+    layer, out = run_layer(axm, cfg, x, w, cuda_device)
+    check_against_oracle(oracle, cfg, x, w, layer, out, tok_range=slice_)
+
+
+def test_c2_full_size_properties(axm, workloads, cuda_device):
+    cfg = workloads.CONFIGS["C2"]
+    x, w = workloads.make_inputs(cfg, device=cuda_device)
+    layer = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+    out1, hist = layer.forward(x)
+    out1 = out1.clone()
+    y1 = layer.y.clone()
+    assert layer.status() == 0
+    assert int(hist.sum()) == cfg.tokens * cfg.top_k
+    assert int(layer.offsets[-1]) == cfg.tokens * cfg.top_k
+    rs = layer.row_src.long()
+    assert torch.equal(torch.sort(rs).values, torch.arange(cfg.tokens * cfg.top_k, device=cuda_device))
+    assert torch.equal(rs[layer.slot_dst.long()], torch.arange(cfg.tokens * cfg.top_k, device=cuda_device))
+    assert torch.isfinite(out1.float()).all()
+    # residual identity: out == bf16(x + y)
+    assert torch.equal(out1, (x.float() + y1.float()).bfloat16())
+    # determinism: a second call gives the same bytes
+    out2, _ = layer.forward(x)
+    assert torch.equal(out1, out2)
+    # in place (out aliases x) gives the same result
+    xin = x.clone()
+    layer.forward(xin, out=xin)
+    assert torch.equal(xin, out1)
+    # without the residual flag the output is y
+    layer_nr = axm.MoeLayer(w, cfg.tokens, cfg.top_k, residual=False)
+    out3, _ = layer_nr.forward(x)
+    assert torch.equal(out3, y1)
+    # token-permutation equivariance: reversing the tokens reverses the outputs
+    out4, _ = layer.forward(x.flip(0).contiguous())
+    assert torch.equal(out4.flip(0), out1)
+
+
+def test_forward_host_matches_forward(axm, workloads, cuda_device):
+    cfg = workloads.scaled(workloads.CONFIGS["C2"], tokens=1024)
+    x, w = workloads.make_inputs(cfg, device=cuda_device)
+    layer = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+    out, _ = layer.forward(x)
+    h_x = x.cpu().pin_memory()
+    h_out = torch.empty_like(h_x).pin_memory()
+    d_x = torch.empty_like(x)
+    d_out = torch.empty_like(x)
+    layer.forward_host(h_x, h_out, d_x, d_out)
+    assert torch.equal(h_out, out.cpu())
+
+
+def test_empty_input(axm, workloads, cuda_device):
+    cfg = workloads.scaled(workloads.CONFIGS["C1"], tokens=0)
+    _, w = workloads.make_inputs(workloads.scaled(cfg, tokens=1), device=cuda_device)
+    layer = axm.MoeLayer(w, 0, cfg.top_k)
+    x = torch.empty(0, cfg.d_model, dtype=torch.bfloat16, device=cuda_device)
+    out, _ = layer.forward(x)
+    assert out.shape == (0, cfg.d_model)
+
+
+def test_bf16_router_weights_drop_in_mode(axm, workloads, oracle, cuda_device):
+    """The reference interface carries bf16 router weights; same checks in that mode."""
+    cfg = workloads.scaled(workloads.CONFIGS["C1"], tokens=256, d_model=32, d_ff=64)
+    x, w = workloads.make_inputs(cfg, router_bf16=True)
+    layer, out = run_layer(axm, cfg, x, w, cuda_device, hist_accumulate=True)
+    check_against_oracle(oracle, cfg, x, w, layer, out)
+    layer.forward(x.to(cuda_device))
+    idx = layer.topk_idx.cpu().numpy()
+    assert (layer.histogram.cpu().numpy() == 2 * np.bincount(idx.ravel(), minlength=cfg.num_experts)).all()
