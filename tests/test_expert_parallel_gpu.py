@@ -1,0 +1,72 @@
+"""Expert-parallel layer on real GPUs (NCCL): every rank's slice of the output
+must equal the single-GPU layer's, bit for bit - the same rows go through the
+same GEMM arithmetic wherever they are computed.  Needs at least two GPUs."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+pytestmark = [pytest.mark.gpu,
+              pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")]
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, name, tokens, out_dir):
+    sys.path.insert(0, HERE)
+    import importlib
+    import conftest
+    axm = conftest.load_package()
+    wl = importlib.import_module("project_axiom_ai_llm_b200.workloads")
+    ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = wl.scaled(wl.CONFIGS[name], tokens=tokens)
+        x, w = wl.make_inputs(cfg)          # CPU generator: identical on every rank
+        x, w = x.to(dev), {k: v.to(dev) for k, v in w.items()}
+        tl = cfg.tokens // world
+        layer = ep.ExpertParallelMoe(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
+                                     cfg.top_k)
+        out = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
+        out2 = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
+        torch.cuda.synchronize()
+        assert int(layer.status.item()) == 0
+        assert torch.equal(out, out2)
+        if rank == 0:
+            single = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+            ref, _ = single.forward(x)
+            torch.cuda.synchronize()
+            torch.save({"ref": ref.cpu(), "hist": single.histogram.cpu()},
+                       os.path.join(out_dir, "ref.pt"))
+        hist = layer.histogram.clone()
+        dist.all_reduce(hist)
+        torch.save({"out": out.cpu(), "hist": hist.cpu()}, os.path.join(out_dir, f"r{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("name,tokens", [("C1", 64), ("C2", 1024), ("C4", 2048)])
+def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens):
+    world = 2
+    mp.start_processes(_worker, args=(world, _free_port(), name, tokens, str(tmp_path)),
+                       nprocs=world, join=True, start_method="spawn")
+    ref = torch.load(os.path.join(str(tmp_path), "ref.pt"))
+    parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
+    assert torch.equal(torch.cat([p["out"] for p in parts]), ref["ref"])
+    assert torch.equal(parts[0]["hist"], ref["hist"])
