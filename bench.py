@@ -214,7 +214,7 @@ def main():
     launches_per_step = 0
 
     if world == 1:
-        layer = axm.MoeLayer(w, T, k)
+        layer = axm.MoeLayer(w, T, k, publish_y=False)
         out = torch.empty_like(x)
         x_local = x
         step = lambda: layer.forward(x_local, out)
@@ -320,6 +320,19 @@ def main():
         if status != 0:
             raise SystemExit(f"GEMM kernel reported a timed-out wait (status {status})")
 
+    ep_stages = None
+    if world > 1:
+        acc = {}
+        reps = 10
+        for _ in range(reps):
+            evs = []
+            layer.forward(x_local, out, events=evs)
+            torch.cuda.synchronize()
+            for (_, a), (n, b) in zip(evs[:-1], evs[1:]):
+                acc[n] = acc.get(n, 0.0) + a.elapsed_time(b) / reps
+        ep_stages = {n: {"ms": v} for n, v in acc.items()}
+        ep_stages["rows_received_rank0"] = layer.last_rows_received
+
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline:
         cpu = cpu_baseline(cfg, x_local, layer.w, args.cpu_tokens)
@@ -342,6 +355,8 @@ def main():
         if roofline is not None:
             line["roofline"] = roofline
             line["stages"] = stages
+        if ep_stages is not None:
+            line["stages_rank0"] = ep_stages
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

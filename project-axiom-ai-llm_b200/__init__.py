@@ -120,7 +120,7 @@ class MoeLayer:
     """
 
     def __init__(self, weights, tokens, top_k, residual=True, hist_accumulate=False,
-                 device="cuda"):
+                 device="cuda", publish_y=True):
         self.lib = load()
         self.w = weights
         wr = weights["router_w"]
@@ -142,7 +142,7 @@ class MoeLayer:
         self.offsets = torch.empty(E + 1, dtype=torch.int32, device=dev)
         self.row_src = torch.empty(tokens * top_k, dtype=torch.int32, device=dev)
         self.slot_dst = torch.empty(tokens * top_k, dtype=torch.int32, device=dev)
-        self.y = torch.empty(tokens, D, dtype=torch.bfloat16, device=dev)
+        self.y = torch.empty(tokens, D, dtype=torch.bfloat16, device=dev) if publish_y else None
 
     def tensors(self, x, out):
         w = self.w
@@ -155,7 +155,7 @@ class MoeLayer:
             None if self.S == 0 else w["shared_down"].data_ptr(),
             self.logits.data_ptr(), self.topk_idx.data_ptr(), self.topk_gate.data_ptr(),
             self.histogram.data_ptr(), self.offsets.data_ptr(), self.row_src.data_ptr(),
-            self.slot_dst.data_ptr(), self.y.data_ptr(), out.data_ptr())
+            self.slot_dst.data_ptr(), None if self.y is None else self.y.data_ptr(), out.data_ptr())
 
     def forward(self, x, out=None):
         assert x.is_cuda and x.dtype == torch.bfloat16 and x.shape == (self.T, self.D)

@@ -22,6 +22,7 @@ namespace axm {
 constexpr int kRouterThreads = 256;
 constexpr int kTokSub = 64;   // tokens handled per pass inside a block
 constexpr int kEC = 8;        // experts per register chunk
+constexpr int kTB = 8;        // tokens whose loads are in flight together
 constexpr int kMaxK = 8;
 
 __host__ __device__ inline int route_block_begin(int b, int T) {
@@ -132,46 +133,57 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ wr,
             for (int e = 0; e < kEC; ++e)
               w[j][e] = (d + j < D && e0 + e < E) ? load_w<WT>(wr + (size_t)(d + j) * E + e0 + e)
                                                   : 0.0f;
-          for (int tt = 0; tt < nt; ++tt) {
-            uint4 xv = make_uint4(0, 0, 0, 0);
-            if (d < D) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(ts + tt) * D + d));
-            float xf[8] = {bf16_lo(xv.x), bf16_hi(xv.x), bf16_lo(xv.y), bf16_hi(xv.y),
-                           bf16_lo(xv.z), bf16_hi(xv.z), bf16_lo(xv.w), bf16_hi(xv.w)};
-            float acc[kEC];
+          // Tokens go through in batches of kTB: all of a batch's 16-byte loads are
+          // issued before the first is used, so each thread keeps kTB loads in flight.
+          for (int tb = 0; tb < nt; tb += kTB) {
+            uint4 xv[kTB];
 #pragma unroll
-            for (int e = 0; e < kEC; ++e) acc[e] = 0.0f;
-#pragma unroll
-            for (int j = 0; j < 8; ++j)
-#pragma unroll
-              for (int e = 0; e < kEC; ++e) acc[e] = fmaf(xf[j], w[j][e], acc[e]);
-            // Transposed butterfly: 8 values on 32 lanes -> one value per lane
-            // after three exchange steps, then two plain steps.  Fixed tree, so
-            // the sum order (and the logits) are reproducible.
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              bool up = lane & 16;
-              float send = up ? acc[i] : acc[i + 4];
-              float keep = up ? acc[i + 4] : acc[i];
-              acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+            for (int b = 0; b < kTB; ++b) {
+              xv[b] = make_uint4(0, 0, 0, 0);
+              if (d < D && tb + b < nt)
+                xv[b] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(ts + tb + b) * D + d));
             }
 #pragma unroll
-            for (int i = 0; i < 2; ++i) {
-              bool up = lane & 8;
-              float send = up ? acc[i] : acc[i + 2];
-              float keep = up ? acc[i + 2] : acc[i];
-              acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
-            }
-            {
-              bool up = lane & 4;
-              float send = up ? acc[0] : acc[1];
-              float keep = up ? acc[1] : acc[0];
-              acc[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
-            }
-            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
-            acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
-            if ((lane & 3) == 0) {
-              int e = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
-              part_s[(warp * kTokSub + tt) * kEC + e] = acc[0];
+            for (int b = 0; b < kTB; ++b) {
+              const int tt = tb + b;
+              float xf[8] = {bf16_lo(xv[b].x), bf16_hi(xv[b].x), bf16_lo(xv[b].y), bf16_hi(xv[b].y),
+                             bf16_lo(xv[b].z), bf16_hi(xv[b].z), bf16_lo(xv[b].w), bf16_hi(xv[b].w)};
+              float acc[kEC];
+#pragma unroll
+              for (int e = 0; e < kEC; ++e) acc[e] = 0.0f;
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+#pragma unroll
+                for (int e = 0; e < kEC; ++e) acc[e] = fmaf(xf[j], w[j][e], acc[e]);
+              // Transposed butterfly: 8 values on 32 lanes -> one value per lane after
+              // three exchange steps, then two plain steps.  Fixed tree, so the sum
+              // order (and the logits) are reproducible.
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                bool up = lane & 16;
+                float send = up ? acc[i] : acc[i + 4];
+                float keep = up ? acc[i + 4] : acc[i];
+                acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, 16);
+              }
+#pragma unroll
+              for (int i = 0; i < 2; ++i) {
+                bool up = lane & 8;
+                float send = up ? acc[i] : acc[i + 2];
+                float keep = up ? acc[i + 2] : acc[i];
+                acc[i] = keep + __shfl_xor_sync(0xffffffffu, send, 8);
+              }
+              {
+                bool up = lane & 4;
+                float send = up ? acc[0] : acc[1];
+                float keep = up ? acc[1] : acc[0];
+                acc[0] = keep + __shfl_xor_sync(0xffffffffu, send, 4);
+              }
+              acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 2);
+              acc[0] += __shfl_xor_sync(0xffffffffu, acc[0], 1);
+              if ((lane & 3) == 0 && tt < nt) {
+                int e = ((lane >> 4) & 1) * 4 + ((lane >> 3) & 1) * 2 + ((lane >> 2) & 1);
+                part_s[(warp * kTokSub + tt) * kEC + e] = acc[0];
+              }
             }
           }
           __syncthreads();

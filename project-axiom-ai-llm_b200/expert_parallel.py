@@ -130,13 +130,23 @@ class ExpertParallelMoe:
             seg = torch.cat([seg, shared], 0)
         return seg.to(torch.int32).contiguous()
 
-    def forward(self, x, out=None):
+    def forward(self, x, out=None, events=None):
+        """events: optional list that receives (name, torch.cuda.Event) marks between phases."""
         st, G, El = self.stages, self.world, self.El
+
+        def mark(name):
+            if events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                events.append((name, ev))
+
         if out is None:
             out = torch.empty_like(x)
+        mark("start")
         st.router(self.desc_route, x, self.w, self.logits, self.idx, self.gate, self.block_counts)
         st.permute(self.desc_route, x, self.idx, self.block_counts, self.histogram, self.offsets,
                    self.row_src, self.slot_dst, self.x_perm)
+        mark("router+permute")
         # counts: send[g][j] = my rows for expert g*El + j; recv[g][j] = rows rank g sends me
         send_counts = (self.offsets[1:] - self.offsets[:-1]).reshape(G, El).contiguous()
         dist.all_to_all_single(self.recv_counts, send_counts, group=self.group)
@@ -144,13 +154,18 @@ class ExpertParallelMoe:
         in_splits, out_splits = both[0].tolist(), both[1].tolist()
         n_recv = sum(out_splits)
         self.last_rows_received = n_recv
+        mark("counts exchange + host sync")
         dist.all_to_all_single(self.recv[:n_recv], self.x_perm, out_splits, in_splits,
                                group=self.group)
+        mark("dispatch all-to-all")
         seg = self.build_segments(self.recv_counts)
         st.expert_ffn(self.desc_ffn, self.recv, self.cap, x, self.Tl, seg, self.w, self.h, self.o,
                       self.rows_total, self.status)
+        mark("segments + expert GEMMs")
         dist.all_to_all_single(self.o_back, self.o[:n_recv], in_splits, out_splits,
                                group=self.group)
+        mark("return all-to-all")
         o_shared = self.o[self.cap:] if self.S else None
         st.combine(self.desc_comb, x, self.o_back, o_shared, self.slot_dst, self.gate, self.y, out)
+        mark("combine")
         return out
