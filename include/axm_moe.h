@@ -203,6 +203,31 @@ AXM_API int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void* o
 /* Number of token blocks the router splits T into (rows of block_counts). */
 #define AXM_ROUTE_BLOCKS 296
 
+/* Routing from fp32 logits followed by the dispatch (axm_moe_route_from_logits +
+ * axm_moe_permute in one call) for callers that may not allocate device memory
+ * and have no scratch buffer to lend: servers that give all of HBM to their own
+ * arena at start-up, plug-ins living in someone else's process, code on a path
+ * where cudaMalloc's implicit synchronisation is not acceptable.  The block-count
+ * scratch is a fixed array inside the library (AXM_NOALLOC_SCRATCH_BYTES of device
+ * memory on every GPU that loads the library, held until the process exits), so
+ * the call allocates nothing and asks the caller only for inputs and outputs
+ * (same meaning as in the two calls it replaces; histogram, offsets, row_src,
+ * slot_dst and x_perm may be NULL, x is needed only with x_perm).
+ * Limits: num_experts <= AXM_NOALLOC_MAX_EXPERTS, else AXM_ERR_ARGUMENT and
+ * nothing is launched.  All calls on a GPU share the array: every call rewrites
+ * the whole part it later reads, so no stale contents are ever used, but calls
+ * whose kernels overlap on the GPU race - serialise them (one stream, or events).
+ * The first call on each device resolves the array's address and may initialise
+ * the CUDA context; make it before any stream capture begins.
+ * This entry point has no counterpart in the reference engine. */
+#define AXM_NOALLOC_MAX_EXPERTS 128
+#define AXM_NOALLOC_SCRATCH_BYTES (4 * AXM_ROUTE_BLOCKS * AXM_NOALLOC_MAX_EXPERTS)
+AXM_API int axm_moe_route_dispatch_noalloc(const AxmMoeDesc* desc, const float* logits,
+                                           const void* x, int32_t* topk_idx, float* topk_gate,
+                                           int32_t* histogram, int32_t* offsets,
+                                           int32_t* row_src, int32_t* slot_dst, void* x_perm,
+                                           void* stream);
+
 #ifdef __cplusplus
 }
 #endif

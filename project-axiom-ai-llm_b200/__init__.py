@@ -29,6 +29,7 @@ FLAG_RESIDUAL = 1
 FLAG_HIST_ACCUMULATE = 2
 ROUTE_BLOCKS = 296
 SEG_ALT_A = 1 << 30
+NOALLOC_MAX_EXPERTS = 128
 
 
 class AxmError(RuntimeError):
@@ -83,6 +84,7 @@ def load():
     lib.axm_moe_expert_ffn.argtypes = [dp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp,
                                        vp, i32, vp, vp]
     lib.axm_moe_combine.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     _lib = lib
     return lib
 

@@ -15,7 +15,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libaxm_moe.so")
 DROPIN = os.path.join(HERE, "libaxm_moe_dropin.so")
 
-CORE_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_ffn.cu"]
+CORE_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_ffn.cu", "noalloc.cu"]
 DROPIN_SOURCES = ["dropin.cu"]
 
 NVCC_FLAGS = [
