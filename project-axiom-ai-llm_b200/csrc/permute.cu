@@ -178,46 +178,50 @@ __global__ void build_segments_kernel(const int32_t* __restrict__ offsets,
   }
 }
 
-// One thread per 16-byte piece of an output row.
-template <int K_MAX>
+// One thread per 16-byte piece of an output row.  K is the exact top-k, so the
+// gathered row pieces live in 2*K float4 registers and all of them are in flight
+// together.
+template <int K>
 __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ o,
                const float* __restrict__ o_shared, const int32_t* __restrict__ slot_dst,
                const float* __restrict__ topk_gate, __nv_bfloat16* __restrict__ y,
-               __nv_bfloat16* __restrict__ out, int T, int D, int k, int S, int residual) {
+               __nv_bfloat16* __restrict__ out, int T, int D, int S, int residual) {
   const int chunks = D / 8;
   const long long total = (long long)T * chunks;
   for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
        g += (long long)gridDim.x * blockDim.x) {
     const int t = (int)(g / chunks);
     const int c = (int)(g - (long long)t * chunks);
+    int r[K];
+    float gw[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+      r[i] = __ldg(slot_dst + (size_t)t * K + i);
+      gw[i] = __ldg(topk_gate + (size_t)t * K + i);
+    }
+    uint4 xv = make_uint4(0, 0, 0, 0);
+    if (residual) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)t * D) + c);
+    float4 va[K], vb[K];
+#pragma unroll
+    for (int i = 0; i < K; ++i) {
+      const float4* row = reinterpret_cast<const float4*>(o + (size_t)r[i] * D) + 2 * c;
+      va[i] = __ldg(row);
+      vb[i] = __ldg(row + 1);
+    }
     float acc[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-    float4 va[K_MAX], vb[K_MAX];
-    float gw[K_MAX];
 #pragma unroll
-    for (int i = 0; i < K_MAX; ++i) {
-      if (i < k) {
-        int r = __ldg(slot_dst + (size_t)t * k + i);
-        gw[i] = __ldg(topk_gate + (size_t)t * k + i);
-        const float4* row = reinterpret_cast<const float4*>(o + (size_t)r * D) + 2 * c;
-        va[i] = __ldg(row);
-        vb[i] = __ldg(row + 1);
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < K_MAX; ++i) {
-      if (i < k) {
-        acc[0] = fmaf(gw[i], va[i].x, acc[0]);
-        acc[1] = fmaf(gw[i], va[i].y, acc[1]);
-        acc[2] = fmaf(gw[i], va[i].z, acc[2]);
-        acc[3] = fmaf(gw[i], va[i].w, acc[3]);
-        acc[4] = fmaf(gw[i], vb[i].x, acc[4]);
-        acc[5] = fmaf(gw[i], vb[i].y, acc[5]);
-        acc[6] = fmaf(gw[i], vb[i].z, acc[6]);
-        acc[7] = fmaf(gw[i], vb[i].w, acc[7]);
-      }
+    for (int i = 0; i < K; ++i) {
+      acc[0] = fmaf(gw[i], va[i].x, acc[0]);
+      acc[1] = fmaf(gw[i], va[i].y, acc[1]);
+      acc[2] = fmaf(gw[i], va[i].z, acc[2]);
+      acc[3] = fmaf(gw[i], va[i].w, acc[3]);
+      acc[4] = fmaf(gw[i], vb[i].x, acc[4]);
+      acc[5] = fmaf(gw[i], vb[i].y, acc[5]);
+      acc[6] = fmaf(gw[i], vb[i].z, acc[6]);
+      acc[7] = fmaf(gw[i], vb[i].w, acc[7]);
     }
     for (int s = 0; s < S; ++s) {
       const float4* row = reinterpret_cast<const float4*>(o_shared + ((size_t)s * T + t) * D) + 2 * c;
@@ -238,17 +242,26 @@ combine_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ o,
     yv.w = pack_bf16(acc[6], acc[7]);
     if (y != nullptr) reinterpret_cast<uint4*>(y + (size_t)t * D)[c] = yv;
     if (residual) {
-      uint4 xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)t * D) + c);
-      uint4 r;
-      r.x = pack_bf16(bf16_lo(xv.x) + bf16_lo(yv.x), bf16_hi(xv.x) + bf16_hi(yv.x));
-      r.y = pack_bf16(bf16_lo(xv.y) + bf16_lo(yv.y), bf16_hi(xv.y) + bf16_hi(yv.y));
-      r.z = pack_bf16(bf16_lo(xv.z) + bf16_lo(yv.z), bf16_hi(xv.z) + bf16_hi(yv.z));
-      r.w = pack_bf16(bf16_lo(xv.w) + bf16_lo(yv.w), bf16_hi(xv.w) + bf16_hi(yv.w));
-      reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = r;
+      uint4 rr;
+      rr.x = pack_bf16(bf16_lo(xv.x) + bf16_lo(yv.x), bf16_hi(xv.x) + bf16_hi(yv.x));
+      rr.y = pack_bf16(bf16_lo(xv.y) + bf16_lo(yv.y), bf16_hi(xv.y) + bf16_hi(yv.y));
+      rr.z = pack_bf16(bf16_lo(xv.z) + bf16_lo(yv.z), bf16_hi(xv.z) + bf16_hi(yv.z));
+      rr.w = pack_bf16(bf16_lo(xv.w) + bf16_lo(yv.w), bf16_hi(xv.w) + bf16_hi(yv.w));
+      reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = rr;
     } else {
       reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = yv;
     }
   }
+}
+
+template <int K>
+static void launch_combine(int blocks, cudaStream_t st, const void* x, const void* o,
+                           const void* o_shared, const int32_t* slot_dst, const float* topk_gate,
+                           void* y, void* out, const AxmMoeDesc* d, int residual) {
+  combine_kernel<K><<<blocks, 256, 0, st>>>(
+      static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(o),
+      static_cast<const float*>(o_shared), slot_dst, topk_gate, static_cast<__nv_bfloat16*>(y),
+      static_cast<__nv_bfloat16*>(out), d->tokens, d->d_model, d->num_shared, residual);
 }
 
 int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
@@ -312,12 +325,22 @@ extern "C" int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void
   if (int rc = require_device()) return rc;
   long long total = (long long)desc->tokens * (desc->d_model / 8);
   int blocks = (int)((total + 255) / 256);
-  int cap = sm_count() * 8;
+  int cap = sm_count() * 16;
   if (blocks > cap) blocks = cap;
-  combine_kernel<8><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(o),
-      static_cast<const float*>(o_shared), slot_dst, topk_gate,
-      static_cast<__nv_bfloat16*>(y), static_cast<__nv_bfloat16*>(out), desc->tokens,
-      desc->d_model, desc->top_k, desc->num_shared, residual);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  switch (desc->top_k) {
+#define AXM_COMBINE_CASE(K) \
+  case K: launch_combine<K>(blocks, st, x, o, o_shared, slot_dst, topk_gate, y, out, desc, residual); break;
+    AXM_COMBINE_CASE(1)
+    AXM_COMBINE_CASE(2)
+    AXM_COMBINE_CASE(3)
+    AXM_COMBINE_CASE(4)
+    AXM_COMBINE_CASE(5)
+    AXM_COMBINE_CASE(6)
+    AXM_COMBINE_CASE(7)
+    AXM_COMBINE_CASE(8)
+#undef AXM_COMBINE_CASE
+    default: return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..8", desc->top_k);
+  }
   return check_launch("combine_kernel");
 }

@@ -22,7 +22,7 @@ namespace axm {
 constexpr int kRouterThreads = 256;
 constexpr int kTokSub = 64;   // tokens handled per pass inside a block
 constexpr int kEC = 8;        // experts per register chunk
-constexpr int kTB = 8;        // tokens whose loads are in flight together
+constexpr int kTB = 4;        // tokens whose loads are in flight together
 constexpr int kMaxK = 8;
 
 __host__ __device__ inline int route_block_begin(int b, int T) {
@@ -90,7 +90,7 @@ __device__ __forceinline__ void route_one_token(float* z, int E, int k, int32_t*
 
 // kFromLogits: skip the GEMV and read z from `logits_in`.
 template <typename WT, bool kFromLogits>
-__global__ void __launch_bounds__(kRouterThreads)
+__global__ void __launch_bounds__(kRouterThreads, 2)
 router_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ wr,
               const float* __restrict__ bias, const float* __restrict__ logits_in,
               float* __restrict__ logits_out, int32_t* __restrict__ topk_idx,
@@ -121,33 +121,69 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ wr,
     } else {
       for (int i = tid; i < nt * EP; i += kRouterThreads) z_s[i] = 0.0f;
       __syncthreads();
-      // Each thread owns 8 consecutive d of every 2048-wide slab and keeps the
-      // matching 8 x kEC weights in registers while it walks the tokens.
+      // Each thread owns four pairs of consecutive d in every 2048-wide slab
+      // (d0 + 512*j + 2*tid + {0,1}) and keeps the matching 8 x kEC weights in
+      // registers while it walks the tokens.  With that interleaving a warp's
+      // weight loads and its 4-byte activation loads are both contiguous.
       for (int e0 = 0; e0 < E; e0 += kEC) {
         for (int d0 = 0; d0 < D; d0 += kRouterThreads * 8) {
-          const int d = d0 + tid * 8;
           float w[8][kEC];
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
+          for (int j = 0; j < 4; ++j) {
+            const int d = d0 + 512 * j + 2 * tid;
 #pragma unroll
-            for (int e = 0; e < kEC; ++e)
-              w[j][e] = (d + j < D && e0 + e < E) ? load_w<WT>(wr + (size_t)(d + j) * E + e0 + e)
-                                                  : 0.0f;
-          // Tokens go through in batches of kTB: all of a batch's 16-byte loads are
-          // issued before the first is used, so each thread keeps kTB loads in flight.
-          for (int tb = 0; tb < nt; tb += kTB) {
-            uint4 xv[kTB];
+            for (int i = 0; i < 2; ++i) {
+              float* wrow = w[2 * j + i];
 #pragma unroll
-            for (int b = 0; b < kTB; ++b) {
-              xv[b] = make_uint4(0, 0, 0, 0);
-              if (d < D && tb + b < nt)
-                xv[b] = __ldg(reinterpret_cast<const uint4*>(x + (size_t)(ts + tb + b) * D + d));
+              for (int e = 0; e < kEC; ++e) wrow[e] = 0.0f;
+              if (d + i < D) {
+                const WT* rowp = wr + (size_t)(d + i) * E + e0;
+                if (sizeof(WT) == 4 && (E & 3) == 0) {
+#pragma unroll
+                  for (int hq = 0; hq < 2; ++hq)
+                    if (e0 + 4 * hq < E) {
+                      float4 v = __ldg(reinterpret_cast<const float4*>(rowp) + hq);
+                      wrow[4 * hq + 0] = v.x;
+                      wrow[4 * hq + 1] = v.y;
+                      wrow[4 * hq + 2] = v.z;
+                      wrow[4 * hq + 3] = v.w;
+                    }
+                } else if (sizeof(WT) == 2 && (E & 7) == 0) {
+                  uint4 v = __ldg(reinterpret_cast<const uint4*>(rowp));
+                  wrow[0] = bf16_lo(v.x);
+                  wrow[1] = bf16_hi(v.x);
+                  wrow[2] = bf16_lo(v.y);
+                  wrow[3] = bf16_hi(v.y);
+                  wrow[4] = bf16_lo(v.z);
+                  wrow[5] = bf16_hi(v.z);
+                  wrow[6] = bf16_lo(v.w);
+                  wrow[7] = bf16_hi(v.w);
+                } else {
+#pragma unroll
+                  for (int e = 0; e < kEC; ++e)
+                    if (e0 + e < E) wrow[e] = load_w<WT>(rowp + e);
+                }
+              }
             }
+          }
+          // Tokens go through in batches of kTB: all of a batch's loads are issued
+          // before the first is used, so each thread keeps 4 * kTB loads in flight.
+          for (int tb = 0; tb < nt; tb += kTB) {
+            uint32_t xv[kTB][4];
+#pragma unroll
+            for (int b = 0; b < kTB; ++b)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const int d = d0 + 512 * j + 2 * tid;
+                xv[b][j] = 0u;
+                if (d < D && tb + b < nt)
+                  xv[b][j] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)(ts + tb + b) * D + d));
+              }
 #pragma unroll
             for (int b = 0; b < kTB; ++b) {
               const int tt = tb + b;
-              float xf[8] = {bf16_lo(xv[b].x), bf16_hi(xv[b].x), bf16_lo(xv[b].y), bf16_hi(xv[b].y),
-                             bf16_lo(xv[b].z), bf16_hi(xv[b].z), bf16_lo(xv[b].w), bf16_hi(xv[b].w)};
+              float xf[8] = {bf16_lo(xv[b][0]), bf16_hi(xv[b][0]), bf16_lo(xv[b][1]), bf16_hi(xv[b][1]),
+                             bf16_lo(xv[b][2]), bf16_hi(xv[b][2]), bf16_lo(xv[b][3]), bf16_hi(xv[b][3])};
               float acc[kEC];
 #pragma unroll
               for (int e = 0; e < kEC; ++e) acc[e] = 0.0f;
