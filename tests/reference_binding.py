@@ -16,17 +16,31 @@ REF_LIB = os.path.join(REF_DIR, "libaxiom_moe_ref.so")
 REF_OFFSETS = os.path.join(REF_DIR, "ref_offsets.json")
 
 
+# Field offsets of the engine's structs on Linux x86-64, as measured by
+# oracle/ref_offsets_probe.cu against the engine's header.  Used when the
+# reference build (and its JSON) is absent, e.g. to drive the drop-in library.
+OFFSETS_LINUX_X86_64 = {
+    "sizeof_GpuWeights": 472, "sizeof_GpuActivations": 328, "w.enable_moe": 328,
+    "w.expert_count": 336, "w.d_router_weights": 344, "w.d_expert_gate": 376, "w.d_expert_up": 384,
+    "w.d_expert_down": 392, "a.d_ffn_output": 144, "a.d_residual_out": 160,
+    "a.d_router_logits": 216, "a.d_expert_first": 224, "a.d_expert_second": 232,
+    "a.d_weight_first": 240, "a.d_weight_second": 248, "a.d_expert_histogram": 256,
+}
+
+
 def available():
     return os.path.exists(REF_LIB) and os.path.exists(REF_OFFSETS)
 
 
 class ReferenceMoe:
     """forward_mixture_experts / download_expert_counts / reset_expert_histogram
-    of the reference (core/src/CUDA/kernel/moe_router.cuh:30-44)."""
+    (core/src/CUDA/kernel/moe_router.cuh:30-44) of the reference build, or of any
+    other library that exports the same three symbols (lib_path)."""
 
-    def __init__(self):
-        self.lib = ctypes.CDLL(REF_LIB)
-        self.off = json.load(open(REF_OFFSETS))
+    def __init__(self, lib_path=None):
+        self.lib = ctypes.CDLL(lib_path or REF_LIB)
+        self.off = (json.load(open(REF_OFFSETS)) if lib_path is None and os.path.exists(REF_OFFSETS)
+                    else dict(OFFSETS_LINUX_X86_64))
         vp, sz = ctypes.c_void_p, ctypes.c_size_t
         self.lib.forward_mixture_experts.argtypes = [vp, vp, vp, sz, sz, sz, vp]
         self.lib.forward_mixture_experts.restype = ctypes.c_bool

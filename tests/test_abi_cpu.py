@@ -22,6 +22,24 @@ def test_exports_every_declared_symbol(axm):
     assert b"sm_100a" in lib.axm_version()
 
 
+def test_dropin_exports_the_reference_symbols(axm):
+    """libaxm_moe_dropin.so exports exactly what include/axm_moe_dropin.h declares."""
+    header = os.path.join(os.path.dirname(axm.HEADER_PATH), "axm_moe_dropin.h")
+    text = open(header).read()
+    names = sorted(set(re.findall(r"AXM_API\s+bool\s+(\w+)\s*\(", text)))
+    assert names == ["download_expert_counts", "forward_mixture_experts", "reset_expert_histogram"]
+    lib = ctypes.CDLL(axm.DROPIN_PATH)
+    for n in names:
+        assert hasattr(lib, n)
+    lib.forward_mixture_experts.restype = ctypes.c_bool
+    lib.forward_mixture_experts.argtypes = [ctypes.c_void_p] * 3 + [ctypes.c_size_t] * 3 + [ctypes.c_void_p]
+    # argument validation happens before any CUDA call
+    assert lib.forward_mixture_experts(None, None, None, 1, 1, 1, None) is False
+    blob = ctypes.create_string_buffer(512)
+    assert lib.forward_mixture_experts(ctypes.addressof(blob), ctypes.addressof(blob),
+                                       ctypes.addressof(blob), 0, 8, 8, None) is False
+
+
 def test_struct_sizes_match_header(axm):
     assert ctypes.sizeof(axm.MoeDesc) == 32
     assert ctypes.sizeof(axm.MoeTensors) == 18 * 8
