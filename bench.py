@@ -183,6 +183,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=256, help="tokens in the CPU baseline sample")
     ap.add_argument("--reference-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
+                    help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -226,10 +228,12 @@ def main():
         x_local = x[rank * tl:(rank + 1) * tl].contiguous()
         wloc = ep.shard_weights(w, rank, world)
         del w
-        layer = ep.ExpertParallelMoe(wloc, tl, cfg.num_experts, k)
+        cls = ep.ExpertParallelMoeP2P if args.ep_transport == "p2p" else ep.ExpertParallelMoe
+        layer = cls(wloc, tl, cfg.num_experts, k)
         out = torch.empty_like(x_local)
         step = lambda: layer.forward(x_local, out)
-        launches_per_step = 5  # router, permute, two GEMMs, combine (exchanges are NCCL's)
+        # router, permute, two GEMMs, combine (+ dispatch, segments, return, wait with p2p)
+        launches_per_step = 9 if args.ep_transport == "p2p" else 5
     del x
     torch.cuda.empty_cache()
 
@@ -357,6 +361,7 @@ def main():
             line["stages"] = stages
         if ep_stages is not None:
             line["stages_rank0"] = ep_stages
+            line["config"]["ep_transport"] = args.ep_transport
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

@@ -200,6 +200,59 @@ AXM_API int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void* o
                             const void* o_shared, const int32_t* slot_dst,
                             const float* topk_gate, void* y, void* out, void* stream);
 
+/* ---- expert-parallel exchange over NVLink peer memory ------------------------
+ * No reference counterpart: the engine is single-GPU (no NCCL/MPI in core/src).
+ * Every rank allocates one exchange region of identical layout in memory its
+ * peers can address (peer access / symmetric memory; the allocation is the
+ * host's) and passes the table of all regions' base addresses.  The kernels reach
+ * peers with plain 16-byte stores and bounded flag waits; see csrc/ep_exchange.cu.
+ * `step` must grow by one per layer call, starting at 1, on every rank alike.
+ * The region must be zero-filled once before the first call (flags).
+ * `scratch` is 2 zero-initialised int32 in local memory, private to the layer. */
+typedef struct AxmEpLayout {
+  const void* const* peers; /* DEVICE array [world]: base address of every rank's region */
+  int32_t rank, world;
+  int32_t num_experts;      /* E over all ranks; E / world experts per rank */
+  int32_t d_model;
+  int32_t slots;            /* T_local * k: rows this rank sends and gets back */
+  int32_t cap;              /* rows the receive buffer holds (slots * world covers every case) */
+  int32_t num_shared;       /* shared experts, run on the local tokens */
+  int32_t tokens_local;
+  int64_t off_flags, off_counts, off_recv, off_oback; /* byte offsets inside a region */
+} AxmEpLayout;
+
+/* Fills the offsets / sizes of `layout` and returns the bytes one region needs:
+ * flags [3][world] u32, counts [world][E] i32, receive buffer [cap][D] bf16,
+ * return buffer [slots][D] fp32. */
+AXM_API int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d_model,
+                                int32_t slots, int32_t cap, AxmEpLayout* layout, size_t* bytes);
+
+/* Dispatch: posts this rank's per-expert counts (from `offsets`, [E+1]) to all
+ * peers, waits for theirs, copies the permuted rows (x_perm [slots][D] bf16) into
+ * the owners' receive buffers and flags them. */
+AXM_API int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const int32_t* offsets,
+                            const void* x_perm, int32_t* scratch, int32_t* status, void* stream);
+
+/* Waits for every source's rows, then writes the segment table for
+ * axm_moe_expert_ffn over the receive buffer (world * E/world segments in arrival
+ * order, then num_shared segments over the local tokens with output rows from
+ * `cap` on), the return map ret_row0 [world * E/world] and the number of rows
+ * received. */
+AXM_API int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
+                            int32_t* ret_row0, int32_t* rows_received, int32_t* status,
+                            void* stream);
+
+/* Return: copies the fp32 expert rows `o` back into each source rank's return
+ * buffer at the rows its own permutation expects, and flags the sources. */
+AXM_API int axm_ep_return(const AxmEpLayout* layout, uint32_t step, const AxmSegment* segments,
+                          const int32_t* ret_row0, const void* o, int32_t* scratch,
+                          int32_t* status, void* stream);
+
+/* Waits until every owner has returned this rank's rows (run before axm_moe_combine
+ * on the return buffer). */
+AXM_API int axm_ep_wait_return(const AxmEpLayout* layout, uint32_t step, int32_t* status,
+                               void* stream);
+
 /* Number of token blocks the router splits T into (rows of block_counts). */
 #define AXM_ROUTE_BLOCKS 296
 

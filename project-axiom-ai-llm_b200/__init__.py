@@ -50,6 +50,13 @@ class MoeTensors(ctypes.Structure):
         "slot_dst", "y", "out")]
 
 
+class EpLayout(ctypes.Structure):
+    _fields_ = ([("peers", ctypes.c_void_p)] +
+                [(n, ctypes.c_int32) for n in ("rank", "world", "num_experts", "d_model", "slots",
+                                               "cap", "num_shared", "tokens_local")] +
+                [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")])
+
+
 class Segment(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("a_row0", "out_row0", "rows", "expert")]
 
@@ -84,6 +91,12 @@ def load():
     lib.axm_moe_expert_ffn.argtypes = [dp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp,
                                        vp, i32, vp, vp]
     lib.axm_moe_combine.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
+    lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
+    lib.axm_ep_dispatch.argtypes = [lp, u32, vp, vp, vp, vp, vp]
+    lib.axm_ep_segments.argtypes = [lp, u32, vp, vp, vp, vp, vp]
+    lib.axm_ep_return.argtypes = [lp, u32, vp, vp, vp, vp, vp, vp]
+    lib.axm_ep_wait_return.argtypes = [lp, u32, vp, vp]
     lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     _lib = lib
     return lib

@@ -1,0 +1,322 @@
+// Expert-parallel exchange over NVLink peer memory: dispatch of permuted token
+// rows to the ranks that own their experts, and return of the expert outputs,
+// written as plain peer stores by this GPU's own kernels, with flags in peer
+// memory instead of host synchronisation.
+//
+// The reference engine is single-GPU; this is the sharded form of its
+// forward_mixture_experts (core/src/CUDA/kernel/moe_router.cu:205-320): each
+// rank routes and permutes its own tokens, the rows travel to the expert's
+// rank, the grouped GEMMs run on local memory only, the fp32 expert rows travel
+// back and are combined where the gates are.
+//
+// Every rank owns one "exchange region" of identical layout (AxmEpLayout) and
+// knows the address of every peer's region (peer access enabled by whoever
+// allocated them).  Per layer call, with `step` a counter the host increments:
+//   axm_ep_dispatch   post my per-expert counts to all peers, flag; wait for all
+//                     peers' counts; copy my permuted rows into each owner's
+//                     receive buffer at the offset the counts imply; flag.
+//   axm_ep_segments   wait for all sources' rows; build the segment table
+//                     (one per source rank and local expert) and the return map.
+//   (grouped GEMMs over the receive buffer - local TMA only)
+//   axm_ep_return     copy fp32 expert rows back into each source's buffer, flag.
+//   axm_ep_wait_return wait for all owners' rows before the combine.
+// Flags only ever grow (they hold the step number), so nothing is reset and a
+// buffer is never overwritten before its reader has signalled: the return flag of
+// step n from rank B tells rank A that B has finished reading everything A sent
+// in step n.
+//
+// All waits are bounded (about two seconds); a wait that gives up stores a code
+// in the status word and the kernel carries on, so a missing peer cannot hang the
+// GPU.  No multicast, no TMA on peer memory: peers are reached with ordinary
+// 16-byte stores.
+#include "common.cuh"
+
+namespace axm {
+
+struct EpArgs {
+  char* const* peers;   // device array [G]: base of every rank's exchange region
+  int rank, G, E, El;   // El = experts per rank
+  int D;                // d_model
+  int slots;            // T_local * k
+  int cap;              // rows the receive buffer holds
+  int S, T_local;       // shared experts, local tokens
+  uint32_t step;
+  long long off_counts, off_flags, off_recv, off_oback;  // byte offsets inside a region
+  int32_t* status;
+};
+
+// flags: [3][G] uint32 = {counts posted, rows delivered, outputs returned}
+__device__ __forceinline__ uint32_t* flag_ptr(const EpArgs& a, int owner, int kind, int src) {
+  return reinterpret_cast<uint32_t*>(a.peers[owner] + a.off_flags) + kind * a.G + src;
+}
+
+__device__ __forceinline__ void store_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ uint32_t load_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Waits until flag >= step (wrap-safe).  Returns false when the wait ran out.
+__device__ __forceinline__ bool wait_flag(const uint32_t* p, uint32_t step) {
+  long long t0 = clock64();
+  while ((int32_t)(load_acquire_sys(p) - step) < 0) {
+    if (clock64() - t0 > kWaitCycles) return false;
+    __nanosleep(64);
+  }
+  return true;
+}
+
+// Thread s < G waits for flag (kind, s) of this rank; the block then syncs.
+__device__ __forceinline__ void wait_all_sources(const EpArgs& a, int kind, int code) {
+  if ((int)threadIdx.x < a.G) {
+    if (!wait_flag(flag_ptr(a, a.rank, kind, threadIdx.x), a.step) && a.status != nullptr)
+      atomicExch(a.status, code);
+  }
+  __syncthreads();
+}
+
+constexpr int kEpThreads = 256;
+constexpr int kEpMaxRanks = 64;
+
+__global__ void __launch_bounds__(kEpThreads)
+ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
+                   const __nv_bfloat16* __restrict__ x_perm, int32_t* __restrict__ done_counter) {
+  __shared__ int dst_begin[kEpMaxRanks + 1];  // first permuted row that goes to rank g
+  __shared__ int dst_base[kEpMaxRanks];       // row in g's receive buffer where my rows start
+  const int tid = threadIdx.x;
+
+  // 1. post my counts into every peer's table (row = my rank) and flag them
+  if (blockIdx.x == 0) {
+    for (int i = tid; i < a.E * a.G; i += kEpThreads) {
+      int g = i / a.E, e = i - g * a.E;
+      int32_t* table = reinterpret_cast<int32_t*>(a.peers[g] + a.off_counts);
+      table[a.rank * a.E + e] = offsets[e + 1] - offsets[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < a.G) store_release_sys(flag_ptr(a, tid, 0, a.rank), a.step);
+  }
+  // 2. wait for everybody's counts (each block on its own: no block depends on another)
+  wait_all_sources(a, 0, 11);
+  // 3. where do my rows go
+  const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
+  if (tid <= a.G) dst_begin[tid] = offsets[min(tid * a.El, a.E)];
+  if (tid < a.G) {
+    int base = 0;
+    for (int s = 0; s < a.rank; ++s)
+      for (int j = 0; j < a.El; ++j) base += __ldcg(table + s * a.E + tid * a.El + j);
+    dst_base[tid] = base;
+  }
+  __syncthreads();
+  // 4. copy: one warp per row, 16-byte pieces, plain stores into the owner's memory
+  const int warp = tid >> 5, lane = tid & 31;
+  const int warps_total = gridDim.x * (kEpThreads / 32);
+  const int chunks = a.D / 8;
+  int g = 0;
+  for (int r = blockIdx.x * (kEpThreads / 32) + warp; r < a.slots; r += warps_total) {
+    while (g + 1 <= a.G && r >= dst_begin[g + 1]) ++g;  // rows ascend, so does the owner
+    const int dst_row = dst_base[g] + (r - dst_begin[g]);
+    if (dst_row >= a.cap) continue;  // cannot happen with cap = slots * G; never write outside
+    const uint4* src = reinterpret_cast<const uint4*>(x_perm + (size_t)r * a.D);
+    uint4* dst = reinterpret_cast<uint4*>(a.peers[g] + a.off_recv) + (size_t)dst_row * chunks;
+    for (int c = lane; c < chunks; c += 32) dst[c] = __ldg(src + c);
+  }
+  // 5. when every block is done, tell every owner that my rows have landed
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    int prev = atomicAdd(done_counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int o = 0; o < a.G; ++o) store_release_sys(flag_ptr(a, o, 1, a.rank), a.step);
+    }
+  }
+}
+
+// One block.  seg[(s, j)] over the receive buffer; ret_row0[(s, j)] = row in rank s's
+// return buffer where that chunk belongs (s's own offset of expert rank*El + j).
+__global__ void __launch_bounds__(kEpThreads)
+ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments, int32_t* __restrict__ ret_row0,
+                   int32_t* __restrict__ rows_received) {
+  __shared__ int rows_s[kEpMaxRanks * 64];
+  wait_all_sources(a, 1, 12);
+  const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
+  const int n = a.G * a.El;
+  for (int i = threadIdx.x; i < n; i += kEpThreads) {
+    int s = i / a.El, j = i - s * a.El;
+    rows_s[i] = __ldcg(table + s * a.E + a.rank * a.El + j);
+    int before = 0;
+    for (int e = 0; e < a.rank * a.El + j; ++e) before += __ldcg(table + s * a.E + e);
+    ret_row0[i] = before;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int i = 0; i < n; ++i) {
+      AxmSegment sg;
+      sg.a_row0 = acc;
+      sg.out_row0 = acc;
+      sg.rows = rows_s[i];
+      sg.expert = i % a.El;
+      segments[i] = sg;
+      acc += rows_s[i];
+    }
+    for (int s = 0; s < a.S; ++s) {
+      AxmSegment sg;
+      sg.a_row0 = 0;
+      sg.out_row0 = a.cap + s * a.T_local;
+      sg.rows = a.T_local;
+      sg.expert = (a.El + s) | AXM_SEG_ALT_A;
+      segments[n + s] = sg;
+    }
+    if (rows_received != nullptr) *rows_received = acc;
+  }
+}
+
+__global__ void __launch_bounds__(kEpThreads)
+ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ segments,
+                 const int32_t* __restrict__ ret_row0, const float* __restrict__ o,
+                 int32_t* __restrict__ done_counter) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warps_total = gridDim.x * (kEpThreads / 32);
+  const int chunks = a.D / 4;  // 16-byte pieces of an fp32 row
+  const int n = a.G * a.El;
+  int seg = 0;
+  AxmSegment sg = segments[0];
+  for (int r = blockIdx.x * (kEpThreads / 32) + warp;; r += warps_total) {
+    while (seg < n && r >= sg.out_row0 + sg.rows) {
+      ++seg;
+      if (seg < n) sg = segments[seg];
+    }
+    if (seg >= n) break;
+    const int src_rank = seg / a.El;
+    const int dst_row = ret_row0[seg] + (r - sg.out_row0);
+    if (dst_row >= a.slots) continue;
+    const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)r * a.D);
+    uint4* dst = reinterpret_cast<uint4*>(a.peers[src_rank] + a.off_oback) + (size_t)dst_row * chunks;
+    for (int c = lane; c < chunks; c += 32) dst[c] = __ldg(src + c);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int prev = atomicAdd(done_counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int s = 0; s < a.G; ++s) store_release_sys(flag_ptr(a, s, 2, a.rank), a.step);
+    }
+  }
+}
+
+__global__ void ep_wait_return_kernel(EpArgs a) { wait_all_sources(a, 2, 13); }
+
+static int validate_ep(const AxmEpLayout* l) {
+  if (l == nullptr || l->peers == nullptr) return fail(AXM_ERR_ARGUMENT, "exchange layout or peer table is null");
+  if (l->world <= 0 || l->world > kEpMaxRanks || l->rank < 0 || l->rank >= l->world)
+    return fail(AXM_ERR_ARGUMENT, "rank %d / world %d out of range (at most %d ranks)", l->rank, l->world, kEpMaxRanks);
+  if (l->num_experts <= 0 || l->num_experts % l->world != 0)
+    return fail(AXM_ERR_ARGUMENT, "num_experts %d must be a positive multiple of world %d", l->num_experts, l->world);
+  if (l->num_experts / l->world > 64) return fail(AXM_ERR_ARGUMENT, "more than 64 experts per rank");
+  if (l->d_model <= 0 || l->d_model % 8 != 0) return fail(AXM_ERR_ARGUMENT, "d_model %d not a multiple of 8", l->d_model);
+  if (l->slots < 0 || l->cap < 0) return fail(AXM_ERR_ARGUMENT, "negative row count");
+  return AXM_OK;
+}
+
+static EpArgs make_args(const AxmEpLayout* l, uint32_t step, int32_t* status) {
+  EpArgs a;
+  a.peers = reinterpret_cast<char* const*>(const_cast<void* const*>(l->peers));
+  a.rank = l->rank;
+  a.G = l->world;
+  a.E = l->num_experts;
+  a.El = l->num_experts / l->world;
+  a.D = l->d_model;
+  a.slots = l->slots;
+  a.cap = l->cap;
+  a.S = l->num_shared;
+  a.T_local = l->tokens_local;
+  a.step = step;
+  a.off_counts = l->off_counts;
+  a.off_flags = l->off_flags;
+  a.off_recv = l->off_recv;
+  a.off_oback = l->off_oback;
+  a.status = status;
+  return a;
+}
+
+}  // namespace axm
+
+using namespace axm;
+
+extern "C" int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d_model,
+                                   int32_t slots, int32_t cap, AxmEpLayout* layout,
+                                   size_t* bytes) {
+  if (!layout || !bytes) return fail(AXM_ERR_ARGUMENT, "axm_ep_region_bytes: null pointer");
+  if (world <= 0 || num_experts <= 0 || d_model <= 0 || slots < 0 || cap < 0)
+    return fail(AXM_ERR_ARGUMENT, "axm_ep_region_bytes: bad sizes");
+  auto up = [](long long v) { return (v + 255) & ~255LL; };
+  long long off = 0;
+  layout->off_flags = off;
+  off = up(off + 4LL * 3 * world);
+  layout->off_counts = off;
+  off = up(off + 4LL * world * num_experts);
+  layout->off_recv = off;
+  off = up(off + 2LL * cap * d_model);
+  layout->off_oback = off;
+  off = up(off + 4LL * slots * d_model);
+  layout->world = world;
+  layout->num_experts = num_experts;
+  layout->d_model = d_model;
+  layout->slots = slots;
+  layout->cap = cap;
+  *bytes = (size_t)off;
+  return AXM_OK;
+}
+
+extern "C" int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const int32_t* offsets,
+                               const void* x_perm, int32_t* scratch, int32_t* status, void* stream) {
+  if (int rc = validate_ep(layout)) return rc;
+  if (!offsets || !x_perm || !scratch) return fail(AXM_ERR_ARGUMENT, "axm_ep_dispatch: null pointer");
+  if (int rc = require_device()) return rc;
+  EpArgs a = make_args(layout, step, status);
+  ep_dispatch_kernel<<<2 * sm_count(), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, offsets, static_cast<const __nv_bfloat16*>(x_perm), scratch);
+  return check_launch("ep_dispatch_kernel");
+}
+
+extern "C" int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
+                               int32_t* ret_row0, int32_t* rows_received, int32_t* status,
+                               void* stream) {
+  if (int rc = validate_ep(layout)) return rc;
+  if (!segments || !ret_row0) return fail(AXM_ERR_ARGUMENT, "axm_ep_segments: null pointer");
+  if (int rc = require_device()) return rc;
+  EpArgs a = make_args(layout, step, status);
+  ep_segments_kernel<<<1, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, segments, ret_row0,
+                                                                             rows_received);
+  return check_launch("ep_segments_kernel");
+}
+
+extern "C" int axm_ep_return(const AxmEpLayout* layout, uint32_t step, const AxmSegment* segments,
+                             const int32_t* ret_row0, const void* o, int32_t* scratch,
+                             int32_t* status, void* stream) {
+  if (int rc = validate_ep(layout)) return rc;
+  if (!segments || !ret_row0 || !o || !scratch) return fail(AXM_ERR_ARGUMENT, "axm_ep_return: null pointer");
+  if (int rc = require_device()) return rc;
+  EpArgs a = make_args(layout, step, status);
+  ep_return_kernel<<<2 * sm_count(), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      a, segments, ret_row0, static_cast<const float*>(o), scratch + 1);
+  return check_launch("ep_return_kernel");
+}
+
+extern "C" int axm_ep_wait_return(const AxmEpLayout* layout, uint32_t step, int32_t* status,
+                                  void* stream) {
+  if (int rc = validate_ep(layout)) return rc;
+  if (int rc = require_device()) return rc;
+  EpArgs a = make_args(layout, step, status);
+  ep_wait_return_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return check_launch("ep_wait_return_kernel");
+}

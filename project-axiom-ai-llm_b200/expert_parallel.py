@@ -21,7 +21,7 @@ import ctypes
 import torch
 import torch.distributed as dist
 
-from . import (FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A, check,
+from . import (FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A, EpLayout, check,
                current_stream, load, make_desc, ptr)
 
 
@@ -168,4 +168,121 @@ class ExpertParallelMoe:
         o_shared = self.o[self.cap:] if self.S else None
         st.combine(self.desc_comb, x, self.o_back, o_shared, self.slot_dst, self.gate, self.y, out)
         mark("combine")
+        return out
+
+
+class ExpertParallelMoeP2P:
+    """The same sharded layer with the two exchanges done by this library's own
+    kernels over NVLink peer memory (csrc/ep_exchange.cu) instead of NCCL
+    all-to-alls: no host synchronisation inside a layer call, seven kernels in all.
+
+    The exchange region is symmetric memory (torch.distributed._symmetric_memory):
+    one allocation per rank, every rank holding the addresses of all of them.
+    forward(x_local) -> out_local.  GPU only.
+    """
+
+    def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, residual=True):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.lib = load()
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.stages = CudaStages()
+        self.w = local_weights
+        wr = local_weights["router_w"]
+        self.dev = wr.device
+        D = wr.shape[0]
+        F = local_weights["w_gate"].shape[2]
+        self.E, self.k, self.D, self.F = num_experts, top_k, D, F
+        self.El = num_experts // self.world
+        assert self.El * self.world == num_experts and local_weights["w_gate"].shape[0] == self.El
+        self.S = 0 if local_weights.get("shared_gate") is None else local_weights["shared_gate"].shape[0]
+        self.Tl = tokens_local
+        rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
+        flags = FLAG_RESIDUAL if residual else 0
+        self.desc_route = make_desc(tokens_local, D, F, num_experts, top_k, 0, rdt, flags)
+        self.desc_ffn = make_desc(tokens_local, D, F, self.El, min(top_k, self.El), self.S, rdt, flags)
+        self.desc_comb = make_desc(tokens_local, D, F, num_experts, top_k, self.S, rdt, flags)
+        dev, i32, bf = self.dev, torch.int32, torch.bfloat16
+        n_slots = tokens_local * top_k
+        self.slots = n_slots
+        self.cap = n_slots * self.world
+        self.rows_total = self.cap + self.S * tokens_local
+        self.n_seg = self.world * self.El + self.S
+
+        self.layout = EpLayout()
+        nbytes = ctypes.c_size_t(0)
+        check(self.lib.axm_ep_region_bytes(self.world, num_experts, D, n_slots, self.cap,
+                                           ctypes.byref(self.layout), ctypes.byref(nbytes)))
+        self.region = symm_mem.empty(nbytes.value, dtype=torch.uint8, device=dev)
+        self.handle = symm_mem.rendezvous(self.region, self.group)
+        self.region.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        self.layout.peers = self.handle.buffer_ptrs_dev
+        self.layout.rank = self.rank
+        self.layout.num_shared = self.S
+        self.layout.tokens_local = tokens_local
+        lo = self.layout
+        self.recv = self.region[lo.off_recv:lo.off_recv + 2 * self.cap * D].view(bf).view(self.cap, D)
+        self.o_back = self.region[lo.off_oback:lo.off_oback + 4 * n_slots * D].view(
+            torch.float32).view(n_slots, D)
+
+        self.logits = torch.empty(tokens_local, num_experts, dtype=torch.float32, device=dev)
+        self.idx = torch.empty(tokens_local, top_k, dtype=i32, device=dev)
+        self.gate = torch.empty(tokens_local, top_k, dtype=torch.float32, device=dev)
+        self.block_counts = torch.empty(ROUTE_BLOCKS, num_experts, dtype=i32, device=dev)
+        self.histogram = torch.zeros(num_experts, dtype=i32, device=dev)
+        self.offsets = torch.empty(num_experts + 1, dtype=i32, device=dev)
+        self.row_src = torch.empty(n_slots, dtype=i32, device=dev)
+        self.slot_dst = torch.empty(n_slots, dtype=i32, device=dev)
+        self.x_perm = torch.empty(n_slots, D, dtype=bf, device=dev)
+        self.h = torch.empty(self.rows_total, F, dtype=bf, device=dev)
+        self.o = torch.empty(self.rows_total, D, dtype=torch.float32, device=dev)
+        self.y = torch.empty(tokens_local, D, dtype=bf, device=dev)
+        self.status = torch.zeros(1, dtype=i32, device=dev)
+        self.scratch = torch.zeros(2, dtype=i32, device=dev)
+        self.segments = torch.zeros(self.n_seg, 4, dtype=i32, device=dev)
+        self.ret_row0 = torch.zeros(self.world * self.El, dtype=i32, device=dev)
+        self.rows_received = torch.zeros(1, dtype=i32, device=dev)
+        self.step = 0
+
+    @property
+    def last_rows_received(self):
+        return int(self.rows_received.item())
+
+    def forward(self, x, out=None, events=None):
+        st, lib, lo = self.stages, self.lib, ctypes.byref(self.layout)
+
+        def mark(name):
+            if events is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                events.append((name, ev))
+
+        if out is None:
+            out = torch.empty_like(x)
+        self.step += 1
+        stream = current_stream()
+        mark("start")
+        st.router(self.desc_route, x, self.w, self.logits, self.idx, self.gate, self.block_counts)
+        st.permute(self.desc_route, x, self.idx, self.block_counts, self.histogram, self.offsets,
+                   self.row_src, self.slot_dst, self.x_perm)
+        mark("router+permute")
+        check(lib.axm_ep_dispatch(lo, self.step, ptr(self.offsets), ptr(self.x_perm),
+                                  ptr(self.scratch), ptr(self.status), stream))
+        mark("dispatch (peer stores)")
+        check(lib.axm_ep_segments(lo, self.step, ptr(self.segments), ptr(self.ret_row0),
+                                  ptr(self.rows_received), ptr(self.status), stream))
+        mark("wait rows + segments")
+        st.expert_ffn(self.desc_ffn, self.recv, self.cap, x, self.Tl, self.segments, self.w, self.h,
+                      self.o, self.rows_total, self.status)
+        mark("expert GEMMs")
+        check(lib.axm_ep_return(lo, self.step, ptr(self.segments), ptr(self.ret_row0), ptr(self.o),
+                                ptr(self.scratch), ptr(self.status), stream))
+        mark("return (peer stores)")
+        check(lib.axm_ep_wait_return(lo, self.step, ptr(self.status), stream))
+        o_shared = self.o[self.cap:] if self.S else None
+        st.combine(self.desc_comb, x, self.o_back, o_shared, self.slot_dst, self.gate, self.y, out)
+        mark("wait return + combine")
         return out

@@ -23,7 +23,7 @@ def _free_port():
     return p
 
 
-def _worker(rank, world, port, name, tokens, out_dir):
+def _worker(rank, world, port, name, tokens, transport, out_dir):
     sys.path.insert(0, HERE)
     import importlib
     import conftest
@@ -41,10 +41,11 @@ def _worker(rank, world, port, name, tokens, out_dir):
         x, w = wl.make_inputs(cfg)          # CPU generator: identical on every rank
         x, w = x.to(dev), {k: v.to(dev) for k, v in w.items()}
         tl = cfg.tokens // world
-        layer = ep.ExpertParallelMoe(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
-                                     cfg.top_k)
-        out = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
-        out2 = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
+        cls = ep.ExpertParallelMoeP2P if transport == "p2p" else ep.ExpertParallelMoe
+        layer = cls(ep.shard_weights(w, rank, world), tl, cfg.num_experts, cfg.top_k)
+        out = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous()).clone()
+        for _ in range(3):      # buffers and flags are reused call after call
+            out2 = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
         torch.cuda.synchronize()
         assert int(layer.status.item()) == 0
         assert torch.equal(out, out2)
@@ -61,10 +62,11 @@ def _worker(rank, world, port, name, tokens, out_dir):
         dist.destroy_process_group()
 
 
+@pytest.mark.parametrize("transport", ["nccl", "p2p"])
 @pytest.mark.parametrize("name,tokens", [("C1", 64), ("C2", 1024), ("C4", 2048)])
-def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens):
-    world = 2
-    mp.start_processes(_worker, args=(world, _free_port(), name, tokens, str(tmp_path)),
+def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens, transport):
+    world = min(torch.cuda.device_count(), 4) if name == "C4" else 2
+    mp.start_processes(_worker, args=(world, _free_port(), name, tokens, transport, str(tmp_path)),
                        nprocs=world, join=True, start_method="spawn")
     ref = torch.load(os.path.join(str(tmp_path), "ref.pt"))
     parts = [torch.load(os.path.join(str(tmp_path), f"r{r}.pt")) for r in range(world)]
