@@ -233,19 +233,21 @@ AXM_API int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d_mo
 AXM_API int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const int32_t* offsets,
                             const void* x_perm, int32_t* scratch, int32_t* status, void* stream);
 
-/* Waits for every source's rows, then writes the segment table for
- * axm_moe_expert_ffn over the receive buffer (world * E/world segments in arrival
- * order, then num_shared segments over the local tokens with output rows from
- * `cap` on), the return map ret_row0 [world * E/world] and the number of rows
- * received. */
+/* Waits for every source's rows, then writes two tables over the receive buffer
+ * (world * E/world entries each): `segments` for axm_moe_expert_ffn, ordered by
+ * (local expert, source rank) so that one expert's segments are neighbours,
+ * followed by num_shared segments over the local tokens with output rows from
+ * `cap` on; and `ret_segments` in arrival order for axm_ep_return
+ * ({a_row0 = row in the source's return buffer, out_row0 = row here, rows,
+ * expert = source rank}).  Also the number of rows received. */
 AXM_API int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
-                            int32_t* ret_row0, int32_t* rows_received, int32_t* status,
+                            AxmSegment* ret_segments, int32_t* rows_received, int32_t* status,
                             void* stream);
 
 /* Return: copies the fp32 expert rows `o` back into each source rank's return
  * buffer at the rows its own permutation expects, and flags the sources. */
-AXM_API int axm_ep_return(const AxmEpLayout* layout, uint32_t step, const AxmSegment* segments,
-                          const int32_t* ret_row0, const void* o, int32_t* scratch,
+AXM_API int axm_ep_return(const AxmEpLayout* layout, uint32_t step,
+                          const AxmSegment* ret_segments, const void* o, int32_t* scratch,
                           int32_t* status, void* stream);
 
 /* Waits until every owner has returned this rank's rows (run before axm_moe_combine

@@ -95,7 +95,7 @@ def load():
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
     lib.axm_ep_dispatch.argtypes = [lp, u32, vp, vp, vp, vp, vp]
     lib.axm_ep_segments.argtypes = [lp, u32, vp, vp, vp, vp, vp]
-    lib.axm_ep_return.argtypes = [lp, u32, vp, vp, vp, vp, vp, vp]
+    lib.axm_ep_return.argtypes = [lp, u32, vp, vp, vp, vp, vp]
     lib.axm_ep_wait_return.argtypes = [lp, u32, vp, vp]
     lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     _lib = lib

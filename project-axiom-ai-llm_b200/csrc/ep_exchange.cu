@@ -123,7 +123,15 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
     if (dst_row >= a.cap) continue;  // cannot happen with cap = slots * G; never write outside
     const uint4* src = reinterpret_cast<const uint4*>(x_perm + (size_t)r * a.D);
     uint4* dst = reinterpret_cast<uint4*>(a.peers[g] + a.off_recv) + (size_t)dst_row * chunks;
-    for (int c = lane; c < chunks; c += 32) dst[c] = __ldg(src + c);
+    for (int c0 = 0; c0 < chunks; c0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + u * 32 + lane < chunks) v[u] = __ldg(src + c0 + u * 32 + lane);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + u * 32 + lane < chunks) dst[c0 + u * 32 + lane] = v[u];
+    }
   }
   // 5. when every block is done, tell every owner that my rows have landed
   __threadfence_system();
@@ -138,34 +146,33 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
   }
 }
 
-// One block.  seg[(s, j)] over the receive buffer; ret_row0[(s, j)] = row in rank s's
-// return buffer where that chunk belongs (s's own offset of expert rank*El + j).
+// One block.  Rows arrive source-major (all of rank 0's rows, then rank 1's ...),
+// sorted by expert inside each source.  Two tables over that buffer:
+//   segments     in (local expert, source) order for the grouped GEMMs, so that the
+//                segments of one expert are neighbours and share its weight tiles;
+//   ret_segments in (source, local expert) = arrival order for the return copy:
+//                {a_row0 = row in the source's return buffer, out_row0 = row here,
+//                 rows, expert = source rank}.
 __global__ void __launch_bounds__(kEpThreads)
-ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments, int32_t* __restrict__ ret_row0,
-                   int32_t* __restrict__ rows_received) {
+ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
+                   AxmSegment* __restrict__ ret_segments, int32_t* __restrict__ rows_received) {
   __shared__ int rows_s[kEpMaxRanks * 64];
+  __shared__ int start_s[kEpMaxRanks * 64];
   wait_all_sources(a, 1, 12);
   const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
   const int n = a.G * a.El;
   for (int i = threadIdx.x; i < n; i += kEpThreads) {
     int s = i / a.El, j = i - s * a.El;
     rows_s[i] = __ldcg(table + s * a.E + a.rank * a.El + j);
-    int before = 0;
-    for (int e = 0; e < a.rank * a.El + j; ++e) before += __ldcg(table + s * a.E + e);
-    ret_row0[i] = before;
   }
   __syncthreads();
   if (threadIdx.x == 0) {
     int acc = 0;
     for (int i = 0; i < n; ++i) {
-      AxmSegment sg;
-      sg.a_row0 = acc;
-      sg.out_row0 = acc;
-      sg.rows = rows_s[i];
-      sg.expert = i % a.El;
-      segments[i] = sg;
+      start_s[i] = acc;
       acc += rows_s[i];
     }
+    if (rows_received != nullptr) *rows_received = acc;
     for (int s = 0; s < a.S; ++s) {
       AxmSegment sg;
       sg.a_row0 = 0;
@@ -174,32 +181,55 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments, int32_t* __restr
       sg.expert = (a.El + s) | AXM_SEG_ALT_A;
       segments[n + s] = sg;
     }
-    if (rows_received != nullptr) *rows_received = acc;
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < n; i += kEpThreads) {
+    int s = i / a.El, j = i - s * a.El;
+    AxmSegment sg;
+    sg.a_row0 = start_s[i];
+    sg.out_row0 = start_s[i];
+    sg.rows = rows_s[i];
+    sg.expert = j;
+    segments[j * a.G + s] = sg;
+    int before = 0;  // source s's own offset of expert rank*El + j
+    for (int e = 0; e < a.rank * a.El + j; ++e) before += __ldcg(table + s * a.E + e);
+    AxmSegment rs;
+    rs.a_row0 = before;
+    rs.out_row0 = start_s[i];
+    rs.rows = rows_s[i];
+    rs.expert = s;
+    ret_segments[i] = rs;
   }
 }
 
 __global__ void __launch_bounds__(kEpThreads)
-ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ segments,
-                 const int32_t* __restrict__ ret_row0, const float* __restrict__ o,
-                 int32_t* __restrict__ done_counter) {
+ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
+                 const float* __restrict__ o, int32_t* __restrict__ done_counter) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * (kEpThreads / 32);
   const int chunks = a.D / 4;  // 16-byte pieces of an fp32 row
   const int n = a.G * a.El;
   int seg = 0;
-  AxmSegment sg = segments[0];
+  AxmSegment sg = ret_segments[0];
   for (int r = blockIdx.x * (kEpThreads / 32) + warp;; r += warps_total) {
     while (seg < n && r >= sg.out_row0 + sg.rows) {
       ++seg;
-      if (seg < n) sg = segments[seg];
+      if (seg < n) sg = ret_segments[seg];
     }
     if (seg >= n) break;
-    const int src_rank = seg / a.El;
-    const int dst_row = ret_row0[seg] + (r - sg.out_row0);
+    const int dst_row = sg.a_row0 + (r - sg.out_row0);
     if (dst_row >= a.slots) continue;
     const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)r * a.D);
-    uint4* dst = reinterpret_cast<uint4*>(a.peers[src_rank] + a.off_oback) + (size_t)dst_row * chunks;
-    for (int c = lane; c < chunks; c += 32) dst[c] = __ldg(src + c);
+    uint4* dst = reinterpret_cast<uint4*>(a.peers[sg.expert] + a.off_oback) + (size_t)dst_row * chunks;
+    for (int c0 = 0; c0 < chunks; c0 += 128) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + u * 32 + lane < chunks) v[u] = __ldg(src + c0 + u * 32 + lane);
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (c0 + u * 32 + lane < chunks) dst[c0 + u * 32 + lane] = v[u];
+    }
   }
   __threadfence_system();
   __syncthreads();
@@ -289,26 +319,26 @@ extern "C" int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const i
 }
 
 extern "C" int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
-                               int32_t* ret_row0, int32_t* rows_received, int32_t* status,
+                               AxmSegment* ret_segments, int32_t* rows_received, int32_t* status,
                                void* stream) {
   if (int rc = validate_ep(layout)) return rc;
-  if (!segments || !ret_row0) return fail(AXM_ERR_ARGUMENT, "axm_ep_segments: null pointer");
+  if (!segments || !ret_segments) return fail(AXM_ERR_ARGUMENT, "axm_ep_segments: null pointer");
   if (int rc = require_device()) return rc;
   EpArgs a = make_args(layout, step, status);
-  ep_segments_kernel<<<1, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, segments, ret_row0,
+  ep_segments_kernel<<<1, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, segments, ret_segments,
                                                                              rows_received);
   return check_launch("ep_segments_kernel");
 }
 
-extern "C" int axm_ep_return(const AxmEpLayout* layout, uint32_t step, const AxmSegment* segments,
-                             const int32_t* ret_row0, const void* o, int32_t* scratch,
+extern "C" int axm_ep_return(const AxmEpLayout* layout, uint32_t step,
+                             const AxmSegment* ret_segments, const void* o, int32_t* scratch,
                              int32_t* status, void* stream) {
   if (int rc = validate_ep(layout)) return rc;
-  if (!segments || !ret_row0 || !o || !scratch) return fail(AXM_ERR_ARGUMENT, "axm_ep_return: null pointer");
+  if (!ret_segments || !o || !scratch) return fail(AXM_ERR_ARGUMENT, "axm_ep_return: null pointer");
   if (int rc = require_device()) return rc;
   EpArgs a = make_args(layout, step, status);
   ep_return_kernel<<<2 * sm_count(), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      a, segments, ret_row0, static_cast<const float*>(o), scratch + 1);
+      a, ret_segments, static_cast<const float*>(o), scratch + 1);
   return check_launch("ep_return_kernel");
 }
 

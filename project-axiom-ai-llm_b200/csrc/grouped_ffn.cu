@@ -54,6 +54,8 @@ struct __align__(8) GemmShared {
   int abort_flag;
   int total_tiles;
   int tile_prefix[kMaxSegments + 1];  // m-tiles before segment s
+  int num_groups;                     // runs of consecutive segments with one expert
+  int group_first[kMaxSegments + 1];  // first segment of group g
   AxmSegment seg[kMaxSegments];
 };
 
@@ -94,20 +96,32 @@ struct TileCoord {
   int n_tile;
 };
 
+// Tiles are ordered group by group, where a group is a run of consecutive
+// segments that use the same expert (one segment on a single GPU; one per source
+// rank under expert parallelism).  Inside a group the order is n-tile major and
+// m-tile minor over ALL the group's m-tiles, so CTAs that run together share a
+// weight column block and each weight tile is fetched from HBM about once.
 __device__ __forceinline__ TileCoord decode_tile(const GemmShared* sh, int num_segments,
                                                  int n_tiles, int linear) {
-  // largest s with tile_prefix[s] * n_tiles <= linear
-  int lo = 0, hi = num_segments - 1;
-  while (lo < hi) {
+  int lo = 0, hi = sh->num_groups - 1;
+  while (lo < hi) {  // largest g whose first tile is <= linear
     int mid = (lo + hi + 1) >> 1;
-    if (sh->tile_prefix[mid] * n_tiles <= linear) lo = mid; else hi = mid - 1;
+    if (sh->tile_prefix[sh->group_first[mid]] * n_tiles <= linear) lo = mid; else hi = mid - 1;
   }
+  const int s0 = sh->group_first[lo], s1 = sh->group_first[lo + 1];
+  const int base = sh->tile_prefix[s0];
+  const int mt = sh->tile_prefix[s1] - base;
+  const int local = linear - base * n_tiles;
   TileCoord tc;
-  tc.seg = lo;
-  int local = linear - sh->tile_prefix[lo] * n_tiles;
-  int mt = sh->tile_prefix[lo + 1] - sh->tile_prefix[lo];
   tc.n_tile = local / mt;
-  tc.m_tile = local - tc.n_tile * mt;
+  const int m_idx = base + (local - tc.n_tile * mt);
+  int a = s0, b = s1 - 1;
+  while (a < b) {  // largest s in the group with tile_prefix[s] <= m_idx
+    int mid = (a + b + 1) >> 1;
+    if (sh->tile_prefix[mid] <= m_idx) a = mid; else b = mid - 1;
+  }
+  tc.seg = a;
+  tc.m_tile = m_idx - sh->tile_prefix[a];
   return tc;
 }
 
@@ -162,6 +176,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     sh->tile_prefix[nseg] = acc;
     sh->total_tiles = acc * n_tiles;
+    int ng = 0;
+    for (int s = 0; s < nseg; ++s)
+      if (s == 0 || sh->seg[s].expert != sh->seg[s - 1].expert) sh->group_first[ng++] = s;
+    sh->group_first[ng] = nseg;
+    sh->num_groups = ng;
   }
   tc_fence_before();
   __syncthreads();

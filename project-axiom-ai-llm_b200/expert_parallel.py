@@ -117,12 +117,15 @@ class ExpertParallelMoe:
         self.last_rows_received = 0
 
     def build_segments(self, recv_counts):
-        """Segment table for the rows received: one per (source rank, local expert),
-        in arrival order, then one per shared expert over the local tokens."""
+        """Segment table for the rows received: one per (source rank, local expert).
+        Rows sit in arrival order (source-major); the table lists them expert-major so
+        that the GEMM kernel sees one expert's segments side by side and shares its
+        weight tiles among them.  Then one segment per shared expert over the local tokens."""
         flat = recv_counts.reshape(-1).to(torch.int64)
         starts = torch.cumsum(flat, 0) - flat
         expert = torch.arange(self.El, device=flat.device).repeat(self.world)
         seg = torch.stack([starts, starts, flat, expert], dim=1)
+        seg = seg.view(self.world, self.El, 4).transpose(0, 1).reshape(-1, 4)
         if self.S:
             s = torch.arange(self.S, device=flat.device)
             shared = torch.stack([torch.zeros_like(s), self.cap + s * self.Tl,
@@ -243,7 +246,7 @@ class ExpertParallelMoeP2P:
         self.status = torch.zeros(1, dtype=i32, device=dev)
         self.scratch = torch.zeros(2, dtype=i32, device=dev)
         self.segments = torch.zeros(self.n_seg, 4, dtype=i32, device=dev)
-        self.ret_row0 = torch.zeros(self.world * self.El, dtype=i32, device=dev)
+        self.ret_segments = torch.zeros(self.world * self.El, 4, dtype=i32, device=dev)
         self.rows_received = torch.zeros(1, dtype=i32, device=dev)
         self.step = 0
 
@@ -272,13 +275,13 @@ class ExpertParallelMoeP2P:
         check(lib.axm_ep_dispatch(lo, self.step, ptr(self.offsets), ptr(self.x_perm),
                                   ptr(self.scratch), ptr(self.status), stream))
         mark("dispatch (peer stores)")
-        check(lib.axm_ep_segments(lo, self.step, ptr(self.segments), ptr(self.ret_row0),
+        check(lib.axm_ep_segments(lo, self.step, ptr(self.segments), ptr(self.ret_segments),
                                   ptr(self.rows_received), ptr(self.status), stream))
         mark("wait rows + segments")
         st.expert_ffn(self.desc_ffn, self.recv, self.cap, x, self.Tl, self.segments, self.w, self.h,
                       self.o, self.rows_total, self.status)
         mark("expert GEMMs")
-        check(lib.axm_ep_return(lo, self.step, ptr(self.segments), ptr(self.ret_row0), ptr(self.o),
+        check(lib.axm_ep_return(lo, self.step, ptr(self.ret_segments), ptr(self.o),
                                 ptr(self.scratch), ptr(self.status), stream))
         mark("return (peer stores)")
         check(lib.axm_ep_wait_return(lo, self.step, ptr(self.status), stream))

@@ -81,8 +81,10 @@ def test_segment_table(workloads, axm):
 
     seg = Shell().build_segments(torch.tensor([[4, 0, 2], [1, 5, 0]], dtype=torch.int32))
     assert seg.dtype == torch.int32
-    assert seg[:6, 0].tolist() == [0, 4, 4, 6, 7, 12]
-    assert seg[:6, 2].tolist() == [4, 0, 2, 1, 5, 0]
-    assert seg[:6, 3].tolist() == [0, 1, 2, 0, 1, 2]
+    # rows arrive source-major: (s0,e0)=4 (s0,e1)=0 (s0,e2)=2 (s1,e0)=1 (s1,e1)=5 (s1,e2)=0;
+    # the table is expert-major
+    assert seg[:6, 0].tolist() == [0, 6, 4, 7, 4, 12]
+    assert seg[:6, 2].tolist() == [4, 1, 0, 5, 2, 0]
+    assert seg[:6, 3].tolist() == [0, 0, 1, 1, 2, 2]
     assert seg[6].tolist() == [0, 40, 10, 3 | axm.SEG_ALT_A]
     assert seg[7].tolist() == [0, 50, 10, 4 | axm.SEG_ALT_A]
