@@ -185,6 +185,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
+    ap.add_argument("--ep-return", default="fused", choices=["fused", "copy"],
+                    help="p2p transport: expert rows returned from the down GEMM's epilogue, or "
+                         "by a separate copy kernel")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "b200" else args.warmup
 
@@ -228,8 +231,11 @@ def main():
         x_local = x[rank * tl:(rank + 1) * tl].contiguous()
         wloc = ep.shard_weights(w, rank, world)
         del w
-        cls = ep.ExpertParallelMoeP2P if args.ep_transport == "p2p" else ep.ExpertParallelMoe
-        layer = cls(wloc, tl, cfg.num_experts, k)
+        if args.ep_transport == "p2p":
+            layer = ep.ExpertParallelMoeP2P(wloc, tl, cfg.num_experts, k,
+                                            fused_return=(args.ep_return == "fused"))
+        else:
+            layer = ep.ExpertParallelMoe(wloc, tl, cfg.num_experts, k)
         out = torch.empty_like(x_local)
         step = lambda: layer.forward(x_local, out)
         # router, permute, two GEMMs, combine (+ dispatch, segments, return, wait with p2p)
@@ -362,6 +368,8 @@ def main():
         if ep_stages is not None:
             line["stages_rank0"] = ep_stages
             line["config"]["ep_transport"] = args.ep_transport
+            if args.ep_transport == "p2p":
+                line["config"]["ep_return"] = args.ep_return
         if cpu is not None:
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)

@@ -190,6 +190,28 @@ AXM_API int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, int32
                                const void* shared_up, const void* shared_down, void* h,
                                void* o, int32_t rows_total, int32_t* status, void* stream);
 
+/* Per-segment redirect of the down projection's output: rows of segment s are
+ * stored at base + (row0 + i) * D floats instead of into `o` (base == NULL keeps
+ * the segment in `o`).  Under expert parallelism base is the source rank's return
+ * buffer in peer memory, so the expert outputs leave the GPU from the GEMM
+ * epilogue itself (plain stores over NVLink) and no separate return copy runs. */
+typedef struct AxmRemoteOut {
+  void* base;
+  int32_t row0;
+  int32_t reserved;
+} AxmRemoteOut;
+
+/* axm_moe_expert_ffn with the redirect table remote_out[num_segments] (device
+ * memory).  No reference counterpart. */
+AXM_API int axm_moe_expert_ffn_remote(const AxmMoeDesc* desc, const void* x_perm, int32_t a_rows,
+                                      const void* x_alt, int32_t alt_rows,
+                                      const AxmSegment* segments, int32_t num_segments,
+                                      const void* w_gate, const void* w_up, const void* w_down,
+                                      const void* shared_gate, const void* shared_up,
+                                      const void* shared_down, void* h, void* o,
+                                      int32_t rows_total, const AxmRemoteOut* remote_out,
+                                      int32_t* status, void* stream);
+
 /* Weighted combine over fp32 expert rows:
  * y[t] = bf16(sum_i gate[t,i] * o[slot_dst[t,i]] + sum_s o_shared[s][t]),
  * out[t] = bf16(x[t] + y[t]) with AXM_FLAG_RESIDUAL.  Replaces the gate-weighted
@@ -239,16 +261,23 @@ AXM_API int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const int3
  * followed by num_shared segments over the local tokens with output rows from
  * `cap` on; and `ret_segments` in arrival order for axm_ep_return
  * ({a_row0 = row in the source's return buffer, out_row0 = row here, rows,
- * expert = source rank}).  Also the number of rows received. */
+ * expert = source rank}).  If remote_out is not NULL it receives, in the order of
+ * `segments`, the redirect table that makes axm_moe_expert_ffn_remote store each
+ * segment straight into its source's return buffer.  Also the number of rows
+ * received. */
 AXM_API int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
-                            AxmSegment* ret_segments, int32_t* rows_received, int32_t* status,
-                            void* stream);
+                            AxmSegment* ret_segments, AxmRemoteOut* remote_out,
+                            int32_t* rows_received, int32_t* status, void* stream);
 
 /* Return: copies the fp32 expert rows `o` back into each source rank's return
  * buffer at the rows its own permutation expects, and flags the sources. */
 AXM_API int axm_ep_return(const AxmEpLayout* layout, uint32_t step,
                           const AxmSegment* ret_segments, const void* o, int32_t* scratch,
                           int32_t* status, void* stream);
+
+/* Fused return: after axm_moe_expert_ffn_remote has stored the rows itself, flags
+ * every source (replaces axm_ep_return). */
+AXM_API int axm_ep_signal_return(const AxmEpLayout* layout, uint32_t step, void* stream);
 
 /* Waits until every owner has returned this rank's rows (run before axm_moe_combine
  * on the return buffer). */

@@ -94,7 +94,10 @@ def load():
     lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
     lib.axm_ep_dispatch.argtypes = [lp, u32, vp, vp, vp, vp, vp]
-    lib.axm_ep_segments.argtypes = [lp, u32, vp, vp, vp, vp, vp]
+    lib.axm_ep_segments.argtypes = [lp, u32, vp, vp, vp, vp, vp, vp]
+    lib.axm_ep_signal_return.argtypes = [lp, u32, vp]
+    lib.axm_moe_expert_ffn_remote.argtypes = [dp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, vp,
+                                              vp, vp, i32, vp, vp, vp]
     lib.axm_ep_return.argtypes = [lp, u32, vp, vp, vp, vp, vp]
     lib.axm_ep_wait_return.argtypes = [lp, u32, vp, vp]
     lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]

@@ -155,7 +155,8 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
 //                 rows, expert = source rank}.
 __global__ void __launch_bounds__(kEpThreads)
 ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
-                   AxmSegment* __restrict__ ret_segments, int32_t* __restrict__ rows_received) {
+                   AxmSegment* __restrict__ ret_segments, AxmRemoteOut* __restrict__ remote_out,
+                   int32_t* __restrict__ rows_received) {
   __shared__ int rows_s[kEpMaxRanks * 64];
   __shared__ int start_s[kEpMaxRanks * 64];
   wait_all_sources(a, 1, 12);
@@ -180,6 +181,13 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
       sg.rows = a.T_local;
       sg.expert = (a.El + s) | AXM_SEG_ALT_A;
       segments[n + s] = sg;
+      if (remote_out != nullptr) {
+        AxmRemoteOut ro;
+        ro.base = nullptr;  // shared experts stay in the local output buffer
+        ro.row0 = 0;
+        ro.reserved = 0;
+        remote_out[n + s] = ro;
+      }
     }
   }
   __syncthreads();
@@ -199,6 +207,13 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
     rs.rows = rows_s[i];
     rs.expert = s;
     ret_segments[i] = rs;
+    if (remote_out != nullptr) {  // same order as `segments`
+      AxmRemoteOut ro;
+      ro.base = a.peers[s] + a.off_oback;
+      ro.row0 = before;
+      ro.reserved = 0;
+      remote_out[j * a.G + s] = ro;
+    }
   }
 }
 
@@ -244,6 +259,13 @@ ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
 }
 
 __global__ void ep_wait_return_kernel(EpArgs a) { wait_all_sources(a, 2, 13); }
+
+// After a down GEMM that stored its rows into the sources' return buffers itself:
+// the kernel boundary has made those stores visible; tell every source.
+__global__ void ep_signal_return_kernel(EpArgs a) {
+  __threadfence_system();
+  if ((int)threadIdx.x < a.G) store_release_sys(flag_ptr(a, threadIdx.x, 2, a.rank), a.step);
+}
 
 static int validate_ep(const AxmEpLayout* l) {
   if (l == nullptr || l->peers == nullptr) return fail(AXM_ERR_ARGUMENT, "exchange layout or peer table is null");
@@ -319,14 +341,14 @@ extern "C" int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const i
 }
 
 extern "C" int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
-                               AxmSegment* ret_segments, int32_t* rows_received, int32_t* status,
-                               void* stream) {
+                               AxmSegment* ret_segments, AxmRemoteOut* remote_out,
+                               int32_t* rows_received, int32_t* status, void* stream) {
   if (int rc = validate_ep(layout)) return rc;
   if (!segments || !ret_segments) return fail(AXM_ERR_ARGUMENT, "axm_ep_segments: null pointer");
   if (int rc = require_device()) return rc;
   EpArgs a = make_args(layout, step, status);
   ep_segments_kernel<<<1, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, segments, ret_segments,
-                                                                             rows_received);
+                                                                             remote_out, rows_received);
   return check_launch("ep_segments_kernel");
 }
 
@@ -340,6 +362,14 @@ extern "C" int axm_ep_return(const AxmEpLayout* layout, uint32_t step,
   ep_return_kernel<<<2 * sm_count(), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
       a, ret_segments, static_cast<const float*>(o), scratch + 1);
   return check_launch("ep_return_kernel");
+}
+
+extern "C" int axm_ep_signal_return(const AxmEpLayout* layout, uint32_t step, void* stream) {
+  if (int rc = validate_ep(layout)) return rc;
+  if (int rc = require_device()) return rc;
+  EpArgs a = make_args(layout, step, nullptr);
+  ep_signal_return_kernel<<<1, 64, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  return check_launch("ep_signal_return_kernel");
 }
 
 extern "C" int axm_ep_wait_return(const AxmEpLayout* layout, uint32_t step, int32_t* status,

@@ -68,6 +68,7 @@ struct GemmArgs {
   int k_total;        // reduction length: D (SwiGLU) or F (down)
   int routed_experts; // expert ids >= this address the shared-expert weights
   void* out;          // bf16 rows (SwiGLU) or fp32 rows (down)
+  const AxmRemoteOut* remote;  // down kernel only: per-segment output redirect, or null
   int* status;
   int dbg[4];         // B leading / stride offsets, B and A k-advance (16-byte units)
 };
@@ -290,7 +291,19 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const int row_in_seg = tc.m_tile * BM + quad * 32 + lane;
       const bool row_ok = row_in_seg < sg.rows;
       const int n0 = tc.n_tile * BN_OUT;
-      const size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+      size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+      void* out_base = args.out;
+      if constexpr (!kSwiGLU) {
+        // Fused return: this segment's rows go straight into another buffer (a
+        // peer GPU's return buffer under expert parallelism) with plain stores.
+        if (args.remote != nullptr) {
+          const AxmRemoteOut ro = args.remote[tc.seg];
+          if (ro.base != nullptr) {
+            out_base = ro.base;
+            out_elem = (size_t)(ro.row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+          }
+        }
+      }
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
@@ -310,7 +323,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             packed[j] = pack_bf16(h0, h1);
           }
           if (row_ok) {
-            __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(args.out) + out_elem;
+            __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(out_base) + out_elem;
 #pragma unroll
             for (int q = 0; q < 4; ++q)
               if (n0 + c0 + q * 8 < args.n_total)
@@ -320,7 +333,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         } else {
           tmem_ld_wait();
           if (row_ok) {
-            float* out_row = static_cast<float*>(args.out) + out_elem;
+            float* out_row = static_cast<float*>(out_base) + out_elem;
 #pragma unroll
             for (int q = 0; q < 8; ++q)
               if (n0 + c0 + q * 4 < args.n_total)
@@ -410,7 +423,7 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       const void* w_gate, const void* w_up, const void* w_down,
                       const void* shared_gate, const void* shared_up, const void* shared_down,
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                      cudaEvent_t between) {
+                      cudaEvent_t between, const AxmRemoteOut* remote) {
   if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
   CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;
@@ -446,6 +459,7 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.num_segments = num_segments;
   ga.routed_experts = E;
   ga.status = status;
+  ga.remote = nullptr;
   ga.dbg[0] = kBChunkBytes >> 4;
   ga.dbg[1] = 1024 >> 4;
   ga.dbg[2] = 128;
@@ -461,6 +475,7 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.n_total = D;
   ga.k_total = F;
   ga.out = o;
+  ga.remote = remote;
   grouped_gemm_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_kernel<down>");
 }
@@ -490,5 +505,26 @@ extern "C" int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, in
   if (int rc = require_device()) return rc;
   return launch_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate,
                            w_up, w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
-                           status, static_cast<cudaStream_t>(stream), nullptr);
+                           status, static_cast<cudaStream_t>(stream), nullptr, nullptr);
+}
+
+extern "C" int axm_moe_expert_ffn_remote(const AxmMoeDesc* desc, const void* x_perm, int32_t a_rows,
+                                         const void* x_alt, int32_t alt_rows,
+                                         const AxmSegment* segments, int32_t num_segments,
+                                         const void* w_gate, const void* w_up, const void* w_down,
+                                         const void* shared_gate, const void* shared_up,
+                                         const void* shared_down, void* h, void* o,
+                                         int32_t rows_total, const AxmRemoteOut* remote_out,
+                                         int32_t* status, void* stream) {
+  if (int rc = axm_moe_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, 0, w_gate, w_up,
+                                  w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
+                                  status, stream))
+    return rc;  // argument checks only: zero segments launch nothing
+  if (num_segments < 0 || num_segments > kMaxSegments)
+    return fail(AXM_ERR_ARGUMENT, "num_segments %d not in 0..%d", num_segments, kMaxSegments);
+  if (rows_total <= 0 || num_segments == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  return launch_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate,
+                           w_up, w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
+                           status, static_cast<cudaStream_t>(stream), nullptr, remote_out);
 }

@@ -184,8 +184,10 @@ class ExpertParallelMoeP2P:
     forward(x_local) -> out_local.  GPU only.
     """
 
-    def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, residual=True):
+    def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, residual=True,
+                 fused_return=True):
         import torch.distributed._symmetric_memory as symm_mem
+        self.fused_return = fused_return
         self.lib = load()
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -247,6 +249,7 @@ class ExpertParallelMoeP2P:
         self.scratch = torch.zeros(2, dtype=i32, device=dev)
         self.segments = torch.zeros(self.n_seg, 4, dtype=i32, device=dev)
         self.ret_segments = torch.zeros(self.world * self.El, 4, dtype=i32, device=dev)
+        self.remote_out = torch.zeros(self.n_seg, 2, dtype=torch.int64, device=dev)
         self.rows_received = torch.zeros(1, dtype=i32, device=dev)
         self.step = 0
 
@@ -276,14 +279,27 @@ class ExpertParallelMoeP2P:
                                   ptr(self.scratch), ptr(self.status), stream))
         mark("dispatch (peer stores)")
         check(lib.axm_ep_segments(lo, self.step, ptr(self.segments), ptr(self.ret_segments),
+                                  ptr(self.remote_out) if self.fused_return else None,
                                   ptr(self.rows_received), ptr(self.status), stream))
         mark("wait rows + segments")
-        st.expert_ffn(self.desc_ffn, self.recv, self.cap, x, self.Tl, self.segments, self.w, self.h,
-                      self.o, self.rows_total, self.status)
-        mark("expert GEMMs")
-        check(lib.axm_ep_return(lo, self.step, ptr(self.ret_segments), ptr(self.o),
-                                ptr(self.scratch), ptr(self.status), stream))
-        mark("return (peer stores)")
+        w, S = self.w, self.S
+        if self.fused_return:
+            # the down GEMM's epilogue stores each row into its source rank's return buffer
+            check(lib.axm_moe_expert_ffn_remote(
+                ctypes.byref(self.desc_ffn), ptr(self.recv), self.cap, ptr(x), self.Tl,
+                ptr(self.segments), self.n_seg, ptr(w["w_gate"]), ptr(w["w_up"]), ptr(w["w_down"]),
+                ptr(w["shared_gate"]) if S else None, ptr(w["shared_up"]) if S else None,
+                ptr(w["shared_down"]) if S else None, ptr(self.h), ptr(self.o), self.rows_total,
+                ptr(self.remote_out), ptr(self.status), stream))
+            mark("expert GEMMs (return fused)")
+            check(lib.axm_ep_signal_return(lo, self.step, stream))
+        else:
+            st.expert_ffn(self.desc_ffn, self.recv, self.cap, x, self.Tl, self.segments, self.w,
+                          self.h, self.o, self.rows_total, self.status)
+            mark("expert GEMMs")
+            check(lib.axm_ep_return(lo, self.step, ptr(self.ret_segments), ptr(self.o),
+                                    ptr(self.scratch), ptr(self.status), stream))
+            mark("return (peer stores)")
         check(lib.axm_ep_wait_return(lo, self.step, ptr(self.status), stream))
         o_shared = self.o[self.cap:] if self.S else None
         st.combine(self.desc_comb, x, self.o_back, o_shared, self.slot_dst, self.gate, self.y, out)

@@ -41,8 +41,12 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         x, w = wl.make_inputs(cfg)          # CPU generator: identical on every rank
         x, w = x.to(dev), {k: v.to(dev) for k, v in w.items()}
         tl = cfg.tokens // world
-        cls = ep.ExpertParallelMoeP2P if transport == "p2p" else ep.ExpertParallelMoe
-        layer = cls(ep.shard_weights(w, rank, world), tl, cfg.num_experts, cfg.top_k)
+        if transport == "nccl":
+            layer = ep.ExpertParallelMoe(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
+                                         cfg.top_k)
+        else:   # own peer-memory kernels; return fused into the down GEMM or as a copy kernel
+            layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
+                                            cfg.top_k, fused_return=(transport == "p2p"))
         out = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous()).clone()
         for _ in range(3):      # buffers and flags are reused call after call
             out2 = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
@@ -62,7 +66,7 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p"])
+@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-copy"])
 @pytest.mark.parametrize("name,tokens", [("C1", 64), ("C2", 1024), ("C4", 2048)])
 def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens, transport):
     world = min(torch.cuda.device_count(), 4) if name == "C4" else 2
