@@ -185,7 +185,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
-    ap.add_argument("--ep-return", default="fused", choices=["fused", "copy"],
+    ap.add_argument("--ep-return", default="copy", choices=["fused", "copy"],
                     help="p2p transport: expert rows returned from the down GEMM's epilogue, or "
                          "by a separate copy kernel")
     args = ap.parse_args()

@@ -182,10 +182,16 @@ class ExpertParallelMoeP2P:
     The exchange region is symmetric memory (torch.distributed._symmetric_memory):
     one allocation per rank, every rank holding the addresses of all of them.
     forward(x_local) -> out_local.  GPU only.
+
+    fused_return=True lets the down GEMM's epilogue store the expert rows into the
+    sources' buffers itself.  Measured on 8 B200s it is slower than the separate
+    copy kernel (the epilogue writes one 128-byte piece per lane, which NVLink
+    carries poorly; the copy kernel writes 512 contiguous bytes per warp), so the
+    copy kernel is the default.
     """
 
     def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, residual=True,
-                 fused_return=True):
+                 fused_return=False):
         import torch.distributed._symmetric_memory as symm_mem
         self.fused_return = fused_return
         self.lib = load()
