@@ -386,3 +386,171 @@ ORC_API void orc_moe_forward(const uint16_t* x, const uint16_t* wg, const uint16
   free(where);
   free(o_tmp);
 }
+
+/* ------------------------------------------------------------------ backward */
+
+/*
+ * Gradients of  L = sum(dY * out) + aux  with  out = x + y  (residual) and
+ * aux = alpha * E * sum_e f_e * P_e  (f_e treated as a constant, gradient through
+ * P_e = mean_t p[t,e] only).  No reference counterpart: the engine's backward pass
+ * covers the dense FFN only (core/src/CUDA/kernel/backward_pass.cu:1701-2005); the
+ * SiLU*mul derivative is the one of core/src/CUDA/kernel/swiglu.cu:34-55.
+ *
+ *   probs [T][E]: router probabilities of the forward pass
+ *   dY    [T][D] fp32 upstream gradient
+ *   act_bf16 != 0 rounds the tensors a GEMM pipeline stores as bf16 (g, u, h,
+ *   gate-scaled dY rows, dG, dU) at the points where it stores them.
+ * Outputs (all fp32, overwritten): dX [T][D], dWg/dWu [E][D][F], dWd [E][F][D],
+ * dWr [D][E], dgate [T][k], dlogits [T][E].  Any output pointer may be NULL.
+ */
+ORC_API void orc_moe_backward(const uint16_t* x, const void* wr, int wr_is_fp32,
+                              const uint16_t* wg, const uint16_t* wu, const uint16_t* wd,
+                              const int32_t* idx, const float* gates, const float* probs,
+                              const float* dY, int T, int D, int E, int k, int F, float alpha,
+                              int act_bf16, float* dX, float* dWg, float* dWu, float* dWd,
+                              float* dWr, float* dgate, float* dlogits) {
+  const size_t DF = (size_t)D * F;
+  if (dX) memcpy(dX, dY, sizeof(float) * (size_t)T * D); /* residual path */
+  if (dWg) memset(dWg, 0, sizeof(float) * (size_t)E * DF);
+  if (dWu) memset(dWu, 0, sizeof(float) * (size_t)E * DF);
+  if (dWd) memset(dWd, 0, sizeof(float) * (size_t)E * DF);
+  if (dWr) memset(dWr, 0, sizeof(float) * (size_t)D * E);
+  float* f_e = (float*)calloc((size_t)E, sizeof(float));
+  for (int64_t i = 0; i < (int64_t)T * k; ++i) f_e[idx[i]] += 1.0f / ((float)T * k);
+  float* dw_all = (float*)calloc((size_t)T * k, sizeof(float));
+  float* dx_slots = (float*)calloc((size_t)T * k * D, sizeof(float)); /* summed in slot order below */
+
+  /* experts one at a time so that the weight gradients need no atomics */
+#pragma omp parallel for schedule(dynamic, 1)
+  for (int e = 0; e < E; ++e) {
+    const uint16_t* Wg = wg + (size_t)e * DF;
+    const uint16_t* Wu = wu + (size_t)e * DF;
+    const uint16_t* Wd = wd + (size_t)e * DF;
+    float* g = (float*)malloc(sizeof(float) * F);
+    float* u = (float*)malloc(sizeof(float) * F);
+    float* h = (float*)malloc(sizeof(float) * F);
+    float* dh = (float*)malloc(sizeof(float) * F);
+    float* dg = (float*)malloc(sizeof(float) * F);
+    float* du = (float*)malloc(sizeof(float) * F);
+    float* dO = (float*)malloc(sizeof(float) * D);
+    float* o = (float*)malloc(sizeof(float) * D);
+    float* dx = (float*)malloc(sizeof(float) * D);
+    for (int t = 0; t < T; ++t)
+      for (int i = 0; i < k; ++i) {
+        if (idx[(size_t)t * k + i] != e) continue;
+        const uint16_t* xt = x + (size_t)t * D;
+        const float w = gates[(size_t)t * k + i];
+        /* forward recomputation */
+        for (int f = 0; f < F; ++f) g[f] = u[f] = 0.0f;
+        for (int d = 0; d < D; ++d) {
+          float xv = bf16_to_f32(xt[d]);
+          const uint16_t* a = Wg + (size_t)d * F;
+          const uint16_t* b = Wu + (size_t)d * F;
+          for (int f = 0; f < F; ++f) {
+            g[f] = fmaf(xv, bf16_to_f32(a[f]), g[f]);
+            u[f] = fmaf(xv, bf16_to_f32(b[f]), u[f]);
+          }
+        }
+        for (int f = 0; f < F; ++f) {
+          float hv = (g[f] / (1.0f + expf(-g[f]))) * u[f];
+          if (act_bf16) {
+            g[f] = round_bf16(g[f]);
+            u[f] = round_bf16(u[f]);
+            hv = round_bf16(hv);
+          }
+          h[f] = hv;
+        }
+        for (int d = 0; d < D; ++d) o[d] = 0.0f;
+        for (int f = 0; f < F; ++f) {
+          const uint16_t* c = Wd + (size_t)f * D;
+          for (int d = 0; d < D; ++d) o[d] = fmaf(h[f], bf16_to_f32(c[d]), o[d]);
+        }
+        /* gate gradient and the gate-scaled upstream rows */
+        float dw = 0.0f;
+        for (int d = 0; d < D; ++d) {
+          float dy = dY[(size_t)t * D + d];
+          dw = fmaf(dy, o[d], dw);
+          dO[d] = act_bf16 ? round_bf16(w * dy) : w * dy;
+        }
+        dw_all[(size_t)t * k + i] = dw;
+        /* dh = dO . Wd^T ; SwiGLU derivative */
+        for (int f = 0; f < F; ++f) {
+          const uint16_t* c = Wd + (size_t)f * D;
+          float acc = 0.0f;
+          for (int d = 0; d < D; ++d) acc = fmaf(dO[d], bf16_to_f32(c[d]), acc);
+          dh[f] = acc;
+          float s = 1.0f / (1.0f + expf(-g[f]));
+          float silu = g[f] * s;
+          float dgv = acc * u[f] * (s * (1.0f + g[f] * (1.0f - s)));
+          float duv = acc * silu;
+          dg[f] = act_bf16 ? round_bf16(dgv) : dgv;
+          du[f] = act_bf16 ? round_bf16(duv) : duv;
+        }
+        /* dx = dg . Wg^T + du . Wu^T */
+        for (int d = 0; d < D; ++d) {
+          const uint16_t* a = Wg + (size_t)d * F;
+          const uint16_t* b = Wu + (size_t)d * F;
+          float acc = 0.0f;
+          for (int f = 0; f < F; ++f) acc = fmaf(dg[f], bf16_to_f32(a[f]), acc);
+          for (int f = 0; f < F; ++f) acc = fmaf(du[f], bf16_to_f32(b[f]), acc);
+          dx[d] = acc;
+        }
+        memcpy(dx_slots + ((size_t)t * k + i) * D, dx, sizeof(float) * (size_t)D);
+        /* weight gradients */
+        if (dWd)
+          for (int f = 0; f < F; ++f) {
+            float* r = dWd + (size_t)e * DF + (size_t)f * D;
+            for (int d = 0; d < D; ++d) r[d] = fmaf(h[f], dO[d], r[d]);
+          }
+        if (dWg || dWu)
+          for (int d = 0; d < D; ++d) {
+            float xv = bf16_to_f32(xt[d]);
+            if (dWg) {
+              float* r = dWg + (size_t)e * DF + (size_t)d * F;
+              for (int f = 0; f < F; ++f) r[f] = fmaf(xv, dg[f], r[f]);
+            }
+            if (dWu) {
+              float* r = dWu + (size_t)e * DF + (size_t)d * F;
+              for (int f = 0; f < F; ++f) r[f] = fmaf(xv, du[f], r[f]);
+            }
+          }
+      }
+    free(g); free(u); free(h); free(dh); free(dg); free(du); free(dO); free(o); free(dx);
+  }
+  if (dgate) memcpy(dgate, dw_all, sizeof(float) * (size_t)T * k);
+  if (dX)
+    for (int t = 0; t < T; ++t)
+      for (int i = 0; i < k; ++i)
+        for (int d = 0; d < D; ++d) dX[(size_t)t * D + d] += dx_slots[((size_t)t * k + i) * D + d];
+  free(dx_slots);
+
+  /* router: gates -> probabilities -> logits -> router weights and x */
+  float* dp = (float*)malloc(sizeof(float) * E);
+  float* dz = (float*)malloc(sizeof(float) * E);
+  for (int t = 0; t < T; ++t) {
+    const float* p = probs + (size_t)t * E;
+    float sel = 0.0f, dot = 0.0f;
+    for (int i = 0; i < k; ++i) sel += p[idx[(size_t)t * k + i]];
+    float denom = sel + 1e-9f;
+    for (int i = 0; i < k; ++i) dot += dw_all[(size_t)t * k + i] * p[idx[(size_t)t * k + i]];
+    for (int e = 0; e < E; ++e) dp[e] = alpha * (float)E * f_e[e] / (float)T;
+    for (int i = 0; i < k; ++i)
+      dp[idx[(size_t)t * k + i]] += dw_all[(size_t)t * k + i] / denom - dot / (denom * denom);
+    float pd = 0.0f;
+    for (int e = 0; e < E; ++e) pd += p[e] * dp[e];
+    for (int e = 0; e < E; ++e) dz[e] = p[e] * (dp[e] - pd);
+    if (dlogits) memcpy(dlogits + (size_t)t * E, dz, sizeof(float) * E);
+    for (int d = 0; d < D; ++d) {
+      float xv = bf16_to_f32(x[(size_t)t * D + d]);
+      float acc = 0.0f;
+      for (int e = 0; e < E; ++e) {
+        float wv = wr_is_fp32 ? ((const float*)wr)[(size_t)d * E + e]
+                              : bf16_to_f32(((const uint16_t*)wr)[(size_t)d * E + e]);
+        acc = fmaf(wv, dz[e], acc);
+        if (dWr) dWr[(size_t)d * E + e] = fmaf(xv, dz[e], dWr[(size_t)d * E + e]);
+      }
+      if (dX) dX[(size_t)t * D + d] += acc;
+    }
+  }
+  free(dp); free(dz); free(f_e); free(dw_all);
+}

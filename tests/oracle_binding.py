@@ -31,6 +31,8 @@ class Oracle:
         lib.orc_aux_loss.argtypes = [vp, vp, i32, i32, i32, ctypes.c_float]
         lib.orc_aux_loss.restype = ctypes.c_float
         lib.orc_expert_ffn.argtypes = [vp, i32, i32, i32, vp, vp, vp, i32, vp]
+        lib.orc_moe_backward.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                         i32, ctypes.c_float, i32, vp, vp, vp, vp, vp, vp, vp]
         lib.orc_moe_forward.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp,
                                         vp, vp, i32, i32, i32, i32, vp, vp]
 
@@ -92,6 +94,30 @@ class Oracle:
                                     self._p(_bf16_np(wu)), self._p(_bf16_np(wd)), int(h_bf16),
                                     self._p(o))
         return o
+
+    def backward(self, x, w, idx, gates, probs, dY, alpha=0.0, act_bf16=False, weight_grads=True):
+        """Returns a dict of fp32 numpy gradients: dX, dWg, dWu, dWd, dWr, dgate, dlogits."""
+        T, D = x.shape
+        E, _, F = w["w_gate"].shape
+        k = idx.shape[1]
+        wr = w["router_w"]
+        is32 = wr.dtype == torch.float32
+        wn = wr.detach().cpu().contiguous().numpy() if is32 else _bf16_np(wr)
+        out = {"dX": np.empty((T, D), np.float32), "dWr": np.empty((D, E), np.float32),
+               "dgate": np.empty((T, k), np.float32), "dlogits": np.empty((T, E), np.float32)}
+        if weight_grads:
+            out.update({"dWg": np.empty((E, D, F), np.float32), "dWu": np.empty((E, D, F), np.float32),
+                        "dWd": np.empty((E, F, D), np.float32)})
+        g = lambda n: self._p(out[n]) if n in out else None
+        self.lib.orc_moe_backward(
+            self._p(_bf16_np(x)), self._p(wn), int(is32), self._p(_bf16_np(w["w_gate"])),
+            self._p(_bf16_np(w["w_up"])), self._p(_bf16_np(w["w_down"])),
+            self._p(np.ascontiguousarray(idx, dtype=np.int32)),
+            self._p(np.ascontiguousarray(gates, dtype=np.float32)),
+            self._p(np.ascontiguousarray(probs, dtype=np.float32)),
+            self._p(np.ascontiguousarray(dY, dtype=np.float32)), T, D, E, k, F, alpha, int(act_bf16),
+            g("dX"), g("dWg"), g("dWu"), g("dWd"), g("dWr"), g("dgate"), g("dlogits"))
+        return out
 
     def forward(self, x, w, idx, gates, h_bf16=False, o_bf16=False, tok_range=None):
         """Returns (y, out) as torch bf16 [T][D]; rows outside tok_range are zero."""
