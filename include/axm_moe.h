@@ -190,6 +190,25 @@ AXM_API int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, int32
                                const void* shared_up, const void* shared_down, void* h,
                                void* o, int32_t rows_total, int32_t* status, void* stream);
 
+/* Backward of the grouped expert FFN over a segment table whose segments are padded
+ * to multiples of 64 rows with zero rows (training layout; a_row0 == out_row0):
+ *   dH  = d_o . Wd[e]^T ; dG = dH * u * silu'(g), dU = dH * silu(g)   -> d_g, d_u bf16 [rows][F]
+ *   dXp = dG . Wg[e]^T + dU . Wu[e]^T                                  -> d_xp fp32 [rows][D]
+ *   dWd[e] = h^T d_o, dWg[e] = x_perm^T dG, dWu[e] = x_perm^T dU       -> fp32, weight layouts
+ * d_o is the gate-scaled upstream gradient per permuted row (bf16 [rows][D]); g, u, h
+ * are what the forward pass saved.  The three weight gradients may all be NULL.
+ * tcgen05 kernels.  No reference counterpart (the engine's backward covers the dense
+ * FFN only, core/src/CUDA/kernel/backward_pass.cu:1701-2005); gradients follow its
+ * conventions: fp32, same [in][out] layout as the weights (backward_pass.cu:1013-1048),
+ * SiLU*mul derivative of core/src/CUDA/kernel/swiglu.cu:34-55. */
+AXM_API int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegment* segments,
+                                        int32_t num_segments, int32_t rows_total,
+                                        const void* x_perm, const void* h, const void* g,
+                                        const void* u, const void* d_o, const void* w_gate,
+                                        const void* w_up, const void* w_down, void* d_g, void* d_u,
+                                        void* d_xp, void* d_w_gate, void* d_w_up, void* d_w_down,
+                                        int32_t* status, void* stream);
+
 /* Per-segment redirect of the down projection's output: rows of segment s are
  * stored at base + (row0 + i) * D floats instead of into `o` (base == NULL keeps
  * the segment in `o`).  Under expert parallelism base is the source rank's return

@@ -91,6 +91,7 @@ def load():
     lib.axm_moe_expert_ffn.argtypes = [dp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp,
                                        vp, i32, vp, vp]
     lib.axm_moe_combine.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.axm_moe_expert_ffn_backward.argtypes = [dp, vp, i32, i32] + [vp] * 16
     lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
     lib.axm_ep_dispatch.argtypes = [lp, u32, vp, vp, vp, vp, vp]

@@ -16,7 +16,7 @@ LIB = os.path.join(HERE, "libaxm_moe.so")
 DROPIN = os.path.join(HERE, "libaxm_moe_dropin.so")
 
 CORE_SOURCES = ["moe_api.cu", "router.cu", "permute.cu", "grouped_ffn.cu", "noalloc.cu",
-                "ep_exchange.cu"]
+                "ep_exchange.cu", "grouped_bwd.cu"]
 DROPIN_SOURCES = ["dropin.cu"]
 
 NVCC_FLAGS = [
@@ -38,8 +38,8 @@ def _stale(target, sources):
     if not os.path.exists(target):
         return True
     t = os.path.getmtime(target)
-    deps = list(sources) + [os.path.join(CSRC, "common.cuh"),
-                            os.path.join(HERE, "..", "include", "axm_moe.h"), __file__]
+    headers = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith(".cuh")]
+    deps = list(sources) + headers + [os.path.join(HERE, "..", "include", "axm_moe.h"), __file__]
     return any(os.path.getmtime(s) > t for s in deps)
 
 

@@ -28,38 +28,9 @@
 #include <cstdlib>
 #include <mutex>
 
-#include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace axm {
-
-constexpr int BM = 128;             // rows per tile
-constexpr int BK = 64;              // reduction elements per stage (128 bytes of bf16)
-constexpr int UMMA_N = 256;         // accumulator columns per tile
-constexpr int UMMA_K = 16;
-constexpr int kStages = 4;
-constexpr int kABytes = BM * BK * 2;          // 16 KiB
-constexpr int kBChunkBytes = 64 * BK * 2;     // 64 output columns x 64 k: 8 KiB
-constexpr int kBBytes = 4 * kBChunkBytes;     // 32 KiB
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kMaxSegments = 512;
-constexpr int kGemmThreads = 192;
-constexpr int kTmemCols = 512;
-
-struct __align__(8) GemmShared {
-  uint64_t full[kStages];
-  uint64_t empty[kStages];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
-  uint32_t tmem_base;
-  int abort_flag;
-  int total_tiles;
-  int tile_prefix[kMaxSegments + 1];  // m-tiles before segment s
-  int num_groups;                     // runs of consecutive segments with one expert
-  int group_first[kMaxSegments + 1];  // first segment of group g
-  AxmSegment seg[kMaxSegments];
-};
-
-constexpr size_t kGemmSmemBytes = 1024 /*alignment slack*/ + (size_t)kStages * kStageBytes + sizeof(GemmShared);
 
 struct GemmArgs {
   const AxmSegment* segments;
@@ -69,62 +40,18 @@ struct GemmArgs {
   int routed_experts; // expert ids >= this address the shared-expert weights
   void* out;          // bf16 rows (SwiGLU) or fp32 rows (down)
   const AxmRemoteOut* remote;  // down kernel only: per-segment output redirect, or null
+  __nv_bfloat16* save_g;  // SwiGLU kernel, training: also store the gate and up
+  __nv_bfloat16* save_u;  // pre-activations (bf16, same shape as h), or null
   int* status;
   int dbg[4];         // B leading / stride offsets, B and A k-advance (16-byte units)
 };
 
-// Shared-memory matrix descriptor (sm_100 format): start address, leading and
-// stride byte offsets in 16-byte units, descriptor version 1, 128-byte swizzle.
-__device__ __forceinline__ uint64_t make_smem_desc(uint32_t smem_addr, uint32_t lbo_bytes,
-                                                   uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3fffu);
-  d |= (uint64_t)((lbo_bytes >> 4) & 0x3fffu) << 16;
-  d |= (uint64_t)((sbo_bytes >> 4) & 0x3fffu) << 32;
-  d |= (uint64_t)1 << 46;  // version
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
-  return d;
-}
 
 // Instruction descriptor: fp32 accumulate, bf16 A and B, A K-major, B MN-major,
 // N = 256, M = 128.
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
                                 ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
 
-struct TileCoord {
-  int seg;
-  int m_tile;
-  int n_tile;
-};
-
-// Tiles are ordered group by group, where a group is a run of consecutive
-// segments that use the same expert (one segment on a single GPU; one per source
-// rank under expert parallelism).  Inside a group the order is n-tile major and
-// m-tile minor over ALL the group's m-tiles, so CTAs that run together share a
-// weight column block and each weight tile is fetched from HBM about once.
-__device__ __forceinline__ TileCoord decode_tile(const GemmShared* sh, int num_segments,
-                                                 int n_tiles, int linear) {
-  int lo = 0, hi = sh->num_groups - 1;
-  while (lo < hi) {  // largest g whose first tile is <= linear
-    int mid = (lo + hi + 1) >> 1;
-    if (sh->tile_prefix[sh->group_first[mid]] * n_tiles <= linear) lo = mid; else hi = mid - 1;
-  }
-  const int s0 = sh->group_first[lo], s1 = sh->group_first[lo + 1];
-  const int base = sh->tile_prefix[s0];
-  const int mt = sh->tile_prefix[s1] - base;
-  const int local = linear - base * n_tiles;
-  TileCoord tc;
-  tc.n_tile = local / mt;
-  const int m_idx = base + (local - tc.n_tile * mt);
-  int a = s0, b = s1 - 1;
-  while (a < b) {  // largest s in the group with tile_prefix[s] <= m_idx
-    int mid = (a + b + 1) >> 1;
-    if (sh->tile_prefix[mid] <= m_idx) a = mid; else b = mid - 1;
-  }
-  tc.seg = a;
-  tc.m_tile = m_idx - sh->tile_prefix[a];
-  return tc;
-}
 
 template <bool kSwiGLU>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -329,6 +256,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               if (n0 + c0 + q * 8 < args.n_total)
                 *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
                     make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            if (args.save_g != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (n0 + c0 + q * 8 < args.n_total) {
+                  uint4 gv, uv;
+                  gv.x = pack_bf16(__uint_as_float(g[8 * q + 0]), __uint_as_float(g[8 * q + 1]));
+                  gv.y = pack_bf16(__uint_as_float(g[8 * q + 2]), __uint_as_float(g[8 * q + 3]));
+                  gv.z = pack_bf16(__uint_as_float(g[8 * q + 4]), __uint_as_float(g[8 * q + 5]));
+                  gv.w = pack_bf16(__uint_as_float(g[8 * q + 6]), __uint_as_float(g[8 * q + 7]));
+                  uv.x = pack_bf16(__uint_as_float(u[8 * q + 0]), __uint_as_float(u[8 * q + 1]));
+                  uv.y = pack_bf16(__uint_as_float(u[8 * q + 2]), __uint_as_float(u[8 * q + 3]));
+                  uv.z = pack_bf16(__uint_as_float(u[8 * q + 4]), __uint_as_float(u[8 * q + 5]));
+                  uv.w = pack_bf16(__uint_as_float(u[8 * q + 6]), __uint_as_float(u[8 * q + 7]));
+                  *reinterpret_cast<uint4*>(args.save_g + out_elem + c0 + q * 8) = gv;
+                  *reinterpret_cast<uint4*>(args.save_u + out_elem + c0 + q * 8) = uv;
+                }
+            }
           }
         } else {
           tmem_ld_wait();
@@ -388,6 +332,23 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+int encode_tensor_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box) {
+  if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
+  cuuint64_t d[3], st[2];
+  cuuint32_t b[3], es[3] = {1, 1, 1};
+  for (int i = 0; i < rank; ++i) {
+    d[i] = dims[i];
+    b[i] = box[i];
+    if (i + 1 < rank) st[i] = strides_bytes[i];
+  }
+  CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base),
+                           d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(AXM_ERR_ARGUMENT, "cuTensorMapEncodeTiled(rank %d) failed: %d", rank, (int)r);
+  return AXM_OK;
+}
+
 // Row-major bf16 matrix [rows][cols]; box = 64 columns x box_rows rows.
 static int make_map_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
                        uint32_t box_rows) {
@@ -423,7 +384,7 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       const void* w_gate, const void* w_up, const void* w_down,
                       const void* shared_gate, const void* shared_up, const void* shared_down,
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                      cudaEvent_t between, const AxmRemoteOut* remote) {
+                      cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u) {
   if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
   CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;
@@ -460,6 +421,8 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.routed_experts = E;
   ga.status = status;
   ga.remote = nullptr;
+  ga.save_g = static_cast<__nv_bfloat16*>(save_g);
+  ga.save_u = static_cast<__nv_bfloat16*>(save_u);
   ga.dbg[0] = kBChunkBytes >> 4;
   ga.dbg[1] = 1024 >> 4;
   ga.dbg[2] = 128;
@@ -476,6 +439,8 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.k_total = F;
   ga.out = o;
   ga.remote = remote;
+  ga.save_g = nullptr;
+  ga.save_u = nullptr;
   grouped_gemm_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_kernel<down>");
 }
@@ -505,7 +470,7 @@ extern "C" int axm_moe_expert_ffn(const AxmMoeDesc* desc, const void* x_perm, in
   if (int rc = require_device()) return rc;
   return launch_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate,
                            w_up, w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
-                           status, static_cast<cudaStream_t>(stream), nullptr, nullptr);
+                           status, static_cast<cudaStream_t>(stream), nullptr, nullptr, nullptr, nullptr);
 }
 
 extern "C" int axm_moe_expert_ffn_remote(const AxmMoeDesc* desc, const void* x_perm, int32_t a_rows,
@@ -526,5 +491,5 @@ extern "C" int axm_moe_expert_ffn_remote(const AxmMoeDesc* desc, const void* x_p
   if (int rc = require_device()) return rc;
   return launch_expert_ffn(desc, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate,
                            w_up, w_down, shared_gate, shared_up, shared_down, h, o, rows_total,
-                           status, static_cast<cudaStream_t>(stream), nullptr, remote_out);
+                           status, static_cast<cudaStream_t>(stream), nullptr, remote_out, nullptr, nullptr);
 }

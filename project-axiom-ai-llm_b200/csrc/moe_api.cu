@@ -86,7 +86,7 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       const void* w_gate, const void* w_up, const void* w_down,
                       const void* shared_gate, const void* shared_up, const void* shared_down,
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                      cudaEvent_t between, const AxmRemoteOut* remote);
+                      cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u);
 
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
@@ -215,7 +215,7 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
   if (ev) cudaEventRecord(ev[2], st);
   rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
                          t->w_down, t->shared_gate, t->shared_up, t->shared_down, w.h, w.o,
-                         T * k + T * S, w.status, st, ev ? ev[3] : nullptr, nullptr);
+                         T * k + T * S, w.status, st, ev ? ev[3] : nullptr, nullptr, nullptr, nullptr);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[4], st);
   const float* o_shared =
