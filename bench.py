@@ -218,7 +218,18 @@ def main():
     x, w = wl.make_inputs(cfg, device=dev)  # same seed on every rank -> same tensors
     launches_per_step = 0
 
-    if world == 1:
+    training = cfg.training
+    if training and world > 1:
+        raise SystemExit("the training step (C5) is single-GPU in this build")
+    if training:
+        # forward (saving activations) + auxiliary loss + backward with all weight gradients
+        layer = axm.MoeTrainLayer(w, T, k, aux_alpha=cfg.aux_alpha)
+        x_local = x
+        d_out = torch.randn(T, D, device=dev, generator=torch.Generator(device=dev).manual_seed(cfg.seed))
+        out = layer.out
+        step = lambda: layer.step(x_local, d_out)
+        launches_per_step = 17
+    elif world == 1:
         layer = axm.MoeLayer(w, T, k, publish_y=False)
         out = torch.empty_like(x)
         x_local = x
@@ -273,7 +284,19 @@ def main():
     h_x = x_local.cpu().pin_memory()
     h_out = torch.empty_like(h_x).pin_memory()
     d_x = torch.empty_like(x_local)
-    if world == 1:
+    if training:
+        h_dy = d_out.cpu().pin_memory()
+        h_dx = torch.empty_like(h_dy).pin_memory()
+        d_dy = torch.empty_like(d_out)
+
+        def e2e_step():
+            d_x.copy_(h_x, non_blocking=True)
+            d_dy.copy_(h_dy, non_blocking=True)
+            layer.step(d_x, d_dy)
+            h_out.copy_(layer.out, non_blocking=True)
+            h_dx.copy_(layer.d_x, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+    elif world == 1:
         e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out)
     else:
         def e2e_step():
@@ -297,11 +320,24 @@ def main():
     e2e_ms /= args.steps
     clocks = sampler.stop() if rank == 0 else None
     copy_bytes = h_x.numel() * 2 * world
+    h2d_bytes = copy_bytes + (h_dy.numel() * 4 if training else 0)
+    d2h_bytes = copy_bytes + (h_dx.numel() * 4 if training else 0)
 
     # ---- roofline of the dominant kernel (gate/up grouped GEMM) ---------------------
     roofline = None
     stages = None
-    if world == 1:
+    if training:
+        # nine grouped tensor-core GEMMs per step: 6TkDF forward, 12TkDF backward
+        fl = 3.0 * cfg.gemm_flops
+        tf = fl / (ms_step * 1e-3) / 1e12
+        roofline = {"kernel": "all grouped GEMMs of the training step (whole-step time)",
+                    "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                    "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
+                    "traffic": None}
+        status = int(layer.workspace[:4].view(torch.int32).item())
+        if status != 0:
+            raise SystemExit(f"a GEMM kernel reported a timed-out wait (status {status})")
+    elif world == 1:
         acc = [0.0] * 5
         reps = 10
         for _ in range(reps):
@@ -344,7 +380,7 @@ def main():
         ep_stages["rows_received_rank0"] = layer.last_rows_received
 
     cpu = None
-    if world == 1 and rank == 0 and not args.no_cpu_baseline:
+    if world == 1 and rank == 0 and not args.no_cpu_baseline and not training:
         cpu = cpu_baseline(cfg, x_local, layer.w, args.cpu_tokens)
 
     if rank == 0:
@@ -356,14 +392,18 @@ def main():
             "config": workload_config(cfg, world, "inputs larger than L2 (expert weights "
                                       f"{cfg.weight_bytes / world / 1e9:.2f} GB per GPU); no flush"),
             "e2e": {"value": T / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
-                    "h2d_bytes_per_step": copy_bytes, "d2h_bytes_per_step": copy_bytes},
+                    "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches_per_step * args.steps * world,
             "clocks": clocks,
-            "gemm_tflops_layer": cfg.gemm_flops / (ms_step * 1e-3) / 1e12,
-            "gemm_frac_of_peak_layer": cfg.gemm_flops / (ms_step * 1e-3) / 1e12 / (peaks["bf16_tflops"] * world),
+            "gemm_tflops_layer": (3 if training else 1) * cfg.gemm_flops / (ms_step * 1e-3) / 1e12,
+            "gemm_frac_of_peak_layer": (3 if training else 1) * cfg.gemm_flops / (ms_step * 1e-3) / 1e12
+                                       / (peaks["bf16_tflops"] * world),
         }
+        if training:
+            line["metric"] = "MoE-layer training step tokens/s (forward + backward)"
         if roofline is not None:
             line["roofline"] = roofline
+        if stages is not None:
             line["stages"] = stages
         if ep_stages is not None:
             line["stages_rank0"] = ep_stages

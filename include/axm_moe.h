@@ -159,6 +159,19 @@ AXM_API int axm_moe_permute(const AxmMoeDesc* desc, const void* x, const int32_t
                             const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
                             int32_t* row_src, int32_t* slot_dst, void* x_perm, void* stream);
 
+struct AxmSegment;
+/* axm_moe_permute in the training layout: every expert's rows start at a multiple
+ * of row_align (64 for the backward kernels); the rows between an expert's last
+ * row and the next expert's first are zero in x_perm and have row_src = -1.
+ * offsets[e] is the padded start, offsets[E] the padded total (<= T*k +
+ * (row_align - 1) * E); the histogram still holds the true counts.  `segments`
+ * ([E], optional) receives one segment per expert with the padded row count. */
+AXM_API int axm_moe_permute_padded(const AxmMoeDesc* desc, const void* x, const int32_t* topk_idx,
+                                   const int32_t* block_counts, int32_t* histogram,
+                                   int32_t* offsets, int32_t* row_src, int32_t* slot_dst,
+                                   void* x_perm, struct AxmSegment* segments, int32_t row_align,
+                                   void* stream);
+
 /* One segment of rows that share an expert, for the grouped GEMMs.  Expert ids
  * >= E address the shared experts. */
 typedef struct AxmSegment {
@@ -208,6 +221,43 @@ AXM_API int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegment
                                         const void* w_up, const void* w_down, void* d_g, void* d_u,
                                         void* d_xp, void* d_w_gate, void* d_w_up, void* d_w_down,
                                         int32_t* status, void* stream);
+
+/* ---- training step -------------------------------------------------------------
+ * No reference counterpart: the engine's MoE branch is forward only, its backward
+ * pass covers the dense FFN (core/src/CUDA/kernel/backward_pass.cu:1701-2005) and a
+ * load-balancing loss is future work there (document/AI_CONTEXT.md:217).
+ *   L = sum(d_out * out) + aux,  out = x + MoE(x),
+ *   aux = aux_alpha * E * sum_e f_e * P_e  (f_e = share of the T*k selections that
+ *   went to expert e, a constant; P_e = mean over tokens of the router probability).
+ * axm_moe_forward_train runs the forward pass, keeps the activations the backward
+ * needs in the workspace (training layout: experts padded to 64 rows) and writes
+ * the auxiliary loss; axm_moe_backward must follow with the same desc, tensors and
+ * workspace.  Gradients are fp32 in the layouts of what they belong to; they are
+ * overwritten, not accumulated.  Shared experts are not supported here. */
+typedef struct AxmMoeTrain {
+  const void* x;            /* [T][D] bf16 */
+  const void* router_w;     /* [D][E] bf16 or fp32 */
+  const float* router_bias; /* [E] or NULL */
+  const void* w_gate;       /* [E][D][F] bf16 */
+  const void* w_up;         /* [E][D][F] bf16 */
+  const void* w_down;       /* [E][F][D] bf16 */
+  void* out;                /* [T][D] bf16 (forward) */
+  float* aux_loss;          /* device scalar, optional (forward) */
+  int32_t* histogram;       /* [E] this call's counts, optional (forward) */
+  float aux_alpha;
+  const float* d_out;       /* [T][D] fp32 upstream gradient (backward) */
+  float* d_x;               /* [T][D] fp32 */
+  float* d_router_w;        /* [D][E] fp32, optional */
+  float* d_w_gate;          /* [E][D][F] fp32; the three expert gradients together or none */
+  float* d_w_up;            /* [E][D][F] fp32 */
+  float* d_w_down;          /* [E][F][D] fp32 */
+} AxmMoeTrain;
+
+AXM_API int axm_moe_train_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes);
+AXM_API int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* tensors,
+                                  void* workspace, size_t workspace_bytes, void* stream);
+AXM_API int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* tensors, void* workspace,
+                             size_t workspace_bytes, void* stream);
 
 /* Per-segment redirect of the down projection's output: rows of segment s are
  * stored at base + (row0 + i) * D floats instead of into `o` (base == NULL keeps

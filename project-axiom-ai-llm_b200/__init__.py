@@ -57,6 +57,14 @@ class EpLayout(ctypes.Structure):
                 [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")])
 
 
+class MoeTrain(ctypes.Structure):
+    _fields_ = ([(n, ctypes.c_void_p) for n in ("x", "router_w", "router_bias", "w_gate", "w_up",
+                                                "w_down", "out", "aux_loss", "histogram")] +
+                [("aux_alpha", ctypes.c_float)] +
+                [(n, ctypes.c_void_p) for n in ("d_out", "d_x", "d_router_w", "d_w_gate", "d_w_up",
+                                                "d_w_down")])
+
+
 class Segment(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("a_row0", "out_row0", "rows", "expert")]
 
@@ -91,6 +99,11 @@ def load():
     lib.axm_moe_expert_ffn.argtypes = [dp, vp, i32, vp, i32, vp, i32, vp, vp, vp, vp, vp, vp, vp,
                                        vp, i32, vp, vp]
     lib.axm_moe_combine.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    tp = ctypes.POINTER(MoeTrain)
+    lib.axm_moe_train_workspace_bytes.argtypes = [dp, ctypes.POINTER(sz)]
+    lib.axm_moe_forward_train.argtypes = [dp, tp, vp, sz, vp]
+    lib.axm_moe_backward.argtypes = [dp, tp, vp, sz, vp]
+    lib.axm_moe_permute_padded.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]
     lib.axm_moe_expert_ffn_backward.argtypes = [dp, vp, i32, i32] + [vp] * 16
     lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
@@ -213,3 +226,66 @@ class MoeLayer:
         off = p.value - self.workspace.data_ptr()
         torch.cuda.synchronize()
         return int(self.workspace[off:off + 4].view(torch.int32).item())
+
+
+class MoeTrainLayer:
+    """Forward + backward of one MoE layer (training step).  step(x, d_out) returns
+    (out, aux_loss, grads) with grads = dict(d_x, d_router_w, d_w_gate, d_w_up, d_w_down)."""
+
+    def __init__(self, weights, tokens, top_k, aux_alpha=0.01, device="cuda", weight_grads=True):
+        self.lib = load()
+        self.w = weights
+        wr = weights["router_w"]
+        D, E = wr.shape
+        F = weights["w_gate"].shape[2]
+        rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
+        self.desc = make_desc(tokens, D, F, E, top_k, 0, rdt, FLAG_RESIDUAL)
+        dev = torch.device(device)
+        n = ctypes.c_size_t(0)
+        check(self.lib.axm_moe_train_workspace_bytes(ctypes.byref(self.desc), ctypes.byref(n)))
+        self.workspace = torch.empty(n.value, dtype=torch.uint8, device=dev)
+        f32 = torch.float32
+        self.out = torch.empty(tokens, D, dtype=torch.bfloat16, device=dev)
+        self.aux = torch.zeros(1, dtype=f32, device=dev)
+        self.histogram = torch.zeros(E, dtype=torch.int32, device=dev)
+        self.d_x = torch.empty(tokens, D, dtype=f32, device=dev)
+        self.d_router_w = torch.empty(D, E, dtype=f32, device=dev)
+        self.weight_grads = weight_grads
+        if weight_grads:
+            self.d_w_gate = torch.empty(E, D, F, dtype=f32, device=dev)
+            self.d_w_up = torch.empty(E, D, F, dtype=f32, device=dev)
+            self.d_w_down = torch.empty(E, F, D, dtype=f32, device=dev)
+        self.aux_alpha = aux_alpha
+
+    def tensors(self, x, d_out):
+        w = self.w
+        g = self.weight_grads
+        return MoeTrain(
+            x.data_ptr(), w["router_w"].data_ptr(),
+            None if w.get("router_bias") is None else w["router_bias"].data_ptr(),
+            w["w_gate"].data_ptr(), w["w_up"].data_ptr(), w["w_down"].data_ptr(),
+            self.out.data_ptr(), self.aux.data_ptr(), self.histogram.data_ptr(), self.aux_alpha,
+            None if d_out is None else d_out.data_ptr(), self.d_x.data_ptr(),
+            self.d_router_w.data_ptr(), self.d_w_gate.data_ptr() if g else None,
+            self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None)
+
+    def forward(self, x):
+        t = self.tensors(x, None)
+        check(self.lib.axm_moe_forward_train(ctypes.byref(self.desc), ctypes.byref(t),
+                                             ptr(self.workspace), self.workspace.numel(),
+                                             current_stream()))
+        return self.out
+
+    def backward(self, x, d_out):
+        t = self.tensors(x, d_out)
+        check(self.lib.axm_moe_backward(ctypes.byref(self.desc), ctypes.byref(t), ptr(self.workspace),
+                                        self.workspace.numel(), current_stream()))
+        return self.d_x
+
+    def step(self, x, d_out):
+        self.forward(x)
+        self.backward(x, d_out)
+        grads = {"d_x": self.d_x, "d_router_w": self.d_router_w}
+        if self.weight_grads:
+            grads.update(d_w_gate=self.d_w_gate, d_w_up=self.d_w_up, d_w_down=self.d_w_down)
+        return self.out, self.aux, grads

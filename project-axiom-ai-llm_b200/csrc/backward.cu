@@ -1,0 +1,416 @@
+// Training step of the MoE layer: forward pass that keeps what the backward pass
+// needs, Switch-style load-balancing loss, and the backward pass (upstream
+// gradient -> dX, router and expert weight gradients).
+//
+// The reference engine has neither (its MoE branch is forward only and its backward
+// pass handles the dense FFN, core/src/CUDA/kernel/backward_pass.cu:1701-2005; an
+// auxiliary loss is listed as future work in document/AI_CONTEXT.md:217).  The maths
+// follows the layer's forward conventions (core/src/CUDA/kernel/moe_router.cu:59-105
+// for softmax / gates) and the engine's dense-backward conventions: fp32 weight
+// gradients in the weights' layout (backward_pass.cu:1013-1048) and the SiLU*mul
+// derivative of core/src/CUDA/kernel/swiglu.cu:34-55.  Unlike the dense backward no
+// gradient is clamped and bf16 weights (not fp32 masters) feed the input gradients.
+//
+//   L = sum(dOut * out) + aux,  out = x + y,  aux = alpha * E * sum_e f_e * P_e,
+//   f_e = count_e / (T k) (constant), P_e = mean_t p[t, e].
+#include "common.cuh"
+
+namespace axm {
+
+__host__ __device__ inline int train_block_begin(int b, int T) {
+  return (int)(((long long)b * T) / AXM_ROUTE_BLOCKS);
+}
+
+// p = softmax(z) with the forward pass's operation order; returns the row maximum's sum etc. in place.
+__device__ __forceinline__ void softmax_row(const float* __restrict__ z, float* p, int E) {
+  float m = z[0];
+  for (int e = 1; e < E; ++e) m = z[e] > m ? z[e] : m;
+  float s = 0.0f;
+  for (int e = 0; e < E; ++e) {
+    p[e] = expf(z[e] - m);
+    s += p[e];
+  }
+  const float inv = 1.0f / (s + 1e-9f);
+  for (int e = 0; e < E; ++e) p[e] *= inv;
+}
+
+// Stage 1 of the auxiliary loss: per token block, column sums of the probabilities.
+// One thread per token keeps its row in shared memory; fixed summation order.
+constexpr int kAuxThreads = 128;
+__global__ void __launch_bounds__(kAuxThreads)
+aux_partial_kernel(const float* __restrict__ logits, float* __restrict__ partial, int T, int E) {
+  extern __shared__ float sm[];  // [kAuxThreads][E + 1]
+  const int EP = E + 1;
+  const int t0 = train_block_begin(blockIdx.x, T), t1 = train_block_begin(blockIdx.x + 1, T);
+  float* mine = sm + threadIdx.x * EP;
+  for (int e = threadIdx.x; e < E; e += kAuxThreads) partial[(size_t)blockIdx.x * E + e] = 0.0f;
+  __syncthreads();
+  for (int ts = t0; ts < t1; ts += kAuxThreads) {
+    const int t = ts + threadIdx.x;
+    if (t < t1) softmax_row(logits + (size_t)t * E, mine, E);
+    __syncthreads();
+    const int nt = min(kAuxThreads, t1 - ts);
+    for (int e = threadIdx.x; e < E; e += kAuxThreads) {
+      float acc = partial[(size_t)blockIdx.x * E + e];
+      for (int i = 0; i < nt; ++i) acc += sm[i * EP + e];
+      partial[(size_t)blockIdx.x * E + e] = acc;
+    }
+    __syncthreads();
+  }
+}
+
+// Stage 2: P_e, f_e, the loss, and the per-expert constant alpha * E * f_e / T that the
+// router backward adds to every dp[t, e].
+__global__ void aux_final_kernel(const float* __restrict__ partial, const int32_t* __restrict__ counts,
+                                 float* __restrict__ aux_coef, float* __restrict__ aux_loss, int T,
+                                 int E, int k, float alpha) {
+  __shared__ float term[256];
+  const int e = threadIdx.x;
+  float v = 0.0f;
+  if (e < E) {
+    float P = 0.0f;
+    for (int b = 0; b < AXM_ROUTE_BLOCKS; ++b) P += partial[(size_t)b * E + e];
+    P /= (float)T;
+    const float f = (float)counts[e] / ((float)T * (float)k);
+    v = f * P;
+    aux_coef[e] = alpha * (float)E * f / (float)T;
+  }
+  term[threadIdx.x] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float acc = 0.0f;
+    for (int i = 0; i < E; ++i) acc += term[i];
+    if (aux_loss != nullptr) *aux_loss = alpha * (float)E * acc;
+  }
+}
+
+// One warp per permuted row r: the gate-scaled upstream gradient row (bf16, zero for
+// padding rows) and the gate gradient dgate[slot] = <dOut[t], o[r]>.
+__global__ void __launch_bounds__(256)
+bwd_prepare_kernel(const float* __restrict__ d_out, const float* __restrict__ o,
+                   const int32_t* __restrict__ row_src, const float* __restrict__ gate,
+                   const int32_t* __restrict__ offsets, __nv_bfloat16* __restrict__ d_o,
+                   float* __restrict__ d_gate, int D, int E, int k) {
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int rows = offsets[E];
+  for (int r = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); r < rows; r += warps) {
+    const int slot = row_src[r];
+    uint2* dst = reinterpret_cast<uint2*>(d_o + (size_t)r * D);
+    if (slot < 0) {
+      for (int c = lane; c < D / 4; c += 32) dst[c] = make_uint2(0u, 0u);
+      continue;
+    }
+    const int t = slot / k;
+    const float w = gate[slot];
+    const float4* dy = reinterpret_cast<const float4*>(d_out + (size_t)t * D);
+    const float4* orow = reinterpret_cast<const float4*>(o + (size_t)r * D);
+    float dot = 0.0f;
+    for (int c = lane; c < D / 4; c += 32) {
+      const float4 a = __ldg(dy + c), b = __ldg(orow + c);
+      dot = fmaf(a.x, b.x, dot);
+      dot = fmaf(a.y, b.y, dot);
+      dot = fmaf(a.z, b.z, dot);
+      dot = fmaf(a.w, b.w, dot);
+      dst[c] = make_uint2(pack_bf16(w * a.x, w * a.y), pack_bf16(w * a.z, w * a.w));
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+    if (lane == 0) d_gate[slot] = dot;
+  }
+}
+
+// One thread per token: gate gradients -> probability gradients (through the
+// renormalisation over the selected experts, plus the auxiliary-loss term) ->
+// logit gradients through the softmax.  dz[t, e] = p_e * (dp_e - sum_j p_j dp_j).
+constexpr int kRbThreads = 128;
+__global__ void __launch_bounds__(kRbThreads)
+router_bwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ topk_idx,
+                  const float* __restrict__ d_gate, const float* __restrict__ aux_coef,
+                  float* __restrict__ dz, int T, int E, int k) {
+  extern __shared__ float sm[];  // [kRbThreads][2][E + 1]
+  const int EP = E + 1;
+  float* p = sm + threadIdx.x * 2 * EP;
+  float* dp = p + EP;
+  const int t = blockIdx.x * kRbThreads + threadIdx.x;
+  if (t >= T) return;
+  softmax_row(logits + (size_t)t * E, p, E);
+  float sel = 0.0f, dot = 0.0f;
+  for (int i = 0; i < k; ++i) sel += p[topk_idx[(size_t)t * k + i]];
+  const float denom = sel + 1e-9f;
+  for (int i = 0; i < k; ++i) dot += d_gate[(size_t)t * k + i] * p[topk_idx[(size_t)t * k + i]];
+  for (int e = 0; e < E; ++e) dp[e] = aux_coef[e];
+  for (int i = 0; i < k; ++i)
+    dp[topk_idx[(size_t)t * k + i]] += d_gate[(size_t)t * k + i] / denom - dot / (denom * denom);
+  float pd = 0.0f;
+  for (int e = 0; e < E; ++e) pd += p[e] * dp[e];
+  for (int e = 0; e < E; ++e) dz[(size_t)t * E + e] = p[e] * (dp[e] - pd);
+}
+
+// dWr[d, e] = sum_t x[t, d] * dz[t, e].  grid (ceil(D / 128), chunks): a thread owns one d
+// and sums its chunk of tokens in order into partial[chunk][d][e]; dwr_reduce adds the
+// chunks in order.  Deterministic.
+constexpr int kDwrChunks = 32;
+template <int EC>
+__global__ void __launch_bounds__(128)
+dwr_partial_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dz,
+                   float* __restrict__ partial, int T, int D, int E) {
+  const int d = blockIdx.x * 128 + threadIdx.x;
+  const int c = blockIdx.y;
+  const int t0 = (int)(((long long)c * T) / kDwrChunks), t1 = (int)(((long long)(c + 1) * T) / kDwrChunks);
+  for (int e0 = 0; e0 < E; e0 += EC) {
+    float acc[EC];
+#pragma unroll
+    for (int j = 0; j < EC; ++j) acc[j] = 0.0f;
+    if (d < D)
+      for (int t = t0; t < t1; ++t) {
+        const float xv = __bfloat162float(x[(size_t)t * D + d]);
+        const float* z = dz + (size_t)t * E + e0;
+#pragma unroll
+        for (int j = 0; j < EC; ++j)
+          if (e0 + j < E) acc[j] = fmaf(xv, __ldg(z + j), acc[j]);
+      }
+    if (d < D)
+#pragma unroll
+      for (int j = 0; j < EC; ++j)
+        if (e0 + j < E) partial[((size_t)c * D + d) * E + e0 + j] = acc[j];
+  }
+}
+
+__global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_wr, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float acc = 0.0f;
+  for (int c = 0; c < kDwrChunks; ++c) acc += partial[(size_t)c * n + i];
+  d_wr[i] = acc;
+}
+
+// dX[t, d] = dOut[t, d] (residual) + sum_i dXp[slot_dst[t, i], d] + sum_e Wr[d, e] * dz[t, e].
+template <typename WT>
+__global__ void __launch_bounds__(256)
+bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d_xp,
+                    const int32_t* __restrict__ slot_dst, const WT* __restrict__ wr,
+                    const float* __restrict__ dz, float* __restrict__ d_x, int T, int D, int E, int k,
+                    int residual) {
+  const int chunks = D / 4;
+  const long long total = (long long)T * chunks;
+  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
+       g += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(g / chunks);
+    const int c = (int)(g - (long long)t * chunks);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (residual) acc = __ldg(reinterpret_cast<const float4*>(d_out + (size_t)t * D) + c);
+    for (int i = 0; i < k; ++i) {
+      const int r = __ldg(slot_dst + (size_t)t * k + i);
+      const float4 v = __ldg(reinterpret_cast<const float4*>(d_xp + (size_t)r * D) + c);
+      acc.x += v.x;
+      acc.y += v.y;
+      acc.z += v.z;
+      acc.w += v.w;
+    }
+    float rx = 0.f, ry = 0.f, rz = 0.f, rw = 0.f;
+    const float* z = dz + (size_t)t * E;
+    const WT* w0 = wr + (size_t)(4 * c) * E;
+    for (int e = 0; e < E; ++e) {
+      const float zv = __ldg(z + e);
+      rx = fmaf((float)w0[e], zv, rx);
+      ry = fmaf((float)w0[E + e], zv, ry);
+      rz = fmaf((float)w0[2 * E + e], zv, rz);
+      rw = fmaf((float)w0[3 * E + e], zv, rw);
+    }
+    acc.x += rx;
+    acc.y += ry;
+    acc.z += rz;
+    acc.w += rw;
+    reinterpret_cast<float4*>(d_x + (size_t)t * D)[c] = acc;
+  }
+}
+
+int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
+                   const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                   int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
+                   int32_t* status, cudaStream_t st, int row_align);
+int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
+                      int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
+                      const void* w_gate, const void* w_up, const void* w_down,
+                      const void* shared_gate, const void* shared_up, const void* shared_down,
+                      void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
+                      cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u);
+
+constexpr int kTrainAlign = 64;
+
+struct TrainWs {
+  int32_t* status;
+  float* logits;
+  int32_t* topk_idx;
+  float* topk_gate;
+  int32_t* block_counts;
+  int32_t* counts;
+  int32_t* offsets;
+  int32_t* row_src;
+  int32_t* slot_dst;
+  AxmSegment* segments;
+  float* aux_partial;
+  float* aux_coef;
+  float* d_gate;
+  float* dz;
+  float* dwr_partial;
+  void *x_perm, *g, *u, *h, *o, *d_o, *d_g, *d_u, *d_xp;
+  int rows_max;
+  size_t bytes;
+};
+
+static TrainWs carve_train(const AxmMoeDesc* d, void* base) {
+  TrainWs w;
+  size_t off = 0;
+  auto take = [&](size_t n) {
+    void* p = base ? static_cast<char*>(base) + off : nullptr;
+    off += (n + 255) & ~static_cast<size_t>(255);
+    return p;
+  };
+  const size_t T = d->tokens, D = d->d_model, F = d->d_ff, E = d->num_experts, k = d->top_k;
+  const size_t R = (T * k + (kTrainAlign - 1) * E + kTrainAlign - 1) / kTrainAlign * kTrainAlign;
+  w.rows_max = (int)R;
+  w.status = static_cast<int32_t*>(take(4));
+  w.logits = static_cast<float*>(take(4 * T * E));
+  w.topk_idx = static_cast<int32_t*>(take(4 * T * k));
+  w.topk_gate = static_cast<float*>(take(4 * T * k));
+  w.block_counts = static_cast<int32_t*>(take(4 * AXM_ROUTE_BLOCKS * E));
+  w.counts = static_cast<int32_t*>(take(4 * E));
+  w.offsets = static_cast<int32_t*>(take(4 * (E + 1)));
+  w.row_src = static_cast<int32_t*>(take(4 * R));
+  w.slot_dst = static_cast<int32_t*>(take(4 * T * k));
+  w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * E));
+  w.aux_partial = static_cast<float*>(take(4 * AXM_ROUTE_BLOCKS * E));
+  w.aux_coef = static_cast<float*>(take(4 * E));
+  w.d_gate = static_cast<float*>(take(4 * T * k));
+  w.dz = static_cast<float*>(take(4 * T * E));
+  w.dwr_partial = static_cast<float*>(take(4 * (size_t)kDwrChunks * D * E));
+  w.x_perm = take(2 * R * D);
+  w.g = take(2 * R * F);
+  w.u = take(2 * R * F);
+  w.h = take(2 * R * F);
+  w.o = take(4 * R * D);
+  w.d_o = take(2 * R * D);
+  w.d_g = take(2 * R * F);
+  w.d_u = take(2 * R * F);
+  w.d_xp = take(4 * R * D);
+  w.bytes = off;
+  return w;
+}
+
+static int validate_train(const AxmMoeDesc* d) {
+  if (d == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
+  if (d->tokens <= 0) return fail(AXM_ERR_ARGUMENT, "tokens %d must be positive", d->tokens);
+  if (d->d_model <= 0 || d->d_ff <= 0 || d->d_model % 8 || d->d_ff % 8)
+    return fail(AXM_ERR_ARGUMENT, "d_model %d and d_ff %d must be positive multiples of 8", d->d_model, d->d_ff);
+  if (d->num_experts <= 0 || d->num_experts > 256)
+    return fail(AXM_ERR_ARGUMENT, "num_experts %d not in 1..256", d->num_experts);
+  if (d->top_k <= 0 || d->top_k > 8 || d->top_k > d->num_experts)
+    return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..min(num_experts, 8)", d->top_k);
+  if (d->num_shared != 0) return fail(AXM_ERR_ARGUMENT, "the training step does not take shared experts");
+  if (d->router_dtype != AXM_ROUTER_BF16 && d->router_dtype != AXM_ROUTER_FP32)
+    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", d->router_dtype);
+  if ((long long)d->tokens * d->top_k + 64LL * d->num_experts > 0x7fffffffLL)
+    return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
+  return AXM_OK;
+}
+
+static int check_ws(const AxmMoeDesc* d, void* ws, size_t bytes, TrainWs* out) {
+  if (ws == nullptr || (reinterpret_cast<uintptr_t>(ws) & 255) != 0)
+    return fail(AXM_ERR_WORKSPACE, "workspace is null or not 256-byte aligned");
+  *out = carve_train(d, ws);
+  if (bytes < out->bytes) return fail(AXM_ERR_WORKSPACE, "workspace has %zu bytes, %zu needed", bytes, out->bytes);
+  return AXM_OK;
+}
+
+}  // namespace axm
+
+using namespace axm;
+
+extern "C" int axm_moe_train_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes) {
+  if (int rc = validate_train(desc)) return rc;
+  if (bytes == nullptr) return fail(AXM_ERR_ARGUMENT, "bytes is null");
+  *bytes = carve_train(desc, nullptr).bytes;
+  return AXM_OK;
+}
+
+extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* t, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+  if (int rc = validate_train(desc)) return rc;
+  if (!t || !t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->out)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_train: x, router_w, w_gate, w_up, w_down, out are required");
+  TrainWs w;
+  if (int rc = check_ws(desc, workspace, workspace_bytes, &w)) return rc;
+  if (int rc = require_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int T = desc->tokens, E = desc->num_experts, k = desc->top_k;
+  AxmMoeDesc d = *desc;
+  d.flags &= ~AXM_FLAG_HIST_ACCUMULATE;  // ws.counts holds this call's counts
+  int rc = axm_moe_router(&d, t->x, t->router_w, t->router_bias, w.logits, w.topk_idx, w.topk_gate,
+                          w.block_counts, stream);
+  if (rc) return rc;
+  if ((rc = launch_permute(&d, t->x, w.topk_idx, w.block_counts, w.counts, w.offsets, w.row_src,
+                           w.slot_dst, w.x_perm, w.segments, w.status, st, kTrainAlign)))
+    return rc;
+  if ((rc = launch_expert_ffn(&d, w.x_perm, w.rows_max, nullptr, 0, w.segments, E, t->w_gate, t->w_up,
+                              t->w_down, nullptr, nullptr, nullptr, w.h, w.o, w.rows_max, w.status, st,
+                              nullptr, nullptr, w.g, w.u)))
+    return rc;
+  if ((rc = axm_moe_combine(desc, t->x, w.o, nullptr, w.slot_dst, w.topk_gate, nullptr, t->out, stream)))
+    return rc;
+  // auxiliary loss and the constants its gradient needs
+  const size_t sm = sizeof(float) * kAuxThreads * (E + 1);
+  cudaFuncSetAttribute(aux_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  aux_partial_kernel<<<AXM_ROUTE_BLOCKS, kAuxThreads, sm, st>>>(w.logits, w.aux_partial, T, E);
+  aux_final_kernel<<<1, 256, 0, st>>>(w.aux_partial, w.counts, w.aux_coef, t->aux_loss, T, E, k,
+                                      t->aux_alpha);
+  if (t->histogram != nullptr)
+    cudaMemcpyAsync(t->histogram, w.counts, sizeof(int32_t) * E, cudaMemcpyDeviceToDevice, st);
+  return check_launch("forward_train");
+}
+
+extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, void* workspace,
+                                size_t workspace_bytes, void* stream) {
+  if (int rc = validate_train(desc)) return rc;
+  if (!t || !t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->d_out || !t->d_x)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_backward: x, weights, d_out and d_x are required");
+  TrainWs w;
+  if (int rc = check_ws(desc, workspace, workspace_bytes, &w)) return rc;
+  if (int rc = require_device()) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
+  const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
+
+  bwd_prepare_kernel<<<4 * sm_count(), 256, 0, st>>>(t->d_out, static_cast<const float*>(w.o), w.row_src,
+                                                     w.topk_gate, w.offsets,
+                                                     static_cast<__nv_bfloat16*>(w.d_o), w.d_gate, D, E, k);
+  int rc = check_launch("bwd_prepare_kernel");
+  if (rc) return rc;
+  if ((rc = axm_moe_expert_ffn_backward(desc, w.segments, E, w.rows_max, w.x_perm, w.h, w.g, w.u, w.d_o,
+                                        t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.d_xp,
+                                        t->d_w_gate, t->d_w_up, t->d_w_down, w.status, stream)))
+    return rc;
+  const size_t sm = sizeof(float) * kRbThreads * 2 * (E + 1);
+  cudaFuncSetAttribute(router_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  router_bwd_kernel<<<(T + kRbThreads - 1) / kRbThreads, kRbThreads, sm, st>>>(
+      w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, T, E, k);
+  if (t->d_router_w != nullptr) {
+    dim3 grid((D + 127) / 128, kDwrChunks);
+    dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), w.dz,
+                                                 w.dwr_partial, T, D, E);
+    dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(w.dwr_partial, t->d_router_w, D * E);
+  }
+  long long total = (long long)T * (D / 4);
+  int blocks = (int)((total + 255) / 256);
+  if (blocks > 16 * sm_count()) blocks = 16 * sm_count();
+  if (desc->router_dtype == AXM_ROUTER_FP32)
+    bwd_finalize_kernel<float><<<blocks, 256, 0, st>>>(t->d_out, static_cast<const float*>(w.d_xp),
+                                                       w.slot_dst, static_cast<const float*>(t->router_w),
+                                                       w.dz, t->d_x, T, D, E, k, residual);
+  else
+    bwd_finalize_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
+        t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
+        static_cast<const __nv_bfloat16*>(t->router_w), w.dz, t->d_x, T, D, E, k, residual);
+  return check_launch("backward");
+}

@@ -80,7 +80,7 @@ int sm_count() { return device_info().sms > 0 ? device_info().sms : 148; }
 int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
                    const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
                    int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
-                   int32_t* status, cudaStream_t st);
+                   int32_t* status, cudaStream_t st, int row_align);
 int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
                       int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
                       const void* w_gate, const void* w_up, const void* w_down,
@@ -210,7 +210,7 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[1], st);
   rc = launch_permute(desc, t->x, idx, w.block_counts, t->histogram, offsets, row_src, slot_dst,
-                      w.x_perm, w.segments, w.status, st);
+                      w.x_perm, w.segments, w.status, st, 1);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[2], st);
   rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,

@@ -29,7 +29,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
                int32_t* __restrict__ offsets, int32_t* __restrict__ row_src,
                int32_t* __restrict__ slot_dst, __nv_bfloat16* __restrict__ x_perm,
                AxmSegment* __restrict__ segments, int32_t* __restrict__ status, int T, int D,
-               int E, int k, int S, int hist_accumulate) {
+               int E, int k, int S, int hist_accumulate, int row_align) {
   __shared__ int total_s[kMaxE];
   __shared__ int run_s[kMaxE];   // next free row per expert for this block
   __shared__ int scan_s[kMaxE + 1];
@@ -59,7 +59,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
     int carry = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
       int e = e0 + lane;
-      int v = e < E ? total_s[e] : 0;
+      // training layout: every expert's rows start at a multiple of row_align
+      int v = e < E ? (total_s[e] + row_align - 1) / row_align * row_align : 0;
       int incl = v;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
@@ -85,7 +86,7 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
         if (e < E) {
           sg.a_row0 = scan_s[e];
           sg.out_row0 = scan_s[e];
-          sg.rows = total_s[e];
+          sg.rows = scan_s[e + 1] - scan_s[e];  // padded rows (equal to the count when row_align is 1)
           sg.expert = e;
         } else {
           sg.a_row0 = 0;
@@ -97,6 +98,17 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
       }
     }
     if (status != nullptr && tid == 0) *status = 0;
+  }
+  // Padding rows (row_align > 1) are zero rows that belong to no slot: block e fills expert e's.
+  if (row_align > 1 && b < E) {
+    const int pad0 = scan_s[b] + total_s[b], pad1 = scan_s[b + 1];
+    const int chunks = D / 8;
+    for (int r = pad0; r < pad1; ++r) {
+      if (row_src != nullptr && tid == 0) row_src[r] = -1;
+      if (x_perm != nullptr)
+        for (int c = tid; c < chunks; c += kPermThreads)
+          reinterpret_cast<uint4*>(x_perm + (size_t)r * D)[c] = make_uint4(0, 0, 0, 0);
+    }
   }
   __syncthreads();
 
@@ -267,11 +279,12 @@ static void launch_combine(int blocks, cudaStream_t st, const void* x, const voi
 int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
                    const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
                    int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
-                   int32_t* status, cudaStream_t st) {
+                   int32_t* status, cudaStream_t st, int row_align) {
   permute_kernel<<<AXM_ROUTE_BLOCKS, kPermThreads, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), topk_idx, block_counts, histogram, offsets, row_src,
       slot_dst, static_cast<__nv_bfloat16*>(x_perm), segments, status, d->tokens, d->d_model,
-      d->num_experts, d->top_k, d->num_shared, (d->flags & AXM_FLAG_HIST_ACCUMULATE) ? 1 : 0);
+      d->num_experts, d->top_k, d->num_shared, (d->flags & AXM_FLAG_HIST_ACCUMULATE) ? 1 : 0,
+      row_align < 1 ? 1 : row_align);
   return check_launch("permute_kernel");
 }
 
@@ -300,7 +313,21 @@ extern "C" int axm_moe_permute(const AxmMoeDesc* desc, const void* x, const int3
   if (x_perm != nullptr && x == nullptr) return fail(AXM_ERR_ARGUMENT, "axm_moe_permute: x_perm without x");
   if (int rc = require_device()) return rc;
   return launch_permute(desc, x, topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
-                        x_perm, nullptr, nullptr, static_cast<cudaStream_t>(stream));
+                        x_perm, nullptr, nullptr, static_cast<cudaStream_t>(stream), 1);
+}
+
+extern "C" int axm_moe_permute_padded(const AxmMoeDesc* desc, const void* x, const int32_t* topk_idx,
+                                      const int32_t* block_counts, int32_t* histogram,
+                                      int32_t* offsets, int32_t* row_src, int32_t* slot_dst,
+                                      void* x_perm, AxmSegment* segments, int32_t row_align,
+                                      void* stream) {
+  if (int rc = validate_perm(desc)) return rc;
+  if (!topk_idx || !block_counts) return fail(AXM_ERR_ARGUMENT, "axm_moe_permute_padded: null pointer");
+  if (x_perm != nullptr && x == nullptr) return fail(AXM_ERR_ARGUMENT, "axm_moe_permute_padded: x_perm without x");
+  if (row_align < 1 || row_align > 1024) return fail(AXM_ERR_ARGUMENT, "row_align %d not in 1..1024", row_align);
+  if (int rc = require_device()) return rc;
+  return launch_permute(desc, x, topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
+                        x_perm, segments, nullptr, static_cast<cudaStream_t>(stream), row_align);
 }
 
 extern "C" int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* offsets,

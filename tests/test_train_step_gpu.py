@@ -1,0 +1,89 @@
+"""Training step (forward + backward + auxiliary loss) through the C ABI against the
+CPU oracle's backward pass on the same routing.  Floating point; every gradient
+tensor is checked element-wise with |err| <= 2e-2 * |ref| + 1e-2 * max|ref|
+against the oracle with fp32 intermediates, and with half that bound against the
+oracle rounding g, u, h, dO, dG, dU to bf16 where this pipeline stores them."""
+import numpy as np
+import pytest
+import torch
+
+import helpers
+
+pytestmark = pytest.mark.gpu
+
+
+def close(got, ref, what, factor=1.0):
+    g = got.float().cpu().numpy() if torch.is_tensor(got) else got
+    err = np.abs(g - ref)
+    bound = factor * (2e-2 * np.abs(ref) + 1e-2 * np.abs(ref).max())
+    bad = err > bound
+    assert not bad.any(), (f"{what}: {int(bad.sum())} of {bad.size} outside the bound, max err "
+                           f"{err.max():.4g}, max |ref| {np.abs(ref).max():.4g}")
+
+
+@pytest.mark.parametrize("name,kw", [
+    ("C1", dict(tokens=96, num_experts=8)),
+    ("C5", dict(tokens=256, d_model=512, d_ff=1024)),
+    ("C5", dict(tokens=192)),                       # C5's d_model 2048, d_ff 4096, E 16
+    ("C1", dict(tokens=70, d_model=72, d_ff=200, num_experts=5, top_k=3)),
+])
+@pytest.mark.parametrize("router_bf16", [False, True])
+def test_train_step_matches_oracle(axm, workloads, oracle, cuda_device, name, kw, router_bf16):
+    cfg = workloads.scaled(workloads.CONFIGS[name], **kw)
+    if router_bf16 and cfg.d_model > 1024:
+        pytest.skip("bf16 router covered on the smaller shapes")
+    alpha = 0.01
+    x, w = workloads.make_inputs(cfg, router_bf16=router_bf16)
+    dY = torch.randn(cfg.tokens, cfg.d_model, generator=torch.Generator().manual_seed(cfg.seed + 100))
+    wd = helpers.to_dev(w, cuda_device)
+    layer = axm.MoeTrainLayer(wd, cfg.tokens, cfg.top_k, aux_alpha=alpha)
+    xd, dYd = x.to(cuda_device), dY.to(cuda_device)
+    out, aux, grads = layer.step(xd, dYd)
+    torch.cuda.synchronize()
+
+    # the routing the GPU used, recovered through the oracle from the GPU's logits
+    z = oracle.router_logits(x, w["router_w"])
+    desc = helpers.desc_for(axm, cfg, axm.ROUTER_BF16 if router_bf16 else axm.ROUTER_FP32)
+    logits, idx_d, gate_d, _ = helpers.run_router(axm, desc, xd, wd["router_w"])
+    zl = logits.cpu().numpy()
+    assert (np.abs(zl - z) <= 1e-4 * np.maximum(1.0, np.abs(z))).all()
+    idx, gates = idx_d.cpu().numpy(), gate_d.cpu().numpy()
+    _, _, probs, counts, _ = oracle.route(zl, cfg.top_k)
+    assert (layer.histogram.cpu().numpy() == np.bincount(idx.ravel(), minlength=cfg.num_experts)).all()
+
+    # forward output and auxiliary loss
+    y_ref, out_ref = oracle.forward(x, w, idx, gates, h_bf16=True)
+    helpers.assert_close_out(out, out_ref, y_ref, what="training forward out")
+    aux_ref = oracle.aux_loss(probs, idx, alpha)
+    assert abs(float(aux.item()) - aux_ref) <= 1e-5 * max(1.0, abs(aux_ref))
+
+    names = {"d_x": "dX", "d_router_w": "dWr", "d_w_gate": "dWg", "d_w_up": "dWu", "d_w_down": "dWd"}
+    ref32 = oracle.backward(x, w, idx, gates, probs, dY.numpy(), alpha=alpha)
+    refbf = oracle.backward(x, w, idx, gates, probs, dY.numpy(), alpha=alpha, act_bf16=True)
+    for gname, oname in names.items():
+        got = grads[gname]
+        if gname == "d_x":   # compare the part that went through the layer, not the residual copy
+            got = got.cpu() - dY
+            r32, rbf = ref32[oname] - dY.numpy(), refbf[oname] - dY.numpy()
+        else:
+            r32, rbf = ref32[oname], refbf[oname]
+        close(got, r32, f"{oname} vs oracle (fp32 intermediates)")
+        close(got, rbf, f"{oname} vs oracle (bf16 rounding points)", factor=0.5)
+
+
+def test_train_step_is_deterministic_and_matches_inference_forward(axm, workloads, cuda_device):
+    cfg = workloads.scaled(workloads.CONFIGS["C5"], tokens=1024)
+    x, w = workloads.make_inputs(cfg, device=cuda_device)
+    dY = torch.randn(cfg.tokens, cfg.d_model, device=cuda_device)
+    layer = axm.MoeTrainLayer(w, cfg.tokens, cfg.top_k)
+    out1, aux1, g1 = layer.step(x, dY)
+    keep = {k: v.clone() for k, v in g1.items()}
+    out1 = out1.clone()
+    out2, aux2, g2 = layer.step(x, dY)
+    assert torch.equal(out1, out2)
+    for k in keep:
+        assert torch.equal(keep[k], g2[k]), k
+    inf = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+    out3, _ = inf.forward(x)
+    assert torch.equal(out3, out1)          # padded layout, same arithmetic per row
+    assert torch.isfinite(keep["d_x"]).all() and torch.isfinite(keep["d_w_down"]).all()
