@@ -150,7 +150,7 @@ router_bwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ 
 // dWr[d, e] = sum_t x[t, d] * dz[t, e].  grid (ceil(D / 128), chunks): a thread owns one d
 // and sums its chunk of tokens in order into partial[chunk][d][e]; dwr_reduce adds the
 // chunks in order.  Deterministic.
-constexpr int kDwrChunks = 32;
+constexpr int kDwrChunks = 128;
 template <int EC>
 __global__ void __launch_bounds__(128)
 dwr_partial_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dz,
@@ -186,18 +186,28 @@ __global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __re
 }
 
 // dX[t, d] = dOut[t, d] (residual) + sum_i dXp[slot_dst[t, i], d] + sum_e Wr[d, e] * dz[t, e].
+// grid (D / d_tile, token chunks); a thread owns 4 consecutive d.  The block's slice of the
+// router weights sits in shared memory as [E][d_tile] (conflict-free float4 reads); dz[t, :]
+// is the same address for the whole block (broadcast).
 template <typename WT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(128)
 bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d_xp,
                     const int32_t* __restrict__ slot_dst, const WT* __restrict__ wr,
                     const float* __restrict__ dz, float* __restrict__ d_x, int T, int D, int E, int k,
-                    int residual) {
-  const int chunks = D / 4;
-  const long long total = (long long)T * chunks;
-  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
-       g += (long long)gridDim.x * blockDim.x) {
-    const int t = (int)(g / chunks);
-    const int c = (int)(g - (long long)t * chunks);
+                    int residual, int d_tile) {
+  extern __shared__ __align__(16) float w_s[];  // [E][d_tile]
+  const int d0 = blockIdx.x * d_tile;
+  for (int i = threadIdx.x; i < E * d_tile; i += blockDim.x) {
+    const int dd = i / E, e = i - dd * E;  // read rows of Wr contiguously
+    w_s[e * d_tile + dd] = d0 + dd < D ? (float)wr[(size_t)(d0 + dd) * E + e] : 0.0f;
+  }
+  __syncthreads();
+  const int dl = threadIdx.x * 4;
+  if (dl >= d_tile || d0 + dl >= D) return;
+  const int c = (d0 + dl) / 4;
+  const int t0 = (int)(((long long)blockIdx.y * T) / gridDim.y);
+  const int t1 = (int)(((long long)(blockIdx.y + 1) * T) / gridDim.y);
+  for (int t = t0; t < t1; ++t) {
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
     if (residual) acc = __ldg(reinterpret_cast<const float4*>(d_out + (size_t)t * D) + c);
     for (int i = 0; i < k; ++i) {
@@ -208,20 +218,20 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
       acc.z += v.z;
       acc.w += v.w;
     }
-    float rx = 0.f, ry = 0.f, rz = 0.f, rw = 0.f;
+    float4 rt = make_float4(0.f, 0.f, 0.f, 0.f);
     const float* z = dz + (size_t)t * E;
-    const WT* w0 = wr + (size_t)(4 * c) * E;
     for (int e = 0; e < E; ++e) {
       const float zv = __ldg(z + e);
-      rx = fmaf((float)w0[e], zv, rx);
-      ry = fmaf((float)w0[E + e], zv, ry);
-      rz = fmaf((float)w0[2 * E + e], zv, rz);
-      rw = fmaf((float)w0[3 * E + e], zv, rw);
+      const float4 wv = *reinterpret_cast<const float4*>(w_s + e * d_tile + dl);
+      rt.x = fmaf(wv.x, zv, rt.x);
+      rt.y = fmaf(wv.y, zv, rt.y);
+      rt.z = fmaf(wv.z, zv, rt.z);
+      rt.w = fmaf(wv.w, zv, rt.w);
     }
-    acc.x += rx;
-    acc.y += ry;
-    acc.z += rz;
-    acc.w += rw;
+    acc.x += rt.x;
+    acc.y += rt.y;
+    acc.z += rt.z;
+    acc.w += rt.w;
     reinterpret_cast<float4*>(d_x + (size_t)t * D)[c] = acc;
   }
 }
@@ -401,16 +411,23 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
                                                  w.dwr_partial, T, D, E);
     dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(w.dwr_partial, t->d_router_w, D * E);
   }
-  long long total = (long long)T * (D / 4);
-  int blocks = (int)((total + 255) / 256);
-  if (blocks > 16 * sm_count()) blocks = 16 * sm_count();
-  if (desc->router_dtype == AXM_ROUTER_FP32)
-    bwd_finalize_kernel<float><<<blocks, 256, 0, st>>>(t->d_out, static_cast<const float*>(w.d_xp),
-                                                       w.slot_dst, static_cast<const float*>(t->router_w),
-                                                       w.dz, t->d_x, T, D, E, k, residual);
-  else
-    bwd_finalize_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>(
-        t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
-        static_cast<const __nv_bfloat16*>(t->router_w), w.dz, t->d_x, T, D, E, k, residual);
+  const int d_tile = E <= 64 ? 512 : 128;
+  const size_t fsm = sizeof(float) * (size_t)E * d_tile;
+  dim3 fgrid((D + d_tile - 1) / d_tile, 1);
+  fgrid.y = (unsigned)((16 * sm_count() + fgrid.x - 1) / fgrid.x);
+  if ((int)fgrid.y > T) fgrid.y = T;
+  if (desc->router_dtype == AXM_ROUTER_FP32) {
+    auto kern = bwd_finalize_kernel<float>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm);
+    kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
+                                  static_cast<const float*>(t->router_w), w.dz, t->d_x, T, D, E, k,
+                                  residual, d_tile);
+  } else {
+    auto kern = bwd_finalize_kernel<__nv_bfloat16>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm);
+    kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
+                                  static_cast<const __nv_bfloat16*>(t->router_w), w.dz, t->d_x, T, D, E,
+                                  k, residual, d_tile);
+  }
   return check_launch("backward");
 }

@@ -234,9 +234,35 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
         out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_tile : 0)) * args.n_total + n0;
       }
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
+      // kDH: the saved g, u pieces of the next 32 columns are fetched while the current
+      // ones are worked on, so their latency stays off the epilogue's critical path.
+      uint4 g_next[4], u_next[4];
+      auto fetch_gu = [&](int c0) {
+        if constexpr (MODE == kDH) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            g_next[q] = make_uint4(0, 0, 0, 0);
+            u_next[q] = make_uint4(0, 0, 0, 0);
+            if (row_ok && c0 < UMMA_N && n0 + c0 + q * 8 < args.n_total) {
+              g_next[q] = __ldg(reinterpret_cast<const uint4*>(args.g + out_elem + c0) + q);
+              u_next[q] = __ldg(reinterpret_cast<const uint4*>(args.u + out_elem + c0) + q);
+            }
+          }
+        }
+      };
+      fetch_gu(0);
 #pragma unroll 1
       for (int c0 = 0; c0 < UMMA_N; c0 += 32) {
         uint32_t v[32];
+        uint4 g_cur[4], u_cur[4];
+        if constexpr (MODE == kDH) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            g_cur[q] = g_next[q];
+            u_cur[q] = u_next[q];
+          }
+          fetch_gu(c0 + 32);
+        }
         __syncwarp();  // tcgen05.ld is warp-wide: rejoin lanes that skipped the stores
         tmem_ld32(t_addr + c0, v);
         tmem_ld_wait();
@@ -247,15 +273,13 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
         }
         if (!row_ok) continue;
         if constexpr (MODE == kDH) {
-          const __nv_bfloat16* gp = args.g + out_elem + c0;
-          const __nv_bfloat16* up = args.u + out_elem + c0;
           __nv_bfloat16* dgp = static_cast<__nv_bfloat16*>(args.out0) + out_elem + c0;
           __nv_bfloat16* dup = static_cast<__nv_bfloat16*>(args.out1) + out_elem + c0;
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             if (n0 + c0 + q * 8 >= args.n_total) continue;
-            const uint4 gv = __ldg(reinterpret_cast<const uint4*>(gp) + q);
-            const uint4 uv = __ldg(reinterpret_cast<const uint4*>(up) + q);
+            const uint4 gv = g_cur[q];
+            const uint4 uv = u_cur[q];
             const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
             const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
             uint32_t dgw[4], duw[4];
