@@ -43,7 +43,6 @@ struct GemmArgs {
   __nv_bfloat16* save_g;  // SwiGLU kernel, training: also store the gate and up
   __nv_bfloat16* save_u;  // pre-activations (bf16, same shape as h), or null
   int* status;
-  int dbg[4];         // B leading / stride offsets, B and A k-advance (16-byte units)
 };
 
 
@@ -185,11 +184,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           // A: K-major, 8-row groups 1024 bytes apart.  B: MN-major, 64-column
           // chunks 8192 bytes apart (leading), 8-k groups 1024 bytes apart (stride).
           const uint64_t da = make_smem_desc(sa, 16, 1024);
-          const uint64_t db = make_smem_desc(sb, (uint32_t)args.dbg[0] << 4, (uint32_t)args.dbg[1] << 4);
+          const uint64_t db = make_smem_desc(sb, kBChunkBytes, 1024);
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j) {
             // +32 bytes along K for A; +16 k-rows x 128 bytes for B
-            tc_mma_bf16(d_tmem, da + (uint64_t)(j * args.dbg[3]), db + (uint64_t)(j * args.dbg[2]), kInstrDesc,
+            tc_mma_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * 128), kInstrDesc,
                         (kb > 0 || j > 0) ? 1u : 0u);
           }
           tc_commit(&sh->empty[stage]);
@@ -423,12 +422,6 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.remote = nullptr;
   ga.save_g = static_cast<__nv_bfloat16*>(save_g);
   ga.save_u = static_cast<__nv_bfloat16*>(save_u);
-  ga.dbg[0] = kBChunkBytes >> 4;
-  ga.dbg[1] = 1024 >> 4;
-  ga.dbg[2] = 128;
-  ga.dbg[3] = 2;
-  if (const char* dbg = getenv("AXM_GEMM_DEBUG_DESC"))
-    sscanf(dbg, "%d,%d,%d,%d", &ga.dbg[0], &ga.dbg[1], &ga.dbg[2], &ga.dbg[3]);
   ga.n_total = F;
   ga.k_total = D;
   ga.out = h;
