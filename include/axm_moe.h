@@ -124,7 +124,10 @@ AXM_API int axm_moe_forward_profiled(const AxmMoeDesc* desc, const AxmMoeTensors
  * from (pinned) host memory, runs the layer, copies out back, all on `stream`,
  * and synchronises the stream before returning.  Weights stay device pointers.
  * Mirrors the host wrapper AI::forward_mixture_experts (core/src/ai.cpp:593-623).
- * d_x / d_out are device staging buffers of T*D bf16 each (may be equal). */
+ * d_x / d_out are device staging buffers of T*D bf16 each.  From 1024 tokens on, if
+ * d_x != d_out and offsets / row_src / slot_dst are not requested, the batch is cut
+ * into chunks whose copies in, compute and copies out overlap (results per token are
+ * the same; the histogram still covers the whole batch). */
 AXM_API int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
                                  const void* h_x, void* h_out, void* d_x, void* d_out,
                                  void* workspace, size_t workspace_bytes, void* stream);

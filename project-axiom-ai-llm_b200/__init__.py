@@ -210,9 +210,11 @@ class MoeLayer:
                                                 current_stream(), ms))
         return out, list(ms)
 
-    def forward_host(self, h_x, h_out, d_x, d_out):
+    def forward_host(self, h_x, h_out, d_x, d_out, keep_permutation=False):
         """Activations in (pinned) host memory; synchronises before returning."""
         t = self.tensors(d_x, d_out)
+        if not keep_permutation:   # lets the call pipeline copies and compute in chunks
+            t.offsets = t.row_src = t.slot_dst = None
         check(self.lib.axm_moe_forward_host(
             ctypes.byref(self.desc), ctypes.byref(t), ptr(h_x), ptr(h_out), ptr(d_x), ptr(d_out),
             ptr(self.workspace), self.workspace.numel(), current_stream()))

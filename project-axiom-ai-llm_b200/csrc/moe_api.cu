@@ -6,6 +6,7 @@
 // scratch comes from the caller's workspace.
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -249,6 +250,39 @@ extern "C" int axm_moe_forward_profiled(const AxmMoeDesc* desc, const AxmMoeTens
   return rc;
 }
 
+// Copy streams and events of the pipelined host-buffer call, created once per device.
+namespace {
+constexpr int kHostChunksMax = 8;
+struct HostPipe {
+  cudaStream_t in = nullptr, out = nullptr;
+  cudaEvent_t arrived[kHostChunksMax] = {}, done[kHostChunksMax] = {}, start = nullptr;
+  bool ok = false;
+};
+HostPipe* host_pipe() {
+  static thread_local HostPipe pipes[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  HostPipe& p = pipes[dev];
+  if (!p.ok) {
+    if (cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int i = 0; i < kHostChunksMax; ++i) {
+      if (cudaEventCreateWithFlags(&p.arrived[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+      if (cudaEventCreateWithFlags(&p.done[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    }
+    p.ok = true;
+  }
+  return &p;
+}
+}  // namespace
+
+// Tokens are independent, so the batch is cut into chunks and pipelined: while chunk c
+// is computed on the caller's stream, chunk c+1 comes in over PCIe on a copy stream and
+// chunk c-1 goes out on another.  Per-token results do not depend on the chunking.
+// Chunking needs the permutation outputs (offsets, row_src, slot_dst), which describe
+// the whole batch, not to be requested, and two chunk workspaces to fit into the
+// caller's workspace; otherwise the call runs as one piece.
 extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors* t,
                                     const void* h_x, void* h_out, void* d_x, void* d_out,
                                     void* workspace, size_t workspace_bytes, void* stream) {
@@ -258,20 +292,86 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
   if (desc->tokens == 0) return AXM_OK;
   if (int rc = require_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t bytes = (size_t)desc->tokens * desc->d_model * 2;
-  cudaError_t e = cudaMemcpyAsync(d_x, h_x, bytes, cudaMemcpyHostToDevice, st);
-  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "H2D copy: %s", cudaGetErrorString(e));
-  AxmMoeTensors tt = *t;
-  tt.x = d_x;
-  tt.out = d_out;
-  if (int rc = axm_moe_forward(desc, &tt, workspace, workspace_bytes, stream)) return rc;
-  e = cudaMemcpyAsync(h_out, d_out, bytes, cudaMemcpyDeviceToHost, st);
-  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "D2H copy: %s", cudaGetErrorString(e));
-  int32_t status = 0;
-  e = cudaMemcpyAsync(&status, carve(desc, workspace).status, sizeof(int32_t),
-                      cudaMemcpyDeviceToHost, st);
+  const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
+  const size_t row_bytes = (size_t)D * 2;
+
+  int chunks = T >= 4096 ? 4 : (T >= 1024 ? 2 : 1);
+  if (const char* env = getenv("AXM_HOST_CHUNKS")) {  // tuning knob: 1..8 pipeline chunks
+    int v = atoi(env);
+    if (v >= 1 && v <= kHostChunksMax) chunks = v;
+  }
+  if (t->offsets || t->row_src || t->slot_dst || d_x == d_out) chunks = 1;
+  HostPipe* pipe = chunks > 1 ? host_pipe() : nullptr;
+  if (pipe == nullptr) chunks = 1;
+  AxmMoeDesc cd = *desc;
+  size_t chunk_ws = 0;
+  if (chunks > 1) {
+    cd.tokens = (T + chunks - 1) / chunks;
+    chunk_ws = carve(&cd, nullptr).bytes;
+    // two chunk workspaces and, behind them, one status word per chunk
+    if (workspace == nullptr || 2 * chunk_ws + 256 > workspace_bytes) chunks = 1;
+  }
+  if (chunks == 1) {
+    const size_t bytes = (size_t)T * row_bytes;
+    cudaError_t e = cudaMemcpyAsync(d_x, h_x, bytes, cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "H2D copy: %s", cudaGetErrorString(e));
+    AxmMoeTensors tt = *t;
+    tt.x = d_x;
+    tt.out = d_out;
+    if (int rc = axm_moe_forward(desc, &tt, workspace, workspace_bytes, stream)) return rc;
+    e = cudaMemcpyAsync(h_out, d_out, bytes, cudaMemcpyDeviceToHost, st);
+    if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "D2H copy: %s", cudaGetErrorString(e));
+    int32_t status = 0;
+    e = cudaMemcpyAsync(&status, carve(desc, workspace).status, sizeof(int32_t),
+                        cudaMemcpyDeviceToHost, st);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "synchronise: %s", cudaGetErrorString(e));
+    if (status != 0) return fail(AXM_ERR_TIMEOUT, "a bounded wait in GEMM kernel %d gave up", status);
+    return AXM_OK;
+  }
+
+  // the copy streams start after whatever the caller already queued on its stream
+  cudaEventRecord(pipe->start, st);
+  cudaStreamWaitEvent(pipe->in, pipe->start, 0);
+  cudaStreamWaitEvent(pipe->out, pipe->start, 0);
+  const int tc = cd.tokens;
+  int32_t status[kHostChunksMax] = {};
+  int32_t* status_all = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + 2 * chunk_ws);
+  for (int c = 0; c < chunks; ++c) {
+    const int t0 = c * tc, n = (T - t0 < tc) ? T - t0 : tc;
+    if (n <= 0) {
+      chunks = c;
+      break;
+    }
+    const size_t off = (size_t)t0 * row_bytes;
+    cudaMemcpyAsync(static_cast<char*>(d_x) + off, static_cast<const char*>(h_x) + off,
+                    (size_t)n * row_bytes, cudaMemcpyHostToDevice, pipe->in);
+    cudaEventRecord(pipe->arrived[c], pipe->in);
+    cudaStreamWaitEvent(st, pipe->arrived[c], 0);
+    AxmMoeDesc d = *desc;
+    d.tokens = n;
+    if (c > 0) d.flags |= AXM_FLAG_HIST_ACCUMULATE;  // the histogram covers the whole batch
+    AxmMoeTensors tt = *t;
+    tt.x = static_cast<char*>(d_x) + off;
+    tt.out = static_cast<char*>(d_out) + off;
+    if (t->y) tt.y = static_cast<char*>(t->y) + off;
+    if (t->logits) tt.logits = t->logits + (size_t)t0 * E;
+    if (t->topk_idx) tt.topk_idx = t->topk_idx + (size_t)t0 * k;
+    if (t->topk_gate) tt.topk_gate = t->topk_gate + (size_t)t0 * k;
+    void* ws = static_cast<char*>(workspace) + (size_t)(c & 1) * chunk_ws;
+    if (int rc = axm_moe_forward(&d, &tt, ws, chunk_ws, stream)) return rc;
+    cudaMemcpyAsync(status_all + c, carve(&d, ws).status, sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
+    cudaEventRecord(pipe->done[c], st);
+    cudaStreamWaitEvent(pipe->out, pipe->done[c], 0);
+    cudaMemcpyAsync(static_cast<char*>(h_out) + off, static_cast<char*>(d_out) + off,
+                    (size_t)n * row_bytes, cudaMemcpyDeviceToHost, pipe->out);
+  }
+  cudaError_t e = cudaStreamSynchronize(pipe->out);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);
-  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "synchronise: %s", cudaGetErrorString(e));
-  if (status != 0) return fail(AXM_ERR_TIMEOUT, "a bounded wait in GEMM kernel %d gave up", status);
+  if (e == cudaSuccess) e = cudaMemcpy(status, status_all, sizeof(int32_t) * chunks, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "pipelined host call: %s", cudaGetErrorString(e));
+  for (int c = 0; c < chunks; ++c)
+    if (status[c] != 0) return fail(AXM_ERR_TIMEOUT, "a bounded wait in GEMM kernel %d gave up", status[c]);
   return AXM_OK;
 }

@@ -132,8 +132,10 @@ def test_c2_full_size_properties(axm, workloads, cuda_device):
     assert torch.equal(out4.flip(0), out1)
 
 
-def test_forward_host_matches_forward(axm, workloads, cuda_device):
-    cfg = workloads.scaled(workloads.CONFIGS["C2"], tokens=1024)
+@pytest.mark.parametrize("tokens", [1000, 1024, 4100])
+def test_forward_host_matches_forward(axm, workloads, cuda_device, tokens):
+    """1000 tokens run as one piece, 1024 as two pipelined chunks, 4100 as four."""
+    cfg = workloads.scaled(workloads.CONFIGS["C2"], tokens=tokens)
     x, w = workloads.make_inputs(cfg, device=cuda_device)
     layer = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
     out, _ = layer.forward(x)
@@ -141,7 +143,20 @@ def test_forward_host_matches_forward(axm, workloads, cuda_device):
     h_out = torch.empty_like(h_x).pin_memory()
     d_x = torch.empty_like(x)
     d_out = torch.empty_like(x)
-    layer.forward_host(h_x, h_out, d_x, d_out)
+    hist = layer.histogram.clone()
+    logits, idx = layer.logits.clone(), layer.topk_idx.clone()
+    # the chunked path needs the whole-batch permutation outputs not to be requested
+    t = layer.tensors(d_x, d_out)
+    t.offsets = t.row_src = t.slot_dst = None
+    import ctypes
+    for _ in range(2):
+        axm.check(layer.lib.axm_moe_forward_host(
+            ctypes.byref(layer.desc), ctypes.byref(t), axm.ptr(h_x), axm.ptr(h_out), axm.ptr(d_x),
+            axm.ptr(d_out), axm.ptr(layer.workspace), layer.workspace.numel(), axm.current_stream()))
+        assert torch.equal(h_out, out.cpu())
+        assert torch.equal(layer.histogram, hist)
+        assert torch.equal(layer.topk_idx, idx) and torch.equal(layer.logits, logits)
+    layer.forward_host(h_x, h_out, d_x, d_out, keep_permutation=True)   # one piece
     assert torch.equal(h_out, out.cpu())
 
 
