@@ -178,3 +178,19 @@ def test_bf16_router_weights_drop_in_mode(axm, workloads, oracle, cuda_device):
     layer.forward(x.to(cuda_device))
     idx = layer.topk_idx.cpu().numpy()
     assert (layer.histogram.cpu().numpy() == 2 * np.bincount(idx.ravel(), minlength=cfg.num_experts)).all()
+
+
+@pytest.mark.parametrize("kw", [
+    dict(tokens=300, d_model=64, d_ff=72, num_experts=256, top_k=8),     # widest routing the ABI takes
+    dict(tokens=129, d_model=8, d_ff=8, num_experts=2, top_k=2),         # smallest rows (16 bytes)
+    dict(tokens=50, d_model=520, d_ff=1032, num_experts=3, top_k=1),     # nothing a multiple of a tile
+    dict(tokens=2000, d_model=128, d_ff=128, num_experts=64, top_k=6, num_shared=2, zipf_s=1.2, zipf_c=6.0),
+])
+def test_edge_shapes(axm, workloads, oracle, cuda_device, kw):
+    """Ragged, tiny and maximal shapes; the last one is so skewed that many experts are empty."""
+    cfg = workloads.scaled(workloads.CONFIGS["C1"], **kw)
+    x, w = workloads.make_inputs(cfg)
+    layer, out = run_layer(axm, cfg, x, w, cuda_device)
+    check_against_oracle(oracle, cfg, x, w, layer, out)
+    if kw.get("zipf_c"):
+        assert int((layer.histogram == 0).sum()) > 0
