@@ -1,0 +1,510 @@
+// Two-SM form of the forward grouped GEMMs: thread-block clusters of two CTAs issue
+// tcgen05.mma.cta_group::2 (M = 256 across the pair, N = 256).  Each CTA stages its
+// own 128 activation rows and only HALF of the weight tile (128 of the 256 columns);
+// the tensor core of the leader CTA reads both halves, so the shared-memory fill per
+// FLOP drops from 48 KB to 32 KB per k-block and the pipeline gets six stages.
+// No cluster multicast is used anywhere: every CTA issues its own TMA loads, and the
+// leader signals the peer's barriers with ordinary (non-multicast) tcgen05.commit
+// instructions addressed to the peer's shared memory.
+//
+// Same operator as grouped_ffn.cu (core/src/CUDA/kernel/moe_router.cu:155-190 of the
+// reference engine); same weight layouts consumed as stored (MN-major B operand).
+// The two m-tiles of a pair are any two consecutive m-tiles of one expert group, so
+// ragged experts cost no extra padding; an odd tile count leaves one half idle.
+#include <mutex>
+
+#include "gemm_common.cuh"
+
+namespace axm {
+
+constexpr int kStages2 = 6;
+constexpr int kBHalfBytes = 2 * kBChunkBytes;              // 128 columns x 64 k
+constexpr int kStageBytes2 = kABytes + kBHalfBytes;        // 32 KiB per CTA and stage
+
+struct __align__(8) GemmShared2 {
+  uint64_t full[kStages2];      // used in the leader: bytes of both CTAs land here
+  uint64_t empty[kStages2];     // own: the leader's MMA commit arrives in both CTAs
+  uint64_t tmem_full[2];        // own
+  uint64_t tmem_empty[2];       // used in the leader: 4 epilogue warps of each CTA
+  uint32_t tmem_base;
+  int abort_flag;
+  int total_units;
+  int num_groups;
+  int tile_prefix[kMaxSegments + 1];
+  int group_first[kMaxSegments + 1];
+  int pair_prefix[kMaxSegments + 1];  // pairs before group g
+  AxmSegment seg[kMaxSegments];
+};
+
+constexpr size_t kGemm2SmemBytes = 1024 + (size_t)kStages2 * kStageBytes2 + sizeof(GemmShared2);
+
+struct Gemm2Args {
+  const AxmSegment* segments;
+  int num_segments;
+  int n_total;
+  int k_total;
+  int routed_experts;
+  void* out;
+  int* status;
+};
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// shared::cluster address of the same shared-memory location in CTA `rank` of the cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, uint32_t v) {
+  asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// TMA loads of a CTA pair: the completion bytes are counted on the mbarrier at
+// `bar_cluster_addr`, which may live in the peer CTA (the leader's barrier).
+__device__ __forceinline__ void tma2_load_2d(void* dst, const void* tmap, uint32_t bar_cluster_addr,
+                                             int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+      : "memory");
+}
+__device__ __forceinline__ void tma2_load_3d(void* dst, const void* tmap, uint32_t bar_cluster_addr,
+                                             int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];" ::"r"(smem_u32(dst)),
+      "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_alloc2(uint32_t* dst_smem, uint32_t cols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)),
+               "r"(cols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish2() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc2(uint32_t taddr, uint32_t cols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// arrives on the mbarrier at a shared::cluster address once the pair's MMAs issued so far are done
+__device__ __forceinline__ void tc_commit2(uint32_t bar_cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar_cluster_addr)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma2_bf16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}" ::"r"(d_tmem),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// fp32 accumulate, bf16 A (K-major) and B (MN-major), N = 256, M = 256 over the pair
+constexpr uint32_t kInstrDesc2 = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
+                                 ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+
+struct UnitCoord {
+  int seg;      // segment of this CTA's m-tile (valid only if live)
+  int m_tile;
+  int n_tile;
+  int seg0;     // first segment of the group (for the weights' expert id)
+  bool live;    // false: this half of the pair has no tile
+  int a_seg, a_m_tile;  // rows to load even when not live (the pair's first tile)
+};
+
+__device__ __forceinline__ void find_tile(const GemmShared2* sh, int s0, int s1, int m_idx, int* seg,
+                                          int* m_tile) {
+  int a = s0, b = s1 - 1;
+  while (a < b) {
+    int mid = (a + b + 1) >> 1;
+    if (sh->tile_prefix[mid] <= m_idx) a = mid; else b = mid - 1;
+  }
+  *seg = a;
+  *m_tile = m_idx - sh->tile_prefix[a];
+}
+
+__device__ __forceinline__ UnitCoord decode_unit(const GemmShared2* sh, int n_tiles, int unit, int rank) {
+  int lo = 0, hi = sh->num_groups - 1;
+  while (lo < hi) {
+    int mid = (lo + hi + 1) >> 1;
+    if (sh->pair_prefix[mid] * n_tiles <= unit) lo = mid; else hi = mid - 1;
+  }
+  const int s0 = sh->group_first[lo], s1 = sh->group_first[lo + 1];
+  const int base = sh->tile_prefix[s0];
+  const int mt = sh->tile_prefix[s1] - base;
+  const int pairs = sh->pair_prefix[lo + 1] - sh->pair_prefix[lo];
+  const int local = unit - sh->pair_prefix[lo] * n_tiles;
+  UnitCoord uc;
+  uc.n_tile = local / pairs;
+  const int p = local - uc.n_tile * pairs;
+  uc.seg0 = s0;
+  find_tile(sh, s0, s1, base + 2 * p, &uc.a_seg, &uc.a_m_tile);
+  uc.live = 2 * p + rank < mt;
+  if (uc.live) {
+    find_tile(sh, s0, s1, base + 2 * p + rank, &uc.seg, &uc.m_tile);
+    uc.a_seg = uc.seg;
+    uc.a_m_tile = uc.m_tile;
+  } else {
+    uc.seg = uc.a_seg;
+    uc.m_tile = uc.a_m_tile;
+  }
+  return uc;
+}
+
+template <bool kSwiGLU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_alt,
+                        const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
+                        const __grid_constant__ CUtensorMap tm_b0_sh, const __grid_constant__ CUtensorMap tm_b1_sh,
+                        Gemm2Args args) {
+  extern __shared__ unsigned char smem_raw[];
+  // both CTAs of a pair compute the same offsets, so their tiles sit at the same place
+  unsigned char* tiles = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  GemmShared2* sh = reinterpret_cast<GemmShared2*>(tiles + (size_t)kStages2 * kStageBytes2);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 = leader
+  const uint32_t peer = rank ^ 1u;
+  const int cluster_id = blockIdx.x >> 1;
+  const int num_clusters = gridDim.x >> 1;
+  constexpr int BN_OUT = kSwiGLU ? 128 : 256;
+  const int n_tiles = (args.n_total + BN_OUT - 1) / BN_OUT;
+  const int k_blocks = (args.k_total + BK - 1) / BK;
+  const int nseg = args.num_segments;
+
+  for (int s = threadIdx.x; s < nseg; s += kGemmThreads) sh->seg[s] = args.segments[s];
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages2; ++i) {
+      mbar_init(&sh->full[i], 1);
+      mbar_init(&sh->empty[i], 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&sh->tmem_full[i], 1);
+      mbar_init(&sh->tmem_empty[i], 8);
+    }
+    sh->abort_flag = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&tm_a);
+    tma_prefetch_desc(&tm_b0);
+    if (kSwiGLU) tma_prefetch_desc(&tm_b1);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    tmem_alloc2(&sh->tmem_base, kTmemCols);
+    tmem_relinquish2();
+  }
+  if (threadIdx.x == 0) {
+    int acc = 0;
+    for (int s = 0; s < nseg; ++s) {
+      sh->tile_prefix[s] = acc;
+      int rows = sh->seg[s].rows;
+      acc += rows > 0 ? (rows + BM - 1) / BM : 0;
+    }
+    sh->tile_prefix[nseg] = acc;
+    int ng = 0;
+    for (int s = 0; s < nseg; ++s)
+      if (s == 0 || sh->seg[s].expert != sh->seg[s - 1].expert) sh->group_first[ng++] = s;
+    sh->group_first[ng] = nseg;
+    sh->num_groups = ng;
+    int pairs = 0;
+    for (int g = 0; g < ng; ++g) {
+      sh->pair_prefix[g] = pairs;
+      int mt = sh->tile_prefix[sh->group_first[g + 1]] - sh->tile_prefix[sh->group_first[g]];
+      pairs += (mt + 1) / 2;
+    }
+    sh->pair_prefix[ng] = pairs;
+    sh->total_units = pairs * n_tiles;
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // barriers of both CTAs are initialised before anyone signals across
+  tc_fence_after();
+
+  const int total_units = sh->total_units;
+  const uint32_t tmem_base = sh->tmem_base;
+  volatile int* abort_flag = &sh->abort_flag;
+  auto raise_abort = [&]() {  // tell the peer too, so that the pair winds down together
+    st_cluster_u32(map_to_cta(smem_u32(&sh->abort_flag), peer), 1u);
+  };
+
+  if (warp == 0) {
+    // ---- TMA producer (each CTA: its rows of A, its half of B) ---------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = cluster_id; ok && unit < total_units; unit += num_clusters) {
+        const UnitCoord uc = decode_unit(sh, n_tiles, unit, (int)rank);
+        const AxmSegment sg = sh->seg[uc.a_seg];
+        const int e_raw = sh->seg[uc.seg0].expert & 0xffff;
+        const bool shared_w = e_raw >= args.routed_experts;
+        const int e = shared_w ? e_raw - args.routed_experts : e_raw;
+        const bool alt_a = kSwiGLU && (sg.expert & AXM_SEG_ALT_A);
+        const int a_row = (kSwiGLU ? sg.a_row0 : sg.out_row0) + uc.a_m_tile * BM;
+        const CUtensorMap* ma = alt_a ? &tm_a_alt : &tm_a;
+        // SwiGLU: the leader stages the gate columns, the peer the up columns of the same f range;
+        // down: the leader stages columns n0..n0+127, the peer n0+128..n0+255
+        const CUtensorMap* mb = kSwiGLU ? (rank == 0 ? (shared_w ? &tm_b0_sh : &tm_b0)
+                                                     : (shared_w ? &tm_b1_sh : &tm_b1))
+                                        : (shared_w ? &tm_b0_sh : &tm_b0);
+        const int n_col = uc.n_tile * BN_OUT + (kSwiGLU ? 0 : (int)rank * 128);
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
+            raise_abort();
+            ok = false;
+            break;
+          }
+          unsigned char* sa = tiles + (size_t)stage * kStageBytes2;
+          unsigned char* sb = sa + kABytes;
+          // the leader's barrier counts the bytes of both CTAs
+          if (rank == 0) mbar_expect_tx(&sh->full[stage], 2 * kStageBytes2);
+          const uint32_t bar = map_to_cta(smem_u32(&sh->full[stage]), 0);
+          tma2_load_2d(sa, ma, bar, kb * BK, a_row);
+          tma2_load_3d(sb, mb, bar, n_col, kb * BK, e);
+          tma2_load_3d(sb + kBChunkBytes, mb, bar, n_col + 64, kb * BK, e);
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---- MMA issuer: the leader CTA only ---------------------------------------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int unit = cluster_id; ok && unit < total_units; unit += num_clusters) {
+        if (!mbar_wait(&sh->tmem_empty[acc], acc_phase ^ 1u, abort_flag)) {
+          raise_abort();
+          break;
+        }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)acc * UMMA_N;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
+            raise_abort();
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + (size_t)stage * kStageBytes2);
+          const uint32_t sb = sa + kABytes;
+          const uint64_t da = make_smem_desc(sa, 16, 1024);
+          const uint64_t db = make_smem_desc(sb, kBChunkBytes, 1024);
+#pragma unroll
+          for (int j = 0; j < BK / UMMA_K; ++j)
+            tc_mma2_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * 128), kInstrDesc2,
+                         (kb > 0 || j > 0) ? 1u : 0u);
+          // free this stage in both CTAs once the MMAs that read it are done
+          tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 0));
+          tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 1));
+          if (++stage == kStages2) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        tc_commit2(map_to_cta(smem_u32(&sh->tmem_full[acc]), 0));
+        tc_commit2(map_to_cta(smem_u32(&sh->tmem_full[acc]), 1));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ---- epilogue: every CTA drains its own 128 accumulator rows -----------------------
+    const int quad = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    const uint32_t leader_tmem_empty0 = map_to_cta(smem_u32(&sh->tmem_empty[0]), 0);
+    const uint32_t leader_tmem_empty1 = map_to_cta(smem_u32(&sh->tmem_empty[1]), 0);
+    for (int unit = cluster_id; unit < total_units; unit += num_clusters) {
+      const UnitCoord uc = decode_unit(sh, n_tiles, unit, (int)rank);
+      const AxmSegment sg = sh->seg[uc.seg];
+      if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag))) break;
+      tc_fence_after();
+      const int row_in_seg = uc.m_tile * BM + quad * 32 + lane;
+      const bool row_ok = uc.live && row_in_seg < sg.rows;
+      const int n0 = uc.n_tile * BN_OUT;
+      const size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
+      if (uc.live) {
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
+          uint32_t g[32];
+          __syncwarp();
+          tmem_ld32(t_addr + c0, g);
+          if constexpr (kSwiGLU) {
+            uint32_t u[32];
+            tmem_ld32(t_addr + 128 + c0, u);
+            tmem_ld_wait();
+            uint32_t packed[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
+              float u0 = __uint_as_float(u[2 * j]), u1 = __uint_as_float(u[2 * j + 1]);
+              float h0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
+              float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+              packed[j] = pack_bf16(h0, h1);
+            }
+            if (row_ok) {
+              __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(args.out) + out_elem;
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (n0 + c0 + q * 8 < args.n_total)
+                  *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
+                      make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+            }
+          } else {
+            tmem_ld_wait();
+            if (row_ok) {
+              float* out_row = static_cast<float*>(args.out) + out_elem;
+#pragma unroll
+              for (int q = 0; q < 8; ++q)
+                if (n0 + c0 + q * 4 < args.n_total)
+                  *reinterpret_cast<uint4*>(out_row + c0 + q * 4) =
+                      make_uint4(g[4 * q], g[4 * q + 1], g[4 * q + 2], g[4 * q + 3]);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc == 0 ? leader_tmem_empty0 : leader_tmem_empty1);
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+
+  // ---- drain: nobody leaves while the peer may still touch its shared memory or TMEM -----
+  tc_fence_before();
+  __syncthreads();
+  if (sh->abort_flag != 0) {
+    long long t0 = clock64();
+    while (clock64() - t0 < 4000000LL) {
+    }
+    if (threadIdx.x == 0 && args.status != nullptr) atomicExch(args.status, kSwiGLU ? 6 : 7);
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc2(tmem_base, kTmemCols);
+  }
+}
+
+static int map2_rows(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+  const uint64_t dims[2] = {cols, rows};
+  const uint64_t strides[1] = {cols * 2};
+  const uint32_t box[2] = {64, (uint32_t)BM};
+  return encode_tensor_map(m, base, 2, dims, strides, box);
+}
+static int map2_weights(CUtensorMap* m, const void* base, uint64_t experts, uint64_t k_rows, uint64_t n_cols) {
+  const uint64_t dims[3] = {n_cols, k_rows, experts};
+  const uint64_t strides[2] = {n_cols * 2, n_cols * k_rows * 2};
+  const uint32_t box[3] = {64, (uint32_t)BK, 1};
+  return encode_tensor_map(m, base, 3, dims, strides, box);
+}
+
+// Number of CTAs to launch (two per cluster), or 0 when pairs cannot be scheduled.
+static int grid_2sm() {
+  static int cached = -1;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    cudaFuncSetAttribute(grouped_gemm_2sm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2SmemBytes);
+    cudaFuncSetAttribute(grouped_gemm_2sm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2SmemBytes);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(sm_count() & ~1), 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = kGemm2SmemBytes;
+    cudaLaunchAttribute attr;
+    attr.id = cudaLaunchAttributeClusterDimension;
+    attr.val.clusterDim.x = 2;
+    attr.val.clusterDim.y = 1;
+    attr.val.clusterDim.z = 1;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    int clusters = 0;
+    cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_2sm_kernel<true>, &cfg);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      clusters = 0;
+    }
+    int want = sm_count() / 2;
+    cached = 2 * (clusters < want ? clusters : want);
+  });
+  return cached;
+}
+
+int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
+                          int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
+                          const void* w_gate, const void* w_up, const void* w_down,
+                          const void* shared_gate, const void* shared_up, const void* shared_down,
+                          void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
+                          cudaEvent_t between) {
+  const int grid = grid_2sm();
+  if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
+  const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
+  CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;
+  int rc;
+  if ((rc = map2_rows(&a1, x_perm, (uint64_t)(a_rows > 0 ? a_rows : 1), D))) return rc;
+  if (x_alt != nullptr && alt_rows > 0) {
+    if ((rc = map2_rows(&a1_alt, x_alt, alt_rows, D))) return rc;
+  } else {
+    a1_alt = a1;
+  }
+  if ((rc = map2_weights(&g, w_gate, E, D, F))) return rc;
+  if ((rc = map2_weights(&u, w_up, E, D, F))) return rc;
+  if ((rc = map2_weights(&dn, w_down, E, F, D))) return rc;
+  if (S > 0) {
+    if ((rc = map2_weights(&g_sh, shared_gate, S, D, F))) return rc;
+    if ((rc = map2_weights(&u_sh, shared_up, S, D, F))) return rc;
+    if ((rc = map2_weights(&dn_sh, shared_down, S, F, D))) return rc;
+  } else {
+    g_sh = g;
+    u_sh = u;
+    dn_sh = dn;
+  }
+  if ((rc = map2_rows(&a2, h, rows_total, F))) return rc;
+  Gemm2Args ga;
+  ga.segments = segments;
+  ga.num_segments = num_segments;
+  ga.routed_experts = E;
+  ga.status = status;
+  ga.n_total = F;
+  ga.k_total = D;
+  ga.out = h;
+  grouped_gemm_2sm_kernel<true><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
+  if ((rc = check_launch("grouped_gemm_2sm_kernel<swiglu>"))) return rc;
+  if (between != nullptr) cudaEventRecord(between, st);
+  ga.n_total = D;
+  ga.k_total = F;
+  ga.out = o;
+  grouped_gemm_2sm_kernel<false><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
+  return check_launch("grouped_gemm_2sm_kernel<down>");
+}
+
+}  // namespace axm
