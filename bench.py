@@ -183,6 +183,8 @@ def main():
     ap.add_argument("--cpu-tokens", type=int, default=256, help="tokens in the CPU baseline sample")
     ap.add_argument("--reference-tokens", type=int, default=256)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=0,
+                    help="override the workload's token count (e.g. 16 for a decode-sized batch)")
     ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
     ap.add_argument("--ep-return", default="copy", choices=["fused", "copy"],
@@ -213,6 +215,8 @@ def main():
         dist.init_process_group("nccl", device_id=dev)
 
     cfg = wl.CONFIGS[args.config]
+    if args.tokens > 0:
+        cfg = wl.scaled(cfg, tokens=args.tokens, name=f"{cfg.name}@T{args.tokens}")
     peaks = measured_peaks()
     T, D, k = cfg.tokens, cfg.d_model, cfg.top_k
     x, w = wl.make_inputs(cfg, device=dev)  # same seed on every rank -> same tensors
