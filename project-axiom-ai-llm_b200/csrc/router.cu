@@ -166,19 +166,29 @@ router_kernel(const __nv_bfloat16* __restrict__ x, const WT* __restrict__ wr,
               }
             }
           }
-          // Tokens go through in batches of kTB: all of a batch's loads are issued
-          // before the first is used, so each thread keeps 4 * kTB loads in flight.
-          for (int tb = 0; tb < nt; tb += kTB) {
-            uint32_t xv[kTB][4];
+          // Tokens go through in batches of kTB, software-pipelined: the loads of batch
+          // i + 1 are issued before batch i is worked on, so 4 * kTB loads per thread are
+          // always in flight and their latency hides behind the arithmetic.
+          uint32_t xn[kTB][4];
+          auto load_batch = [&](int tb) {
 #pragma unroll
             for (int b = 0; b < kTB; ++b)
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
                 const int d = d0 + 512 * j + 2 * tid;
-                xv[b][j] = 0u;
+                xn[b][j] = 0u;
                 if (d < D && tb + b < nt)
-                  xv[b][j] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)(ts + tb + b) * D + d));
+                  xn[b][j] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)(ts + tb + b) * D + d));
               }
+          };
+          load_batch(0);
+          for (int tb = 0; tb < nt; tb += kTB) {
+            uint32_t xv[kTB][4];
+#pragma unroll
+            for (int b = 0; b < kTB; ++b)
+#pragma unroll
+              for (int j = 0; j < 4; ++j) xv[b][j] = xn[b][j];
+            load_batch(tb + kTB);
 #pragma unroll
             for (int b = 0; b < kTB; ++b) {
               const int tt = tb + b;
