@@ -1,6 +1,6 @@
 #!/bin/sh
 # Builds the reference engine's MoE kernels, UNMODIFIED, from the sources where
-# they lie (REF, default /root/reference) into oracle/_ref/ as a second checker
+# they lie (the directory named by REF) into oracle/_ref/ as a second checker
 # beside the CPU oracle.  Nothing of the reference is copied into this
 # repository: the output directory is git-ignored and holds only a binary and a
 # small JSON of struct offsets measured by compiling a probe against the
