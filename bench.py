@@ -27,9 +27,9 @@ PKG_DIR = os.path.join(ROOT, "project-axiom-ai-llm_b200")
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
-# DRAM bytes per launch of the gate/up GEMM from the committed ncu capture
-# (profiles/): {workload: bytes}.  None where no capture exists yet.
-NCU_TRAFFIC_BYTES = {}
+# DRAM bytes (read + write) per launch of the gate/up GEMM from the committed ncu
+# captures (profiles/grouped_gemm_2sm_C2.md, profiles/gemm_dram_traffic_C3.md).
+NCU_TRAFFIC_BYTES = {"C2": 402870016 + 80332800, "C3": 2418811648 + 461718784}
 
 
 def load_package():

@@ -375,8 +375,10 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 #pragma unroll
               for (int q = 0; q < 4; ++q)
                 if (n0 + c0 + q * 8 < args.n_total)
-                  *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
-                      make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                  // streaming store: h is not read again by this kernel and must not push
+                  // the activations and weights the other CTAs share out of L2
+                  __stcs(reinterpret_cast<uint4*>(out_row + c0 + q * 8),
+                         make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]));
             }
           } else {
             tmem_ld_wait();
@@ -385,8 +387,8 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 #pragma unroll
               for (int q = 0; q < 8; ++q)
                 if (n0 + c0 + q * 4 < args.n_total)
-                  *reinterpret_cast<uint4*>(out_row + c0 + q * 4) =
-                      make_uint4(g[4 * q], g[4 * q + 1], g[4 * q + 2], g[4 * q + 3]);
+                  __stcs(reinterpret_cast<uint4*>(out_row + c0 + q * 4),
+                         make_uint4(g[4 * q], g[4 * q + 1], g[4 * q + 2], g[4 * q + 3]));
             }
           }
         }
