@@ -112,6 +112,21 @@ AXM_API int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes);
 AXM_API int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
                             void* workspace, size_t workspace_bytes, void* stream);
 
+/* The layer at its call site in a pre-norm transformer block:
+ *   out = x + MoE(RMSNorm(x)),  RMSNorm(x) = bf16(x * rsqrt(mean(x^2) + eps) * gamma).
+ * The engine normalises before its MoE branch (core/src/CUDA/kernel/forward_pass.cu:1580-1598,
+ * RMSNorm at forward_pass.cu:404-461) but then adds the NORMALISED activations as the
+ * residual and leaves the block's hidden state untouched; this entry point wires the
+ * residual to the block input, which is what a pre-norm block means.  gamma is fp32 [D]
+ * or NULL (ones).  x_norm is a caller buffer of T*D bf16 that receives RMSNorm(x). */
+AXM_API int axm_moe_forward_prenorm(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
+                                    const float* gamma, float eps, void* x_norm, void* workspace,
+                                    size_t workspace_bytes, void* stream);
+
+/* RMSNorm alone (the first kernel of axm_moe_forward_prenorm). */
+AXM_API int axm_moe_rmsnorm(const void* x, const float* gamma, void* y, int32_t tokens,
+                            int32_t d_model, float eps, void* stream);
+
 /* axm_moe_forward with CUDA events between its five kernels; synchronises the
  * stream and returns the device time of each stage in milliseconds:
  * stage_ms[0..4] = router, permute, gate/up GEMM, down GEMM, combine.  A

@@ -554,3 +554,22 @@ ORC_API void orc_moe_backward(const uint16_t* x, const void* wr, int wr_is_fp32,
   }
   free(dp); free(dz); free(f_e); free(dw_all);
 }
+
+/* RMSNorm of each row: y = bf16(x * rstd * gamma), rstd = 1 / sqrt(mean(x^2) + eps), fp32
+ * throughout, sum of squares in ascending d.  gamma may be NULL (ones).  Placement and role
+ * in the block: core/src/CUDA/kernel/forward_pass.cu:404-461,1580-1598 of the engine. */
+ORC_API void orc_rmsnorm(const uint16_t* x, const float* gamma, int T, int D, float eps, uint16_t* y) {
+#pragma omp parallel for schedule(static)
+  for (int t = 0; t < T; ++t) {
+    float ss = 0.0f;
+    for (int d = 0; d < D; ++d) {
+      float v = bf16_to_f32(x[(size_t)t * D + d]);
+      ss = fmaf(v, v, ss);
+    }
+    float rstd = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int d = 0; d < D; ++d) {
+      float v = bf16_to_f32(x[(size_t)t * D + d]) * rstd * (gamma ? gamma[d] : 1.0f);
+      y[(size_t)t * D + d] = f32_to_bf16(v);
+    }
+  }
+}

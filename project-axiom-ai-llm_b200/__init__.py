@@ -90,6 +90,8 @@ def load():
     lib.axm_moe_forward.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, sz, vp]
     lib.axm_moe_forward_profiled.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, sz, vp,
                                              ctypes.POINTER(ctypes.c_float)]
+    lib.axm_moe_forward_prenorm.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, ctypes.c_float, vp, vp, sz, vp]
+    lib.axm_moe_rmsnorm.argtypes = [vp, vp, vp, i32, i32, ctypes.c_float, vp]
     lib.axm_moe_forward_host.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, vp, vp, vp, vp, sz, vp]
     lib.axm_moe_status_word.argtypes = [dp, vp, ctypes.POINTER(vp)]
     lib.axm_moe_router.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
@@ -198,6 +200,16 @@ class MoeLayer:
         check(self.lib.axm_moe_forward(ctypes.byref(self.desc), ctypes.byref(t), ptr(self.workspace),
                                        self.workspace.numel(), current_stream()))
         return out, self.histogram
+
+    def forward_prenorm(self, x, gamma, eps, x_norm, out=None):
+        """out = x + MoE(RMSNorm(x)); x_norm receives the normalised activations."""
+        if out is None:
+            out = torch.empty_like(x)
+        t = self.tensors(x, out)
+        check(self.lib.axm_moe_forward_prenorm(ctypes.byref(self.desc), ctypes.byref(t), ptr(gamma), eps,
+                                               ptr(x_norm), ptr(self.workspace), self.workspace.numel(),
+                                               current_stream()))
+        return out
 
     def forward_profiled(self, x, out=None):
         """forward() with per-stage device times: returns (out, [ms] * 5)."""

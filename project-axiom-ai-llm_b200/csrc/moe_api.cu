@@ -180,8 +180,11 @@ extern "C" int axm_moe_status_word(const AxmMoeDesc* desc, void* workspace, int3
   return AXM_OK;
 }
 
+// residual_src: what the combine adds to y (t->x for the plain layer; the un-normalised
+// block input when x is the output of a preceding RMSNorm).
 static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
-                        size_t workspace_bytes, void* stream, cudaEvent_t* ev) {
+                        size_t workspace_bytes, void* stream, cudaEvent_t* ev,
+                        const void* residual_src = nullptr) {
   if (int rc = validate_forward(desc)) return rc;
   if (t == nullptr) return fail(AXM_ERR_ARGUMENT, "tensors is null");
   if (desc->tokens == 0) return AXM_OK;  // empty input: nothing to enqueue
@@ -221,7 +224,8 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
   if (ev) cudaEventRecord(ev[4], st);
   const float* o_shared =
       S > 0 ? static_cast<const float*>(w.o) + (size_t)T * k * desc->d_model : nullptr;
-  rc = axm_moe_combine(desc, t->x, w.o, o_shared, slot_dst, gate, t->y, t->out, stream);
+  rc = axm_moe_combine(desc, residual_src ? residual_src : t->x, w.o, o_shared, slot_dst, gate, t->y, t->out,
+                       stream);
   if (ev) cudaEventRecord(ev[5], st);
   return rc;
 }
@@ -229,6 +233,88 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
 extern "C" int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
                                size_t workspace_bytes, void* stream) {
   return forward_impl(desc, t, workspace, workspace_bytes, stream, nullptr);
+}
+
+// y[t, :] = bf16(x[t, :] * rsqrt(mean(x[t, :]^2) + eps) * gamma).  One warp per token:
+// the row stays in registers between the sum of squares and the scaling.
+constexpr int kNormMaxChunks = 16;  // 16-byte pieces per lane kept in registers (D <= 4096)
+__global__ void __launch_bounds__(256)
+rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
+               __nv_bfloat16* __restrict__ y, int T, int D, float eps) {
+  const int lane = threadIdx.x & 31;
+  const int warps = gridDim.x * (blockDim.x >> 5);
+  const int chunks = D / 8;
+  for (int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); t < T; t += warps) {
+    const uint4* row = reinterpret_cast<const uint4*>(x + (size_t)t * D);
+    uint4 v[kNormMaxChunks];
+    float ss = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxChunks; ++i) {
+      const int c = lane + 32 * i;
+      v[i] = make_uint4(0, 0, 0, 0);
+      if (c < chunks) v[i] = __ldg(row + c);
+      const uint32_t w4[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        ss = fmaf(bf16_lo(w4[j]), bf16_lo(w4[j]), ss);
+        ss = fmaf(bf16_hi(w4[j]), bf16_hi(w4[j]), ss);
+      }
+    }
+    for (int c = lane + 32 * kNormMaxChunks; c < chunks; c += 32) {  // rows longer than the register tile
+      const uint4 u = __ldg(row + c);
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+      for (int j = 0; j < 4; ++j) {
+        ss = fmaf(bf16_lo(w4[j]), bf16_lo(w4[j]), ss);
+        ss = fmaf(bf16_hi(w4[j]), bf16_hi(w4[j]), ss);
+      }
+    }
+#pragma unroll
+    for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
+    const float rstd = rsqrtf(ss / (float)D + eps);
+    uint4* out = reinterpret_cast<uint4*>(y + (size_t)t * D);
+    auto scale = [&](uint4 u, int c) {
+      const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
+      uint32_t r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int d = c * 8 + 2 * j;
+        const float g0 = gamma ? __ldg(gamma + d) : 1.0f, g1 = gamma ? __ldg(gamma + d + 1) : 1.0f;
+        r[j] = pack_bf16(bf16_lo(w4[j]) * rstd * g0, bf16_hi(w4[j]) * rstd * g1);
+      }
+      return make_uint4(r[0], r[1], r[2], r[3]);
+    };
+#pragma unroll
+    for (int i = 0; i < kNormMaxChunks; ++i) {
+      const int c = lane + 32 * i;
+      if (c < chunks) out[c] = scale(v[i], c);
+    }
+    for (int c = lane + 32 * kNormMaxChunks; c < chunks; c += 32) out[c] = scale(__ldg(row + c), c);
+  }
+}
+
+extern "C" int axm_moe_rmsnorm(const void* x, const float* gamma, void* y, int32_t tokens,
+                               int32_t d_model, float eps, void* stream) {
+  if (!x || !y) return fail(AXM_ERR_ARGUMENT, "axm_moe_rmsnorm: null pointer");
+  if (tokens < 0 || d_model <= 0 || d_model % 8) return fail(AXM_ERR_ARGUMENT, "axm_moe_rmsnorm: bad shape");
+  if (tokens == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  int blocks = (tokens + 7) / 8;
+  if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
+  rmsnorm_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(y), tokens, d_model, eps);
+  return check_launch("rmsnorm_kernel");
+}
+
+extern "C" int axm_moe_forward_prenorm(const AxmMoeDesc* desc, const AxmMoeTensors* t, const float* gamma,
+                                       float eps, void* x_norm, void* workspace, size_t workspace_bytes,
+                                       void* stream) {
+  if (int rc = validate_forward(desc)) return rc;
+  if (!t || !t->x || !x_norm) return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_prenorm: null pointer");
+  if (x_norm == t->out) return fail(AXM_ERR_ARGUMENT, "x_norm must not alias out");
+  if (int rc = axm_moe_rmsnorm(t->x, gamma, x_norm, desc->tokens, desc->d_model, eps, stream)) return rc;
+  AxmMoeTensors tt = *t;
+  tt.x = x_norm;  // the experts and the router see the normalised activations ...
+  return forward_impl(desc, &tt, workspace, workspace_bytes, stream, nullptr, t->x);  // ... the residual does not
 }
 
 extern "C" int axm_moe_forward_profiled(const AxmMoeDesc* desc, const AxmMoeTensors* t,

@@ -33,6 +33,7 @@ class Oracle:
         lib.orc_expert_ffn.argtypes = [vp, i32, i32, i32, vp, vp, vp, i32, vp]
         lib.orc_moe_backward.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                          i32, ctypes.c_float, i32, vp, vp, vp, vp, vp, vp, vp]
+        lib.orc_rmsnorm.argtypes = [vp, vp, i32, i32, ctypes.c_float, vp]
         lib.orc_moe_forward.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp,
                                         vp, vp, i32, i32, i32, i32, vp, vp]
 
@@ -83,6 +84,13 @@ class Oracle:
         return float(self.lib.orc_aux_loss(self._p(np.ascontiguousarray(probs)),
                                            self._p(np.ascontiguousarray(idx)), T, E, idx.shape[1],
                                            alpha))
+
+    def rmsnorm(self, x, gamma, eps):
+        T, D = x.shape
+        y = np.empty((T, D), dtype=np.uint16)
+        gn = None if gamma is None else gamma.detach().cpu().contiguous().numpy().astype(np.float32)
+        self.lib.orc_rmsnorm(self._p(_bf16_np(x)), self._p(gn), T, D, eps, self._p(y))
+        return _np_bf16(y).view(T, D)
 
     def expert_ffn(self, x_rows, wg, wu, wd, h_bf16=False):
         """One expert over the given bf16 rows: fp32 [n][D] numpy."""

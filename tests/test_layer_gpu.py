@@ -238,3 +238,34 @@ def test_forward_is_graph_capturable(axm, workloads, cuda_device):
     t_graph = timed(graph.replay)
     t_eager = timed(lambda: layer.forward(static_x, static_out))
     print(f"C1 layer: {t_eager:.1f} us per call from Python, {t_graph:.1f} us per graph replay")
+
+
+@pytest.mark.parametrize("name,tokens,with_gamma", [("C1", None, True), ("C2", 640, True), ("C3", 300, False)])
+def test_prenorm_call_site(axm, workloads, oracle, cuda_device, name, tokens, with_gamma):
+    """out = x + MoE(RMSNorm(x)): the normalised activations feed router and experts, the
+    residual is the block input.  RMSNorm output: identical bf16 values to the oracle's
+    except where rsqrt rounding flips the last bit (at most one bf16 step, < 0.1 %)."""
+    cfg = workloads.scaled(workloads.CONFIGS[name], tokens=tokens)
+    x, w = workloads.make_inputs(cfg, device=cuda_device)
+    x = (x.float() * 3.0 + 0.5).bfloat16()          # not unit-variance, so that the norm matters
+    gamma = (1.0 + 0.1 * torch.randn(cfg.d_model, device=cuda_device)) if with_gamma else None
+    eps = 1e-5
+    layer = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+    x_norm = torch.empty_like(x)
+    out = layer.forward_prenorm(x, gamma, eps, x_norm)
+    assert layer.status() == 0
+    xn_ref = oracle.rmsnorm(x.cpu(), gamma, eps)
+    diff = (x_norm.cpu().float() - xn_ref.float()).abs()
+    assert float((diff > 0).float().mean()) < 1e-3
+    assert bool((diff <= 2.0 ** -7 * xn_ref.float().abs() + 1e-30).all())
+    # downstream of the GPU's own normalised activations
+    xc, wc = x_norm.cpu(), {k: v.cpu() for k, v in w.items()}
+    idx, gate = layer.topk_idx.cpu().numpy(), layer.topk_gate.cpu().numpy()
+    z = oracle.router_logits(xc, wc["router_w"])
+    assert (np.abs(layer.logits.cpu().numpy() - z) <= 1e-4 * np.maximum(1.0, np.abs(z))).all()
+    lo, hi = 0, min(cfg.tokens, 128)
+    y_ref, _ = oracle.forward(xc, wc, idx, gate, h_bf16=True, tok_range=(lo, hi))
+    helpers.assert_close_layer(layer.y[lo:hi], y_ref[lo:hi], what="y after pre-norm")
+    out_ref = (x.cpu()[lo:hi].float() + y_ref[lo:hi].float()).bfloat16()   # residual = block input
+    helpers.assert_close_out(out[lo:hi], out_ref, y_ref[lo:hi], what="out = x + MoE(RMSNorm(x))")
+    assert not torch.equal(out[lo:hi].cpu(), (xc[lo:hi].float() + y_ref[lo:hi].float()).bfloat16())
