@@ -277,6 +277,16 @@ AXM_API int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* ten
 AXM_API int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* tensors, void* workspace,
                              size_t workspace_bytes, void* stream);
 
+/* AdamW step (decoupled weight decay, bias correction with `step` >= 1) over one MoE
+ * weight matrix as the engine stores it: fp32 master, two fp32 moments, bf16 working
+ * copy (core/src/CUDA/util/gpu_types.cuh:148-168); `grad` is what axm_moe_backward
+ * wrote.  Follows the textbook update; the engine's own fused AdamW for the dense
+ * weights is core/src/CUDA/kernel/backward_pass.cu:812-852.  n elements, fp32
+ * buffers 16-byte aligned. */
+AXM_API int axm_moe_adamw_step(float* master, float* m, float* v, const float* grad, void* w_bf16,
+                               int64_t n, float lr, float beta1, float beta2, float eps,
+                               float weight_decay, int32_t step, void* stream);
+
 /* Per-segment redirect of the down projection's output: rows of segment s are
  * stored at base + (row0 + i) * D floats instead of into `o` (base == NULL keeps
  * the segment in `o`).  Under expert parallelism base is the source rank's return

@@ -106,6 +106,7 @@ def load():
     lib.axm_moe_forward_train.argtypes = [dp, tp, vp, sz, vp]
     lib.axm_moe_backward.argtypes = [dp, tp, vp, sz, vp]
     lib.axm_moe_permute_padded.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]
+    lib.axm_moe_adamw_step.argtypes = [vp, vp, vp, vp, vp, ctypes.c_int64] + [ctypes.c_float] * 5 + [i32, vp]
     lib.axm_moe_expert_ffn_backward.argtypes = [dp, vp, i32, i32] + [vp] * 16
     lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]

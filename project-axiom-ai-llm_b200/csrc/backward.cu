@@ -431,3 +431,66 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   }
   return check_launch("backward");
 }
+
+// ---- optimizer step for the MoE weights ---------------------------------------------
+// AdamW with decoupled weight decay over an fp32 master copy, two fp32 moments and the
+// bf16 working copy the kernels read - the storage the engine keeps for every MoE matrix
+// (core/src/CUDA/util/gpu_types.cuh:148-168; its fused AdamW for the dense weights is
+// core/src/CUDA/kernel/backward_pass.cu:812-852).  Textbook update, bias-corrected:
+//   m = b1 m + (1 - b1) g;  v = b2 v + (1 - b2) g^2;
+//   w -= lr * ( (m / (1 - b1^t)) / (sqrt(v / (1 - b2^t)) + eps) + wd * w );  w_bf16 = bf16(w).
+namespace axm {
+__global__ void __launch_bounds__(256)
+adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
+             const float* __restrict__ grad, __nv_bfloat16* __restrict__ w_bf16, long long n, float lr,
+             float b1, float b2, float eps, float wd, float c1, float c2) {
+  for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4; i < n;
+       i += (long long)gridDim.x * blockDim.x * 4) {
+    if (i + 3 < n) {
+      float4 g = __ldg(reinterpret_cast<const float4*>(grad + i));
+      float4 mm = *reinterpret_cast<float4*>(m + i), vv = *reinterpret_cast<float4*>(v + i);
+      float4 ww = *reinterpret_cast<float4*>(master + i);
+      float* gp = &g.x; float* mp = &mm.x; float* vp = &vv.x; float* wp = &ww.x;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        mp[j] = b1 * mp[j] + (1.0f - b1) * gp[j];
+        vp[j] = b2 * vp[j] + (1.0f - b2) * gp[j] * gp[j];
+        wp[j] -= lr * ((mp[j] / c1) / (sqrtf(vp[j] / c2) + eps) + wd * wp[j]);
+      }
+      *reinterpret_cast<float4*>(m + i) = mm;
+      *reinterpret_cast<float4*>(v + i) = vv;
+      *reinterpret_cast<float4*>(master + i) = ww;
+      *reinterpret_cast<uint2*>(w_bf16 + i) = make_uint2(pack_bf16(ww.x, ww.y), pack_bf16(ww.z, ww.w));
+    } else {
+      for (long long e = i; e < n; ++e) {
+        float mj = b1 * m[e] + (1.0f - b1) * grad[e];
+        float vj = b2 * v[e] + (1.0f - b2) * grad[e] * grad[e];
+        float wj = master[e] - lr * ((mj / c1) / (sqrtf(vj / c2) + eps) + wd * master[e]);
+        m[e] = mj;
+        v[e] = vj;
+        master[e] = wj;
+        w_bf16[e] = __float2bfloat16_rn(wj);
+      }
+    }
+  }
+}
+}  // namespace axm
+
+extern "C" int axm_moe_adamw_step(float* master, float* m, float* v, const float* grad, void* w_bf16,
+                                  int64_t n, float lr, float beta1, float beta2, float eps,
+                                  float weight_decay, int32_t step, void* stream) {
+  if (!master || !m || !v || !grad || !w_bf16) return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: null pointer");
+  if (n < 0 || step < 1) return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: n must be >= 0 and step >= 1");
+  if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(grad)) & 15)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: fp32 buffers must be 16-byte aligned");
+  if (n == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  const float c1 = 1.0f - powf(beta1, (float)step), c2 = 1.0f - powf(beta2, (float)step);
+  long long blocks = (n / 4 + 255) / 256;
+  if (blocks > 16LL * sm_count()) blocks = 16LL * sm_count();
+  if (blocks < 1) blocks = 1;
+  adamw_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      master, m, v, grad, static_cast<__nv_bfloat16*>(w_bf16), n, lr, beta1, beta2, eps, weight_decay, c1, c2);
+  return check_launch("adamw_kernel");
+}

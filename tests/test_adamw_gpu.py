@@ -1,0 +1,36 @@
+"""AdamW step over an MoE weight matrix (fp32 master + moments, bf16 working copy)
+against the same update written in numpy fp32.  Elementwise fp32: |err| <= 1e-6 * max(1, |ref|);
+the bf16 copy must be the rounding of the GPU's own master."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("n", [1, 7, 4096, 1000003])
+def test_adamw_step(axm, cuda_device, n):
+    lib = axm.load()
+    rng = np.random.default_rng(n)
+    w = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    lr, b1, b2, eps, wd = np.float32(1e-3), np.float32(0.9), np.float32(0.95), np.float32(1e-8), np.float32(0.1)
+    dw, dm, dv = (torch.from_numpy(a.copy()).to(cuda_device) for a in (w, m, v))
+    wb = torch.empty(n, dtype=torch.bfloat16, device=cuda_device)
+    for step in (1, 2, 3):
+        g = rng.standard_normal(n).astype(np.float32)
+        dg = torch.from_numpy(g).to(cuda_device)
+        axm.check(lib.axm_moe_adamw_step(axm.ptr(dw), axm.ptr(dm), axm.ptr(dv), axm.ptr(dg), axm.ptr(wb), n,
+                                         float(lr), float(b1), float(b2), float(eps), float(wd), step,
+                                         axm.current_stream()))
+        c1 = np.float32(1) - np.float32(b1) ** np.float32(step)
+        c2 = np.float32(1) - np.float32(b2) ** np.float32(step)
+        m = b1 * m + (np.float32(1) - b1) * g
+        v = b2 * v + (np.float32(1) - b2) * g * g
+        w = w - lr * ((m / c1) / (np.sqrt(v / c2) + eps) + wd * w)
+        torch.cuda.synchronize()
+        for got, ref in ((dw, w), (dm, m), (dv, v)):
+            err = np.abs(got.cpu().numpy() - ref)
+            assert (err <= 1e-6 * np.maximum(1.0, np.abs(ref))).all()
+        assert torch.equal(wb, dw.bfloat16())
