@@ -353,13 +353,13 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
                           const void* w_gate, const void* w_up, const void* w_down,
                           const void* shared_gate, const void* shared_up, const void* shared_down,
                           void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                          cudaEvent_t between);
+                          cudaEvent_t between, void* save_g, void* save_u);
 
 static bool use_2sm() {
   static int v = -1;
   if (v < 0) {
     // two-SM (cta_group::2) kernels are the default forward path; AXM_GEMM_2SM=0 selects
-    // the one-SM kernels of this file (which training and the fused return always use)
+    // the one-SM kernels of this file (which the fused return always uses)
     const char* e = getenv("AXM_GEMM_2SM");
     v = (e != nullptr && e[0] == '0') ? 0 : 1;
   }
@@ -402,10 +402,10 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       const void* shared_gate, const void* shared_up, const void* shared_down,
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                       cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u) {
-  if (remote == nullptr && save_g == nullptr && use_2sm())
+  if (remote == nullptr && use_2sm())
     return launch_expert_ffn_2sm(d, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate, w_up,
                                  w_down, shared_gate, shared_up, shared_down, h, o, rows_total, status, st,
-                                 between);
+                                 between, save_g, save_u);
   if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
   CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;

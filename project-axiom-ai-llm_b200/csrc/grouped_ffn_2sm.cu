@@ -45,6 +45,8 @@ struct Gemm2Args {
   int k_total;
   int routed_experts;
   void* out;
+  __nv_bfloat16* save_g;  // training: also store the gate / up pre-activations (bf16), or null
+  __nv_bfloat16* save_u;
   int* status;
 };
 
@@ -379,6 +381,23 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                   // the activations and weights the other CTAs share out of L2
                   __stcs(reinterpret_cast<uint4*>(out_row + c0 + q * 8),
                          make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]));
+              if (args.save_g != nullptr) {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  if (n0 + c0 + q * 8 < args.n_total) {
+                    uint4 gv, uv;
+                    gv.x = pack_bf16(__uint_as_float(g[8 * q + 0]), __uint_as_float(g[8 * q + 1]));
+                    gv.y = pack_bf16(__uint_as_float(g[8 * q + 2]), __uint_as_float(g[8 * q + 3]));
+                    gv.z = pack_bf16(__uint_as_float(g[8 * q + 4]), __uint_as_float(g[8 * q + 5]));
+                    gv.w = pack_bf16(__uint_as_float(g[8 * q + 6]), __uint_as_float(g[8 * q + 7]));
+                    uv.x = pack_bf16(__uint_as_float(u[8 * q + 0]), __uint_as_float(u[8 * q + 1]));
+                    uv.y = pack_bf16(__uint_as_float(u[8 * q + 2]), __uint_as_float(u[8 * q + 3]));
+                    uv.z = pack_bf16(__uint_as_float(u[8 * q + 4]), __uint_as_float(u[8 * q + 5]));
+                    uv.w = pack_bf16(__uint_as_float(u[8 * q + 6]), __uint_as_float(u[8 * q + 7]));
+                    __stcs(reinterpret_cast<uint4*>(args.save_g + out_elem + c0 + q * 8), gv);
+                    __stcs(reinterpret_cast<uint4*>(args.save_u + out_elem + c0 + q * 8), uv);
+                  }
+              }
             }
           } else {
             tmem_ld_wait();
@@ -466,7 +485,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
                           const void* w_gate, const void* w_up, const void* w_down,
                           const void* shared_gate, const void* shared_up, const void* shared_down,
                           void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                          cudaEvent_t between) {
+                          cudaEvent_t between, void* save_g, void* save_u) {
   const int grid = grid_2sm();
   if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
@@ -499,12 +518,16 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.n_total = F;
   ga.k_total = D;
   ga.out = h;
+  ga.save_g = static_cast<__nv_bfloat16*>(save_g);
+  ga.save_u = static_cast<__nv_bfloat16*>(save_u);
   grouped_gemm_2sm_kernel<true><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
   if ((rc = check_launch("grouped_gemm_2sm_kernel<swiglu>"))) return rc;
   if (between != nullptr) cudaEventRecord(between, st);
   ga.n_total = D;
   ga.k_total = F;
   ga.out = o;
+  ga.save_g = nullptr;
+  ga.save_u = nullptr;
   grouped_gemm_2sm_kernel<false><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_2sm_kernel<down>");
 }
