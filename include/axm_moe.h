@@ -348,20 +348,24 @@ AXM_API int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d_mo
 
 /* Dispatch: posts this rank's per-expert counts (from `offsets`, [E+1]) to all
  * peers, waits for theirs, copies the permuted rows (x_perm [slots][D] bf16) into
- * the owners' receive buffers and flags them. */
+ * the owners' receive buffers and flags them.  A receive buffer is expert-major:
+ * the rows of the owner's first expert from source 0, 1, ..., then its second
+ * expert's, so one expert's rows are one contiguous run. */
 AXM_API int axm_ep_dispatch(const AxmEpLayout* layout, uint32_t step, const int32_t* offsets,
                             const void* x_perm, int32_t* scratch, int32_t* status, void* stream);
 
 /* Waits for every source's rows, then writes two tables over the receive buffer
- * (world * E/world entries each): `segments` for axm_moe_expert_ffn, ordered by
- * (local expert, source rank) so that one expert's segments are neighbours,
+ * (world * E/world entries each, entry j * world + s for local expert j and source
+ * rank s, which is ascending row order): `segments` for axm_moe_expert_ffn,
  * followed by num_shared segments over the local tokens with output rows from
- * `cap` on; and `ret_segments` in arrival order for axm_ep_return
- * ({a_row0 = row in the source's return buffer, out_row0 = row here, rows,
- * expert = source rank}).  If remote_out is not NULL it receives, in the order of
- * `segments`, the redirect table that makes axm_moe_expert_ffn_remote store each
- * segment straight into its source's return buffer.  Also the number of rows
- * received. */
+ * `cap` on; and `ret_segments` for axm_ep_return ({a_row0 = row in the source's
+ * return buffer, out_row0 = row here, rows, expert = source rank}).
+ * With remote_out == NULL the rows of one expert form ONE segment (entry j * world;
+ * the expert's other entries hold zero rows), so the GEMMs cut their m-tiles as on
+ * a single GPU.  If remote_out is not NULL every source keeps its own segment and
+ * remote_out receives, in the order of `segments`, the redirect table that makes
+ * axm_moe_expert_ffn_remote store each segment straight into its source's return
+ * buffer.  Also the number of rows received. */
 AXM_API int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegment* segments,
                             AxmSegment* ret_segments, AxmRemoteOut* remote_out,
                             int32_t* rows_received, int32_t* status, void* stream);

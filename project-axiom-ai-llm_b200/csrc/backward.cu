@@ -162,14 +162,42 @@ dwr_partial_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
     float acc[EC];
 #pragma unroll
     for (int j = 0; j < EC; ++j) acc[j] = 0.0f;
-    if (d < D)
-      for (int t = t0; t < t1; ++t) {
+    if (d < D) {
+      // four tokens per trip: their activation loads are independent and overlap; the
+      // token's logit gradients (the same address for the whole warp) come as float4
+      int t = t0;
+      const bool vec = (E & 3) == 0 && e0 + EC <= E;
+      for (; t + 3 < t1; t += 4) {
+        float xv[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) xv[q] = __bfloat162float(x[(size_t)(t + q) * D + d]);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float* z = dz + (size_t)(t + q) * E + e0;
+          if (vec) {
+#pragma unroll
+            for (int j4 = 0; j4 < EC / 4; ++j4) {
+              const float4 zz = __ldg(reinterpret_cast<const float4*>(z) + j4);
+              acc[4 * j4 + 0] = fmaf(xv[q], zz.x, acc[4 * j4 + 0]);
+              acc[4 * j4 + 1] = fmaf(xv[q], zz.y, acc[4 * j4 + 1]);
+              acc[4 * j4 + 2] = fmaf(xv[q], zz.z, acc[4 * j4 + 2]);
+              acc[4 * j4 + 3] = fmaf(xv[q], zz.w, acc[4 * j4 + 3]);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < EC; ++j)
+              if (e0 + j < E) acc[j] = fmaf(xv[q], __ldg(z + j), acc[j]);
+          }
+        }
+      }
+      for (; t < t1; ++t) {
         const float xv = __bfloat162float(x[(size_t)t * D + d]);
         const float* z = dz + (size_t)t * E + e0;
 #pragma unroll
         for (int j = 0; j < EC; ++j)
           if (e0 + j < E) acc[j] = fmaf(xv, __ldg(z + j), acc[j]);
       }
+    }
     if (d < D)
 #pragma unroll
       for (int j = 0; j < EC; ++j)
@@ -220,13 +248,23 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
     }
     float4 rt = make_float4(0.f, 0.f, 0.f, 0.f);
     const float* z = dz + (size_t)t * E;
-    for (int e = 0; e < E; ++e) {
-      const float zv = __ldg(z + e);
+    auto add_e = [&](int e, float zv) {
       const float4 wv = *reinterpret_cast<const float4*>(w_s + e * d_tile + dl);
       rt.x = fmaf(wv.x, zv, rt.x);
       rt.y = fmaf(wv.y, zv, rt.y);
       rt.z = fmaf(wv.z, zv, rt.z);
       rt.w = fmaf(wv.w, zv, rt.w);
+    };
+    if ((E & 3) == 0) {
+      for (int e = 0; e < E; e += 4) {
+        const float4 zz = __ldg(reinterpret_cast<const float4*>(z + e));
+        add_e(e, zz.x);
+        add_e(e + 1, zz.y);
+        add_e(e + 2, zz.z);
+        add_e(e + 3, zz.w);
+      }
+    } else {
+      for (int e = 0; e < E; ++e) add_e(e, __ldg(z + e));
     }
     acc.x += rt.x;
     acc.y += rt.y;

@@ -14,9 +14,13 @@
 // allocated them).  Per layer call, with `step` a counter the host increments:
 //   axm_ep_dispatch   post my per-expert counts to all peers, flag; wait for all
 //                     peers' counts; copy my permuted rows into each owner's
-//                     receive buffer at the offset the counts imply; flag.
-//   axm_ep_segments   wait for all sources' rows; build the segment table
-//                     (one per source rank and local expert) and the return map.
+//                     receive buffer at the offset the counts imply; flag.  The
+//                     receive buffer is expert-major (all sources' rows of local
+//                     expert 0, then of expert 1 ...; inside an expert by source
+//                     rank), so one expert's rows are one contiguous run.
+//   axm_ep_segments   wait for all sources' rows; build the segment table (one
+//                     merged segment per local expert, so the GEMMs tile the rows
+//                     exactly as on a single GPU) and the return map.
 //   (grouped GEMMs over the receive buffer - local TMA only)
 //   axm_ep_return     copy fp32 expert rows back into each source's buffer, flag.
 //   axm_ep_wait_return wait for all owners' rows before the combine.
@@ -81,12 +85,13 @@ __device__ __forceinline__ void wait_all_sources(const EpArgs& a, int kind, int 
 
 constexpr int kEpThreads = 256;
 constexpr int kEpMaxRanks = 64;
+constexpr int kEpMaxExperts = 4096;  // 64 ranks x 64 experts per rank
 
 __global__ void __launch_bounds__(kEpThreads)
 ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
                    const __nv_bfloat16* __restrict__ x_perm, int32_t* __restrict__ done_counter) {
-  __shared__ int dst_begin[kEpMaxRanks + 1];  // first permuted row that goes to rank g
-  __shared__ int dst_base[kEpMaxRanks];       // row in g's receive buffer where my rows start
+  __shared__ int off_s[kEpMaxExperts + 1];  // my permuted rows of expert e start here
+  __shared__ int dst_base[kEpMaxExperts];   // row in the owner's receive buffer where they go
   const int tid = threadIdx.x;
 
   // 1. post my counts into every peer's table (row = my rank) and flag them
@@ -102,27 +107,33 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
   }
   // 2. wait for everybody's counts (each block on its own: no block depends on another)
   wait_all_sources(a, 0, 11);
-  // 3. where do my rows go
+  // 3. where do my rows go: the owner's buffer holds, expert by expert, the rows of
+  //    source 0, 1, ... - mine start after all rows of the owner's earlier experts and
+  //    the rows that lower ranks send to this expert
   const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
-  if (tid <= a.G) dst_begin[tid] = offsets[min(tid * a.El, a.E)];
-  if (tid < a.G) {
+  for (int e = tid; e <= a.E; e += kEpThreads) off_s[e] = offsets[e];
+  for (int e = tid; e < a.E; e += kEpThreads) {
+    const int e_first = (e / a.El) * a.El;  // the owner's first expert
     int base = 0;
-    for (int s = 0; s < a.rank; ++s)
-      for (int j = 0; j < a.El; ++j) base += __ldcg(table + s * a.E + tid * a.El + j);
-    dst_base[tid] = base;
+    for (int s = 0; s < a.G; ++s) {
+      const int32_t* row = table + s * a.E;
+      for (int q = e_first; q < e; ++q) base += __ldcg(row + q);
+      if (s < a.rank) base += __ldcg(row + e);
+    }
+    dst_base[e] = base;
   }
   __syncthreads();
   // 4. copy: one warp per row, 16-byte pieces, plain stores into the owner's memory
   const int warp = tid >> 5, lane = tid & 31;
   const int warps_total = gridDim.x * (kEpThreads / 32);
   const int chunks = a.D / 8;
-  int g = 0;
+  int e = 0;
   for (int r = blockIdx.x * (kEpThreads / 32) + warp; r < a.slots; r += warps_total) {
-    while (g + 1 <= a.G && r >= dst_begin[g + 1]) ++g;  // rows ascend, so does the owner
-    const int dst_row = dst_base[g] + (r - dst_begin[g]);
-    if (dst_row >= a.cap) continue;  // cannot happen with cap = slots * G; never write outside
+    while (e + 1 < a.E && r >= off_s[e + 1]) ++e;  // rows ascend, so does the expert
+    const int dst_row = dst_base[e] + (r - off_s[e]);
+    if (dst_row < 0 || dst_row >= a.cap) continue;  // cannot happen with cap = slots * G; never write outside
     const uint4* src = reinterpret_cast<const uint4*>(x_perm + (size_t)r * a.D);
-    uint4* dst = reinterpret_cast<uint4*>(a.peers[g] + a.off_recv) + (size_t)dst_row * chunks;
+    uint4* dst = reinterpret_cast<uint4*>(a.peers[e / a.El] + a.off_recv) + (size_t)dst_row * chunks;
     for (int c0 = 0; c0 < chunks; c0 += 128) {
       uint4 v[4];
 #pragma unroll
@@ -146,13 +157,17 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
   }
 }
 
-// One block.  Rows arrive source-major (all of rank 0's rows, then rank 1's ...),
-// sorted by expert inside each source.  Two tables over that buffer:
-//   segments     in (local expert, source) order for the grouped GEMMs, so that the
-//                segments of one expert are neighbours and share its weight tiles;
-//   ret_segments in (source, local expert) = arrival order for the return copy:
-//                {a_row0 = row in the source's return buffer, out_row0 = row here,
-//                 rows, expert = source rank}.
+// One block.  The receive buffer is expert-major: all sources' rows of local expert 0
+// (source 0 first), then of expert 1, ...  Two tables over that buffer, both indexed
+// j * G + s (local expert j, source rank s), which is also ascending row order:
+//   segments     for the grouped GEMMs.  Without a remote-output table the rows of one
+//                expert are ONE segment (entry j * G holds all of them, the other G - 1
+//                entries of that expert hold zero rows), so the m-tiles are cut exactly as
+//                on a single GPU instead of once per source.  With a remote-output table
+//                (the down GEMM stores into the sources' buffers itself) every source keeps
+//                its own segment, because a segment has one destination.
+//   ret_segments for the return copy: {a_row0 = row in the source's return buffer,
+//                out_row0 = row here, rows, expert = source rank}.
 __global__ void __launch_bounds__(kEpThreads)
 ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
                    AxmSegment* __restrict__ ret_segments, AxmRemoteOut* __restrict__ remote_out,
@@ -163,7 +178,7 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
   const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
   const int n = a.G * a.El;
   for (int i = threadIdx.x; i < n; i += kEpThreads) {
-    int s = i / a.El, j = i - s * a.El;
+    int j = i / a.G, s = i - j * a.G;
     rows_s[i] = __ldcg(table + s * a.E + a.rank * a.El + j);
   }
   __syncthreads();
@@ -192,13 +207,7 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
   }
   __syncthreads();
   for (int i = threadIdx.x; i < n; i += kEpThreads) {
-    int s = i / a.El, j = i - s * a.El;
-    AxmSegment sg;
-    sg.a_row0 = start_s[i];
-    sg.out_row0 = start_s[i];
-    sg.rows = rows_s[i];
-    sg.expert = j;
-    segments[j * a.G + s] = sg;
+    int j = i / a.G, s = i - j * a.G;
     int before = 0;  // source s's own offset of expert rank*El + j
     for (int e = 0; e < a.rank * a.El + j; ++e) before += __ldcg(table + s * a.E + e);
     AxmSegment rs;
@@ -207,13 +216,25 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
     rs.rows = rows_s[i];
     rs.expert = s;
     ret_segments[i] = rs;
-    if (remote_out != nullptr) {  // same order as `segments`
+    AxmSegment sg;
+    sg.expert = j;
+    if (remote_out != nullptr) {
+      sg.a_row0 = start_s[i];
+      sg.out_row0 = start_s[i];
+      sg.rows = rows_s[i];
       AxmRemoteOut ro;
       ro.base = a.peers[s] + a.off_oback;
       ro.row0 = before;
       ro.reserved = 0;
-      remote_out[j * a.G + s] = ro;
+      remote_out[i] = ro;
+    } else {
+      const int first = j * a.G;  // the expert's run starts where its source 0 starts
+      const int end = (j + 1 < a.El) ? start_s[first + a.G] : start_s[n - 1] + rows_s[n - 1];
+      sg.a_row0 = start_s[first];
+      sg.out_row0 = start_s[first];
+      sg.rows = (s == 0) ? end - start_s[first] : 0;
     }
+    segments[i] = sg;
   }
 }
 
