@@ -214,9 +214,13 @@ __global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __re
 }
 
 // dX[t, d] = dOut[t, d] (residual) + sum_i dXp[slot_dst[t, i], d] + sum_e Wr[d, e] * dz[t, e].
-// grid (D / d_tile, token chunks); a thread owns 4 consecutive d.  The block's slice of the
-// router weights sits in shared memory as [E][d_tile] (conflict-free float4 reads); dz[t, :]
-// is the same address for the whole block (broadcast).
+// grid (D / d_tile, token chunks); a thread owns 4 consecutive d and works on four tokens
+// at a time, so that their gathers are in flight together and one shared-memory read of
+// the router weights serves four tokens.  The block's slice of the router weights sits in
+// shared memory as [E][d_tile] (conflict-free float4 reads); dz[t, :] is the same address
+// for the whole block (broadcast).
+constexpr int kFinTokens = 4;
+
 template <typename WT>
 __global__ void __launch_bounds__(128)
 bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d_xp,
@@ -225,9 +229,11 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
                     int residual, int d_tile) {
   extern __shared__ __align__(16) float w_s[];  // [E][d_tile]
   const int d0 = blockIdx.x * d_tile;
+  // a warp fills 32 consecutive d of one expert: no bank conflicts; the strided reads of
+  // Wr stay in L1/L2 (the slice is E * d_tile elements)
   for (int i = threadIdx.x; i < E * d_tile; i += blockDim.x) {
-    const int dd = i / E, e = i - dd * E;  // read rows of Wr contiguously
-    w_s[e * d_tile + dd] = d0 + dd < D ? (float)wr[(size_t)(d0 + dd) * E + e] : 0.0f;
+    const int e = i / d_tile, dd = i - e * d_tile;
+    w_s[i] = d0 + dd < D ? (float)wr[(size_t)(d0 + dd) * E + e] : 0.0f;
   }
   __syncthreads();
   const int dl = threadIdx.x * 4;
@@ -235,42 +241,66 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
   const int c = (d0 + dl) / 4;
   const int t0 = (int)(((long long)blockIdx.y * T) / gridDim.y);
   const int t1 = (int)(((long long)(blockIdx.y + 1) * T) / gridDim.y);
-  for (int t = t0; t < t1; ++t) {
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (residual) acc = __ldg(reinterpret_cast<const float4*>(d_out + (size_t)t * D) + c);
-    for (int i = 0; i < k; ++i) {
-      const int r = __ldg(slot_dst + (size_t)t * k + i);
-      const float4 v = __ldg(reinterpret_cast<const float4*>(d_xp + (size_t)r * D) + c);
-      acc.x += v.x;
-      acc.y += v.y;
-      acc.z += v.z;
-      acc.w += v.w;
+  for (int t = t0; t < t1; t += kFinTokens) {
+    float4 acc[kFinTokens], rt[kFinTokens];
+    int tq[kFinTokens];
+#pragma unroll
+    for (int q = 0; q < kFinTokens; ++q) {
+      tq[q] = min(t + q, t1 - 1);  // a short last group repeats its last token; stores are masked
+      acc[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      rt[q] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (residual) acc[q] = __ldg(reinterpret_cast<const float4*>(d_out + (size_t)tq[q] * D) + c);
     }
-    float4 rt = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float* z = dz + (size_t)t * E;
-    auto add_e = [&](int e, float zv) {
+    for (int i = 0; i < k; ++i) {
+      float4 v[kFinTokens];
+#pragma unroll
+      for (int q = 0; q < kFinTokens; ++q) {
+        const int r = __ldg(slot_dst + (size_t)tq[q] * k + i);
+        v[q] = __ldg(reinterpret_cast<const float4*>(d_xp + (size_t)r * D) + c);
+      }
+#pragma unroll
+      for (int q = 0; q < kFinTokens; ++q) {
+        acc[q].x += v[q].x;
+        acc[q].y += v[q].y;
+        acc[q].z += v[q].z;
+        acc[q].w += v[q].w;
+      }
+    }
+    auto add_e = [&](int e, int q, float zv) {
       const float4 wv = *reinterpret_cast<const float4*>(w_s + e * d_tile + dl);
-      rt.x = fmaf(wv.x, zv, rt.x);
-      rt.y = fmaf(wv.y, zv, rt.y);
-      rt.z = fmaf(wv.z, zv, rt.z);
-      rt.w = fmaf(wv.w, zv, rt.w);
+      rt[q].x = fmaf(wv.x, zv, rt[q].x);
+      rt[q].y = fmaf(wv.y, zv, rt[q].y);
+      rt[q].z = fmaf(wv.z, zv, rt[q].z);
+      rt[q].w = fmaf(wv.w, zv, rt[q].w);
     };
     if ((E & 3) == 0) {
       for (int e = 0; e < E; e += 4) {
-        const float4 zz = __ldg(reinterpret_cast<const float4*>(z + e));
-        add_e(e, zz.x);
-        add_e(e + 1, zz.y);
-        add_e(e + 2, zz.z);
-        add_e(e + 3, zz.w);
+        float4 zz[kFinTokens];
+#pragma unroll
+        for (int q = 0; q < kFinTokens; ++q)
+          zz[q] = __ldg(reinterpret_cast<const float4*>(dz + (size_t)tq[q] * E + e));
+#pragma unroll
+        for (int q = 0; q < kFinTokens; ++q) {
+          add_e(e, q, zz[q].x);
+          add_e(e + 1, q, zz[q].y);
+          add_e(e + 2, q, zz[q].z);
+          add_e(e + 3, q, zz[q].w);
+        }
       }
     } else {
-      for (int e = 0; e < E; ++e) add_e(e, __ldg(z + e));
+      for (int e = 0; e < E; ++e)
+#pragma unroll
+        for (int q = 0; q < kFinTokens; ++q) add_e(e, q, __ldg(dz + (size_t)tq[q] * E + e));
     }
-    acc.x += rt.x;
-    acc.y += rt.y;
-    acc.z += rt.z;
-    acc.w += rt.w;
-    reinterpret_cast<float4*>(d_x + (size_t)t * D)[c] = acc;
+#pragma unroll
+    for (int q = 0; q < kFinTokens; ++q) {
+      if (t + q >= t1) break;
+      acc[q].x += rt[q].x;
+      acc[q].y += rt[q].y;
+      acc[q].z += rt[q].z;
+      acc[q].w += rt[q].w;
+      reinterpret_cast<float4*>(d_x + (size_t)tq[q] * D)[c] = acc[q];
+    }
   }
 }
 
@@ -452,7 +482,10 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   const int d_tile = E <= 64 ? 512 : 128;
   const size_t fsm = sizeof(float) * (size_t)E * d_tile;
   dim3 fgrid((D + d_tile - 1) / d_tile, 1);
-  fgrid.y = (unsigned)((16 * sm_count() + fgrid.x - 1) / fgrid.x);
+  // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory)
+  int per_sm = (int)((200u * 1024u) / (fsm + 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 12 ? 12 : per_sm);
+  fgrid.y = (unsigned)((per_sm * sm_count() + fgrid.x - 1) / fgrid.x);
   if ((int)fgrid.y > T) fgrid.y = T;
   if (desc->router_dtype == AXM_ROUTER_FP32) {
     auto kern = bwd_finalize_kernel<float>;

@@ -98,5 +98,8 @@ __host__ __device__ constexpr uint32_t instr_desc(bool a_mn, bool b_mn) {
 // strides in bytes for dimensions 1.. (rank - 1).  Defined in grouped_ffn.cu.
 int encode_tensor_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box);
+// The same for an fp32 tensor (used for TMA stores of fp32 tiles; box inner extent 32 = 128 bytes).
+int encode_tensor_map_f32(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                          const uint64_t* strides_bytes, const uint32_t* box);
 
 }  // namespace axm

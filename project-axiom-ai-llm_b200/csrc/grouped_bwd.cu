@@ -17,7 +17,13 @@
 //          operands MN-major (rows are the reduction index).  Used for
 //          dWd = h^T dO, dWg = x^T dG, dWu = x^T dU.  Segments must be padded to
 //          a multiple of 64 rows with zero rows (training layout), so that the
-//          reduction has no ragged tail.
+//          reduction has no ragged tail.  Its fp32 tiles leave through shared
+//          memory and TMA stores (whole 128-byte row pieces) instead of per-lane
+//          stores, which had kept the L1 store path busier than the tensor pipe.
+//
+// kDH has eight epilogue warps (two per TMEM lane quadrant, half the columns each):
+// its epilogue evaluates the SwiGLU derivative and one warp per scheduler could not
+// hide its own instruction latency.  The others have four.
 #include <cstdio>
 #include <mutex>
 
@@ -41,6 +47,15 @@ struct BwdArgs {
 };
 
 template <int MODE>
+struct BwdCfg {
+  static constexpr int kEpiWarps = MODE == kDH ? 8 : 4;
+  static constexpr int kThreads = 64 + 32 * kEpiWarps;
+  // kWGRAD: one 32 x 32 fp32 block (4 KiB, 128-byte swizzled rows) per epilogue warp
+  static constexpr int kStagingBytes = MODE == kWGRAD ? 4 * 4096 : 0;
+  static constexpr size_t kSmemBytes = kGemmSmemBytes + kStagingBytes;
+};
+
+template <int MODE>
 __device__ __forceinline__ TileCoord decode_bwd(const GemmShared* sh, int nseg, int n_tiles,
                                                 int m_tiles, int linear) {
   if constexpr (MODE == kWGRAD) {
@@ -56,15 +71,19 @@ __device__ __forceinline__ TileCoord decode_bwd(const GemmShared* sh, int nseg, 
   }
 }
 
+// tm_a1 carries, for kWGRAD, the fp32 map of the output [E][m_total][n_total] (box 32 x 32 x 1).
 template <int MODE>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(BwdCfg<MODE>::kThreads, 1)
 grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_constant__ CUtensorMap tm_a1,
                    const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                    BwdArgs args) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  GemmShared* sh = reinterpret_cast<GemmShared*>(tiles + (size_t)kStages * kStageBytes);
+  unsigned char* staging = tiles + (size_t)kStages * kStageBytes;  // 1024-byte aligned
+  GemmShared* sh = reinterpret_cast<GemmShared*>(staging + BwdCfg<MODE>::kStagingBytes);
+  constexpr int kThreads = BwdCfg<MODE>::kThreads;
+  constexpr int kEpiWarps = BwdCfg<MODE>::kEpiWarps;
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -73,7 +92,7 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
   const int kb_half = (args.k_total + BK - 1) / BK;
   const int nseg = args.num_segments;
 
-  for (int s = threadIdx.x; s < nseg; s += kGemmThreads) sh->seg[s] = args.segments[s];
+  for (int s = threadIdx.x; s < nseg; s += kThreads) sh->seg[s] = args.segments[s];
   if (threadIdx.x == 0) {
     for (int i = 0; i < kStages; ++i) {
       mbar_init(&sh->full[i], 1);
@@ -81,12 +100,13 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh->tmem_full[i], 1);
-      mbar_init(&sh->tmem_empty[i], 4);
+      mbar_init(&sh->tmem_empty[i], kEpiWarps);
     }
     sh->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_a0);
     tma_prefetch_desc(&tm_b0);
+    if (MODE == kWGRAD) tma_prefetch_desc(&tm_a1);
   }
   __syncthreads();
   if (warp == 1) {
@@ -213,7 +233,10 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
     }
   } else {
     // ---- epilogue ------------------------------------------------------------------
-    const int quad = warp & 3;
+    const int quad = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp id mod 4)
+    constexpr int kColsPerWarp = UMMA_N / (kEpiWarps / 4);
+    const int c_begin = ((warp - 2) >> 2) * kColsPerWarp, c_end = c_begin + kColsPerWarp;
+    unsigned char* stage_w = staging + (size_t)((warp - 2) & 3) * 4096;  // kWGRAD only
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -243,16 +266,16 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
           for (int q = 0; q < 4; ++q) {
             g_next[q] = make_uint4(0, 0, 0, 0);
             u_next[q] = make_uint4(0, 0, 0, 0);
-            if (row_ok && c0 < UMMA_N && n0 + c0 + q * 8 < args.n_total) {
+            if (row_ok && c0 < c_end && n0 + c0 + q * 8 < args.n_total) {
               g_next[q] = __ldg(reinterpret_cast<const uint4*>(args.g + out_elem + c0) + q);
               u_next[q] = __ldg(reinterpret_cast<const uint4*>(args.u + out_elem + c0) + q);
             }
           }
         }
       };
-      fetch_gu(0);
+      fetch_gu(c_begin);
 #pragma unroll 1
-      for (int c0 = 0; c0 < UMMA_N; c0 += 32) {
+      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t v[32];
         uint4 g_cur[4], u_cur[4];
         if constexpr (MODE == kDH) {
@@ -270,6 +293,28 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
           // an expert without rows: its weight gradient is zero, the accumulator was never written
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+        if constexpr (MODE == kWGRAD) {
+          // Lane = row of the block.  Its eight 16-byte pieces go to shared memory in the
+          // 128-byte-swizzle pattern of the output map (piece q of row r at q ^ (r & 7)),
+          // which also keeps the eight lanes of a store phase on different banks; then one
+          // TMA store writes the 32 x 32 block.  The map clips rows beyond m_total and
+          // columns beyond n_total.
+          if (lane == 0) bulk_wait_read();  // the previous block's store has read the buffer
+          __syncwarp();
+          if (n0 + c0 < args.n_total && tc.m_tile * BM + quad * 32 < args.m_total) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(stage_w + lane * 128 + ((q ^ (lane & 7)) << 4)) =
+                  make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_3d(&tm_a1, stage_w, n0 + c0, tc.m_tile * BM + quad * 32, sg.expert & 0xffff);
+              bulk_commit_group();
+            }
+          }
+          continue;
         }
         if (!row_ok) continue;
         if constexpr (MODE == kDH) {
@@ -319,6 +364,7 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
   }
 
   // ---- drain -----------------------------------------------------------------------
+  if (MODE == kWGRAD && warp >= 2 && lane == 0) bulk_wait_all();
   tc_fence_before();
   __syncthreads();
   if (sh->abort_flag != 0) {
@@ -352,15 +398,24 @@ static int map_weights_kmajor(CUtensorMap* m, const void* base, uint64_t experts
   return encode_tensor_map(m, base, 3, dims, strides, box);
 }
 
+// fp32 weight gradient [experts][m][n]: box = 32 columns (128 bytes) x 32 rows x 1 expert.
+static int map_wgrad_out(CUtensorMap* m, void* base, uint64_t experts, uint64_t rows, uint64_t cols) {
+  const uint64_t dims[3] = {cols, rows, experts};
+  const uint64_t strides[2] = {cols * 4, cols * rows * 4};
+  const uint32_t box[3] = {32, 32, 1};
+  return encode_tensor_map_f32(m, base, 3, dims, strides, box);
+}
+
 template <int MODE>
 static int launch_bwd(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                       const CUtensorMap& b1, const BwdArgs& args, cudaStream_t st, const char* what) {
   static std::once_flag once;
   std::call_once(once, [] {
     cudaFuncSetAttribute(grouped_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)kGemmSmemBytes);
+                         (int)BwdCfg<MODE>::kSmemBytes);
   });
-  grouped_bwd_kernel<MODE><<<sm_count(), kGemmThreads, kGemmSmemBytes, st>>>(a0, a1, b0, b1, args);
+  grouped_bwd_kernel<MODE><<<sm_count(), BwdCfg<MODE>::kThreads, BwdCfg<MODE>::kSmemBytes, st>>>(a0, a1, b0, b1,
+                                                                                               args);
   return check_launch(what);
 }
 
@@ -426,15 +481,19 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   if ((rc = map_rows(&k_x, x_perm, R, D, 64))) return rc;
   if ((rc = map_rows(&k_dg, d_g, R, F, 64))) return rc;
   if ((rc = map_rows(&k_du, d_u, R, F, 64))) return rc;
+  CUtensorMap o_wd, o_wg, o_wu;  // fp32 outputs, stored tile by tile through TMA
+  if ((rc = map_wgrad_out(&o_wd, d_w_down, E, F, D))) return rc;
+  if ((rc = map_wgrad_out(&o_wg, d_w_gate, E, D, F))) return rc;
+  if ((rc = map_wgrad_out(&o_wu, d_w_up, E, D, F))) return rc;
   a.k_total = 0;
   a.m_total = F;  // dWd[e] = h^T dO : [F][D]
   a.n_total = D;
   a.out0 = d_w_down;
-  if ((rc = launch_bwd<kWGRAD>(k_h, k_h, k_do, k_do, a, st, "grouped_bwd_kernel<dWd>"))) return rc;
+  if ((rc = launch_bwd<kWGRAD>(k_h, o_wd, k_do, k_do, a, st, "grouped_bwd_kernel<dWd>"))) return rc;
   a.m_total = D;  // dWg[e] = x^T dG : [D][F]
   a.n_total = F;
   a.out0 = d_w_gate;
-  if ((rc = launch_bwd<kWGRAD>(k_x, k_x, k_dg, k_dg, a, st, "grouped_bwd_kernel<dWg>"))) return rc;
+  if ((rc = launch_bwd<kWGRAD>(k_x, o_wg, k_dg, k_dg, a, st, "grouped_bwd_kernel<dWg>"))) return rc;
   a.out0 = d_w_up;
-  return launch_bwd<kWGRAD>(k_x, k_x, k_du, k_du, a, st, "grouped_bwd_kernel<dWu>");
+  return launch_bwd<kWGRAD>(k_x, o_wu, k_du, k_du, a, st, "grouped_bwd_kernel<dWu>");
 }
