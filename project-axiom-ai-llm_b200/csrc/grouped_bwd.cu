@@ -21,9 +21,10 @@
 //          memory and TMA stores (whole 128-byte row pieces) instead of per-lane
 //          stores, which had kept the L1 store path busier than the tensor pipe.
 //
-// kDH has eight epilogue warps (two per TMEM lane quadrant, half the columns each):
-// its epilogue evaluates the SwiGLU derivative and one warp per scheduler could not
-// hide its own instruction latency.  The others have four.
+// kDH's epilogue reads g, u and writes dG, dU through a per-warp staging block in shared
+// memory so that global requests are row-contiguous; with one 16-byte piece of a different
+// row per lane the L1 path, not the tensor pipe, had set the pace (eight epilogue warps
+// instead of four did not help, which is how that showed).
 #include <cstdio>
 #include <mutex>
 
@@ -48,10 +49,11 @@ struct BwdArgs {
 
 template <int MODE>
 struct BwdCfg {
-  static constexpr int kEpiWarps = MODE == kDH ? 8 : 4;
+  static constexpr int kEpiWarps = 4;
   static constexpr int kThreads = 64 + 32 * kEpiWarps;
-  // kWGRAD: one 32 x 32 fp32 block (4 KiB, 128-byte swizzled rows) per epilogue warp
-  static constexpr int kStagingBytes = MODE == kWGRAD ? 4 * 4096 : 0;
+  // per epilogue warp 4 KiB: kWGRAD one 32 x 32 fp32 block (128-byte swizzled rows),
+  // kDH two 32 x 32 bf16 blocks (g / dG and u / dU)
+  static constexpr int kStagingBytes = MODE == kDX ? 0 : 4 * 4096;
   static constexpr size_t kSmemBytes = kGemmSmemBytes + kStagingBytes;
 };
 
@@ -236,7 +238,7 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
     const int quad = warp & 3;  // the TMEM lanes a warp may read: 32 * (warp id mod 4)
     constexpr int kColsPerWarp = UMMA_N / (kEpiWarps / 4);
     const int c_begin = ((warp - 2) >> 2) * kColsPerWarp, c_end = c_begin + kColsPerWarp;
-    unsigned char* stage_w = staging + (size_t)((warp - 2) & 3) * 4096;  // kWGRAD only
+    unsigned char* stage_w = staging + (size_t)((warp - 2) & 3) * 4096;  // kWGRAD, kDH
     int acc = 0;
     uint32_t acc_phase = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x) {
@@ -257,18 +259,32 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
         out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_tile : 0)) * args.n_total + n0;
       }
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
-      // kDH: the saved g, u pieces of the next 32 columns are fetched while the current
-      // ones are worked on, so their latency stays off the epilogue's critical path.
-      uint4 g_next[4], u_next[4];
+      // kDH: g, u, dG, dU move between global memory and the warp's staging block in
+      // row-contiguous 64-byte runs (a request touches 8 rows, not 32), and each lane
+      // works on its own row out of shared memory.  Piece p of a 32 x 32 bf16 block:
+      // row p / 4, 16-byte piece p % 4; in shared memory at row * 64 + ((piece ^ (row / 2 % 4)) * 16,
+      // which keeps both access patterns free of bank conflicts.  The pieces of the next
+      // 32 columns are fetched while the current ones are worked on.
+      uint4 g_next[4], u_next[4];  // 128 pieces per 32 x 32 block: four per lane and tensor
+      const int rows_left = sg.rows - (tc.m_tile * BM + quad * 32);  // rows of this warp's block
+      auto piece_ok = [&](int p, int c0) {
+        return (p >> 2) < rows_left && c0 < c_end && n0 + c0 + (p & 3) * 8 < args.n_total;
+      };
+      auto piece_elem = [&](int p, int c0) {
+        return (size_t)(sg.out_row0 + tc.m_tile * BM + quad * 32 + (p >> 2)) * args.n_total + n0 + c0 +
+               (p & 3) * 8;
+      };
+      auto piece_smem = [&](int row, int piece) { return row * 64 + ((piece ^ ((row >> 1) & 3)) << 4); };
       auto fetch_gu = [&](int c0) {
         if constexpr (MODE == kDH) {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            g_next[q] = make_uint4(0, 0, 0, 0);
-            u_next[q] = make_uint4(0, 0, 0, 0);
-            if (row_ok && c0 < c_end && n0 + c0 + q * 8 < args.n_total) {
-              g_next[q] = __ldg(reinterpret_cast<const uint4*>(args.g + out_elem + c0) + q);
-              u_next[q] = __ldg(reinterpret_cast<const uint4*>(args.u + out_elem + c0) + q);
+          for (int i = 0; i < 4; ++i) {
+            const int p = lane + 32 * i;
+            g_next[i] = make_uint4(0, 0, 0, 0);
+            u_next[i] = make_uint4(0, 0, 0, 0);
+            if (piece_ok(p, c0)) {
+              g_next[i] = __ldg(reinterpret_cast<const uint4*>(args.g + piece_elem(p, c0)));
+              u_next[i] = __ldg(reinterpret_cast<const uint4*>(args.u + piece_elem(p, c0)));
             }
           }
         }
@@ -277,14 +293,59 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
 #pragma unroll 1
       for (int c0 = c_begin; c0 < c_end; c0 += 32) {
         uint32_t v[32];
-        uint4 g_cur[4], u_cur[4];
         if constexpr (MODE == kDH) {
+          unsigned char* g_s = stage_w;
+          unsigned char* u_s = stage_w + 2048;
+          __syncwarp();  // the previous block's read-back is done; also rejoins the warp for tcgen05.ld
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            g_cur[q] = g_next[q];
-            u_cur[q] = u_next[q];
+          for (int i = 0; i < 4; ++i) {
+            const int p = lane + 32 * i;
+            *reinterpret_cast<uint4*>(g_s + piece_smem(p >> 2, p & 3)) = g_next[i];
+            *reinterpret_cast<uint4*>(u_s + piece_smem(p >> 2, p & 3)) = u_next[i];
           }
           fetch_gu(c0 + 32);
+          __syncwarp();
+          tmem_ld32(t_addr + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4* gp = reinterpret_cast<uint4*>(g_s + piece_smem(lane, q));
+            uint4* up = reinterpret_cast<uint4*>(u_s + piece_smem(lane, q));
+            const uint4 gv = *gp;
+            const uint4 uv = *up;
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+            const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+            uint32_t dgw[4], duw[4];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+              float r0[2], r1[2];
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const float gval = hh ? bf16_hi(gw[pp]) : bf16_lo(gw[pp]);
+                const float uval = hh ? bf16_hi(uw[pp]) : bf16_lo(uw[pp]);
+                const float dh = __uint_as_float(v[q * 8 + pp * 2 + hh]);
+                const float sg_ = __fdividef(1.0f, 1.0f + __expf(-gval));
+                r0[hh] = dh * uval * (sg_ * (1.0f + gval * (1.0f - sg_)));  // dG
+                r1[hh] = dh * gval * sg_;                                    // dU
+              }
+              dgw[pp] = pack_bf16(r0[0], r0[1]);
+              duw[pp] = pack_bf16(r1[0], r1[1]);
+            }
+            *gp = make_uint4(dgw[0], dgw[1], dgw[2], dgw[3]);  // in place: the lane's own row
+            *up = make_uint4(duw[0], duw[1], duw[2], duw[3]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int p = lane + 32 * i;
+            if (piece_ok(p, c0)) {
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out0) + piece_elem(p, c0)) =
+                  *reinterpret_cast<const uint4*>(g_s + piece_smem(p >> 2, p & 3));
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out1) + piece_elem(p, c0)) =
+                  *reinterpret_cast<const uint4*>(u_s + piece_smem(p >> 2, p & 3));
+            }
+          }
+          continue;
         }
         __syncwarp();  // tcgen05.ld is warp-wide: rejoin lanes that skipped the stores
         tmem_ld32(t_addr + c0, v);
@@ -317,36 +378,7 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
           continue;
         }
         if (!row_ok) continue;
-        if constexpr (MODE == kDH) {
-          __nv_bfloat16* dgp = static_cast<__nv_bfloat16*>(args.out0) + out_elem + c0;
-          __nv_bfloat16* dup = static_cast<__nv_bfloat16*>(args.out1) + out_elem + c0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (n0 + c0 + q * 8 >= args.n_total) continue;
-            const uint4 gv = g_cur[q];
-            const uint4 uv = u_cur[q];
-            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-            const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
-            uint32_t dgw[4], duw[4];
-#pragma unroll
-            for (int p = 0; p < 4; ++p) {
-              float r0[2], r1[2];
-#pragma unroll
-              for (int hh = 0; hh < 2; ++hh) {
-                const float gval = hh ? bf16_hi(gw[p]) : bf16_lo(gw[p]);
-                const float uval = hh ? bf16_hi(uw[p]) : bf16_lo(uw[p]);
-                const float dh = __uint_as_float(v[q * 8 + p * 2 + hh]);
-                const float sg_ = __fdividef(1.0f, 1.0f + __expf(-gval));
-                r0[hh] = dh * uval * (sg_ * (1.0f + gval * (1.0f - sg_)));  // dG
-                r1[hh] = dh * gval * sg_;                                    // dU
-              }
-              dgw[p] = pack_bf16(r0[0], r0[1]);
-              duw[p] = pack_bf16(r1[0], r1[1]);
-            }
-            reinterpret_cast<uint4*>(dgp)[q] = make_uint4(dgw[0], dgw[1], dgw[2], dgw[3]);
-            reinterpret_cast<uint4*>(dup)[q] = make_uint4(duw[0], duw[1], duw[2], duw[3]);
-          }
-        } else {
+        {
           float* out_row = static_cast<float*>(args.out0) + out_elem;
 #pragma unroll
           for (int q = 0; q < 8; ++q)
