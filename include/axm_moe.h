@@ -287,6 +287,58 @@ AXM_API int axm_moe_adamw_step(float* master, float* m, float* v, const float* g
                                int64_t n, float lr, float beta1, float beta2, float eps,
                                float weight_decay, int32_t step, void* stream);
 
+/* ---- MoE block of the engine's checkpoint file ----------------------------------
+ * The engine's `weights.axiom` (56-byte packed header "AXIOM_V1", fp32 weights, bias,
+ * embeddings, optional transformer block tagged "TXFM"; core/include/config.hpp:41-55,92,
+ * writer core/src/training.cpp:283-392, loader core/src/ai.cpp:273-491) holds no router
+ * or expert tensors, so a model with MoE layers cannot be saved or resumed.  These
+ * entry points keep the MoE weights in a tagged block appended AFTER the transformer
+ * block; the stock loader stops reading after the transformer block, so a file with
+ * the MoE block still loads there.  All of it is host code: no GPU is needed.
+ *
+ * Block layout (little-endian, packed):
+ *   u64 magic = 0x4D4F4558 ("MOEX", written like the engine's 0x5458464D "TXFM" tag)
+ *   u64 version = 1
+ *   u64 d_model, d_ff, num_experts, top_k, num_shared
+ *   u64 flags            bit 0: router bias present
+ *   u64 payload_bytes    bytes of the tensors that follow
+ *   fp32 router_w [D][E]; router_bias [E] (if flagged); w_gate [E][D][F]; w_up [E][D][F];
+ *        w_down [E][F][D]; shared_gate, shared_up [S][D][F]; shared_down [S][F][D] (if S > 0)
+ *   u64 checksum         sum of the payload's 32-bit words, modulo 2^64
+ * fp32 because the engine checkpoints its fp32 master copies; the bf16 working copy
+ * is rebuilt with axm_moe_cast_master.
+ *
+ * save: `path` must be an existing checkpoint WITH a transformer block (the stock
+ *   loader rejects any other tag at that position).  An MoE block already present is
+ *   replaced.  Like the engine's writer: refuses non-finite values, writes
+ *   `path`.tmp, then renames over `path`; on any failure the .tmp is removed and
+ *   `path` is untouched.
+ * probe: fills desc->{d_model, d_ff, num_experts, top_k, num_shared} and *has_bias
+ *   from the block; AXM_ERR_ARGUMENT if the file has none or is damaged.
+ * load: `desc` must match the block; fills the host buffers; verifies sizes, the
+ *   checksum and that every value is finite before anything is returned as valid. */
+typedef struct AxmMoeCheckpoint {
+  float* router_w;    /* HOST fp32, layouts as in AxmMoeTensors */
+  float* router_bias; /* [E] or NULL */
+  float* w_gate;
+  float* w_up;
+  float* w_down;
+  float* shared_gate; /* NULL when num_shared == 0 */
+  float* shared_up;
+  float* shared_down;
+} AxmMoeCheckpoint;
+
+AXM_API int axm_moe_checkpoint_save(const char* path, const AxmMoeDesc* desc,
+                                    const AxmMoeCheckpoint* tensors);
+AXM_API int axm_moe_checkpoint_probe(const char* path, AxmMoeDesc* desc, int32_t* has_bias);
+AXM_API int axm_moe_checkpoint_load(const char* path, const AxmMoeDesc* desc,
+                                    const AxmMoeCheckpoint* tensors);
+
+/* bf16 working copy of an fp32 master matrix (both on the device), n elements,
+ * round-to-nearest-even: what the kernels read after a checkpoint was loaded. */
+AXM_API int axm_moe_cast_master(const float* master, void* w_bf16, size_t n, void* stream);
+
+
 /* Per-segment redirect of the down projection's output: rows of segment s are
  * stored at base + (row0 + i) * D floats instead of into `o` (base == NULL keeps
  * the segment in `o`).  Under expert parallelism base is the source rank's return

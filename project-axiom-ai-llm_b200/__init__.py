@@ -65,6 +65,11 @@ class MoeTrain(ctypes.Structure):
                                                 "d_w_down")])
 
 
+class MoeCheckpoint(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in ("router_w", "router_bias", "w_gate", "w_up", "w_down",
+                                               "shared_gate", "shared_up", "shared_down")]
+
+
 class Segment(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int32) for n in ("a_row0", "out_row0", "rows", "expert")]
 
@@ -118,6 +123,11 @@ def load():
     lib.axm_ep_return.argtypes = [lp, u32, vp, vp, vp, vp, vp]
     lib.axm_ep_wait_return.argtypes = [lp, u32, vp, vp]
     lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
+    cp = ctypes.POINTER(MoeCheckpoint)
+    lib.axm_moe_checkpoint_save.argtypes = [ctypes.c_char_p, dp, cp]
+    lib.axm_moe_checkpoint_probe.argtypes = [ctypes.c_char_p, dp, ctypes.POINTER(i32)]
+    lib.axm_moe_checkpoint_load.argtypes = [ctypes.c_char_p, dp, cp]
+    lib.axm_moe_cast_master.argtypes = [vp, vp, sz, vp]
     _lib = lib
     return lib
 
