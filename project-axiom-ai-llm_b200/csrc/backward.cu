@@ -439,12 +439,14 @@ extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* 
     return rc;
   // auxiliary loss and the constants its gradient needs
   const size_t sm = sizeof(float) * kAuxThreads * (E + 1);
-  cudaFuncSetAttribute(aux_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  static SmemLimitCache aux_cache = {};
+  if (int rc2 = ensure_dynamic_smem(reinterpret_cast<const void*>(aux_partial_kernel), sm, &aux_cache, "aux_partial_kernel"))
+    return rc2;
   aux_partial_kernel<<<AXM_ROUTE_BLOCKS, kAuxThreads, sm, st>>>(w.logits, w.aux_partial, T, E);
   aux_final_kernel<<<1, 256, 0, st>>>(w.aux_partial, w.counts, w.aux_coef, t->aux_loss, T, E, k,
                                       t->aux_alpha);
   if (t->histogram != nullptr)
-    cudaMemcpyAsync(t->histogram, w.counts, sizeof(int32_t) * E, cudaMemcpyDeviceToDevice, st);
+    AXM_CUDA(cudaMemcpyAsync(t->histogram, w.counts, sizeof(int32_t) * E, cudaMemcpyDeviceToDevice, st));
   return check_launch("forward_train");
 }
 
@@ -470,7 +472,9 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
                                         t->d_w_gate, t->d_w_up, t->d_w_down, w.status, stream)))
     return rc;
   const size_t sm = sizeof(float) * kRbThreads * 2 * (E + 1);
-  cudaFuncSetAttribute(router_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)sm);
+  static SmemLimitCache rb_cache = {};
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_bwd_kernel), sm, &rb_cache, "router_bwd_kernel")))
+    return rc;
   router_bwd_kernel<<<(T + kRbThreads - 1) / kRbThreads, kRbThreads, sm, st>>>(
       w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, T, E, k);
   if (t->d_router_w != nullptr) {
@@ -489,13 +493,15 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   if ((int)fgrid.y > T) fgrid.y = T;
   if (desc->router_dtype == AXM_ROUTER_FP32) {
     auto kern = bwd_finalize_kernel<float>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm);
+    static SmemLimitCache cache = {};
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), fsm, &cache, "bwd_finalize_kernel"))) return rc;
     kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
                                   static_cast<const float*>(t->router_w), w.dz, t->d_x, T, D, E, k,
                                   residual, d_tile);
   } else {
     auto kern = bwd_finalize_kernel<__nv_bfloat16>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fsm);
+    static SmemLimitCache cache = {};
+    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), fsm, &cache, "bwd_finalize_kernel"))) return rc;
     kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
                                   static_cast<const __nv_bfloat16*>(t->router_w), w.dz, t->d_x, T, D, E,
                                   k, residual, d_tile);

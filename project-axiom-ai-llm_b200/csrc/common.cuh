@@ -16,6 +16,21 @@ int fail(int status, const char* fmt, ...);
 int check_launch(const char* what);   // cudaGetLastError() -> AXM_ERR_LAUNCH
 int require_device();                 // sm_100 present, else AXM_ERR_DEVICE
 int sm_count();
+int current_device();                 // -1 if none
+// AXM_OK, or AXM_ERR_LAUNCH with the runtime's message for `what`.
+int cuda_status(cudaError_t e, const char* what);
+// Raises the dynamic shared memory limit of a kernel.  Function attributes belong to
+// a device's context, so `cache` remembers per device (up to 64) the largest size
+// already granted and the runtime is only asked when a call needs more.
+struct SmemLimitCache {
+  int granted[64];
+};
+int ensure_dynamic_smem(const void* kernel, size_t bytes, SmemLimitCache* cache, const char* what);
+
+#define AXM_CUDA(call)                                              \
+  do {                                                              \
+    if (int axm_rc_ = ::axm::cuda_status((call), #call)) return axm_rc_; \
+  } while (0)
 
 // ---- device helpers -------------------------------------------------------------
 #if defined(__CUDACC__)

@@ -441,11 +441,10 @@ static int map_wgrad_out(CUtensorMap* m, void* base, uint64_t experts, uint64_t 
 template <int MODE>
 static int launch_bwd(const CUtensorMap& a0, const CUtensorMap& a1, const CUtensorMap& b0,
                       const CUtensorMap& b1, const BwdArgs& args, cudaStream_t st, const char* what) {
-  static std::once_flag once;
-  std::call_once(once, [] {
-    cudaFuncSetAttribute(grouped_bwd_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         (int)BwdCfg<MODE>::kSmemBytes);
-  });
+  static SmemLimitCache smem = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_bwd_kernel<MODE>),
+                                   BwdCfg<MODE>::kSmemBytes, &smem, what))
+    return rc;
   grouped_bwd_kernel<MODE><<<sm_count(), BwdCfg<MODE>::kThreads, BwdCfg<MODE>::kSmemBytes, st>>>(a0, a1, b0, b1,
                                                                                                args);
   return check_launch(what);

@@ -440,11 +440,13 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   }
   if ((rc = make_map_2d(&a2, h, rows_total, F, BM))) return rc;
 
-  static std::once_flag attr_once;
-  std::call_once(attr_once, [] {
-    cudaFuncSetAttribute(grouped_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
-    cudaFuncSetAttribute(grouped_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemmSmemBytes);
-  });
+  static SmemLimitCache smem_swiglu = {}, smem_down = {};
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_kernel<true>), kGemmSmemBytes,
+                                &smem_swiglu, "grouped_gemm_kernel<SwiGLU>")))
+    return rc;
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_kernel<false>), kGemmSmemBytes,
+                                &smem_down, "grouped_gemm_kernel<down>")))
+    return rc;
   const int grid = sm_count();
   GemmArgs ga;
   ga.segments = segments;

@@ -450,34 +450,41 @@ static int map2_weights(CUtensorMap* m, const void* base, uint64_t experts, uint
   return encode_tensor_map(m, base, 3, dims, strides, box);
 }
 
-// Number of CTAs to launch (two per cluster), or 0 when pairs cannot be scheduled.
+// Number of CTAs to launch (two per cluster), or 0 when pairs cannot be scheduled; a
+// negative status when the shared-memory limit could not be raised.  Function attributes
+// and the occupancy answer belong to a device's context, so both are kept per device.
 static int grid_2sm() {
-  static int cached = -1;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    cudaFuncSetAttribute(grouped_gemm_2sm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2SmemBytes);
-    cudaFuncSetAttribute(grouped_gemm_2sm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kGemm2SmemBytes);
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)(sm_count() & ~1), 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
-    cfg.dynamicSmemBytes = kGemm2SmemBytes;
-    cudaLaunchAttribute attr;
-    attr.id = cudaLaunchAttributeClusterDimension;
-    attr.val.clusterDim.x = 2;
-    attr.val.clusterDim.y = 1;
-    attr.val.clusterDim.z = 1;
-    cfg.attrs = &attr;
-    cfg.numAttrs = 1;
-    int clusters = 0;
-    cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_2sm_kernel<true>, &cfg);
-    if (e != cudaSuccess) {
-      cudaGetLastError();
-      clusters = 0;
-    }
-    int want = sm_count() / 2;
-    cached = 2 * (clusters < want ? clusters : want);
-  });
-  return cached;
+  static SmemLimitCache smem_swiglu = {}, smem_down = {};
+  static int cached[64];  // 0 = not asked yet, else grid + 1
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<true>), kGemm2SmemBytes,
+                                   &smem_swiglu, "grouped_gemm_2sm_kernel<SwiGLU>"))
+    return rc;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<false>), kGemm2SmemBytes,
+                                   &smem_down, "grouped_gemm_2sm_kernel<down>"))
+    return rc;
+  const int dev = current_device();
+  if (dev >= 0 && dev < 64 && cached[dev] != 0) return cached[dev] - 1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(sm_count() & ~1), 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = kGemm2SmemBytes;
+  cudaLaunchAttribute attr;
+  attr.id = cudaLaunchAttributeClusterDimension;
+  attr.val.clusterDim.x = 2;
+  attr.val.clusterDim.y = 1;
+  attr.val.clusterDim.z = 1;
+  cfg.attrs = &attr;
+  cfg.numAttrs = 1;
+  int clusters = 0;
+  cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_2sm_kernel<true>, &cfg);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    clusters = 0;
+  }
+  const int want = sm_count() / 2;
+  const int grid = 2 * (clusters < want ? clusters : want);
+  if (dev >= 0 && dev < 64) cached[dev] = grid + 1;
+  return grid;
 }
 
 int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
@@ -487,6 +494,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
                           void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                           cudaEvent_t between, void* save_g, void* save_u) {
   const int grid = grid_2sm();
+  if (grid < 0) return grid;  // status, message already set
   if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
   CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;

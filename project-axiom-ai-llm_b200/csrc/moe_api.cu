@@ -78,6 +78,35 @@ int require_device() {
 
 int sm_count() { return device_info().sms > 0 ? device_info().sms : 148; }
 
+int current_device() {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    cudaGetLastError();
+    return -1;
+  }
+  return dev;
+}
+
+int cuda_status(cudaError_t e, const char* what) {
+  if (e == cudaSuccess) return AXM_OK;
+  cudaGetLastError();  // the error is reported here; do not leave it for a later launch check
+  return fail(AXM_ERR_LAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+int ensure_dynamic_smem(const void* kernel, size_t bytes, SmemLimitCache* cache, const char* what) {
+  if (bytes <= 48u * 1024u) return AXM_OK;  // within the default limit
+  const int dev = current_device();
+  // Racing threads may both ask the runtime; the attribute only ever grows, so that is harmless.
+  if (dev >= 0 && dev < 64 && cache->granted[dev] >= (int)bytes) return AXM_OK;
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail(AXM_ERR_LAUNCH, "%s: %zu bytes of shared memory refused: %s", what, bytes, cudaGetErrorString(e));
+  }
+  if (dev >= 0 && dev < 64) cache->granted[dev] = (int)bytes;
+  return AXM_OK;
+}
+
 int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
                    const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
                    int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
@@ -417,9 +446,9 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
   }
 
   // the copy streams start after whatever the caller already queued on its stream
-  cudaEventRecord(pipe->start, st);
-  cudaStreamWaitEvent(pipe->in, pipe->start, 0);
-  cudaStreamWaitEvent(pipe->out, pipe->start, 0);
+  AXM_CUDA(cudaEventRecord(pipe->start, st));
+  AXM_CUDA(cudaStreamWaitEvent(pipe->in, pipe->start, 0));
+  AXM_CUDA(cudaStreamWaitEvent(pipe->out, pipe->start, 0));
   const int tc = cd.tokens;
   int32_t status[kHostChunksMax] = {};
   int32_t* status_all = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + 2 * chunk_ws);
@@ -430,10 +459,9 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
       break;
     }
     const size_t off = (size_t)t0 * row_bytes;
-    cudaMemcpyAsync(static_cast<char*>(d_x) + off, static_cast<const char*>(h_x) + off,
-                    (size_t)n * row_bytes, cudaMemcpyHostToDevice, pipe->in);
-    cudaEventRecord(pipe->arrived[c], pipe->in);
-    cudaStreamWaitEvent(st, pipe->arrived[c], 0);
+    AXM_CUDA(cudaMemcpyAsync(static_cast<char*>(d_x) + off, static_cast<const char*>(h_x) + off, (size_t)n * row_bytes, cudaMemcpyHostToDevice, pipe->in));
+    AXM_CUDA(cudaEventRecord(pipe->arrived[c], pipe->in));
+    AXM_CUDA(cudaStreamWaitEvent(st, pipe->arrived[c], 0));
     AxmMoeDesc d = *desc;
     d.tokens = n;
     if (c > 0) d.flags |= AXM_FLAG_HIST_ACCUMULATE;  // the histogram covers the whole batch
@@ -446,11 +474,10 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
     if (t->topk_gate) tt.topk_gate = t->topk_gate + (size_t)t0 * k;
     void* ws = static_cast<char*>(workspace) + (size_t)(c & 1) * chunk_ws;
     if (int rc = axm_moe_forward(&d, &tt, ws, chunk_ws, stream)) return rc;
-    cudaMemcpyAsync(status_all + c, carve(&d, ws).status, sizeof(int32_t), cudaMemcpyDeviceToDevice, st);
-    cudaEventRecord(pipe->done[c], st);
-    cudaStreamWaitEvent(pipe->out, pipe->done[c], 0);
-    cudaMemcpyAsync(static_cast<char*>(h_out) + off, static_cast<char*>(d_out) + off,
-                    (size_t)n * row_bytes, cudaMemcpyDeviceToHost, pipe->out);
+    AXM_CUDA(cudaMemcpyAsync(status_all + c, carve(&d, ws).status, sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    AXM_CUDA(cudaEventRecord(pipe->done[c], st));
+    AXM_CUDA(cudaStreamWaitEvent(pipe->out, pipe->done[c], 0));
+    AXM_CUDA(cudaMemcpyAsync(static_cast<char*>(h_out) + off, static_cast<char*>(d_out) + off, (size_t)n * row_bytes, cudaMemcpyDeviceToHost, pipe->out));
   }
   cudaError_t e = cudaStreamSynchronize(pipe->out);
   if (e == cudaSuccess) e = cudaStreamSynchronize(st);

@@ -394,20 +394,23 @@ static size_t router_smem_bytes(int E, bool mma = false) {
 static bool router_use_mma(int E) { return E >= 32 && E % 8 == 0; }
 
 template <typename WT>
-static void launch_router(bool mma, size_t smem, cudaStream_t st, const __nv_bfloat16* x, const WT* w,
+static int launch_router(bool mma, size_t smem, cudaStream_t st, const __nv_bfloat16* x, const WT* w,
                           const float* bias, float* logits, int32_t* idx, float* gate, int32_t* bc,
                           const AxmMoeDesc* d) {
   if (mma) {
     auto kern = router_kernel<WT, false, true>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemLimitCache cache = {};
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem, &cache, "router_kernel")) return rc;
     kern<<<AXM_ROUTE_BLOCKS, kRouterThreads, smem, st>>>(x, w, bias, nullptr, logits, idx, gate, bc,
                                                          d->tokens, d->d_model, d->num_experts, d->top_k);
   } else {
     auto kern = router_kernel<WT, false, false>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    static SmemLimitCache cache = {};
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem, &cache, "router_kernel")) return rc;
     kern<<<AXM_ROUTE_BLOCKS, kRouterThreads, smem, st>>>(x, w, bias, nullptr, logits, idx, gate, bc,
                                                          d->tokens, d->d_model, d->num_experts, d->top_k);
   }
+  return check_launch("router_kernel");
 }
 
 static int validate_route(const AxmMoeDesc* d) {
@@ -437,14 +440,12 @@ extern "C" int axm_moe_router(const AxmMoeDesc* desc, const void* x, const void*
   size_t smem = router_smem_bytes(desc->num_experts, mma);
   const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
   if (desc->router_dtype == AXM_ROUTER_FP32)
-    launch_router<float>(mma, smem, st, xb, static_cast<const float*>(router_w), router_bias, logits,
-                         topk_idx, topk_gate, block_counts, desc);
-  else if (desc->router_dtype == AXM_ROUTER_BF16)
-    launch_router<__nv_bfloat16>(mma, smem, st, xb, static_cast<const __nv_bfloat16*>(router_w),
-                                 router_bias, logits, topk_idx, topk_gate, block_counts, desc);
-  else
-    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", desc->router_dtype);
-  return check_launch("router_kernel");
+    return launch_router<float>(mma, smem, st, xb, static_cast<const float*>(router_w), router_bias, logits,
+                                topk_idx, topk_gate, block_counts, desc);
+  if (desc->router_dtype == AXM_ROUTER_BF16)
+    return launch_router<__nv_bfloat16>(mma, smem, st, xb, static_cast<const __nv_bfloat16*>(router_w),
+                                        router_bias, logits, topk_idx, topk_gate, block_counts, desc);
+  return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", desc->router_dtype);
 }
 
 extern "C" int axm_moe_route_from_logits(const AxmMoeDesc* desc, const float* logits,
@@ -457,7 +458,9 @@ extern "C" int axm_moe_route_from_logits(const AxmMoeDesc* desc, const float* lo
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   size_t smem = router_smem_bytes(desc->num_experts);
   auto kern = router_kernel<float, true, false>;
-  cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static SmemLimitCache cache = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), smem, &cache, "router_kernel(from logits)"))
+    return rc;
   kern<<<AXM_ROUTE_BLOCKS, kRouterThreads, smem, st>>>(nullptr, nullptr, nullptr, logits, nullptr,
                                                        topk_idx, topk_gate, block_counts,
                                                        desc->tokens, desc->d_model,
