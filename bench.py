@@ -361,7 +361,9 @@ def main():
             tf = fl / (stages[n]["ms"] * 1e-3) / 1e12
             stages[n].update({"flops": fl, "tflop_s": tf, "frac_tensor": tf / peaks["bf16_tflops"]})
         a = stages["gate_up_gemm"]["tflop_s"]
-        roofline = {"kernel": "grouped_gemm_kernel<SwiGLU> (gate/up)", "bound": "tensor",
+        two_sm = os.environ.get("AXM_GEMM_2SM", "1")[:1] != "0"
+        roofline = {"kernel": ("grouped_gemm_2sm_kernel<SwiGLU>" if two_sm else "grouped_gemm_kernel<SwiGLU>") +
+                              " (gate/up)", "bound": "tensor",
                     "achieved": a, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": a / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
                     "frac_of_sustained": a / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,

@@ -40,8 +40,8 @@ def test_resume_from_checkpoint(axm, workloads, cuda_device, tmp_path):
         else:
             resumed[n] = dev_master
     torch.cuda.synchronize()
-    a = axm.MoeLayer(w, cfg.tokens, cfg.top_k).forward(x)
-    b = axm.MoeLayer(resumed, cfg.tokens, cfg.top_k).forward(x)
+    a, _ = axm.MoeLayer(w, cfg.tokens, cfg.top_k).forward(x)
+    b, _ = axm.MoeLayer(resumed, cfg.tokens, cfg.top_k).forward(x)
     torch.cuda.synchronize()
     assert torch.equal(a, b)
 

@@ -132,9 +132,10 @@ def test_c2_full_size_properties(axm, workloads, cuda_device):
     assert torch.equal(out4.flip(0), out1)
 
 
-@pytest.mark.parametrize("tokens", [1000, 1024, 4100])
+@pytest.mark.parametrize("tokens", [1000, 1024, 4100, 8200])
 def test_forward_host_matches_forward(axm, workloads, cuda_device, tokens):
-    """1000 tokens run as one piece, 1024 as two pipelined chunks, 4100 as four."""
+    """1000 tokens run as one piece, 1024 as two pipelined chunks, 4100 and 8200 as four even
+    ones (this layer's copies take as long as its compute); an explicit schedule is honoured."""
     cfg = workloads.scaled(workloads.CONFIGS["C2"], tokens=tokens)
     x, w = workloads.make_inputs(cfg, device=cuda_device)
     layer = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
@@ -158,6 +159,17 @@ def test_forward_host_matches_forward(axm, workloads, cuda_device, tokens):
         assert torch.equal(layer.topk_idx, idx) and torch.equal(layer.logits, logits)
     layer.forward_host(h_x, h_out, d_x, d_out, keep_permutation=True)   # one piece
     assert torch.equal(h_out, out.cpu())
+    if tokens == 4100:  # uneven chunks 1:2:1, the default of compute-heavy layers
+        import os
+        os.environ["AXM_HOST_SCHEDULE"] = "1,2,1"
+        try:
+            h_out.zero_()
+            axm.check(layer.lib.axm_moe_forward_host(
+                ctypes.byref(layer.desc), ctypes.byref(t), axm.ptr(h_x), axm.ptr(h_out), axm.ptr(d_x),
+                axm.ptr(d_out), axm.ptr(layer.workspace), layer.workspace.numel(), axm.current_stream()))
+        finally:
+            del os.environ["AXM_HOST_SCHEDULE"]
+        assert torch.equal(h_out, out.cpu()) and torch.equal(layer.histogram, hist)
 
 
 def test_empty_input(axm, workloads, cuda_device):
