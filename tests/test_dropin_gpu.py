@@ -80,3 +80,22 @@ def test_dropin_refuses_what_it_cannot_do(axm, workloads, cuda_device):
     hidden = x.to(cuda_device).clone()
     assert m.forward(hidden, cfg.d_ff) is False      # more than 16 experts
     assert torch.equal(hidden.cpu(), x)
+
+
+def test_engine_moe_test_through_the_dropin(axm, cuda_device):
+    """The engine's own MoE test (core/test/test_ai.cpp:944-1015) against the drop-in library:
+    same shape and checks (histogram of 8 entries summing to 2 * 256, no dead expert,
+    AI::verify_routing_balance's ratio below 3, finite in-place output)."""
+    from test_oracle_cpu import engine_test_inputs, routing_balance_ok
+    x, w = engine_test_inputs()
+    wd = helpers.to_dev(w, cuda_device)
+    m = reference_binding.ReferenceMoe(axm.DROPIN_PATH)
+    m.set_weights(wd["router_w"], wd["w_gate"], wd["w_up"], wd["w_down"])
+    hidden = x.to(cuda_device).clone()
+    assert m.forward(hidden, 64)
+    ok, hist = m.download_counts()
+    assert ok and len(hist) == 8
+    assert sum(hist) == 512 and min(hist) > 0
+    assert routing_balance_ok(hist, 256, 8)
+    assert torch.isfinite(hidden.float()).all()
+    assert not torch.equal(hidden, x.to(cuda_device)), "the hidden states are updated in place"

@@ -142,3 +142,42 @@ def test_golden_small(oracle):
     y, out = oracle.forward(x, w, idx, gates)
     assert (out.view(torch.int16).numpy().view(np.uint16) == g["out_bits"]).all()
     assert (y.view(torch.int16).numpy().view(np.uint16) == g["y_bits"]).all()
+
+
+def engine_test_inputs():
+    """The shape of the engine's own MoE test (core/test/test_ai.cpp:944-1015): 256 tokens drawn
+    uniformly from (-1, 1) in a 32-dim space, 8 experts of width 64, top-2, weights uniform in
+    +-1/sqrt(D) drawn in the order router, gate, up, down as allocate_expert_weights does
+    (core/src/CUDA/util/memory_allocation.cu:543-569).  Seeded Mersenne twisters as there; the draws
+    themselves differ from libstdc++'s distributions, so only the structural checks carry over."""
+    T, D, F, E = 256, 32, 64, 8
+    x = torch.from_numpy(np.random.RandomState(1337).uniform(-1.0, 1.0, (T, D)).astype(np.float32)).bfloat16()
+    rs = np.random.RandomState(1337)
+    lim = 1.0 / np.sqrt(D)
+    draw = lambda *shape: torch.from_numpy(rs.uniform(-lim, lim, shape).astype(np.float32)).bfloat16()
+    w = {"router_w": draw(D, E), "w_gate": draw(E, D, F), "w_up": draw(E, D, F), "w_down": draw(E, F, D)}
+    return x, w
+
+
+def routing_balance_ok(hist, tokens, experts):
+    """The engine's acceptance rule for a routing histogram (AI::verify_routing_balance,
+    core/src/ai.cpp:625-656): every selection counted, no dead expert, hottest expert below
+    three times the mean load."""
+    hist = [int(c) for c in hist]
+    if len(hist) != experts or tokens == 0 or sum(hist) != 2 * tokens or min(hist) <= 0:
+        return False
+    return max(hist) / (sum(hist) / experts) < 3.0
+
+
+def test_engine_moe_test_invariants_hold_for_the_oracle(oracle):
+    x, w = engine_test_inputs()
+    z = oracle.router_logits(x, w["router_w"])
+    idx, gates, _, counts, _ = oracle.route(z, 2)
+    assert len(counts) == 8 and counts.sum() == 512
+    assert (counts > 0).all(), "dead expert"
+    assert routing_balance_ok(counts, 256, 8)
+    assert (idx[:, 0] != idx[:, 1]).all()
+    _, out = oracle.forward(x, w, idx, gates)
+    assert torch.isfinite(out.float()).all()
+    assert not routing_balance_ok([512, 0, 0, 0, 0, 0, 0, 0], 256, 8)
+    assert not routing_balance_ok([200, 45, 45, 45, 45, 44, 44, 44], 256, 8)
