@@ -123,16 +123,6 @@ __device__ __forceinline__ void tma_load_3d(void* dst, const void* tmap, uint64_
       : "memory");
 }
 
-// Untiled bulk copy global -> shared (both 16-byte aligned, size a multiple of 16),
-// completion counted on an mbarrier.
-__device__ __forceinline__ void bulk_g2s(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
-          smem_u32(dst)),
-      "l"(src), "r"(bytes), "r"(smem_u32(bar))
-      : "memory");
-}
-
 // TMA tiled store shared -> global (3-d map), tracked by the issuing thread's bulk
 // group.  Elements outside the tensor's extents are not written.
 __device__ __forceinline__ void tma_store_3d(const void* tmap, const void* src, int x, int y, int z) {

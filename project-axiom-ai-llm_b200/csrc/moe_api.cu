@@ -414,25 +414,21 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
   // hidden behind compute, which asks for many small chunks; but every chunk streams all
   // expert weights from HBM once more, which asks for few.  Measured on the largest
   // workload (8192 tokens, d_model 4096, 8 experts of 14336: 2.8 GB of weights; host link
-  // 29 GB/s in, 57 GB/s out): three chunks 1:2:1 6.03 ms, three even 6.05, 1:3:3:1 6.23,
-  // four even 6.43, six 7.04, against 4.6 ms for the layer alone.  Where the copies take as
+  // 29 GB/s in, 57 GB/s out): three even chunks 6.03 ms, 1:3:3:1 6.23, four even 6.43,
+  // 2:3:3:2 6.55, six 7.04, against 4.6 ms for the layer alone.  Where the copies take as
   // long as the compute (smaller layers), more chunks pay.  So: from 4096 tokens on, three
-  // chunks 1:2:1 if the estimated compute time is well above the copy-in time, else four
-  // even chunks; two from 1024 tokens.  AXM_HOST_CHUNKS = n (1..8) asks for n even chunks,
-  // AXM_HOST_SCHEDULE = "a,b,..." (up to 8 positive integers) for chunks in those proportions.
+  // chunks if the estimated compute time is well above the copy-in time, else four; two
+  // from 1024 tokens.  AXM_HOST_CHUNKS = n (1..8) asks for n even chunks,
+  // AXM_HOST_SCHEDULE = "a,b,..." (up to 8 positive integers) for chunks in those
+  // proportions; a schedule whose largest chunk does not fit twice into the workspace
+  // falls back to even chunks of the same count.
   int weights[kHostChunksMax] = {0};
   int chunks = T >= 4096 ? 4 : (T >= 1024 ? 2 : 1);
   bool uneven = false;
   if (T >= 4096) {
     const double compute_s = 6.0 * T * (double)(k + desc->num_shared) * D * (double)desc->d_ff / 1.3e15;
     const double copy_in_s = (double)T * row_bytes / 28e9;
-    if (compute_s > 1.5 * copy_in_s) {
-      chunks = 3;
-      weights[0] = 1;
-      weights[1] = 2;
-      weights[2] = 1;
-      uneven = true;
-    }
+    if (compute_s > 1.5 * copy_in_s) chunks = 3;
   }
   if (const char* env = getenv("AXM_HOST_CHUNKS")) {
     int v = atoi(env);

@@ -159,9 +159,9 @@ def test_forward_host_matches_forward(axm, workloads, cuda_device, tokens):
         assert torch.equal(layer.topk_idx, idx) and torch.equal(layer.logits, logits)
     layer.forward_host(h_x, h_out, d_x, d_out, keep_permutation=True)   # one piece
     assert torch.equal(h_out, out.cpu())
-    if tokens == 4100:  # uneven chunks 1:2:1, the default of compute-heavy layers
+    if tokens == 4100:  # an explicit uneven schedule
         import os
-        os.environ["AXM_HOST_SCHEDULE"] = "1,2,1"
+        os.environ["AXM_HOST_SCHEDULE"] = "2,3,3,2"
         try:
             h_out.zero_()
             axm.check(layer.lib.axm_moe_forward_host(
