@@ -102,4 +102,11 @@ int encode_tensor_map(CUtensorMap* m, const void* base, int rank, const uint64_t
 int encode_tensor_map_f32(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box);
 
+// Two-SM (cta_group::2) kernels are the default; AXM_GEMM_2SM=0 selects the one-SM kernels.
+bool use_2sm_kernels();
+// Input-gradient GEMM of the backward pass on CTA pairs (grouped_ffn_2sm.cu).
+int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t num_segments,
+                      int32_t rows_total, const void* d_g, const void* d_u, const void* w_gate,
+                      const void* w_up, void* d_xp, int32_t* status, cudaStream_t st);
+
 }  // namespace axm

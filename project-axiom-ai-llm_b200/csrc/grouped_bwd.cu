@@ -13,6 +13,8 @@
 //          SwiGLU derivative with the saved g, u and stores dG, dU (bf16).
 //   kDX    dXp[r, d] = dG_r . Wg[e][d, :] + dU_r . Wu[e][d, :]   one accumulator,
 //          reduction over 2F (first dG x Wg, then dU x Wu); B K-major; fp32 out.
+//          By default this product runs on CTA pairs instead (kModeDX of
+//          grouped_ffn_2sm.cu); the kernel here is the one-SM fallback.
 //   kWGRAD dW[e][m, n] = sum_r A[r, m] * B[r, n] over the expert's rows: both
 //          operands MN-major (rows are the reduction index).  Used for
 //          dWd = h^T dO, dWg = x^T dG, dWu = x^T dU.  Segments must be padded to
@@ -503,7 +505,12 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   a.k_total = F;
   a.out0 = d_xp;
   a.out1 = nullptr;
-  if ((rc = launch_bwd<kDX>(m_dg, m_du, m_wg, m_wu, a, st, "grouped_bwd_kernel<dX>"))) return rc;
+  rc = AXM_ERR_DEVICE;
+  if (use_2sm_kernels())
+    rc = launch_bwd_dx_2sm(desc, segments, num_segments, rows_total, d_g, d_u, w_gate, w_up, d_xp, status, st);
+  if (rc == AXM_ERR_DEVICE)  // pairs not wanted or not schedulable: the one-SM kernel
+    rc = launch_bwd<kDX>(m_dg, m_du, m_wg, m_wu, a, st, "grouped_bwd_kernel<dX>");
+  if (rc) return rc;
   if (!wgrad) return AXM_OK;
 
   CUtensorMap k_h, k_do, k_x, k_dg, k_du;  // 64-row boxes: rows are the reduction index

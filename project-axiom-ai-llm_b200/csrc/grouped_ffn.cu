@@ -365,7 +365,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
                           void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                           cudaEvent_t between, void* save_g, void* save_u);
 
-static bool use_2sm() {
+bool use_2sm_kernels() {
   static int v = -1;
   if (v < 0) {
     // two-SM (cta_group::2) kernels are the default forward path; AXM_GEMM_2SM=0 selects
@@ -412,7 +412,7 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       const void* shared_gate, const void* shared_up, const void* shared_down,
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                       cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u) {
-  if (remote == nullptr && use_2sm())
+  if (remote == nullptr && use_2sm_kernels())
     return launch_expert_ffn_2sm(d, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate, w_up,
                                  w_down, shared_gate, shared_up, shared_down, h, o, rows_total, status, st,
                                  between, save_g, save_u);

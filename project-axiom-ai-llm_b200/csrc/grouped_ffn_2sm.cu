@@ -11,6 +11,13 @@
 // reference engine); same weight layouts consumed as stored (MN-major B operand).
 // The two m-tiles of a pair are any two consecutive m-tiles of one expert group, so
 // ragged experts cost no extra padding; an odd tile count leaves one half idle.
+//
+// Modes: kModeDown (h . Wd, fp32 rows), kModeSwiGLU (x . [Wg | Wu] -> h), and kModeDX, the
+// backward input gradient dXp = dG . Wg^T + dU . Wu^T: one accumulator over a reduction of
+// 2F (first dG with Wg, then dU with Wu), the weights read K-major as stored ([E][D][F], the
+// reduction index f contiguous), each CTA staging 128 of the tile's 256 output columns d.
+// The one-SM kernels move 48 KB per k-block and CTA through L2; at about 16 TB/s summed over
+// the SMs that, not the tensor pipe, bounds them - the pair form moves 32 KB.
 #include <mutex>
 
 #include "gemm_common.cuh"
@@ -37,6 +44,8 @@ struct __align__(8) GemmShared2 {
 };
 
 constexpr size_t kGemm2SmemBytes = 1024 + (size_t)kStages2 * kStageBytes2 + sizeof(GemmShared2);
+
+enum { kModeDown = 0, kModeSwiGLU = 1, kModeDX = 2 };
 
 struct Gemm2Args {
   const AxmSegment* segments;
@@ -122,6 +131,9 @@ __device__ __forceinline__ void tc_mma2_bf16(uint32_t d_tmem, uint64_t desc_a, u
 constexpr uint32_t kInstrDesc2 = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
                                  ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 
+// the same with a K-major B operand (kModeDX)
+constexpr uint32_t kInstrDesc2KB = kInstrDesc2 & ~(1u << 16);
+
 struct UnitCoord {
   int seg;      // segment of this CTA's m-tile (valid only if live)
   int m_tile;
@@ -170,12 +182,14 @@ __device__ __forceinline__ UnitCoord decode_unit(const GemmShared2* sh, int n_ti
   return uc;
 }
 
-template <bool kSwiGLU>
+template <int kMode>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_alt,
                         const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                         const __grid_constant__ CUtensorMap tm_b0_sh, const __grid_constant__ CUtensorMap tm_b1_sh,
                         Gemm2Args args) {
+  constexpr bool kSwiGLU = kMode == kModeSwiGLU;
+  constexpr bool kDX = kMode == kModeDX;
   extern __shared__ unsigned char smem_raw[];
   // both CTAs of a pair compute the same offsets, so their tiles sit at the same place
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
@@ -190,7 +204,8 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   const int num_clusters = gridDim.x >> 1;
   constexpr int BN_OUT = kSwiGLU ? 128 : 256;
   const int n_tiles = (args.n_total + BN_OUT - 1) / BN_OUT;
-  const int k_blocks = (args.k_total + BK - 1) / BK;
+  const int kb_half = (args.k_total + BK - 1) / BK;
+  const int k_blocks = kDX ? 2 * kb_half : kb_half;  // kModeDX: dG x Wg, then dU x Wu
   const int nseg = args.num_segments;
 
   for (int s = threadIdx.x; s < nseg; s += kGemmThreads) sh->seg[s] = args.segments[s];
@@ -281,9 +296,17 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           // the leader's barrier counts the bytes of both CTAs
           if (rank == 0) mbar_expect_tx(&sh->full[stage], 2 * kStageBytes2);
           const uint32_t bar = map_to_cta(smem_u32(&sh->full[stage]), 0);
-          tma2_load_2d(sa, ma, bar, kb * BK, a_row);
-          tma2_load_3d(sb, mb, bar, n_col, kb * BK, e);
-          tma2_load_3d(sb + kBChunkBytes, mb, bar, n_col + 64, kb * BK, e);
+          if constexpr (kDX) {
+            const bool second = kb >= kb_half;
+            const int kk = (second ? kb - kb_half : kb) * BK;
+            tma2_load_2d(sa, second ? &tm_a_alt : &tm_a, bar, kk, a_row);
+            // K-major weights: one box of 64 k x 128 output columns
+            tma2_load_3d(sb, second ? &tm_b1 : &tm_b0, bar, kk, n_col, e);
+          } else {
+            tma2_load_2d(sa, ma, bar, kb * BK, a_row);
+            tma2_load_3d(sb, mb, bar, n_col, kb * BK, e);
+            tma2_load_3d(sb + kBChunkBytes, mb, bar, n_col + 64, kb * BK, e);
+          }
           if (++stage == kStages2) {
             stage = 0;
             phase ^= 1u;
@@ -316,11 +339,12 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           const uint32_t sa = smem_u32(tiles + (size_t)stage * kStageBytes2);
           const uint32_t sb = sa + kABytes;
           const uint64_t da = make_smem_desc(sa, 16, 1024);
-          const uint64_t db = make_smem_desc(sb, kBChunkBytes, 1024);
+          // MN-major B: 64-wide chunks 8192 B apart, +2048 B per 16 k; K-major B (kModeDX): like A
+          const uint64_t db = kDX ? make_smem_desc(sb, 16, 1024) : make_smem_desc(sb, kBChunkBytes, 1024);
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j)
-            tc_mma2_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * 128), kInstrDesc2,
-                         (kb > 0 || j > 0) ? 1u : 0u);
+            tc_mma2_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * (kDX ? 2 : 128)),
+                         kDX ? kInstrDesc2KB : kInstrDesc2, (kb > 0 || j > 0) ? 1u : 0u);
           // free this stage in both CTAs once the MMAs that read it are done
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 0));
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 1));
@@ -427,7 +451,7 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     long long t0 = clock64();
     while (clock64() - t0 < 4000000LL) {
     }
-    if (threadIdx.x == 0 && args.status != nullptr) atomicExch(args.status, kSwiGLU ? 6 : 7);
+    if (threadIdx.x == 0 && args.status != nullptr) atomicExch(args.status, kSwiGLU ? 6 : (kDX ? 8 : 7));
   }
   cluster_sync_all();
   if (warp == 1) {
@@ -456,10 +480,10 @@ static int map2_weights(CUtensorMap* m, const void* base, uint64_t experts, uint
 static int grid_2sm() {
   static SmemLimitCache smem_swiglu = {}, smem_down = {};
   static int cached[64];  // 0 = not asked yet, else grid + 1
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<true>), kGemm2SmemBytes,
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<kModeSwiGLU>), kGemm2SmemBytes,
                                    &smem_swiglu, "grouped_gemm_2sm_kernel<SwiGLU>"))
     return rc;
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<false>), kGemm2SmemBytes,
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<kModeDown>), kGemm2SmemBytes,
                                    &smem_down, "grouped_gemm_2sm_kernel<down>"))
     return rc;
   const int dev = current_device();
@@ -476,7 +500,7 @@ static int grid_2sm() {
   cfg.attrs = &attr;
   cfg.numAttrs = 1;
   int clusters = 0;
-  cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_2sm_kernel<true>, &cfg);
+  cudaError_t e = cudaOccupancyMaxActiveClusters(&clusters, grouped_gemm_2sm_kernel<kModeSwiGLU>, &cfg);
   if (e != cudaSuccess) {
     cudaGetLastError();
     clusters = 0;
@@ -528,7 +552,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.out = h;
   ga.save_g = static_cast<__nv_bfloat16*>(save_g);
   ga.save_u = static_cast<__nv_bfloat16*>(save_u);
-  grouped_gemm_2sm_kernel<true><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
+  grouped_gemm_2sm_kernel<kModeSwiGLU><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
   if ((rc = check_launch("grouped_gemm_2sm_kernel<swiglu>"))) return rc;
   if (between != nullptr) cudaEventRecord(between, st);
   ga.n_total = D;
@@ -536,8 +560,51 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.out = o;
   ga.save_g = nullptr;
   ga.save_u = nullptr;
-  grouped_gemm_2sm_kernel<false><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
+  grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_2sm_kernel<down>");
+}
+
+// Weights [experts][n_rows][k_cols] read K-major by a CTA pair: box = 64 k x 128 n x 1 expert.
+static int map2_weights_kmajor(CUtensorMap* m, const void* base, uint64_t experts, uint64_t n_rows,
+                               uint64_t k_cols) {
+  const uint64_t dims[3] = {k_cols, n_rows, experts};
+  const uint64_t strides[2] = {k_cols * 2, k_cols * n_rows * 2};
+  const uint32_t box[3] = {64, 128, 1};
+  return encode_tensor_map(m, base, 3, dims, strides, box);
+}
+
+// dXp[r, :] = dG[r, :] . Wg[e]^T + dU[r, :] . Wu[e]^T over the segments' rows (fp32 out).
+// Returns AXM_ERR_DEVICE when pairs cannot be scheduled, so that the caller can fall back.
+int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t num_segments,
+                      int32_t rows_total, const void* d_g, const void* d_u, const void* w_gate,
+                      const void* w_up, void* d_xp, int32_t* status, cudaStream_t st) {
+  static SmemLimitCache smem_dx = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<kModeDX>), kGemm2SmemBytes,
+                                   &smem_dx, "grouped_gemm_2sm_kernel<dX>"))
+    return rc;
+  const int grid = grid_2sm();
+  if (grid < 0) return grid;
+  if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
+  const int D = d->d_model, F = d->d_ff, E = d->num_experts;
+  CUtensorMap m_dg, m_du, m_wg, m_wu;
+  int rc;
+  if ((rc = map2_rows(&m_dg, d_g, (uint64_t)rows_total, F))) return rc;
+  if ((rc = map2_rows(&m_du, d_u, (uint64_t)rows_total, F))) return rc;
+  if ((rc = map2_weights_kmajor(&m_wg, w_gate, E, D, F))) return rc;
+  if ((rc = map2_weights_kmajor(&m_wu, w_up, E, D, F))) return rc;
+  Gemm2Args ga;
+  ga.segments = segments;
+  ga.num_segments = num_segments;
+  ga.routed_experts = E;
+  ga.status = status;
+  ga.n_total = D;
+  ga.k_total = F;
+  ga.out = d_xp;
+  ga.save_g = nullptr;
+  ga.save_u = nullptr;
+  grouped_gemm_2sm_kernel<kModeDX><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(m_dg, m_du, m_wg, m_wu, m_wg,
+                                                                                m_wu, ga);
+  return check_launch("grouped_gemm_2sm_kernel<dX>");
 }
 
 }  // namespace axm
