@@ -524,14 +524,19 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   if ((rc = map_wgrad_out(&o_wg, d_w_gate, E, D, F))) return rc;
   if ((rc = map_wgrad_out(&o_wu, d_w_up, E, D, F))) return rc;
   a.k_total = 0;
-  a.m_total = F;  // dWd[e] = h^T dO : [F][D]
-  a.n_total = D;
-  a.out0 = d_w_down;
-  if ((rc = launch_bwd<kWGRAD>(k_h, o_wd, k_do, k_do, a, st, "grouped_bwd_kernel<dWd>"))) return rc;
-  a.m_total = D;  // dWg[e] = x^T dG : [D][F]
-  a.n_total = F;
-  a.out0 = d_w_gate;
-  if ((rc = launch_bwd<kWGRAD>(k_x, o_wg, k_dg, k_dg, a, st, "grouped_bwd_kernel<dWg>"))) return rc;
-  a.out0 = d_w_up;
-  return launch_bwd<kWGRAD>(k_x, o_wu, k_du, k_du, a, st, "grouped_bwd_kernel<dWu>");
+  // each product on CTA pairs by default, on the one-SM kernel if pairs are not wanted or not schedulable
+  auto wgrad_one = [&](const void* am, const CUtensorMap& ka, int m_total, const void* bm, const CUtensorMap& kb,
+                       int n_total, void* out, const CUtensorMap& omap, const char* what) -> int {
+    int r = AXM_ERR_DEVICE;
+    if (use_2sm_kernels())
+      r = launch_wgrad_2sm(segments, num_segments, rows_total, E, am, m_total, bm, n_total, out, status, st);
+    if (r != AXM_ERR_DEVICE) return r;
+    a.m_total = m_total;
+    a.n_total = n_total;
+    a.out0 = out;
+    return launch_bwd<kWGRAD>(ka, omap, kb, kb, a, st, what);
+  };
+  if ((rc = wgrad_one(h, k_h, F, d_o, k_do, D, d_w_down, o_wd, "grouped_bwd_kernel<dWd>"))) return rc;  // h^T dO : [F][D]
+  if ((rc = wgrad_one(x_perm, k_x, D, d_g, k_dg, F, d_w_gate, o_wg, "grouped_bwd_kernel<dWg>"))) return rc;  // x^T dG : [D][F]
+  return wgrad_one(x_perm, k_x, D, d_u, k_du, F, d_w_up, o_wu, "grouped_bwd_kernel<dWu>");
 }
