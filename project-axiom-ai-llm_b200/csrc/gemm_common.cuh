@@ -108,6 +108,10 @@ bool use_2sm_kernels();
 int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t num_segments,
                       int32_t rows_total, const void* d_g, const void* d_u, const void* w_gate,
                       const void* w_up, void* d_xp, int32_t* status, cudaStream_t st);
+// dH GEMM of the backward pass with the SwiGLU derivative, on CTA pairs (grouped_ffn_2sm.cu).
+int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t num_segments,
+                      int32_t rows_total, const void* d_o, const void* w_down, const void* g, const void* u,
+                      void* d_g, void* d_u, int32_t* status, cudaStream_t st);
 // Weight-gradient GEMM of the backward pass on CTA pairs (grouped_bwd_2sm.cu).
 int launch_wgrad_2sm(const AxmSegment* segments, int32_t num_segments, int32_t rows_total, int32_t experts,
                      const void* a, int32_t m_total, const void* b, int32_t n_total, void* d_w,

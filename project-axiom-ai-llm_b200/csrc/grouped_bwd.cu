@@ -28,6 +28,7 @@
 // row per lane the L1 path, not the tensor pipe, had set the pace (eight epilogue warps
 // instead of four did not help, which is how that showed).
 #include <cstdio>
+#include <cstdlib>
 #include <mutex>
 
 #include "gemm_common.cuh"
@@ -499,7 +500,16 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   a.k_total = D;
   a.out0 = d_g;
   a.out1 = d_u;
-  if ((rc = launch_bwd<kDH>(m_do, m_do, m_wd, m_wd, a, st, "grouped_bwd_kernel<dH>"))) return rc;
+  rc = AXM_ERR_DEVICE;
+  static const bool dh_pairs = [] {  // opt-in until it has run against the tests on hardware
+    const char* e = getenv("AXM_DH_2SM");
+    return e != nullptr && e[0] == '1';
+  }();
+  if (dh_pairs && use_2sm_kernels())
+    rc = launch_bwd_dh_2sm(desc, segments, num_segments, rows_total, d_o, w_down, g, u, d_g, d_u, status, st);
+  if (rc == AXM_ERR_DEVICE)  // pairs not wanted or not schedulable: the one-SM kernel
+    rc = launch_bwd<kDH>(m_do, m_do, m_wd, m_wd, a, st, "grouped_bwd_kernel<dH>");
+  if (rc) return rc;
   // dXp = dG . Wg^T + dU . Wu^T
   a.n_total = D;
   a.k_total = F;

@@ -16,6 +16,9 @@
 // backward input gradient dXp = dG . Wg^T + dU . Wu^T: one accumulator over a reduction of
 // 2F (first dG with Wg, then dU with Wu), the weights read K-major as stored ([E][D][F], the
 // reduction index f contiguous), each CTA staging 128 of the tile's 256 output columns d.
+// kModeDH is the other backward product on the rows, dH = dO . Wd^T (Wd as stored, [E][F][D], is
+// K-major for it), with the SwiGLU derivative in the epilogue: the saved g, u come in and dG, dU
+// go out through a per-warp staging block in row-contiguous 64-byte runs (see grouped_bwd.cu).
 // The one-SM kernels move 48 KB per k-block and CTA through L2; at about 16 TB/s summed over
 // the SMs that, not the tensor pipe, bounds them - the pair form moves 32 KB.
 #include <mutex>
@@ -24,7 +27,7 @@
 
 namespace axm {
 
-enum { kModeDown = 0, kModeSwiGLU = 1, kModeDX = 2 };
+enum { kModeDown = 0, kModeSwiGLU = 1, kModeDX = 2, kModeDH = 3 };
 
 struct Gemm2Args {
   const AxmSegment* segments;
@@ -33,8 +36,9 @@ struct Gemm2Args {
   int k_total;
   int routed_experts;
   void* out;
-  __nv_bfloat16* save_g;  // training: also store the gate / up pre-activations (bf16), or null
-  __nv_bfloat16* save_u;
+  __nv_bfloat16* save_g;  // training: also store the gate / up pre-activations (bf16), or null;
+  __nv_bfloat16* save_u;  //   kModeDH: the saved pre-activations, read
+  void* out1;             // kModeDH: dU (out is dG)
   int* status;
 };
 
@@ -101,11 +105,16 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
                         Gemm2Args args) {
   constexpr bool kSwiGLU = kMode == kModeSwiGLU;
   constexpr bool kDX = kMode == kModeDX;
+  constexpr bool kDH = kMode == kModeDH;
+  constexpr bool kBKmajor = kDX || kDH;  // weights read K-major: one box of 64 k x 128 columns per CTA
   extern __shared__ unsigned char smem_raw[];
   // both CTAs of a pair compute the same offsets, so their tiles sit at the same place
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   GemmShared2* sh = reinterpret_cast<GemmShared2*>(tiles + (size_t)kStages2 * kStageBytes2);
+  // kModeDH: 4 KiB per epilogue warp behind the control block
+  unsigned char* staging = reinterpret_cast<unsigned char*>(
+      (reinterpret_cast<uintptr_t>(sh + 1) + 127) & ~static_cast<uintptr_t>(127));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -207,7 +216,10 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           // the leader's barrier counts the bytes of both CTAs
           if (rank == 0) mbar_expect_tx(&sh->full[stage], 2 * kStageBytes2);
           const uint32_t bar = map_to_cta(smem_u32(&sh->full[stage]), 0);
-          if constexpr (kDX) {
+          if constexpr (kDH) {
+            tma2_load_2d(sa, &tm_a, bar, kb * BK, a_row);
+            tma2_load_3d(sb, &tm_b0, bar, kb * BK, n_col, e);
+          } else if constexpr (kDX) {
             const bool second = kb >= kb_half;
             const int kk = (second ? kb - kb_half : kb) * BK;
             tma2_load_2d(sa, second ? &tm_a_alt : &tm_a, bar, kk, a_row);
@@ -251,11 +263,11 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           const uint32_t sb = sa + kABytes;
           const uint64_t da = make_smem_desc(sa, 16, 1024);
           // MN-major B: 64-wide chunks 8192 B apart, +2048 B per 16 k; K-major B (kModeDX): like A
-          const uint64_t db = kDX ? make_smem_desc(sb, 16, 1024) : make_smem_desc(sb, kBChunkBytes, 1024);
+          const uint64_t db = kBKmajor ? make_smem_desc(sb, 16, 1024) : make_smem_desc(sb, kBChunkBytes, 1024);
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j)
-            tc_mma2_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * (kDX ? 2 : 128)),
-                         kDX ? kInstrDesc2KB : kInstrDesc2, (kb > 0 || j > 0) ? 1u : 0u);
+            tc_mma2_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * (kBKmajor ? 2 : 128)),
+                         kBKmajor ? kInstrDesc2KB : kInstrDesc2, (kb > 0 || j > 0) ? 1u : 0u);
           // free this stage in both CTAs once the MMAs that read it are done
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 0));
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 1));
@@ -288,7 +300,92 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       const int n0 = uc.n_tile * BN_OUT;
       const size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
-      if (uc.live) {
+      if constexpr (kDH) {
+        // The SwiGLU derivative with the saved g, u: dG = dH u s (1 + g (1 - s)), dU = dH g s,
+        // s = sigmoid(g) (core/src/CUDA/kernel/swiglu.cu:34-55 of the reference engine).
+        // g, u, dG, dU move between global memory and the warp's staging block in row-contiguous
+        // 64-byte runs; piece p of a 32 x 32 bf16 block: row p / 4, 16-byte piece p % 4, in shared
+        // memory at row * 64 + ((piece ^ (row / 2 % 4)) * 16 (no bank conflicts either way).  The
+        // pieces of the next 32 columns are fetched while the current ones are worked on.
+        unsigned char* g_s = staging + (size_t)((warp - 2) & 3) * 4096;
+        unsigned char* u_s = g_s + 2048;
+        const int rows_left = uc.live ? sg.rows - (uc.m_tile * BM + quad * 32) : 0;
+        const size_t block_elem = (size_t)(sg.out_row0 + uc.m_tile * BM + quad * 32) * args.n_total + n0;
+        auto piece_ok = [&](int p, int c0) {
+          return (p >> 2) < rows_left && c0 < BN_OUT && n0 + c0 + (p & 3) * 8 < args.n_total;
+        };
+        auto piece_elem = [&](int p, int c0) { return block_elem + (size_t)(p >> 2) * args.n_total + c0 + (p & 3) * 8; };
+        auto piece_smem = [&](int row, int piece) { return row * 64 + ((piece ^ ((row >> 1) & 3)) << 4); };
+        uint4 g_next[4], u_next[4];
+        auto fetch_gu = [&](int c0) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int p = lane + 32 * i;
+            g_next[i] = make_uint4(0, 0, 0, 0);
+            u_next[i] = make_uint4(0, 0, 0, 0);
+            if (piece_ok(p, c0)) {
+              g_next[i] = __ldg(reinterpret_cast<const uint4*>(args.save_g + piece_elem(p, c0)));
+              u_next[i] = __ldg(reinterpret_cast<const uint4*>(args.save_u + piece_elem(p, c0)));
+            }
+          }
+        };
+        if (uc.live) {
+          fetch_gu(0);
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
+            uint32_t v[32];
+            __syncwarp();  // the previous block's read-back is done; also rejoins the warp for tcgen05.ld
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int p = lane + 32 * i;
+              *reinterpret_cast<uint4*>(g_s + piece_smem(p >> 2, p & 3)) = g_next[i];
+              *reinterpret_cast<uint4*>(u_s + piece_smem(p >> 2, p & 3)) = u_next[i];
+            }
+            fetch_gu(c0 + 32);
+            __syncwarp();
+            tmem_ld32(t_addr + c0, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint4* gp = reinterpret_cast<uint4*>(g_s + piece_smem(lane, q));
+              uint4* up = reinterpret_cast<uint4*>(u_s + piece_smem(lane, q));
+              const uint4 gv = *gp;
+              const uint4 uv = *up;
+              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+              const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+              uint32_t dgw[4], duw[4];
+#pragma unroll
+              for (int pp = 0; pp < 4; ++pp) {
+                float r0[2], r1[2];
+#pragma unroll
+                for (int hh = 0; hh < 2; ++hh) {
+                  const float gval = hh ? bf16_hi(gw[pp]) : bf16_lo(gw[pp]);
+                  const float uval = hh ? bf16_hi(uw[pp]) : bf16_lo(uw[pp]);
+                  const float dh = __uint_as_float(v[q * 8 + pp * 2 + hh]);
+                  const float sg_ = __fdividef(1.0f, 1.0f + __expf(-gval));
+                  r0[hh] = dh * uval * (sg_ * (1.0f + gval * (1.0f - sg_)));  // dG
+                  r1[hh] = dh * gval * sg_;                                    // dU
+                }
+                dgw[pp] = pack_bf16(r0[0], r0[1]);
+                duw[pp] = pack_bf16(r1[0], r1[1]);
+              }
+              *gp = make_uint4(dgw[0], dgw[1], dgw[2], dgw[3]);  // in place: the lane's own row
+              *up = make_uint4(duw[0], duw[1], duw[2], duw[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int p = lane + 32 * i;
+              if (piece_ok(p, c0)) {
+                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out) + piece_elem(p, c0)) =
+                    *reinterpret_cast<const uint4*>(g_s + piece_smem(p >> 2, p & 3));
+                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out1) + piece_elem(p, c0)) =
+                    *reinterpret_cast<const uint4*>(u_s + piece_smem(p >> 2, p & 3));
+              }
+            }
+          }
+        }
+      } else if (uc.live) {
 #pragma unroll 1
         for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
           uint32_t g[32];
@@ -362,7 +459,7 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     long long t0 = clock64();
     while (clock64() - t0 < 4000000LL) {
     }
-    if (threadIdx.x == 0 && args.status != nullptr) atomicExch(args.status, kSwiGLU ? 6 : (kDX ? 8 : 7));
+    if (threadIdx.x == 0 && args.status != nullptr) atomicExch(args.status, kSwiGLU ? 6 : (kDX ? 8 : (kDH ? 10 : 7)));
   }
   cluster_sync_all();
   if (warp == 1) {
@@ -471,6 +568,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.out = o;
   ga.save_g = nullptr;
   ga.save_u = nullptr;
+  ga.out1 = nullptr;
   grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_2sm_kernel<down>");
 }
@@ -482,6 +580,42 @@ static int map2_weights_kmajor(CUtensorMap* m, const void* base, uint64_t expert
   const uint64_t strides[2] = {k_cols * 2, k_cols * n_rows * 2};
   const uint32_t box[3] = {64, 128, 1};
   return encode_tensor_map(m, base, 3, dims, strides, box);
+}
+
+// dH = dO . Wd[e]^T with the SwiGLU derivative in the epilogue: dG, dU (bf16) from the saved g, u.
+// AXM_ERR_DEVICE when pairs cannot be scheduled, so that the caller can fall back.
+constexpr size_t kGemm2DhSmemBytes = kGemm2SmemBytes + 128 + 4 * 4096;
+static_assert(kGemm2DhSmemBytes <= 227u * 1024u, "shared memory of the pair dH kernel");
+
+int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t num_segments,
+                      int32_t rows_total, const void* d_o, const void* w_down, const void* g, const void* u,
+                      void* d_g, void* d_u, int32_t* status, cudaStream_t st) {
+  static SmemLimitCache smem_dh = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_2sm_kernel<kModeDH>), kGemm2DhSmemBytes,
+                                   &smem_dh, "grouped_gemm_2sm_kernel<dH>"))
+    return rc;
+  const int grid = grid_2sm();
+  if (grid < 0) return grid;
+  if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
+  const int D = d->d_model, F = d->d_ff, E = d->num_experts;
+  CUtensorMap m_do, m_wd;
+  int rc;
+  if ((rc = map2_rows(&m_do, d_o, (uint64_t)rows_total, D))) return rc;
+  if ((rc = map2_weights_kmajor(&m_wd, w_down, E, F, D))) return rc;
+  Gemm2Args ga;
+  ga.segments = segments;
+  ga.num_segments = num_segments;
+  ga.routed_experts = E;
+  ga.status = status;
+  ga.n_total = F;
+  ga.k_total = D;
+  ga.out = d_g;
+  ga.out1 = d_u;
+  ga.save_g = static_cast<__nv_bfloat16*>(const_cast<void*>(g));
+  ga.save_u = static_cast<__nv_bfloat16*>(const_cast<void*>(u));
+  grouped_gemm_2sm_kernel<kModeDH><<<grid, kGemmThreads, kGemm2DhSmemBytes, st>>>(m_do, m_do, m_wd, m_wd, m_wd,
+                                                                                  m_wd, ga);
+  return check_launch("grouped_gemm_2sm_kernel<dH>");
 }
 
 // dXp[r, :] = dG[r, :] . Wg[e]^T + dU[r, :] . Wu[e]^T over the segments' rows (fp32 out).
@@ -513,6 +647,7 @@ int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.out = d_xp;
   ga.save_g = nullptr;
   ga.save_u = nullptr;
+  ga.out1 = nullptr;
   grouped_gemm_2sm_kernel<kModeDX><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(m_dg, m_du, m_wg, m_wu, m_wg,
                                                                                 m_wu, ga);
   return check_launch("grouped_gemm_2sm_kernel<dX>");
