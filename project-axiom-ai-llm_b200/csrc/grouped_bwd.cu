@@ -248,10 +248,43 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
       const TileCoord tc = decode_bwd<MODE>(sh, nseg, n_tiles, m_tiles_w, tile);
       const AxmSegment sg = sh->seg[tc.seg];
       const int k_blocks = tile_k_blocks(sg);
+      const int n0 = tc.n_tile * UMMA_N;
+      // kDH: g, u, dG, dU move between global memory and the warp's staging block in
+      // row-contiguous 64-byte runs (a request touches 8 rows, not 32), and each lane
+      // works on its own row out of shared memory.  Piece p of a 32 x 32 bf16 block:
+      // row p / 4, 16-byte piece p % 4; in shared memory at row * 64 + ((piece ^ (row / 2 % 4)) * 16,
+      // which keeps both access patterns free of bank conflicts.  g and u stream from HBM, so
+      // their pieces are fetched two blocks ahead, the first two before the accumulator is
+      // even waited for: with one block of lead every block had cost a memory latency.
+      uint4 g_q0[4], u_q0[4], g_q1[4], u_q1[4];  // 128 pieces per 32 x 32 block: four per lane and tensor
+      const int rows_left = sg.rows - (tc.m_tile * BM + quad * 32);  // rows of this warp's block
+      auto piece_ok = [&](int p, int c0) {
+        return (p >> 2) < rows_left && c0 < c_end && n0 + c0 + (p & 3) * 8 < args.n_total;
+      };
+      auto piece_elem = [&](int p, int c0) {
+        return (size_t)(sg.out_row0 + tc.m_tile * BM + quad * 32 + (p >> 2)) * args.n_total + n0 + c0 +
+               (p & 3) * 8;
+      };
+      auto piece_smem = [&](int row, int piece) { return row * 64 + ((piece ^ ((row >> 1) & 3)) << 4); };
+      auto fetch_gu = [&](int c0, uint4 (&gq)[4], uint4 (&uq)[4]) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int p = lane + 32 * i;
+          gq[i] = make_uint4(0, 0, 0, 0);
+          uq[i] = make_uint4(0, 0, 0, 0);
+          if (piece_ok(p, c0)) {
+            gq[i] = __ldg(reinterpret_cast<const uint4*>(args.g + piece_elem(p, c0)));
+            uq[i] = __ldg(reinterpret_cast<const uint4*>(args.u + piece_elem(p, c0)));
+          }
+        }
+      };
+      if constexpr (MODE == kDH) {
+        fetch_gu(c_begin, g_q0, u_q0);
+        fetch_gu(c_begin + 32, g_q1, u_q1);
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag))) break;
       tc_fence_after();
       const int row_in_tile = tc.m_tile * BM + quad * 32 + lane;
-      const int n0 = tc.n_tile * UMMA_N;
       bool row_ok;
       size_t out_elem;
       if constexpr (MODE == kWGRAD) {
@@ -262,51 +295,19 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
         out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_tile : 0)) * args.n_total + n0;
       }
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
-      // kDH: g, u, dG, dU move between global memory and the warp's staging block in
-      // row-contiguous 64-byte runs (a request touches 8 rows, not 32), and each lane
-      // works on its own row out of shared memory.  Piece p of a 32 x 32 bf16 block:
-      // row p / 4, 16-byte piece p % 4; in shared memory at row * 64 + ((piece ^ (row / 2 % 4)) * 16,
-      // which keeps both access patterns free of bank conflicts.  The pieces of the next
-      // 32 columns are fetched while the current ones are worked on.
-      uint4 g_next[4], u_next[4];  // 128 pieces per 32 x 32 block: four per lane and tensor
-      const int rows_left = sg.rows - (tc.m_tile * BM + quad * 32);  // rows of this warp's block
-      auto piece_ok = [&](int p, int c0) {
-        return (p >> 2) < rows_left && c0 < c_end && n0 + c0 + (p & 3) * 8 < args.n_total;
-      };
-      auto piece_elem = [&](int p, int c0) {
-        return (size_t)(sg.out_row0 + tc.m_tile * BM + quad * 32 + (p >> 2)) * args.n_total + n0 + c0 +
-               (p & 3) * 8;
-      };
-      auto piece_smem = [&](int row, int piece) { return row * 64 + ((piece ^ ((row >> 1) & 3)) << 4); };
-      auto fetch_gu = [&](int c0) {
-        if constexpr (MODE == kDH) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int p = lane + 32 * i;
-            g_next[i] = make_uint4(0, 0, 0, 0);
-            u_next[i] = make_uint4(0, 0, 0, 0);
-            if (piece_ok(p, c0)) {
-              g_next[i] = __ldg(reinterpret_cast<const uint4*>(args.g + piece_elem(p, c0)));
-              u_next[i] = __ldg(reinterpret_cast<const uint4*>(args.u + piece_elem(p, c0)));
-            }
-          }
-        }
-      };
-      fetch_gu(c_begin);
-#pragma unroll 1
-      for (int c0 = c_begin; c0 < c_end; c0 += 32) {
-        uint32_t v[32];
-        if constexpr (MODE == kDH) {
-          unsigned char* g_s = stage_w;
-          unsigned char* u_s = stage_w + 2048;
+      if constexpr (MODE == kDH) {
+        unsigned char* g_s = stage_w;
+        unsigned char* u_s = stage_w + 2048;
+        auto dh_block = [&](int c0, uint4 (&gq)[4], uint4 (&uq)[4]) {
+          uint32_t v[32];
           __syncwarp();  // the previous block's read-back is done; also rejoins the warp for tcgen05.ld
 #pragma unroll
           for (int i = 0; i < 4; ++i) {
             const int p = lane + 32 * i;
-            *reinterpret_cast<uint4*>(g_s + piece_smem(p >> 2, p & 3)) = g_next[i];
-            *reinterpret_cast<uint4*>(u_s + piece_smem(p >> 2, p & 3)) = u_next[i];
+            *reinterpret_cast<uint4*>(g_s + piece_smem(p >> 2, p & 3)) = gq[i];
+            *reinterpret_cast<uint4*>(u_s + piece_smem(p >> 2, p & 3)) = uq[i];
           }
-          fetch_gu(c0 + 32);
+          fetch_gu(c0 + 64, gq, uq);  // this queue's next block is two blocks on
           __syncwarp();
           tmem_ld32(t_addr + c0, v);
           tmem_ld_wait();
@@ -348,8 +349,16 @@ grouped_bwd_kernel(const __grid_constant__ CUtensorMap tm_a0, const __grid_const
                   *reinterpret_cast<const uint4*>(u_s + piece_smem(p >> 2, p & 3));
             }
           }
-          continue;
+        };
+#pragma unroll 1
+        for (int c0 = c_begin; c0 < c_end; c0 += 64) {
+          dh_block(c0, g_q0, u_q0);
+          dh_block(c0 + 32, g_q1, u_q1);
         }
+      }
+#pragma unroll 1
+      for (int c0 = c_begin; MODE != kDH && c0 < c_end; c0 += 32) {
+        uint32_t v[32];
         __syncwarp();  // tcgen05.ld is warp-wide: rejoin lanes that skipped the stores
         tmem_ld32(t_addr + c0, v);
         tmem_ld_wait();
