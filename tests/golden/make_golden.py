@@ -1,5 +1,7 @@
 """Writes tests/golden/moe_small.npz: a small MoE layer case (inputs and every
-published output) computed by the CPU oracle.  Run from the repository root:
+published output) computed by the CPU oracle, and tests/golden/moe_small_bwd.npz: the
+gradients of the same case for a stored upstream gradient (auxiliary-loss weight 0.01).
+Run from the repository root:
 
     python tests/golden/make_golden.py
 
@@ -39,6 +41,12 @@ def main():
         w_down_bits=bits(w["w_down"]), logits=z, topk_idx=idx, topk_gate=gates, histogram=counts,
         offsets=offsets, row_src=row_src, slot_dst=slot_dst, y_bits=bits(y), out_bits=bits(out))
     print("wrote moe_small.npz", os.path.getsize(os.path.join(HERE, "moe_small.npz")), "bytes")
+    g = torch.Generator().manual_seed(12)
+    d_y = torch.randn(cfg.tokens, cfg.d_model, generator=g).numpy()
+    grads = orc.backward(x, w, idx, gates, probs, d_y, alpha=0.01)
+    np.savez_compressed(os.path.join(HERE, "moe_small_bwd.npz"), d_y=d_y, aux_alpha=0.01,
+                        aux_loss=orc.aux_loss(probs, idx, 0.01), **grads)
+    print("wrote moe_small_bwd.npz", os.path.getsize(os.path.join(HERE, "moe_small_bwd.npz")), "bytes")
 
 
 if __name__ == "__main__":

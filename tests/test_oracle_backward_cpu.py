@@ -58,3 +58,27 @@ def test_backward_bf16_rounding_points_stay_close(oracle, workloads):
     for n in ("dX", "dWg", "dWu", "dWd", "dWr"):
         scale = np.abs(a[n]).max()
         assert np.abs(a[n] - b[n]).max() <= 2e-2 * scale + 1e-6, n
+
+
+def test_golden_small_backward(oracle):
+    """The committed gradients (tests/golden/make_golden.py) of the committed forward case are
+    reproduced: the oracle's backward sums in a fixed order per output element, so only the
+    last bits may differ between builds (1e-6 relative)."""
+    import os
+    import torch
+    gdir = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+    f = np.load(os.path.join(gdir, "moe_small.npz"))
+    b = np.load(os.path.join(gdir, "moe_small_bwd.npz"))
+    x = torch.from_numpy(f["x_bits"].view(np.int16).copy()).view(torch.bfloat16)
+    w = {n: torch.from_numpy(f[n + "_bits"].view(np.int16).copy()).view(torch.bfloat16)
+         for n in ("w_gate", "w_up", "w_down")}
+    w["router_w"] = torch.from_numpy(f["router_w"].copy())
+    z = oracle.router_logits(x, w["router_w"])
+    idx, gates, probs, _, _ = oracle.route(z, int(f["top_k"]))
+    assert (idx == f["topk_idx"]).all()
+    assert abs(oracle.aux_loss(probs, idx, float(b["aux_alpha"])) - float(b["aux_loss"])) < 1e-7
+    got = oracle.backward(x, w, idx, gates, probs, b["d_y"], alpha=float(b["aux_alpha"]))
+    for name in ("dX", "dWr", "dWg", "dWu", "dWd", "dgate", "dlogits"):
+        ref = b[name]
+        err = np.abs(got[name] - ref).max()
+        assert err <= 1e-6 * max(1.0, float(np.abs(ref).max())), (name, err)
