@@ -27,9 +27,24 @@ PKG_DIR = os.path.join(ROOT, "project-axiom-ai-llm_b200")
 FALLBACK_HBM_GBS = 6650.0
 FALLBACK_BF16_TFLOPS = 1590.0
 
-# DRAM bytes (read + write) per launch of the gate/up GEMM from the committed ncu
-# captures (profiles/grouped_gemm_2sm_C2.md, profiles/gemm_dram_traffic_C3.md).
-NCU_TRAFFIC_BYTES = {"C2": 402870016 + 80332800, "C3": 2418811648 + 461718784}
+TRAFFIC_FILE = os.path.join(ROOT, "profiles", "dram_traffic_of_dominant_kernel.md")
+
+
+def ncu_traffic(workload):
+    """DRAM bytes (read + write) per launch of the gate/up GEMM for `workload`, from the
+    committed ncu summary: lines of the form
+    `traffic: workload=C3 ... read_bytes=N write_bytes=M commit=H`.  None when the file
+    has no line for the workload."""
+    import re
+    try:
+        text = open(TRAFFIC_FILE).read()
+    except OSError:
+        return None, None
+    for line in text.splitlines():
+        m = re.match(r"\s*traffic:\s+workload=(\S+)\s.*read_bytes=(\d+)\s+write_bytes=(\d+)\s+commit=(\S+)", line)
+        if m and m.group(1) == workload:
+            return int(m.group(2)) + int(m.group(3)), m.group(4)
+    return None, None
 
 
 def load_package():
@@ -109,6 +124,8 @@ def cpu_baseline(cfg, x, w, sample_tokens, repeats=1):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_binding
     orc = oracle_binding.load()
+    # every core this process may run on, whatever OMP_NUM_THREADS a launcher exported
+    orc.set_threads(len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1))
     n = min(sample_tokens, cfg.tokens)
     xs = x[:n].cpu()
     wc = {k: (v.cpu() if v is not None else None) for k, v in w.items()}
@@ -123,7 +140,53 @@ def cpu_baseline(cfg, x, w, sample_tokens, repeats=1):
         best = dt if best is None else min(best, dt)
     return {"value": n / best, "unit": "tokens/s", "cores": orc.threads(), "kind": "port",
             "sample": f"first {n} tokens of the batch through router, permutation and expert FFN "
-                      f"(C, OpenMP, fp32 accumulate), {best:.2f} s"}
+                      f"(C, OpenMP, fp32 accumulate), {best:.2f} s; tokens/s = {n} / that time, i.e. scaled "
+                      f"linearly in T, every slice streaming all expert weights once"}
+
+
+def reference_gpu(cfg, wl, dev, repeats=30):
+    """The reference engine's own, unmodified GPU kernels (oracle/_ref, built by
+    oracle/build_ref.sh) timed on this GPU with CUDA events around forward_mixture_experts:
+    median of `repeats` calls after warm-up, the hidden states restored before each call
+    (the reference works in place), the histogram reset first.  Only the shapes it can run."""
+    import ctypes
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import reference_binding
+    if cfg.num_shared or cfg.top_k != 2 or cfg.num_experts > 16 or cfg.training:
+        return {"unavailable": "the reference kernels do top-2 over at most 16 experts, forward only, "
+                               "without shared experts or router bias"}
+    if 2 * cfg.d_ff * 4 > 48 * 1024:
+        return {"unavailable": f"the reference dispatch kernel needs {2 * cfg.d_ff * 4} bytes of dynamic shared "
+                               "memory and never raises the 48 KiB default limit: its launch fails at this d_ff"}
+    if not reference_binding.available():
+        return {"unavailable": "oracle/_ref is not built (oracle/build_ref.sh)"}
+    x, w = wl.make_inputs(cfg, device=dev, router_bf16=True)
+    ref = reference_binding.ReferenceMoe()
+    ref.set_weights(w["router_w"], w["w_gate"], w["w_up"], w["w_down"])
+    hidden = x.clone()
+    for _ in range(3):
+        hidden.copy_(x)
+        if not ref.forward(hidden, cfg.d_ff):
+            return {"unavailable": "forward_mixture_experts returned false"}
+    ref.reset_histogram()
+    times = []
+    for _ in range(repeats):
+        hidden.copy_(x)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()            # torch's default stream is the legacy stream the reference enqueues on
+        ok = bool(ref.lib.forward_mixture_experts(hidden.data_ptr(), ctypes.addressof(ref.weights),
+                                                  ctypes.addressof(ref.acts), cfg.tokens, cfg.d_model,
+                                                  cfg.d_ff, None))
+        e1.record()
+        torch.cuda.synchronize()
+        if not ok:
+            return {"unavailable": "forward_mixture_experts returned false"}
+        times.append(e0.elapsed_time(e1))
+    ms = statistics.median(times)
+    return {"ms_per_step": ms, "value": cfg.tokens / (ms / 1000.0), "unit": "tokens/s", "calls": repeats,
+            "what": "unmodified reference kernels (router, per-token dispatch on CUDA cores, residual) "
+                    "compiled for sm_100a, bf16 router weights, device-resident inputs"}
 
 
 def run_reference(args, wl):
@@ -151,7 +214,7 @@ def run_reference(args, wl):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "gpu_launches": 0,
-        "config": workload_config(cfg, args.gpus, f"CPU sample of {sample} tokens per step"),
+        "config": workload_config(cfg, args.gpus),
         "cpu_baseline": info,
         "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "note": "the reference engine has no CPU MoE path; this is the CPU port of its layer "
@@ -160,7 +223,9 @@ def run_reference(args, wl):
     print(json.dumps(line), flush=True)
 
 
-def workload_config(cfg, n_gpus, l2_note):
+def workload_config(cfg, n_gpus):
+    l2_note = ("inputs larger than L2 (expert weights "
+               f"{cfg.weight_bytes / n_gpus / 1e9:.2f} GB per GPU); no flush")
     return {
         "workload": f"{cfg.name}: MoE layer forward, T={cfg.tokens} d_model={cfg.d_model} "
                     f"E={cfg.num_experts}+{cfg.num_shared} shared top-{cfg.top_k} d_ff={cfg.d_ff}, "
@@ -180,8 +245,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--config", default="C3", choices=["C1", "C2", "C3", "C4", "C5"])
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--cpu-tokens", type=int, default=256, help="tokens in the CPU baseline sample")
-    ap.add_argument("--reference-tokens", type=int, default=256)
+    ap.add_argument("--cpu-tokens", type=int, default=512, help="tokens in the CPU baseline sample")
+    ap.add_argument("--reference-tokens", type=int, default=512)
+    ap.add_argument("--sustained-seconds", type=float, default=2.0,
+                    help="length of the extra back-to-back loop that gives the steady-state rate (0: skip)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tokens", type=int, default=0,
                     help="override the workload's token count (e.g. 16 for a decode-sized batch)")
@@ -284,6 +351,52 @@ def main():
     ms_step = ms_total / args.steps
     value = T / (ms_step / 1000.0)
 
+    # ---- steady state: the same step back to back for a few seconds ---------------
+    sustained = None
+    if args.sustained_seconds > 0:
+        n_loop = max(args.steps, int(args.sustained_seconds * 1000.0 / ms_step) + 1)
+        s_sampler = ClockSampler(local_rank)
+        barrier()
+        if rank == 0:
+            s_sampler.start()
+        e0.record()
+        for _ in range(n_loop):
+            step()
+        e1.record()
+        barrier()
+        s_ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([s_ms], device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            s_ms = float(t.item())
+        if rank == 0:
+            sc = s_sampler.stop()
+            s_step = s_ms / n_loop
+            sustained = {"steps": n_loop, "seconds": s_ms / 1000.0, "ms_per_step": s_step,
+                         "value": T / (s_step / 1000.0), "unit": "tokens/s", "clocks": sc,
+                         "ms_x_sm_mhz": s_step * sc["sm_mhz"] if sc.get("sm_mhz") else None}
+
+    # ---- the strict-tolerance mode (two-term SwiGLU intermediate) -------------------
+    h_exact = None
+    if world == 1 and not training:
+        layer_x = axm.MoeLayer(layer.w, T, k, publish_y=False, h_exact=True)
+        for _ in range(3):
+            layer_x.forward(x_local, out)
+        barrier()
+        e0.record()
+        for _ in range(args.steps):
+            layer_x.forward(x_local, out)
+        e1.record()
+        barrier()
+        hx_ms = e0.elapsed_time(e1) / args.steps
+        if layer_x.status() != 0:
+            raise SystemExit("GEMM kernel reported a timed-out wait (exact mode)")
+        h_exact = {"ms_per_step": hx_ms, "value": T / (hx_ms / 1000.0), "unit": "tokens/s",
+                   "what": "AXM_FLAG_H_EXACT: SwiGLU intermediate kept as two bf16 terms, every output "
+                           "element within 1e-2 + 2e-2*|ref| of an fp32 intermediate"}
+        del layer_x
+        torch.cuda.empty_cache()
+
     # ---- end to end: host buffers, copies inside the timed region ----------------
     h_x = x_local.cpu().pin_memory()
     h_out = torch.empty_like(h_x).pin_memory()
@@ -367,7 +480,7 @@ def main():
                     "achieved": a, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": a / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
                     "frac_of_sustained": a / peaks["bf16_tflops_sustained"] if peaks["bf16_tflops_sustained"] else None,
-                    "traffic": NCU_TRAFFIC_BYTES.get(cfg.name)}
+                    "traffic": ncu_traffic(cfg.name)[0], "traffic_commit": ncu_traffic(cfg.name)[1]}
         status = layer.status()
         if status != 0:
             raise SystemExit(f"GEMM kernel reported a timed-out wait (status {status})")
@@ -385,9 +498,38 @@ def main():
         ep_stages = {n: {"ms": v} for n, v in acc.items()}
         ep_stages["rows_received_rank0"] = layer.last_rows_received
 
+    # ---- expert parallel: the answer itself, against the single-GPU layer ------------
+    ep_check = None
+    if world > 1:
+        if hasattr(layer, "check_status"):
+            layer.check_status()
+        out_final = layer.forward(x_local, out).clone()
+        gathered = [torch.empty_like(out_final) for _ in range(world)] if rank == 0 else None
+        dist.gather(out_final, gathered, dst=0)
+        verdict = torch.zeros(1, dtype=torch.int32, device=dev)
+        if rank == 0:
+            xs, ws = wl.make_inputs(cfg, device=dev)      # the same seeded batch, all experts
+            single = axm.MoeLayer(ws, T, k, publish_y=False)
+            ref_out, _ = single.forward(xs)
+            torch.cuda.synchronize()
+            same = torch.equal(torch.cat(gathered), ref_out)
+            ep_check = "bit-equal" if same else "MISMATCH"
+            if not same:
+                diff = (torch.cat(gathered).float() - ref_out.float()).abs()
+                ep_check += f": {int((diff > 0).sum())} elements differ, max |diff| {float(diff.max()):.4g}"
+            verdict[0] = 0 if same else 1
+            del single, ws, xs, ref_out, gathered
+        dist.broadcast(verdict, src=0)
+        ep_failed = int(verdict.item()) != 0
+    else:
+        ep_failed = False
+
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline and not training:
         cpu = cpu_baseline(cfg, x_local, layer.w, args.cpu_tokens)
+    ref_gpu = None
+    if world == 1 and rank == 0 and not training:
+        ref_gpu = reference_gpu(cfg, wl, dev)
 
     if rank == 0:
         line = {
@@ -395,8 +537,7 @@ def main():
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
-            "config": workload_config(cfg, world, "inputs larger than L2 (expert weights "
-                                      f"{cfg.weight_bytes / world / 1e9:.2f} GB per GPU); no flush"),
+            "config": workload_config(cfg, world),
             "e2e": {"value": T / (e2e_ms / 1000.0), "unit": "tokens/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": d2h_bytes},
             "gpu_launches": launches_per_step * args.steps * world,
@@ -418,10 +559,20 @@ def main():
                 line["config"]["ep_return"] = args.ep_return
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if ref_gpu is not None:
+            line["reference_gpu"] = ref_gpu
+        if sustained is not None:
+            line["sustained"] = sustained
+        if h_exact is not None:
+            line["h_exact"] = h_exact
+        if ep_check is not None:
+            line["ep_check"] = ep_check
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+    if ep_failed:
+        raise SystemExit("expert-parallel output differs from the single-GPU layer's")
 
 
 if __name__ == "__main__":

@@ -53,8 +53,17 @@ typedef enum AxmStatus {
 enum { AXM_ROUTER_BF16 = 0, AXM_ROUTER_FP32 = 1 };
 
 enum {
-  AXM_FLAG_RESIDUAL = 1,       /* out = bf16(x + y), else out = y            */
-  AXM_FLAG_HIST_ACCUMULATE = 2 /* histogram[e] += counts, else histogram = counts */
+  AXM_FLAG_RESIDUAL = 1,        /* out = bf16(x + y), else out = y            */
+  AXM_FLAG_HIST_ACCUMULATE = 2, /* histogram[e] += counts, else histogram = counts */
+  /* The reference keeps the SwiGLU intermediate h = SiLU(g) * u in fp32 between its two
+   * projections (core/src/CUDA/kernel/moe_router.cu:155-190).  By default this library
+   * stores h as one bf16 value, which leaves a few outputs per million just outside
+   * 1e-2 + 2e-2 * |ref| where two large expert outputs cancel.  With this flag h is
+   * stored as two bf16 terms (hi = bf16(h), lo = bf16(h - hi): 16 mantissa bits) and the
+   * down projection multiplies both by the same weights, so every output meets that
+   * bound; the down projection then does twice the tensor-core work and h takes twice
+   * the room (workspace sizes follow the flag).  Inference entry points only. */
+  AXM_FLAG_H_EXACT = 4
 };
 
 /* Problem shape.  D and F must be multiples of 8 (16-byte rows); E <= 256;
@@ -207,6 +216,7 @@ AXM_API int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* offset
 
 /* Grouped SwiGLU expert FFN over `num_segments` segments read from device memory:
  *   h   = SiLU(A . Wg[e]) * (A . Wu[e])     -> bf16 [rows_total][F]
+ *                                             ([rows_total][2F], hi | lo, with AXM_FLAG_H_EXACT)
  *   o   = h . Wd[e]                         -> fp32 [rows_total][D]
  * tcgen05 tensor-core kernels, bf16 in, fp32 accumulate in tensor memory.
  * Replaces moe_top2_dispatch_kernel phases A and B
@@ -280,12 +290,27 @@ AXM_API int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* tensors,
 /* AdamW step (decoupled weight decay, bias correction with `step` >= 1) over one MoE
  * weight matrix as the engine stores it: fp32 master, two fp32 moments, bf16 working
  * copy (core/src/CUDA/util/gpu_types.cuh:148-168); `grad` is what axm_moe_backward
- * wrote.  Follows the textbook update; the engine's own fused AdamW for the dense
- * weights is core/src/CUDA/kernel/backward_pass.cu:812-852.  n elements, fp32
- * buffers 16-byte aligned. */
+ * wrote.  Follows the textbook update (axm_moe_adamw_step_engine below follows the
+ * engine's own fused AdamW, core/src/CUDA/kernel/backward_pass.cu:812-852).  n elements,
+ * fp32 buffers 16-byte aligned, the bf16 copy 8-byte aligned (else AXM_ERR_ARGUMENT). */
 AXM_API int axm_moe_adamw_step(float* master, float* m, float* v, const float* grad, void* w_bf16,
                                int64_t n, float lr, float beta1, float beta2, float eps,
                                float weight_decay, int32_t step, void* stream);
+
+/* The same step with the conventions of the engine's own fused AdamW kernel
+ * (core/src/CUDA/kernel/backward_pass.cu:812-852), so that weights of an engine
+ * checkpoint move exactly as the engine's optimiser would move them:
+ *   a non-finite gradient counts as 0 and gradients are clamped to [-100, 100];
+ *   the step size is lr / sqrt(in_dim), in_dim = the matrix's input dimension
+ *   (D for router, gate and up weights, F for down weights);
+ *   a bias-correction term 1 - beta^step that is <= 1e-7 is replaced by 1 (step 0 counts as 1);
+ *   the new weight is clamped to [-2, 2]; if it is not finite the weight is left unchanged
+ *   (the moments are still updated).
+ * Also requires the bf16 copy to be 8-byte aligned, like axm_moe_adamw_step. */
+AXM_API int axm_moe_adamw_step_engine(float* master, float* m, float* v, const float* grad,
+                                      void* w_bf16, int64_t n, int64_t in_dim, float lr, float beta1,
+                                      float beta2, float eps, float weight_decay, int64_t step,
+                                      void* stream);
 
 /* ---- MoE block of the engine's checkpoint file ----------------------------------
  * The engine's `weights.axiom` (56-byte packed header "AXIOM_V1", fp32 weights, bias,

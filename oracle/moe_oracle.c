@@ -24,12 +24,13 @@
  *   residual add with a second bf16 rounding ........ core/src/CUDA/kernel/moe_router.cu:193-203
  *   weight layouts [D][E], [E][D][F], [E][F][D] ..... core/src/CUDA/util/gpu_types.cuh:147-157
  *   SiLU*mul and its derivative ..................... core/src/CUDA/kernel/swiglu.cu:19-55
+ *   AdamW as the engine's fused kernel applies it ... core/src/CUDA/kernel/backward_pass.cu:812-852
  *
  * Parity status: the engine's own tests hold no numeric vectors for this layer
  * (only "histogram sums to 2T, no dead expert, outputs finite").  The oracle is
  * pinned by running the engine's unmodified kernels next to it on a GPU (see
- * oracle/ref_driver.cu and tests/test_reference_parity.py); where that binary is
- * not present the header of the test report says "parity unpinned".
+ * oracle/build_ref.sh and tests/test_reference_parity_gpu.py); where that binary is
+ * not present those tests skip with the reason "parity unpinned".
  *
  * All tensors are row-major.  bf16 values travel as uint16_t.
  */
@@ -68,6 +69,16 @@ ORC_API int orc_num_threads(void) {
   return omp_get_max_threads();
 #else
   return 1;
+#endif
+}
+
+/* Number of threads the parallel loops use from now on (n <= 0: leave as is).  A launcher
+ * may have set OMP_NUM_THREADS=1 for its workers; a timing run asks for the cores it wants. */
+ORC_API void orc_set_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
 #endif
 }
 
@@ -570,6 +581,39 @@ ORC_API void orc_rmsnorm(const uint16_t* x, const float* gamma, int T, int D, fl
     for (int d = 0; d < D; ++d) {
       float v = bf16_to_f32(x[(size_t)t * D + d]) * rstd * (gamma ? gamma[d] : 1.0f);
       y[(size_t)t * D + d] = f32_to_bf16(v);
+    }
+  }
+}
+
+/* One AdamW step over a weight matrix kept as fp32 master + two fp32 moments + bf16 working
+ * copy, with the conventions of the engine's fused optimiser kernel
+ * (core/src/CUDA/kernel/backward_pass.cu:812-852): a non-finite gradient counts as zero,
+ * gradients are clamped to [-100, 100], the step size is lr / sqrt(in_dim), each bias
+ * correction 1 - beta^step is replaced by 1 when it is not above 1e-7 (and step 0 counts as
+ * 1), the moments are always written, and the weight is written (clamped to [-2, 2]) only
+ * when the new value is finite. */
+ORC_API void orc_adamw_engine(float* master, float* m, float* v, const float* grad, uint16_t* w_bf16,
+                              int64_t n, int64_t in_dim, float lr, float beta1, float beta2, float eps,
+                              float weight_decay, int64_t step) {
+  const float t = (float)(step > 0 ? step : 1);
+  float c1 = 1.0f - powf(beta1, t), c2 = 1.0f - powf(beta2, t);
+  if (!(c1 > 1e-7f)) c1 = 1.0f;
+  if (!(c2 > 1e-7f)) c2 = 1.0f;
+  const float step_size = lr * (1.0f / sqrtf((float)(in_dim > 0 ? in_dim : 1)));
+#pragma omp parallel for schedule(static)
+  for (int64_t i = 0; i < n; ++i) {
+    float g = grad[i];
+    if (!isfinite(g)) g = 0.0f;
+    g = fmaxf(-100.0f, fminf(100.0f, g));
+    const float mi = beta1 * m[i] + (1.0f - beta1) * g;
+    const float vi = beta2 * v[i] + (1.0f - beta2) * g * g;
+    m[i] = mi;
+    v[i] = vi;
+    const float upd = (mi / c1) / (sqrtf(vi / c2) + eps);
+    const float w_new = master[i] - step_size * (upd + weight_decay * master[i]);
+    if (isfinite(w_new)) {
+      master[i] = fmaxf(-2.0f, fminf(2.0f, w_new));
+      w_bf16[i] = f32_to_bf16(master[i]);
     }
   }
 }

@@ -27,6 +27,7 @@ ROUTER_BF16 = 0
 ROUTER_FP32 = 1
 FLAG_RESIDUAL = 1
 FLAG_HIST_ACCUMULATE = 2
+FLAG_H_EXACT = 4
 ROUTE_BLOCKS = 296
 SEG_ALT_A = 1 << 30
 NOALLOC_MAX_EXPERTS = 128
@@ -112,6 +113,8 @@ def load():
     lib.axm_moe_backward.argtypes = [dp, tp, vp, sz, vp]
     lib.axm_moe_permute_padded.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp]
     lib.axm_moe_adamw_step.argtypes = [vp, vp, vp, vp, vp, ctypes.c_int64] + [ctypes.c_float] * 5 + [i32, vp]
+    lib.axm_moe_adamw_step_engine.argtypes = ([vp] * 5 + [ctypes.c_int64, ctypes.c_int64] +
+                                              [ctypes.c_float] * 5 + [ctypes.c_int64, vp])
     lib.axm_moe_expert_ffn_backward.argtypes = [dp, vp, i32, i32] + [vp] * 16
     lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
@@ -161,18 +164,21 @@ class MoeLayer:
     """One MoE layer bound to its weights, with a workspace sized for `tokens`.
 
     forward(x) returns (out, histogram) like the reference host wrapper; the
-    routing tensors of the last call stay readable as attributes.
+    routing tensors of the last call stay readable as attributes.  h_exact keeps
+    the SwiGLU intermediate in two bf16 terms (AXM_FLAG_H_EXACT): every output
+    element then meets the layer tolerance against an fp32 intermediate.
     """
 
     def __init__(self, weights, tokens, top_k, residual=True, hist_accumulate=False,
-                 device="cuda", publish_y=True):
+                 device="cuda", publish_y=True, h_exact=False):
         self.lib = load()
         self.w = weights
         wr = weights["router_w"]
         D, E = wr.shape
         F = weights["w_gate"].shape[2]
         S = 0 if weights.get("shared_gate") is None else weights["shared_gate"].shape[0]
-        flags = (FLAG_RESIDUAL if residual else 0) | (FLAG_HIST_ACCUMULATE if hist_accumulate else 0)
+        flags = ((FLAG_RESIDUAL if residual else 0) | (FLAG_HIST_ACCUMULATE if hist_accumulate else 0) |
+                 (FLAG_H_EXACT if h_exact else 0))
         rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
         self.desc = make_desc(tokens, D, F, E, top_k, S, rdt, flags)
         self.T, self.D, self.F, self.E, self.k, self.S = tokens, D, F, E, top_k, S

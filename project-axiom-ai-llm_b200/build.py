@@ -50,11 +50,29 @@ def _run(cmd, verbose):
     subprocess.run(cmd, check=True)
 
 
+def _compile_objects(sources, extra, force, verbose):
+    """One object per source under csrc/build/, compiled in parallel; an object is
+    rebuilt when its source, a header or this script is newer."""
+    from concurrent.futures import ThreadPoolExecutor
+    obj_dir = os.path.join(CSRC, "build")
+    os.makedirs(obj_dir, exist_ok=True)
+    objs, jobs = [], []
+    for src in sources:
+        obj = os.path.join(obj_dir, os.path.basename(src)[:-3] + ".o")
+        objs.append(obj)
+        if force or _stale(obj, [src]):
+            jobs.append([_nvcc()] + NVCC_FLAGS + extra + ["-c", src, "-o", obj])
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 1)) as pool:
+        list(pool.map(lambda c: _run(c, verbose), jobs))
+    return objs, bool(jobs)
+
+
 def build(force=False, verbose=True, ptxas_info=False):
     core = [os.path.join(CSRC, s) for s in CORE_SOURCES]
     extra = ["-Xptxas", "-v"] if ptxas_info else []
     if force or _stale(LIB, core):
-        _run([_nvcc()] + NVCC_FLAGS + extra + ["-shared", "-o", LIB] + core + ["-cudart", "shared"], verbose)
+        objs, _ = _compile_objects(core, extra, force, verbose)
+        _run([_nvcc()] + NVCC_FLAGS + ["-shared", "-o", LIB] + objs + ["-cudart", "shared"], verbose)
     drop = [os.path.join(CSRC, s) for s in DROPIN_SOURCES]
     if all(os.path.exists(s) for s in drop) and (force or _stale(DROPIN, drop + [LIB])):
         _run([_nvcc()] + NVCC_FLAGS + ["-shared", "-o", DROPIN] + drop +

@@ -123,16 +123,23 @@ bwd_prepare_kernel(const float* __restrict__ d_out, const float* __restrict__ o,
 // One thread per token: gate gradients -> probability gradients (through the
 // renormalisation over the selected experts, plus the auxiliary-loss term) ->
 // logit gradients through the softmax.  dz[t, e] = p_e * (dp_e - sum_j p_j dp_j).
-constexpr int kRbThreads = 128;
+constexpr int kRbThreads = 128;  // at most; fewer when E rows of p and dp per thread would not fit
+// Threads per block such that blockDim * 2 * (E + 1) floats fit in 200 KB of shared memory
+// (E = 256: 96 threads), a multiple of a warp.
+static int router_bwd_threads(int E) {
+  int t = (int)((200u * 1024u) / (8u * (unsigned)(E + 1)));
+  t = t > kRbThreads ? kRbThreads : t;
+  return t / 32 * 32;
+}
 __global__ void __launch_bounds__(kRbThreads)
 router_bwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ topk_idx,
                   const float* __restrict__ d_gate, const float* __restrict__ aux_coef,
                   float* __restrict__ dz, int T, int E, int k) {
-  extern __shared__ float sm[];  // [kRbThreads][2][E + 1]
+  extern __shared__ float sm[];  // [blockDim.x][2][E + 1]
   const int EP = E + 1;
   float* p = sm + threadIdx.x * 2 * EP;
   float* dp = p + EP;
-  const int t = blockIdx.x * kRbThreads + threadIdx.x;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
   if (t >= T) return;
   softmax_row(logits + (size_t)t * E, p, E);
   float sel = 0.0f, dot = 0.0f;
@@ -424,7 +431,8 @@ extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* 
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int T = desc->tokens, E = desc->num_experts, k = desc->top_k;
   AxmMoeDesc d = *desc;
-  d.flags &= ~AXM_FLAG_HIST_ACCUMULATE;  // ws.counts holds this call's counts
+  // ws.counts holds this call's counts; the saved h of the training layout is one bf16 term
+  d.flags &= ~(AXM_FLAG_HIST_ACCUMULATE | AXM_FLAG_H_EXACT);
   int rc = axm_moe_router(&d, t->x, t->router_w, t->router_bias, w.logits, w.topk_idx, w.topk_gate,
                           w.block_counts, stream);
   if (rc) return rc;
@@ -462,20 +470,35 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
   const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
 
+  // Shared-memory limits of the two router-gradient kernels are settled before anything is
+  // launched, so that a refusal leaves no half-finished backward pass behind.
+  const int rb_threads = router_bwd_threads(E);
+  const size_t sm = sizeof(float) * (size_t)rb_threads * 2 * (E + 1);
+  static SmemLimitCache rb_cache = {};
+  int rc;
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_bwd_kernel), sm, &rb_cache, "router_bwd_kernel")))
+    return rc;
+  const int d_tile = E <= 64 ? 512 : 128;
+  const size_t fsm = sizeof(float) * (size_t)E * d_tile;
+  {
+    static SmemLimitCache cache32 = {}, cache16 = {};
+    if (desc->router_dtype == AXM_ROUTER_FP32)
+      rc = ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<float>), fsm, &cache32, "bwd_finalize_kernel");
+    else
+      rc = ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<__nv_bfloat16>), fsm, &cache16, "bwd_finalize_kernel");
+    if (rc) return rc;
+  }
+
   bwd_prepare_kernel<<<4 * sm_count(), 256, 0, st>>>(t->d_out, static_cast<const float*>(w.o), w.row_src,
                                                      w.topk_gate, w.offsets,
                                                      static_cast<__nv_bfloat16*>(w.d_o), w.d_gate, D, E, k);
-  int rc = check_launch("bwd_prepare_kernel");
+  rc = check_launch("bwd_prepare_kernel");
   if (rc) return rc;
   if ((rc = axm_moe_expert_ffn_backward(desc, w.segments, E, w.rows_max, w.x_perm, w.h, w.g, w.u, w.d_o,
                                         t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.d_xp,
                                         t->d_w_gate, t->d_w_up, t->d_w_down, w.status, stream)))
     return rc;
-  const size_t sm = sizeof(float) * kRbThreads * 2 * (E + 1);
-  static SmemLimitCache rb_cache = {};
-  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_bwd_kernel), sm, &rb_cache, "router_bwd_kernel")))
-    return rc;
-  router_bwd_kernel<<<(T + kRbThreads - 1) / kRbThreads, kRbThreads, sm, st>>>(
+  router_bwd_kernel<<<(T + rb_threads - 1) / rb_threads, rb_threads, sm, st>>>(
       w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, T, E, k);
   if (t->d_router_w != nullptr) {
     dim3 grid((D + 127) / 128, kDwrChunks);
@@ -483,8 +506,6 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
                                                  w.dwr_partial, T, D, E);
     dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(w.dwr_partial, t->d_router_w, D * E);
   }
-  const int d_tile = E <= 64 ? 512 : 128;
-  const size_t fsm = sizeof(float) * (size_t)E * d_tile;
   dim3 fgrid((D + d_tile - 1) / d_tile, 1);
   // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory)
   int per_sm = (int)((200u * 1024u) / (fsm + 1024));
@@ -493,15 +514,11 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   if ((int)fgrid.y > T) fgrid.y = T;
   if (desc->router_dtype == AXM_ROUTER_FP32) {
     auto kern = bwd_finalize_kernel<float>;
-    static SmemLimitCache cache = {};
-    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), fsm, &cache, "bwd_finalize_kernel"))) return rc;
     kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
                                   static_cast<const float*>(t->router_w), w.dz, t->d_x, T, D, E, k,
                                   residual, d_tile);
   } else {
     auto kern = bwd_finalize_kernel<__nv_bfloat16>;
-    static SmemLimitCache cache = {};
-    if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), fsm, &cache, "bwd_finalize_kernel"))) return rc;
     kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
                                   static_cast<const __nv_bfloat16*>(t->router_w), w.dz, t->d_x, T, D, E,
                                   k, residual, d_tile);
@@ -516,7 +533,37 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
 // core/src/CUDA/kernel/backward_pass.cu:812-852).  Textbook update, bias-corrected:
 //   m = b1 m + (1 - b1) g;  v = b2 v + (1 - b2) g^2;
 //   w -= lr * ( (m / (1 - b1^t)) / (sqrt(v / (1 - b2^t)) + eps) + wd * w );  w_bf16 = bf16(w).
+//
+// kEngine selects the conventions of the engine's own fused AdamW, so that an engine
+// checkpoint trains the same way under either optimiser:
+//   g: non-finite -> 0, then clamped to [-100, 100];  m, v updated with that g;
+//   bias corrections 1 - b^t replaced by 1 when they are <= 1e-7;
+//   step size lr * rsqrt(in_dim) (in_dim = rows of the [in][out] matrix);
+//   w' = w - step * (m_hat / (sqrt(v_hat) + eps) + wd * w); if w' is finite it is clamped to
+//   [-2, 2] and stored (master and bf16 copy), else the weight is left as it was.
+// The host passes lr already scaled and c1, c2 already floored.
 namespace axm {
+template <bool kEngine>
+__device__ __forceinline__ void adamw_one(float g, float& mj, float& vj, float& wj, bool& store, float lr,
+                                          float b1, float b2, float eps, float wd, float c1, float c2) {
+  if (kEngine) {
+    if (!isfinite(g)) g = 0.0f;
+    g = fmaxf(-100.0f, fminf(100.0f, g));
+  }
+  mj = b1 * mj + (1.0f - b1) * g;
+  vj = b2 * vj + (1.0f - b2) * g * g;
+  if (kEngine) {
+    const float upd = (mj / c1) / (sqrtf(vj / c2) + eps);
+    const float w_new = wj - lr * (upd + wd * wj);
+    store = isfinite(w_new);
+    if (store) wj = fmaxf(-2.0f, fminf(2.0f, w_new));
+  } else {
+    wj -= lr * ((mj / c1) / (sqrtf(vj / c2) + eps) + wd * wj);
+    store = true;
+  }
+}
+
+template <bool kEngine>
 __global__ void __launch_bounds__(256)
 adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restrict__ v,
              const float* __restrict__ grad, __nv_bfloat16* __restrict__ w_bf16, long long n, float lr,
@@ -530,19 +577,20 @@ adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restric
       float* gp = &g.x; float* mp = &mm.x; float* vp = &vv.x; float* wp = &ww.x;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        mp[j] = b1 * mp[j] + (1.0f - b1) * gp[j];
-        vp[j] = b2 * vp[j] + (1.0f - b2) * gp[j] * gp[j];
-        wp[j] -= lr * ((mp[j] / c1) / (sqrtf(vp[j] / c2) + eps) + wd * wp[j]);
+        bool st;
+        adamw_one<kEngine>(gp[j], mp[j], vp[j], wp[j], st, lr, b1, b2, eps, wd, c1, c2);
       }
       *reinterpret_cast<float4*>(m + i) = mm;
       *reinterpret_cast<float4*>(v + i) = vv;
+      // a weight whose update was refused keeps its value (wp[j] untouched) and its bf16 copy
+      // is the rounding of that unchanged master: storing both changes nothing
       *reinterpret_cast<float4*>(master + i) = ww;
       *reinterpret_cast<uint2*>(w_bf16 + i) = make_uint2(pack_bf16(ww.x, ww.y), pack_bf16(ww.z, ww.w));
     } else {
       for (long long e = i; e < n; ++e) {
-        float mj = b1 * m[e] + (1.0f - b1) * grad[e];
-        float vj = b2 * v[e] + (1.0f - b2) * grad[e] * grad[e];
-        float wj = master[e] - lr * ((mj / c1) / (sqrtf(vj / c2) + eps) + wd * master[e]);
+        float mj = m[e], vj = v[e], wj = master[e];
+        bool st;
+        adamw_one<kEngine>(grad[e], mj, vj, wj, st, lr, b1, b2, eps, wd, c1, c2);
         m[e] = mj;
         v[e] = vj;
         master[e] = wj;
@@ -553,21 +601,47 @@ adamw_kernel(float* __restrict__ master, float* __restrict__ m, float* __restric
 }
 }  // namespace axm
 
-extern "C" int axm_moe_adamw_step(float* master, float* m, float* v, const float* grad, void* w_bf16,
-                                  int64_t n, float lr, float beta1, float beta2, float eps,
-                                  float weight_decay, int32_t step, void* stream) {
+static int adamw_launch(bool engine, float* master, float* m, float* v, const float* grad, void* w_bf16,
+                        int64_t n, float lr, float beta1, float beta2, float eps, float weight_decay,
+                        int64_t step, int64_t in_dim, void* stream) {
   if (!master || !m || !v || !grad || !w_bf16) return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: null pointer");
-  if (n < 0 || step < 1) return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: n must be >= 0 and step >= 1");
+  if (n < 0 || (!engine && step < 1)) return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: n must be >= 0 and step >= 1");
   if ((reinterpret_cast<uintptr_t>(master) | reinterpret_cast<uintptr_t>(m) | reinterpret_cast<uintptr_t>(v) |
        reinterpret_cast<uintptr_t>(grad)) & 15)
     return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: fp32 buffers must be 16-byte aligned");
+  // the kernel stores four bf16 values at a time
+  if (reinterpret_cast<uintptr_t>(w_bf16) & 7)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_adamw_step: the bf16 copy must be 8-byte aligned");
   if (n == 0) return AXM_OK;
   if (int rc = require_device()) return rc;
-  const float c1 = 1.0f - powf(beta1, (float)step), c2 = 1.0f - powf(beta2, (float)step);
+  float c1 = 1.0f - powf(beta1, (float)(step > 0 ? step : 1)), c2 = 1.0f - powf(beta2, (float)(step > 0 ? step : 1));
+  if (engine) {
+    if (!(c1 > 1e-7f)) c1 = 1.0f;
+    if (!(c2 > 1e-7f)) c2 = 1.0f;
+    lr = lr * (1.0f / sqrtf((float)(in_dim > 0 ? in_dim : 1)));
+  }
   long long blocks = (n / 4 + 255) / 256;
   if (blocks > 16LL * sm_count()) blocks = 16LL * sm_count();
   if (blocks < 1) blocks = 1;
-  adamw_kernel<<<(unsigned)blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      master, m, v, grad, static_cast<__nv_bfloat16*>(w_bf16), n, lr, beta1, beta2, eps, weight_decay, c1, c2);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (engine)
+    adamw_kernel<true><<<(unsigned)blocks, 256, 0, st>>>(master, m, v, grad, static_cast<__nv_bfloat16*>(w_bf16), n,
+                                                         lr, beta1, beta2, eps, weight_decay, c1, c2);
+  else
+    adamw_kernel<false><<<(unsigned)blocks, 256, 0, st>>>(master, m, v, grad, static_cast<__nv_bfloat16*>(w_bf16), n,
+                                                          lr, beta1, beta2, eps, weight_decay, c1, c2);
   return check_launch("adamw_kernel");
+}
+
+extern "C" int axm_moe_adamw_step(float* master, float* m, float* v, const float* grad, void* w_bf16,
+                                  int64_t n, float lr, float beta1, float beta2, float eps,
+                                  float weight_decay, int32_t step, void* stream) {
+  return adamw_launch(false, master, m, v, grad, w_bf16, n, lr, beta1, beta2, eps, weight_decay, step, 1, stream);
+}
+
+extern "C" int axm_moe_adamw_step_engine(float* master, float* m, float* v, const float* grad, void* w_bf16,
+                                         int64_t n, int64_t in_dim, float lr, float beta1, float beta2,
+                                         float eps, float weight_decay, int64_t step, void* stream) {
+  return adamw_launch(true, master, m, v, grad, w_bf16, n, lr, beta1, beta2, eps, weight_decay, step, in_dim,
+                      stream);
 }

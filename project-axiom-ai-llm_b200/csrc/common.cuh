@@ -27,6 +27,10 @@ struct SmemLimitCache {
 };
 int ensure_dynamic_smem(const void* kernel, size_t bytes, SmemLimitCache* cache, const char* what);
 
+// Shape checks of the routing and of the permute / combine entry points (router.cu, permute.cu).
+int validate_route(const AxmMoeDesc* d);
+int validate_perm(const AxmMoeDesc* d);
+
 #define AXM_CUDA(call)                                              \
   do {                                                              \
     if (int axm_rc_ = ::axm::cuda_status((call), #call)) return axm_rc_; \

@@ -18,13 +18,18 @@
 //   * the histogram is zeroed when allocated and accumulates across calls until
 //     reset_expert_histogram;
 //   * top-2 routing, bf16 router weights, everything enqueued on the caller's
-//     stream, the return value reflects enqueue-time errors only.
+//     stream, the return value reflects enqueue-time errors only;
+//   * the SwiGLU intermediate keeps 16 mantissa bits (AXM_FLAG_H_EXACT) so that every
+//     output element is within the layer tolerance of the engine's fp32 intermediate.
+// Private scratch (workspace, [T][2] index and gate arrays) is kept per device and
+// activation struct and re-sized when a call needs more; what it replaces is freed.
 // One deliberate difference: the engine looks at the first 16 experts only and
 // ignores the rest; this library refuses expert_count > 16 instead of routing to
 // a different set of experts than the weights describe.
 #include <dlfcn.h>
 
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -46,10 +51,21 @@ T load_field(const void* base, size_t off) {
 void store_ptr(void* base, size_t off, void* p) { memcpy(static_cast<char*>(base) + off, &p, sizeof(p)); }
 
 typedef void* (*AllocFn)(size_t, void*);
+typedef void (*FreeFn)(void*, void*);
+
+// The engine's allocator when its symbols are loaded in the process (then its
+// free_gpu_activations / free_vram accept what is published here), else the runtime's.
+AllocFn engine_alloc() {
+  static AllocFn fn = reinterpret_cast<AllocFn>(dlsym(RTLD_DEFAULT, "allocate_vram"));
+  return fn;
+}
+FreeFn engine_free() {
+  static FreeFn fn = reinterpret_cast<FreeFn>(dlsym(RTLD_DEFAULT, "free_vram"));
+  return fn;
+}
 
 void* vram_alloc(size_t bytes, void* stream) {
-  static AllocFn engine_alloc = reinterpret_cast<AllocFn>(dlsym(RTLD_DEFAULT, "allocate_vram"));
-  if (engine_alloc != nullptr) return engine_alloc(bytes, stream);
+  if (engine_alloc() != nullptr && engine_free() != nullptr) return engine_alloc()(bytes, stream);
   void* p = nullptr;
   if (cudaMalloc(&p, bytes) != cudaSuccess) {
     cudaGetLastError();
@@ -58,12 +74,61 @@ void* vram_alloc(size_t bytes, void* stream) {
   return p;
 }
 
+// Releases a buffer this library allocated and has outgrown.  Work that still uses it
+// was enqueued on `stream`: the engine's free is ordered on that stream, cudaFree
+// waits for the device.
+void vram_free(void* p, void* stream) {
+  if (p == nullptr) return;
+  if (engine_alloc() != nullptr && engine_free() != nullptr) {
+    engine_free()(p, stream);
+    return;
+  }
+  if (cudaFree(p) != cudaSuccess) cudaGetLastError();
+}
+
+// What this library keeps per (device, activation struct): its private scratch and the
+// token / expert counts the published buffers of that struct were sized for.  The engine
+// runs one forward at a time per activation struct (its own buffers have the same
+// restriction), so calls on the same struct must not overlap; different structs, or the
+// same process driving several GPUs, get separate state.
+struct Instance {
+  int device = -1;
+  const void* acts = nullptr;
+  void* workspace = nullptr;
+  size_t workspace_bytes = 0;
+  int32_t* idx = nullptr;  // [T][2]
+  float* gate = nullptr;   // [T][2]
+  size_t scratch_tokens = 0;
+  size_t pub_tokens = 0, pub_experts = 0, pub_dim = 0;  // 0: nothing published yet
+};
+
+constexpr int kMaxInstances = 64;
 std::mutex g_mutex;
-void* g_workspace = nullptr;
-size_t g_workspace_bytes = 0;
-int32_t* g_idx = nullptr;   // [T][2]
-float* g_gate = nullptr;    // [T][2]
-size_t g_tokens = 0;
+Instance g_instances[kMaxInstances];
+int g_num_instances = 0;
+
+Instance* instance_for(int device, const void* acts) {
+  for (int i = 0; i < g_num_instances; ++i)
+    if (g_instances[i].device == device && g_instances[i].acts == acts) return &g_instances[i];
+  if (g_num_instances == kMaxInstances) return nullptr;
+  Instance* in = &g_instances[g_num_instances++];
+  *in = Instance();
+  in->device = device;
+  in->acts = acts;
+  return in;
+}
+
+bool h_exact_mode() {
+  // The engine keeps the SwiGLU intermediate in fp32; the two-term intermediate is what
+  // meets its tolerance on every element, so it is the default behind the engine's
+  // interface.  AXM_DROPIN_H_EXACT=0 selects the faster one-term form.
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("AXM_DROPIN_H_EXACT");
+    v = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return v == 1;
+}
 
 __global__ void split_top2_kernel(const int32_t* __restrict__ idx, const float* __restrict__ gate,
                                   int32_t* __restrict__ first, int32_t* __restrict__ second,
@@ -105,11 +170,21 @@ extern "C" AXM_API bool forward_mixture_experts(void* hidden_states, const void*
   cudaStream_t st = static_cast<cudaStream_t>(stream);
 
   AxmMoeDesc d = {(int32_t)T, (int32_t)D, (int32_t)F, (int32_t)E, 2, 0, AXM_ROUTER_BF16,
-                  AXM_FLAG_RESIDUAL | AXM_FLAG_HIST_ACCUMULATE};
+                  AXM_FLAG_RESIDUAL | AXM_FLAG_HIST_ACCUMULATE | (h_exact_mode() ? AXM_FLAG_H_EXACT : 0)};
   size_t need = 0;
   if (axm_moe_workspace_bytes(&d, &need) != AXM_OK) return report("shape");
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
 
   std::lock_guard<std::mutex> lock(g_mutex);
+  Instance* in = instance_for(device, gpu_activations);
+  if (in == nullptr) {
+    fprintf(stderr, "axm_moe drop-in: more than %d activation structs in one process\n", kMaxInstances);
+    return false;
+  }
   // published buffers: allocate the ones the caller's struct does not hold yet
   struct Buf { size_t off; size_t bytes; bool zero; };
   const Buf bufs[] = {
@@ -117,6 +192,19 @@ extern "C" AXM_API bool forward_mixture_experts(void* hidden_states, const void*
       {kA_second, sizeof(int32_t) * T, false},     {kA_w_first, sizeof(float) * T, false},
       {kA_w_second, sizeof(float) * T, false},     {kA_histogram, sizeof(int32_t) * E, true},
       {kA_ffn_output, 2 * T * D, false},           {kA_residual_out, 2 * T * D, false}};
+  bool any_present = false;
+  for (const Buf& b : bufs) any_present = any_present || load_field<void*>(gpu_activations, b.off) != nullptr;
+  // The engine sizes these buffers on the first call and never again
+  // (core/src/CUDA/kernel/moe_router.cu:223-250), so a later call with more tokens or
+  // experts would write past them.  This library remembers the sizes and refuses.
+  if (any_present && in->pub_tokens != 0 && (T > in->pub_tokens || E > in->pub_experts || D > in->pub_dim)) {
+    fprintf(stderr,
+            "axm_moe drop-in: the published buffers of this activation struct hold %zu tokens x %zu "
+            "experts x %zu columns; a call with %zu x %zu x %zu does not fit (free them first)\n",
+            in->pub_tokens, in->pub_experts, in->pub_dim, T, E, D);
+    return false;
+  }
+  if (!any_present) in->pub_tokens = in->pub_experts = in->pub_dim = 0;  // the caller freed them
   for (const Buf& b : bufs) {
     if (load_field<void*>(gpu_activations, b.off) != nullptr) continue;
     void* p = vram_alloc(b.bytes, stream);
@@ -124,19 +212,36 @@ extern "C" AXM_API bool forward_mixture_experts(void* hidden_states, const void*
     if (b.zero && cudaMemsetAsync(p, 0, b.bytes, st) != cudaSuccess) return false;
     store_ptr(gpu_activations, b.off, p);
   }
-  if (need > g_workspace_bytes) {
+  if (in->pub_tokens == 0) {
+    in->pub_tokens = T;
+    in->pub_experts = E;
+    in->pub_dim = D;
+  }
+  if (need > in->workspace_bytes) {
     void* p = vram_alloc(need + 256, stream);
     if (p == nullptr) return false;
-    g_workspace = p;  // an outgrown workspace stays with the allocator (it may still be in use on a stream)
-    g_workspace_bytes = need;
+    vram_free(in->workspace, stream);
+    in->workspace = p;
+    in->workspace_bytes = need;
   }
-  if (T > g_tokens) {
-    g_idx = static_cast<int32_t*>(vram_alloc(sizeof(int32_t) * 2 * T, stream));
-    g_gate = static_cast<float*>(vram_alloc(sizeof(float) * 2 * T, stream));
-    if (!g_idx || !g_gate) return false;
-    g_tokens = T;
+  if (T > in->scratch_tokens) {
+    int32_t* ni = static_cast<int32_t*>(vram_alloc(sizeof(int32_t) * 2 * T, stream));
+    float* ng = static_cast<float*>(vram_alloc(sizeof(float) * 2 * T, stream));
+    if (!ni || !ng) {
+      vram_free(ni, stream);
+      vram_free(ng, stream);
+      return false;
+    }
+    vram_free(in->idx, stream);
+    vram_free(in->gate, stream);
+    in->idx = ni;
+    in->gate = ng;
+    in->scratch_tokens = T;
   }
-  void* ws = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(g_workspace) + 255) & ~uintptr_t(255));
+  void* ws = reinterpret_cast<void*>((reinterpret_cast<uintptr_t>(in->workspace) + 255) & ~uintptr_t(255));
+  int32_t* g_idx = in->idx;
+  float* g_gate = in->gate;
+  const size_t g_workspace_bytes = in->workspace_bytes;
 
   AxmMoeTensors t;
   memset(&t, 0, sizeof(t));

@@ -43,6 +43,13 @@ struct GemmArgs {
   __nv_bfloat16* save_g;  // SwiGLU kernel, training: also store the gate and up
   __nv_bfloat16* save_u;  // pre-activations (bf16, same shape as h), or null
   int* status;
+  // Two-term SwiGLU intermediate (AXM_FLAG_H_EXACT): h rows are [hi | lo], hi = bf16(h),
+  // lo = bf16(h - hi).  SwiGLU kernel: h_ld = row stride of h in elements, lo_off = column
+  // offset of the lo half (0: one term).  Down kernel: with two_term every weight k-block is
+  // used twice, against the hi rows (tm_a) and the lo rows (tm_a_alt).
+  int h_ld;
+  int lo_off;
+  int two_term;
 };
 
 
@@ -68,7 +75,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const int lane = threadIdx.x & 31;
   constexpr int BN_OUT = kSwiGLU ? 128 : 256;
   const int n_tiles = (args.n_total + BN_OUT - 1) / BN_OUT;
-  const int k_blocks = (args.k_total + BK - 1) / BK;
+  const bool two_term = !kSwiGLU && args.two_term != 0;
+  const int k_blocks = (two_term ? 2 : 1) * ((args.k_total + BK - 1) / BK);
   const int nseg = args.num_segments;
 
   // ---- set-up -------------------------------------------------------------------
@@ -142,16 +150,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           unsigned char* sa = tiles + (size_t)stage * kStageBytes;
           unsigned char* sb = sa + kABytes;
           mbar_expect_tx(&sh->full[stage], kStageBytes);
-          tma_load_2d(sa, ma, &sh->full[stage], kb * BK, a_row);
+          const int kk = (two_term ? (kb >> 1) : kb) * BK;
+          tma_load_2d(sa, (two_term && (kb & 1)) ? &tm_a_alt : ma, &sh->full[stage], kk, a_row);
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             if (kSwiGLU) {
               const CUtensorMap* mb = c < 2 ? mb0 : mb1;
               tma_load_3d(sb + c * kBChunkBytes, mb, &sh->full[stage],
-                          tc.n_tile * BN_OUT + (c & 1) * 64, kb * BK, e);
+                          tc.n_tile * BN_OUT + (c & 1) * 64, kk, e);
             } else {
               tma_load_3d(sb + c * kBChunkBytes, mb0, &sh->full[stage],
-                          tc.n_tile * BN_OUT + c * 64, kb * BK, e);
+                          tc.n_tile * BN_OUT + c * 64, kk, e);
             }
           }
           if (++stage == kStages) {
@@ -239,7 +248,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           uint32_t u[32];
           tmem_ld32(t_addr + 128 + c0, u);
           tmem_ld_wait();
-          uint32_t packed[16];
+          uint32_t packed[16], packed_lo[16];
+          const bool with_lo = args.lo_off != 0;
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
@@ -247,14 +257,22 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             float h0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
             float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
             packed[j] = pack_bf16(h0, h1);
+            // second term: what the first bf16 rounding dropped
+            packed_lo[j] = with_lo ? pack_bf16(h0 - bf16_lo(packed[j]), h1 - bf16_hi(packed[j])) : 0u;
           }
           if (row_ok) {
-            __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(out_base) + out_elem;
+            __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(out_base) +
+                                     (size_t)(sg.out_row0 + row_in_seg) * args.h_ld + n0;
 #pragma unroll
             for (int q = 0; q < 4; ++q)
-              if (n0 + c0 + q * 8 < args.n_total)
+              if (n0 + c0 + q * 8 < args.n_total) {
                 *reinterpret_cast<uint4*>(out_row + c0 + q * 8) =
                     make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+                if (with_lo)
+                  *reinterpret_cast<uint4*>(out_row + args.lo_off + c0 + q * 8) =
+                      make_uint4(packed_lo[4 * q], packed_lo[4 * q + 1], packed_lo[4 * q + 2],
+                                 packed_lo[4 * q + 3]);
+              }
             if (args.save_g != nullptr) {
 #pragma unroll
               for (int q = 0; q < 4; ++q)
@@ -378,9 +396,9 @@ bool use_2sm_kernels() {
 
 // Row-major bf16 matrix [rows][cols]; box = 64 columns x box_rows rows.
 static int make_map_2d(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols,
-                       uint32_t box_rows) {
+                       uint32_t box_rows, uint64_t ld = 0) {
   cuuint64_t dims[2] = {cols, rows};
-  cuuint64_t strides[1] = {cols * 2};
+  cuuint64_t strides[1] = {(ld ? ld : cols) * 2};  // ld: distance between rows in elements
   cuuint32_t box[2] = {64, box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = encode_fn()(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims,
@@ -438,7 +456,13 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
     u_sh = u;
     dn_sh = dn;
   }
-  if ((rc = make_map_2d(&a2, h, rows_total, F, BM))) return rc;
+  const bool exact = (d->flags & AXM_FLAG_H_EXACT) != 0;
+  const uint64_t h_ld = exact ? 2 * (uint64_t)F : (uint64_t)F;
+  CUtensorMap a2_lo;
+  if ((rc = make_map_2d(&a2, h, rows_total, F, BM, h_ld))) return rc;
+  a2_lo = a2;
+  if (exact && (rc = make_map_2d(&a2_lo, static_cast<const __nv_bfloat16*>(h) + F, rows_total, F, BM, h_ld)))
+    return rc;
 
   static SmemLimitCache smem_swiglu = {}, smem_down = {};
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(grouped_gemm_kernel<true>), kGemmSmemBytes,
@@ -459,6 +483,9 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.n_total = F;
   ga.k_total = D;
   ga.out = h;
+  ga.h_ld = (int)h_ld;
+  ga.lo_off = exact ? F : 0;
+  ga.two_term = 0;
   grouped_gemm_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
   if ((rc = check_launch("grouped_gemm_kernel<swiglu>"))) return rc;
   if (between != nullptr) cudaEventRecord(between, st);
@@ -468,7 +495,8 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.remote = remote;
   ga.save_g = nullptr;
   ga.save_u = nullptr;
-  grouped_gemm_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
+  ga.two_term = exact ? 1 : 0;
+  grouped_gemm_kernel<false><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a2, a2_lo, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_kernel<down>");
 }
 

@@ -40,6 +40,14 @@ struct Gemm2Args {
   __nv_bfloat16* save_u;  //   kModeDH: the saved pre-activations, read
   void* out1;             // kModeDH: dU (out is dG)
   int* status;
+  // Two-term SwiGLU intermediate (AXM_FLAG_H_EXACT): h rows are [hi | lo] of 2 * n_total bf16,
+  // hi = bf16(h), lo = bf16(h - hi).  kModeSwiGLU: h_ld is the row stride of h in elements and
+  // lo_off the column offset of the lo half (0: one term).  kModeDown: with two_term the
+  // reduction runs over both halves, k-block by k-block (hi, lo, hi, lo, ...) against the same
+  // weight rows, so the accumulator receives (hi + lo) . Wd.
+  int h_ld;
+  int lo_off;
+  int two_term;
 };
 
 // fp32 accumulate, bf16 A (K-major) and B (MN-major), N = 256, M = 256 over the pair
@@ -125,7 +133,9 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   constexpr int BN_OUT = kSwiGLU ? 128 : 256;
   const int n_tiles = (args.n_total + BN_OUT - 1) / BN_OUT;
   const int kb_half = (args.k_total + BK - 1) / BK;
-  const int k_blocks = kDX ? 2 * kb_half : kb_half;  // kModeDX: dG x Wg, then dU x Wu
+  const bool two_term = kMode == kModeDown && args.two_term != 0;
+  // kModeDX: dG x Wg, then dU x Wu; two-term down: every weight k-block twice (hi rows, lo rows)
+  const int k_blocks = (kDX || two_term) ? 2 * kb_half : kb_half;
   const int nseg = args.num_segments;
 
   for (int s = threadIdx.x; s < nseg; s += kGemmThreads) sh->seg[s] = args.segments[s];
@@ -226,9 +236,10 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             // K-major weights: one box of 64 k x 128 output columns
             tma2_load_3d(sb, second ? &tm_b1 : &tm_b0, bar, kk, n_col, e);
           } else {
-            tma2_load_2d(sa, ma, bar, kb * BK, a_row);
-            tma2_load_3d(sb, mb, bar, n_col, kb * BK, e);
-            tma2_load_3d(sb + kBChunkBytes, mb, bar, n_col + 64, kb * BK, e);
+            const int kk = (two_term ? (kb >> 1) : kb) * BK;
+            tma2_load_2d(sa, (two_term && (kb & 1)) ? &tm_a_alt : ma, bar, kk, a_row);
+            tma2_load_3d(sb, mb, bar, n_col, kk, e);
+            tma2_load_3d(sb + kBChunkBytes, mb, bar, n_col + 64, kk, e);
           }
           if (++stage == kStages2) {
             stage = 0;
@@ -395,7 +406,8 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             uint32_t u[32];
             tmem_ld32(t_addr + 128 + c0, u);
             tmem_ld_wait();
-            uint32_t packed[16];
+            uint32_t packed[16], packed_lo[16];
+            const bool with_lo = args.lo_off != 0;
 #pragma unroll
             for (int j = 0; j < 16; ++j) {
               float g0 = __uint_as_float(g[2 * j]), g1 = __uint_as_float(g[2 * j + 1]);
@@ -403,16 +415,24 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
               float h0 = __fdividef(g0, 1.0f + __expf(-g0)) * u0;
               float h1 = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
               packed[j] = pack_bf16(h0, h1);
+              // second term: what the first bf16 rounding dropped
+              packed_lo[j] = with_lo ? pack_bf16(h0 - bf16_lo(packed[j]), h1 - bf16_hi(packed[j])) : 0u;
             }
             if (row_ok) {
-              __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(args.out) + out_elem;
+              __nv_bfloat16* out_row = static_cast<__nv_bfloat16*>(args.out) +
+                                       (size_t)(sg.out_row0 + row_in_seg) * args.h_ld + n0;
 #pragma unroll
               for (int q = 0; q < 4; ++q)
-                if (n0 + c0 + q * 8 < args.n_total)
+                if (n0 + c0 + q * 8 < args.n_total) {
                   // streaming store: h is not read again by this kernel and must not push
                   // the activations and weights the other CTAs share out of L2
                   __stcs(reinterpret_cast<uint4*>(out_row + c0 + q * 8),
                          make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]));
+                  if (with_lo)
+                    __stcs(reinterpret_cast<uint4*>(out_row + args.lo_off + c0 + q * 8),
+                           make_uint4(packed_lo[4 * q], packed_lo[4 * q + 1], packed_lo[4 * q + 2],
+                                      packed_lo[4 * q + 3]));
+                }
               if (args.save_g != nullptr) {
 #pragma unroll
                 for (int q = 0; q < 4; ++q)
@@ -469,9 +489,10 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   }
 }
 
-static int map2_rows(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols) {
+// Row-major bf16 matrix of `rows` x `cols` whose rows are `ld` elements apart (0: cols).
+static int map2_rows(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld = 0) {
   const uint64_t dims[2] = {cols, rows};
-  const uint64_t strides[1] = {cols * 2};
+  const uint64_t strides[1] = {(ld ? ld : cols) * 2};
   const uint32_t box[2] = {64, (uint32_t)BM};
   return encode_tensor_map(m, base, 2, dims, strides, box);
 }
@@ -549,8 +570,16 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
     u_sh = u;
     dn_sh = dn;
   }
-  if ((rc = map2_rows(&a2, h, rows_total, F))) return rc;
+  const bool exact = (d->flags & AXM_FLAG_H_EXACT) != 0;
+  const uint64_t h_ld = exact ? 2 * (uint64_t)F : (uint64_t)F;
+  CUtensorMap a2_lo;
+  if ((rc = map2_rows(&a2, h, rows_total, F, h_ld))) return rc;
+  a2_lo = a2;
+  if (exact && (rc = map2_rows(&a2_lo, static_cast<const __nv_bfloat16*>(h) + F, rows_total, F, h_ld))) return rc;
   Gemm2Args ga;
+  ga.h_ld = (int)h_ld;
+  ga.lo_off = exact ? F : 0;
+  ga.two_term = 0;
   ga.segments = segments;
   ga.num_segments = num_segments;
   ga.routed_experts = E;
@@ -569,7 +598,8 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.save_g = nullptr;
   ga.save_u = nullptr;
   ga.out1 = nullptr;
-  grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2, dn, dn, dn_sh, dn_sh, ga);
+  ga.two_term = exact ? 1 : 0;
+  grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2_lo, dn, dn, dn_sh, dn_sh, ga);
   return check_launch("grouped_gemm_2sm_kernel<down>");
 }
 
@@ -613,6 +643,9 @@ int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.out1 = d_u;
   ga.save_g = static_cast<__nv_bfloat16*>(const_cast<void*>(g));
   ga.save_u = static_cast<__nv_bfloat16*>(const_cast<void*>(u));
+  ga.h_ld = F;
+  ga.lo_off = 0;
+  ga.two_term = 0;
   grouped_gemm_2sm_kernel<kModeDH><<<grid, kGemmThreads, kGemm2DhSmemBytes, st>>>(m_do, m_do, m_wd, m_wd, m_wd,
                                                                                   m_wd, ga);
   return check_launch("grouped_gemm_2sm_kernel<dH>");
@@ -648,6 +681,9 @@ int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.save_g = nullptr;
   ga.save_u = nullptr;
   ga.out1 = nullptr;
+  ga.h_ld = D;
+  ga.lo_off = 0;
+  ga.two_term = 0;
   grouped_gemm_2sm_kernel<kModeDX><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(m_dg, m_du, m_wg, m_wu, m_wg,
                                                                                 m_wu, ga);
   return check_launch("grouped_gemm_2sm_kernel<dX>");

@@ -158,7 +158,7 @@ static Workspace carve(const AxmMoeDesc* d, void* base) {
   w.slot_dst = static_cast<int32_t*>(take(sizeof(int32_t) * T * k));
   w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (E + S)));
   w.x_perm = take(2 * T * k * D);
-  w.h = take(2 * rows * F);
+  w.h = take(((d->flags & AXM_FLAG_H_EXACT) ? 4 : 2) * rows * F);  // one or two bf16 terms per element
   w.o = take(4 * rows * D);
   w.bytes = off;
   return w;

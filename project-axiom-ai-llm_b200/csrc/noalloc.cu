@@ -81,13 +81,19 @@ extern "C" int axm_moe_route_dispatch_noalloc(const AxmMoeDesc* desc, const floa
                 "(at most %d experts); use axm_moe_route_from_logits + axm_moe_permute with "
                 "caller-provided scratch",
                 desc->num_experts, kNoAllocMaxExperts);
+  // Everything both stages check is checked here, before the first launch: a call that
+  // is going to be refused must not have written routing results already.
+  if (int rc = validate_route(desc)) return rc;
+  if (int rc = validate_perm(desc)) return rc;
   if (!logits || !topk_idx || !topk_gate)
     return fail(AXM_ERR_ARGUMENT, "axm_moe_route_dispatch_noalloc: null pointer");
+  if (x_perm != nullptr && x == nullptr)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_route_dispatch_noalloc: x_perm without x");
   if (int rc = require_device()) return rc;
   int32_t* scratch = nullptr;
   if (int rc = scratch_for_current_device(&scratch)) return rc;
   // Same kernels as the regular entry points, with the library's own array as
-  // the block-count scratch.  Both calls validate the remaining arguments.
+  // the block-count scratch.
   if (int rc = axm_moe_route_from_logits(desc, logits, topk_idx, topk_gate, scratch, stream)) return rc;
   return axm_moe_permute(desc, x, topk_idx, scratch, histogram, offsets, row_src, slot_dst, x_perm,
                          stream);

@@ -290,9 +290,8 @@ int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
 
 }  // namespace axm
 
-using namespace axm;
-
-static int validate_perm(const AxmMoeDesc* d) {
+namespace axm {
+int validate_perm(const AxmMoeDesc* d) {
   if (d == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
   if (d->tokens < 0 || d->d_model <= 0 || d->num_experts <= 0 || d->top_k <= 0)
     return fail(AXM_ERR_ARGUMENT, "tokens/d_model/num_experts/top_k must be positive");
@@ -304,6 +303,9 @@ static int validate_perm(const AxmMoeDesc* d) {
     return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
   return AXM_OK;
 }
+}  // namespace axm
+
+using namespace axm;
 
 extern "C" int axm_moe_permute(const AxmMoeDesc* desc, const void* x, const int32_t* topk_idx,
                                const int32_t* block_counts, int32_t* histogram, int32_t* offsets,

@@ -413,7 +413,7 @@ static int launch_router(bool mma, size_t smem, cudaStream_t st, const __nv_bflo
   return check_launch("router_kernel");
 }
 
-static int validate_route(const AxmMoeDesc* d) {
+int validate_route(const AxmMoeDesc* d) {
   if (d == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
   if (d->tokens < 0 || d->d_model <= 0 || d->num_experts <= 0 || d->top_k <= 0)
     return fail(AXM_ERR_ARGUMENT, "tokens/d_model/num_experts/top_k must be positive");

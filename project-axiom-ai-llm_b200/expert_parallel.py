@@ -21,8 +21,8 @@ import ctypes
 import torch
 import torch.distributed as dist
 
-from . import (FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A, EpLayout, check,
-               current_stream, load, make_desc, ptr)
+from . import (AXM_ERR_TIMEOUT, FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A,
+               AxmError, EpLayout, check, current_stream, load, make_desc, ptr)
 
 
 class CudaStages:
@@ -262,6 +262,18 @@ class ExpertParallelMoeP2P:
     @property
     def last_rows_received(self):
         return int(self.rows_received.item())
+
+    def check_status(self):
+        """Reads the status word (synchronises this rank's stream) and raises AxmError with
+        AXM_ERR_TIMEOUT if a bounded wait of an exchange or GEMM kernel gave up since the last
+        check: the outputs of the calls in between must then be thrown away.  forward() never
+        synchronises, so a caller decides how often to look (every step costs one host sync;
+        once per optimiser step or per request batch is the usual place)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise AxmError(AXM_ERR_TIMEOUT, f"a bounded device-side wait gave up (kernel code {code}) "
+                                            f"on rank {self.rank}")
 
     def forward(self, x, out=None, events=None):
         st, lib, lo = self.stages, self.lib, ctypes.byref(self.layout)

@@ -34,6 +34,9 @@ class Oracle:
         lib.orc_moe_backward.argtypes = [vp, vp, i32, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
                                          i32, ctypes.c_float, i32, vp, vp, vp, vp, vp, vp, vp]
         lib.orc_rmsnorm.argtypes = [vp, vp, i32, i32, ctypes.c_float, vp]
+        lib.orc_set_threads.argtypes = [i32]
+        lib.orc_adamw_engine.argtypes = ([vp] * 5 + [ctypes.c_int64, ctypes.c_int64] +
+                                         [ctypes.c_float] * 5 + [ctypes.c_int64])
         lib.orc_moe_forward.argtypes = [vp, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp,
                                         vp, vp, i32, i32, i32, i32, vp, vp]
 
@@ -43,6 +46,14 @@ class Oracle:
 
     def threads(self):
         return self.lib.orc_num_threads()
+
+    def set_threads(self, n):
+        self.lib.orc_set_threads(int(n))
+
+    def adamw_engine(self, master, m, v, grad, w_bf16, in_dim, lr, b1, b2, eps, wd, step):
+        """In place on the numpy arrays (fp32 master, m, v; uint16 bf16 copy)."""
+        self.lib.orc_adamw_engine(self._p(master), self._p(m), self._p(v), self._p(grad),
+                                  self._p(w_bf16), master.size, in_dim, lr, b1, b2, eps, wd, step)
 
     def router_logits(self, x, wr, bias=None):
         T, D = x.shape

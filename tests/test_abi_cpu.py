@@ -110,3 +110,27 @@ def test_no_cpu_fallback(axm):
     assert rc == axm.AXM_ERR_DEVICE
     with pytest.raises(axm.AxmError):
         axm.check(rc)
+
+
+def test_exact_intermediate_flag_doubles_the_h_region(axm):
+    """AXM_FLAG_H_EXACT keeps the SwiGLU intermediate as two bf16 terms: T*k*F more elements."""
+    d = axm.make_desc(4096, 2048, 5632, 8, 2)
+    dx = axm.make_desc(4096, 2048, 5632, 8, 2, flags=axm.FLAG_RESIDUAL | axm.FLAG_H_EXACT)
+    assert axm.workspace_bytes(dx) - axm.workspace_bytes(d) == 2 * 4096 * 2 * 5632
+
+
+def test_adamw_argument_checks(axm):
+    """Refusals happen before any CUDA call: null pointers, a step below 1, fp32 buffers off a
+    16-byte boundary, and a bf16 working copy off an 8-byte boundary (the kernel stores four
+    bf16 values at a time; a misaligned store would fault on the device)."""
+    lib = axm.load()
+    a = ctypes.c_void_p(0x10000)
+    args = (64, 1e-3, 0.9, 0.95, 1e-8, 0.0, 1, None)
+    assert lib.axm_moe_adamw_step(None, a, a, a, a, *args) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_adamw_step(a, a, a, a, a, 64, 1e-3, 0.9, 0.95, 1e-8, 0.0, 0, None) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_adamw_step(ctypes.c_void_p(0x10004), a, a, a, a, *args) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_adamw_step(a, a, a, a, ctypes.c_void_p(0x10002), *args) == axm.AXM_ERR_ARGUMENT
+    assert b"8-byte aligned" in lib.axm_last_error()
+    assert lib.axm_moe_adamw_step_engine(a, a, a, a, ctypes.c_void_p(0x10004), 64, 2048, 1e-3, 0.9, 0.95,
+                                         1e-8, 0.0, 1, None) == axm.AXM_ERR_ARGUMENT
+    assert lib.axm_moe_adamw_step(a, a, a, a, a, 0, 1e-3, 0.9, 0.95, 1e-8, 0.0, 1, None) == axm.AXM_OK

@@ -34,3 +34,37 @@ def test_adamw_step(axm, cuda_device, n):
             err = np.abs(got.cpu().numpy() - ref)
             assert (err <= 1e-6 * np.maximum(1.0, np.abs(ref))).all()
         assert torch.equal(wb, dw.bfloat16())
+
+
+@pytest.mark.parametrize("n,in_dim", [(5, 1), (4099, 2048), (300001, 4096)])
+def test_adamw_engine_conventions_match_oracle(axm, oracle, cuda_device, n, in_dim):
+    """axm_moe_adamw_step_engine against the oracle's statement of the engine's optimiser
+    (lr / sqrt(in_dim), gradient clamp and non-finite -> 0, floored bias corrections, weight
+    clamp, update skipped when not finite).  The moments agree to fp32 rounding; weights
+    within 1e-6 * max(1, |w|) (the kernel's sqrt and divisions are IEEE, powf runs on the host)."""
+    lib = axm.load()
+    rng = np.random.default_rng(n)
+    w = (rng.standard_normal(n) * 0.5).astype(np.float32)
+    w[::97] = 1.9999                       # next to the weight clamp
+    m = np.zeros(n, np.float32)
+    v = np.zeros(n, np.float32)
+    wb_ref = np.zeros(n, np.uint16)
+    lr, b1, b2, eps, wd = 0.3, 0.9, 0.95, 1e-8, 0.1
+    dw, dm, dv = (torch.from_numpy(a.copy()).to(cuda_device) for a in (w, m, v))
+    wb = torch.zeros(n, dtype=torch.bfloat16, device=cuda_device)
+    for step in (0, 1, 2, 3):               # the engine counts step 0 as 1
+        g = (rng.standard_normal(n) * 30.0).astype(np.float32)
+        g[::11] = 1e4                       # clamped to 100
+        g[3::13] = np.nan                   # counts as zero
+        g[5::17] = -np.inf
+        dg = torch.from_numpy(g).to(cuda_device)
+        axm.check(lib.axm_moe_adamw_step_engine(axm.ptr(dw), axm.ptr(dm), axm.ptr(dv), axm.ptr(dg), axm.ptr(wb),
+                                                n, in_dim, lr, b1, b2, eps, wd, step, axm.current_stream()))
+        oracle.adamw_engine(w, m, v, g, wb_ref, in_dim, lr, b1, b2, eps, wd, step)
+        torch.cuda.synchronize()
+        for got, ref, what in ((dw, w, "w"), (dm, m, "m"), (dv, v, "v")):
+            err = np.abs(got.cpu().numpy() - ref)
+            assert (err <= 1e-6 * np.maximum(1.0, np.abs(ref))).all(), what
+        assert np.isfinite(dw.cpu().numpy()).all() and float(dw.abs().max()) <= 2.0
+        assert torch.equal(wb, dw.bfloat16())
+

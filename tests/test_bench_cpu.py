@@ -9,9 +9,10 @@ import sys
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def run_bench(*args):
+def run_bench(*args, env=None):
     return subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), *args], cwd=ROOT,
-                          capture_output=True, text=True, timeout=600)
+                          capture_output=True, text=True, timeout=600,
+                          env=dict(os.environ, **(env or {})))
 
 
 def test_reference_arm_prints_the_contract_line():
@@ -28,6 +29,25 @@ def test_reference_arm_prints_the_contract_line():
     assert line["e2e"] == {"value": line["value"], "unit": "tokens/s", "h2d_bytes_per_step": 0,
                            "d2h_bytes_per_step": 0}
     assert line["config"]["workload"].startswith("C1")
+
+
+def test_reference_arm_uses_all_cores_under_a_launcher_that_sets_one_thread():
+    """torch.distributed.run exports OMP_NUM_THREADS=1 to its workers; the reference arm asks
+    for every core it may run on instead of inheriting that."""
+    r = run_bench("--impl", "reference", "--config", "C1", "--steps", "1", "--warmup", "0",
+                  "--reference-tokens", "64", env={"OMP_NUM_THREADS": "1"})
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = json.loads(r.stdout.strip().splitlines()[-1])
+    assert line["cpu_baseline"]["cores"] == len(os.sched_getaffinity(0))
+
+
+def test_traffic_figure_comes_from_the_committed_summary():
+    sys.path.insert(0, ROOT)
+    import importlib
+    bench = importlib.import_module("bench")
+    total, commit = bench.ncu_traffic("C3")
+    assert total and total > 2e9 and commit
+    assert bench.ncu_traffic("no such workload") == (None, None)
 
 
 def test_product_arm_needs_a_gpu():

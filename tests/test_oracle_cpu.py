@@ -181,3 +181,36 @@ def test_engine_moe_test_invariants_hold_for_the_oracle(oracle):
     assert torch.isfinite(out.float()).all()
     assert not routing_balance_ok([512, 0, 0, 0, 0, 0, 0, 0], 256, 8)
     assert not routing_balance_ok([200, 45, 45, 45, 45, 44, 44, 44], 256, 8)
+
+
+def test_adamw_engine_statement():
+    """The oracle's AdamW with the engine's conventions against the same update spelled out
+    in numpy fp32 (step size lr / sqrt(in_dim), clamps, floored bias corrections)."""
+    import oracle_binding
+    orc = oracle_binding.load()
+    rng = np.random.default_rng(5)
+    n, in_dim = 1000, 256
+    w = (rng.standard_normal(n) * 0.5).astype(np.float32)
+    m = (rng.standard_normal(n) * 0.1).astype(np.float32)
+    v = np.abs(rng.standard_normal(n)).astype(np.float32)
+    g = (rng.standard_normal(n) * 60).astype(np.float32)
+    g[::7] = np.nan
+    g[1::9] = np.inf
+    lr, b1, b2, eps, wd, step = (np.float32(a) for a in (0.5, 0.9, 0.999, 1e-8, 0.01, 3))
+    gc = np.where(np.isfinite(g), g, np.float32(0)).clip(-100, 100).astype(np.float32)
+    m_ref = b1 * m + (np.float32(1) - b1) * gc
+    v_ref = b2 * v + (np.float32(1) - b2) * gc * gc
+    c1 = np.float32(1) - b1 ** step
+    c2 = np.float32(1) - b2 ** step
+    size = lr * (np.float32(1) / np.sqrt(np.float32(in_dim)))
+    w_ref = (w - size * ((m_ref / c1) / (np.sqrt(v_ref / c2) + eps) + wd * w)).clip(-2, 2).astype(np.float32)
+    wb = np.zeros(n, np.uint16)
+    orc.adamw_engine(w, m, v, g, wb, in_dim, float(lr), float(b1), float(b2), float(eps), float(wd), 3)
+    assert np.abs(m - m_ref).max() <= 1e-6 * np.abs(m_ref).max()
+    assert np.abs(v - v_ref).max() <= 1e-6 * np.abs(v_ref).max()
+    assert np.abs(w - w_ref).max() <= 1e-6
+    assert (wb == (torch.from_numpy(w).bfloat16().view(torch.int16).numpy().view(np.uint16))).all()
+    # a bias correction that underflows counts as 1: beta = 1 makes 1 - beta^t = 0
+    w2, m2, v2 = np.ones(4, np.float32), np.zeros(4, np.float32), np.zeros(4, np.float32)
+    orc.adamw_engine(w2, m2, v2, np.ones(4, np.float32), np.zeros(4, np.uint16), 1, 0.1, 1.0, 1.0, 1e-8, 0.0, 5)
+    assert np.isfinite(w2).all() and (m2 == 0).all() and (v2 == 0).all()

@@ -87,3 +87,43 @@ def test_train_step_is_deterministic_and_matches_inference_forward(axm, workload
     out3, _ = inf.forward(x)
     assert torch.equal(out3, out1)          # padded layout, same arithmetic per row
     assert torch.isfinite(keep["d_x"]).all() and torch.isfinite(keep["d_w_down"]).all()
+
+
+def test_full_size_c5_step_matches_oracle(axm, workloads, oracle, cuda_device):
+    """The training step at the full size of the forward + backward workload (8192 tokens,
+    d_model 2048, 16 experts of d_ff 4096, top-2: about 1024 rows per expert, so several
+    m-tiles per expert, 16 k-blocks per weight-gradient tile, CTA-pair kernels) against the
+    CPU oracle's backward on the same routing: every element of dX, dWr, dWg, dWu, dWd.
+    The oracle needs about a minute of host time for this size."""
+    cfg = workloads.CONFIGS["C5"]
+    alpha = cfg.aux_alpha
+    x, w = workloads.make_inputs(cfg)
+    dY = torch.randn(cfg.tokens, cfg.d_model, generator=torch.Generator().manual_seed(cfg.seed + 100))
+    wd = helpers.to_dev(w, cuda_device)
+    layer = axm.MoeTrainLayer(wd, cfg.tokens, cfg.top_k, aux_alpha=alpha)
+    xd, dYd = x.to(cuda_device), dY.to(cuda_device)
+    out, aux, grads = layer.step(xd, dYd)
+    torch.cuda.synchronize()
+    assert int(layer.workspace[:4].view(torch.int32).item()) == 0, "a GEMM kernel reported a timed-out wait"
+
+    desc = helpers.desc_for(axm, cfg)
+    logits, idx_d, gate_d, _ = helpers.run_router(axm, desc, xd, wd["router_w"])
+    zl = logits.cpu().numpy()
+    idx, gates = idx_d.cpu().numpy(), gate_d.cpu().numpy()
+    _, _, probs, _, _ = oracle.route(zl, cfg.top_k)
+    hist = np.bincount(idx.ravel(), minlength=cfg.num_experts)
+    assert (layer.histogram.cpu().numpy() == hist).all()
+    assert hist.max() > 2 * 128 and hist.min() > 128, "every expert spans several m-tiles at this size"
+    aux_ref = oracle.aux_loss(probs, idx, alpha)
+    assert abs(float(aux.item()) - aux_ref) <= 1e-5 * max(1.0, abs(aux_ref))
+
+    ref = oracle.backward(x, w, idx, gates, probs, dY.numpy(), alpha=alpha)
+    close(grads["d_x"].cpu() - dY, ref["dX"] - dY.numpy(), "dX at full size")
+    close(grads["d_router_w"], ref["dWr"], "dWr at full size")
+    for gname, oname in (("d_w_gate", "dWg"), ("d_w_up", "dWu"), ("d_w_down", "dWd")):
+        for e in range(cfg.num_experts):    # one expert at a time keeps the host copies small
+            close(grads[gname][e], ref[oname][e], f"{oname}[{e}] at full size")
+    # forward output of the same step on a token slice
+    lo, hi = 4000, 4064
+    y_ref, out_ref = oracle.forward(x, w, idx, gates, h_bf16=True, tok_range=(lo, hi))
+    helpers.assert_close_out(out[lo:hi], out_ref[lo:hi], y_ref[lo:hi], what="training forward out (slice)")

@@ -56,7 +56,7 @@ def case(axm, cuda_device, T, D, E, k, seed):
     return desc, logits, x
 
 
-def test_two_calls_in_a_row_match_the_regular_entry_points(axm, cuda_device):
+def test_two_calls_in_a_row_match_the_regular_entry_points(axm, oracle, cuda_device):
     # a wide case first, then a narrower one that reuses the front of the same scratch
     for (T, D, E, k, seed) in [(3000, 128, 128, 6, 1), (1111, 64, 8, 2, 2)]:
         desc, logits, x = case(axm, cuda_device, T, D, E, k, seed)
@@ -72,6 +72,19 @@ def test_two_calls_in_a_row_match_the_regular_entry_points(axm, cuda_device):
             else:
                 assert torch.equal(a, b), n
         assert int(got[2].sum()) == T * k
+        # and against the CPU oracle from the same logits: the same experts except where it
+        # flags a near-tie (CPU and GPU expf may differ in the last bit), and the placement
+        # rule applied to the indices this call produced
+        idx = got[0].cpu().numpy()
+        oi, og, _, oc, tie = oracle.route(logits.cpu().numpy(), k)
+        mism = (oi != idx).any(axis=1)
+        assert not (mism & (tie == 0)).any()
+        ooff, ors, osd = oracle.permutation(idx, E)
+        assert (got[3].cpu().numpy() == ooff).all()
+        assert (got[4].cpu().numpy() == ors).all() and (got[5].cpu().numpy() == osd).all()
+        assert (got[2].cpu().numpy() == np.bincount(idx.ravel(), minlength=E)).all()
+        rows = got[6].cpu()
+        assert torch.equal(rows, x.cpu()[torch.from_numpy(ors).long() // k])
 
 
 def test_more_experts_than_the_builtin_scratch_holds_is_refused(axm, cuda_device):
@@ -87,3 +100,19 @@ def test_more_experts_than_the_builtin_scratch_holds_is_refused(axm, cuda_device
     assert rc == axm.AXM_ERR_ARGUMENT
     assert b"exceeds the built-in scratch" in lib.axm_last_error()
     assert int((idx != -7).sum()) == 0          # nothing was launched
+
+
+def test_a_refused_call_has_launched_nothing(axm, cuda_device):
+    """Every argument is checked before the first kernel: x_perm without x is refused
+    with the routing outputs untouched."""
+    desc, logits, x = case(axm, cuda_device, 64, 64, 8, 2, 4)
+    lib = axm.load()
+    idx = torch.full((64, 2), -7, dtype=torch.int32, device=cuda_device)
+    gate = torch.zeros(64, 2, dtype=torch.float32, device=cuda_device)
+    xp = torch.zeros(128, 64, dtype=torch.bfloat16, device=cuda_device)
+    rc = lib.axm_moe_route_dispatch_noalloc(ctypes.byref(desc), axm.ptr(logits), None,
+                                            axm.ptr(idx), axm.ptr(gate), None, None, None, None,
+                                            axm.ptr(xp), axm.current_stream())
+    torch.cuda.synchronize()
+    assert rc == axm.AXM_ERR_ARGUMENT
+    assert int((idx != -7).sum()) == 0
