@@ -11,7 +11,10 @@
 # asks for an explicit acceptance (AXIOM_ACCEPT_LICENSE=ON); this script asks for
 # the same variable and does nothing without it.  Read $REF/LICENSE first.
 set -e
-REF="${REF:-/root/reference}"
+if [ -z "${REF}" ]; then
+  echo "build_ref.sh: set REF to the directory that holds the reference engine's sources" >&2
+  exit 2
+fi
 HERE="$(cd "$(dirname "$0")" && pwd)"
 if [ "${AXIOM_ACCEPT_LICENSE}" != "ON" ]; then
   echo "build_ref.sh: set AXIOM_ACCEPT_LICENSE=ON to accept ${REF}/LICENSE and build the reference kernels" >&2

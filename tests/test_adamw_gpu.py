@@ -40,8 +40,8 @@ def test_adamw_step(axm, cuda_device, n):
 def test_adamw_engine_conventions_match_oracle(axm, oracle, cuda_device, n, in_dim):
     """axm_moe_adamw_step_engine against the oracle's statement of the engine's optimiser
     (lr / sqrt(in_dim), gradient clamp and non-finite -> 0, floored bias corrections, weight
-    clamp, update skipped when not finite).  The moments agree to fp32 rounding; weights
-    within 1e-6 * max(1, |w|) (the kernel's sqrt and divisions are IEEE, powf runs on the host)."""
+    clamp, update skipped when not finite).  fp32 throughout; the kernel's sqrt and divisions
+    are IEEE and powf runs on the host, so the two differ only by fused multiply-adds."""
     lib = axm.load()
     rng = np.random.default_rng(n)
     w = (rng.standard_normal(n) * 0.5).astype(np.float32)
@@ -62,9 +62,13 @@ def test_adamw_engine_conventions_match_oracle(axm, oracle, cuda_device, n, in_d
                                                 n, in_dim, lr, b1, b2, eps, wd, step, axm.current_stream()))
         oracle.adamw_engine(w, m, v, g, wb_ref, in_dim, lr, b1, b2, eps, wd, step)
         torch.cuda.synchronize()
-        for got, ref, what in ((dw, w, "w"), (dm, m, "m"), (dv, v, "v")):
+        # m = b1 * m + (1 - b1) * g adds terms of magnitude up to 100 that may cancel, and the
+        # kernel contracts it into a fused multiply-add: absolute 1e-5 there; v sums positive
+        # terms and w moves by a small step: relative 1e-6
+        for got, ref, what, tol in ((dw, w, "w", 1e-6 * np.maximum(1.0, np.abs(w))), (dm, m, "m", 1e-5),
+                                    (dv, v, "v", 1e-6 * np.maximum(1.0, np.abs(v)))):
             err = np.abs(got.cpu().numpy() - ref)
-            assert (err <= 1e-6 * np.maximum(1.0, np.abs(ref))).all(), what
+            assert (err <= tol).all(), what
         assert np.isfinite(dw.cpu().numpy()).all() and float(dw.abs().max()) <= 2.0
         assert torch.equal(wb, dw.bfloat16())
 
