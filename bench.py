@@ -10,6 +10,7 @@ statement of the layer (the reference engine has no CPU implementation of its
 own and its GPU kernels are single-GPU CUDA-core code) on the host cores.
 """
 import argparse
+import ctypes
 import importlib
 import importlib.util
 import json
@@ -299,13 +300,13 @@ def main():
         d_out = torch.randn(T, D, device=dev, generator=torch.Generator(device=dev).manual_seed(cfg.seed))
         out = layer.out
         step = lambda: layer.step(x_local, d_out)
-        launches_per_step = 17
+        launches_per_step = 17 + (1 if axm.router_scratch_bytes(layer.desc) else 0)
     elif world == 1:
         layer = axm.MoeLayer(w, T, k, publish_y=False)
         out = torch.empty_like(x)
         x_local = x
         step = lambda: layer.forward(x_local, out)
-        launches_per_step = 5
+        launches_per_step = layer.lib.axm_moe_forward_launches(ctypes.byref(layer.desc))
     else:
         ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
         assert T % world == 0 and cfg.num_experts % world == 0
@@ -321,7 +322,8 @@ def main():
         out = torch.empty_like(x_local)
         step = lambda: layer.forward(x_local, out)
         # router, permute, two GEMMs, combine (+ dispatch, segments, return, wait with p2p)
-        launches_per_step = 9 if args.ep_transport == "p2p" else 5
+        launches_per_step = (9 if args.ep_transport == "p2p" else 5) + \
+            (1 if axm.router_scratch_bytes(layer.desc_route) else 0)
     del x
     torch.cuda.empty_cache()
 

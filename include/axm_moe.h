@@ -171,6 +171,20 @@ AXM_API int axm_moe_router(const AxmMoeDesc* desc, const void* x, const void* ro
                            const float* router_bias, float* logits, int32_t* topk_idx,
                            float* topk_gate, int32_t* block_counts, void* stream);
 
+/* The same router with scratch memory for its tensor-core form: the logits are computed as
+ * a tcgen05 product streamed through TMA (x is read from HBM once, at bandwidth), which needs
+ * the router weights split into bf16 terms and transposed - `scratch`, of
+ * axm_moe_router_scratch_bytes() bytes (16-byte aligned), written by a small preparation
+ * kernel at every call.  0 bytes means the shape is not served by that kernel (more than 80
+ * experts with fp32 weights); then, and when scratch is NULL or too small, the call runs
+ * axm_moe_router.  `status` (optional int32 device word): cleared at the start of the call on
+ * the tensor-core path, then set to a non-zero code if a bounded wait gave up. */
+AXM_API int axm_moe_router_scratch_bytes(const AxmMoeDesc* desc, size_t* bytes);
+AXM_API int axm_moe_router_ws(const AxmMoeDesc* desc, const void* x, const void* router_w,
+                              const float* router_bias, float* logits, int32_t* topk_idx,
+                              float* topk_gate, int32_t* block_counts, void* scratch,
+                              size_t scratch_bytes, int32_t* status, void* stream);
+
 /* Routing from caller-supplied fp32 logits: the part of the router whose
  * results must equal the reference bit for bit
  * (core/src/CUDA/kernel/moe_router.cu:59-110). */

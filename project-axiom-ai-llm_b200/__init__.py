@@ -101,6 +101,8 @@ def load():
     lib.axm_moe_forward_host.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, vp, vp, vp, vp, sz, vp]
     lib.axm_moe_status_word.argtypes = [dp, vp, ctypes.POINTER(vp)]
     lib.axm_moe_router.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
+    lib.axm_moe_router_scratch_bytes.argtypes = [dp, ctypes.POINTER(sz)]
+    lib.axm_moe_router_ws.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, sz, vp, vp]
     lib.axm_moe_route_from_logits.argtypes = [dp, vp, vp, vp, vp, vp]
     lib.axm_moe_permute.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.axm_moe_build_segments.argtypes = [dp, vp, vp, vp]
@@ -152,6 +154,13 @@ def current_stream():
 def make_desc(tokens, d_model, d_ff, num_experts, top_k, num_shared=0, router_dtype=ROUTER_FP32,
               flags=FLAG_RESIDUAL):
     return MoeDesc(tokens, d_model, d_ff, num_experts, top_k, num_shared, router_dtype, flags)
+
+
+def router_scratch_bytes(desc):
+    """Bytes of scratch axm_moe_router_ws wants for this shape (0: no tensor-core router for it)."""
+    n = ctypes.c_size_t(0)
+    check(load().axm_moe_router_scratch_bytes(ctypes.byref(desc), ctypes.byref(n)))
+    return n.value
 
 
 def workspace_bytes(desc):

@@ -13,7 +13,7 @@
 //
 //   L = sum(dOut * out) + aux,  out = x + y,  aux = alpha * E * sum_e f_e * P_e,
 //   f_e = count_e / (T k) (constant), P_e = mean_t p[t, e].
-#include "common.cuh"
+#include "router.cuh"
 
 namespace axm {
 
@@ -341,6 +341,8 @@ struct TrainWs {
   float* dz;
   float* dwr_partial;
   void *x_perm, *g, *u, *h, *o, *d_o, *d_g, *d_u, *d_xp;
+  void* router_scratch;
+  size_t router_scratch_bytes;
   int rows_max;
   size_t bytes;
 };
@@ -380,6 +382,9 @@ static TrainWs carve_train(const AxmMoeDesc* d, void* base) {
   w.d_g = take(2 * R * F);
   w.d_u = take(2 * R * F);
   w.d_xp = take(4 * R * D);
+  w.router_scratch_bytes = 0;
+  axm_moe_router_scratch_bytes(d, &w.router_scratch_bytes);
+  w.router_scratch = take(w.router_scratch_bytes);
   w.bytes = off;
   return w;
 }
@@ -433,11 +438,14 @@ extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* 
   AxmMoeDesc d = *desc;
   // ws.counts holds this call's counts; the saved h of the training layout is one bf16 term
   d.flags &= ~(AXM_FLAG_HIST_ACCUMULATE | AXM_FLAG_H_EXACT);
-  int rc = axm_moe_router(&d, t->x, t->router_w, t->router_bias, w.logits, w.topk_idx, w.topk_gate,
-                          w.block_counts, stream);
+  bool router_cleared_status = false;
+  int rc = launch_router_auto(&d, t->x, t->router_w, t->router_bias, w.logits, w.topk_idx, w.topk_gate,
+                              w.block_counts, w.router_scratch, w.router_scratch_bytes, w.status, stream,
+                              &router_cleared_status);
   if (rc) return rc;
   if ((rc = launch_permute(&d, t->x, w.topk_idx, w.block_counts, w.counts, w.offsets, w.row_src,
-                           w.slot_dst, w.x_perm, w.segments, w.status, st, kTrainAlign)))
+                           w.slot_dst, w.x_perm, w.segments, router_cleared_status ? nullptr : w.status, st,
+                           kTrainAlign)))
     return rc;
   if ((rc = launch_expert_ffn(&d, w.x_perm, w.rows_max, nullptr, 0, w.segments, E, t->w_gate, t->w_up,
                               t->w_down, nullptr, nullptr, nullptr, w.h, w.o, w.rows_max, w.status, st,

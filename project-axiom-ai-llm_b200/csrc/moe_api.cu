@@ -9,7 +9,7 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "common.cuh"
+#include "router.cuh"
 
 namespace axm {
 
@@ -134,6 +134,8 @@ struct Workspace {
   void* x_perm;
   void* h;
   void* o;
+  void* router_scratch;  // split, transposed router weights of the tensor-core router (may be empty)
+  size_t router_scratch_bytes;
   size_t bytes;
 };
 
@@ -160,6 +162,9 @@ static Workspace carve(const AxmMoeDesc* d, void* base) {
   w.x_perm = take(2 * T * k * D);
   w.h = take(((d->flags & AXM_FLAG_H_EXACT) ? 4 : 2) * rows * F);  // one or two bf16 terms per element
   w.o = take(4 * rows * D);
+  w.router_scratch_bytes = 0;
+  axm_moe_router_scratch_bytes(d, &w.router_scratch_bytes);
+  w.router_scratch = take(w.router_scratch_bytes);
   w.bytes = off;
   return w;
 }
@@ -192,7 +197,12 @@ extern "C" const char* axm_version(void) { return "axm_moe 0.1 sm_100a"; }
 
 extern "C" int axm_moe_forward_launches(const AxmMoeDesc* desc) {
   if (validate_forward(desc) != AXM_OK) return AXM_ERR_ARGUMENT;
-  return desc->tokens == 0 ? 0 : 5;  // router, permute, gate/up GEMM, down GEMM, combine
+  if (desc->tokens == 0) return 0;
+  size_t scratch = 0;
+  axm_moe_router_scratch_bytes(desc, &scratch);
+  // router (preceded by its weight-preparation kernel on the tensor-core path), permute,
+  // gate/up GEMM, down GEMM, combine
+  return scratch > 0 ? 6 : 5;
 }
 
 extern "C" int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes) {
@@ -238,12 +248,13 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
   const int T = desc->tokens, k = desc->top_k, S = desc->num_shared, E = desc->num_experts;
 
   if (ev) cudaEventRecord(ev[0], st);
-  int rc = axm_moe_router(desc, t->x, t->router_w, t->router_bias, logits, idx, gate,
-                          w.block_counts, stream);
+  bool router_cleared_status = false;  // the tensor-core router's preparation kernel clears the word
+  int rc = launch_router_auto(desc, t->x, t->router_w, t->router_bias, logits, idx, gate, w.block_counts,
+                              w.router_scratch, w.router_scratch_bytes, w.status, stream, &router_cleared_status);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[1], st);
   rc = launch_permute(desc, t->x, idx, w.block_counts, t->histogram, offsets, row_src, slot_dst,
-                      w.x_perm, w.segments, w.status, st, 1);
+                      w.x_perm, w.segments, router_cleared_status ? nullptr : w.status, st, 1);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[2], st);
   rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,

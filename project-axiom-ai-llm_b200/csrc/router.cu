@@ -15,7 +15,7 @@
 // one CTA each.  The permute kernel uses the same split, so the per-block
 // counts written here give it a stable placement without atomics on global
 // memory.
-#include "common.cuh"
+#include "router.cuh"
 
 namespace axm {
 
@@ -23,7 +23,7 @@ constexpr int kRouterThreads = 256;
 constexpr int kTokSub = 64;   // tokens handled per pass inside a block
 constexpr int kEC = 8;        // experts per register chunk
 constexpr int kTB = 4;        // tokens whose loads are in flight together
-constexpr int kMaxK = 8;
+constexpr int kMaxK = kRouteMaxK;
 
 __host__ __device__ inline int route_block_begin(int b, int T) {
   return (int)(((long long)b * T) / AXM_ROUTE_BLOCKS);
@@ -38,54 +38,6 @@ __device__ __forceinline__ float load_w<float>(const float* p) {
 template <>
 __device__ __forceinline__ float load_w<__nv_bfloat16>(const __nv_bfloat16* p) {
   return __bfloat162float(*p);
-}
-
-// Softmax / top-k / gates for one token whose logits sit in shared memory
-// (row `z`, overwritten with probabilities and then scratched).
-template <int K_MAX>
-__device__ __forceinline__ void route_one_token(float* z, int E, int k, int32_t* idx_out,
-                                                float* gate_out, int* hist_s) {
-  float m = z[0];
-  for (int e = 1; e < E; ++e) m = z[e] > m ? z[e] : m;
-  float s = 0.0f;
-  for (int e = 0; e < E; ++e) {
-    float p = expf(z[e] - m);
-    z[e] = p;
-    s += p;
-  }
-  float inv = 1.0f / (s + 1e-9f);
-  for (int e = 0; e < E; ++e) z[e] *= inv;
-
-  int sel[K_MAX];
-  float pv[K_MAX];
-  float sel_sum = 0.0f;
-#pragma unroll
-  for (int i = 0; i < K_MAX; ++i) {
-    if (i < k) {
-      int best = 0;
-      float bv = -1.0f;
-      for (int e = 0; e < E; ++e) {
-        float p = z[e];
-        if (p > bv) {
-          bv = p;
-          best = e;
-        }
-      }
-      z[best] = -2.0f;  // taken
-      sel[i] = best;
-      pv[i] = bv;
-      sel_sum += bv;
-    }
-  }
-  float denom = sel_sum + 1e-9f;
-#pragma unroll
-  for (int i = 0; i < K_MAX; ++i) {
-    if (i < k) {
-      idx_out[i] = sel[i];
-      gate_out[i] = pv[i] / denom;
-      atomicAdd(&hist_s[sel[i]], 1);
-    }
-  }
 }
 
 // ---- tensor-core logits for many experts --------------------------------------------
@@ -446,6 +398,45 @@ extern "C" int axm_moe_router(const AxmMoeDesc* desc, const void* x, const void*
     return launch_router<__nv_bfloat16>(mma, smem, st, xb, static_cast<const __nv_bfloat16*>(router_w),
                                         router_bias, logits, topk_idx, topk_gate, block_counts, desc);
   return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", desc->router_dtype);
+}
+
+extern "C" int axm_moe_router_scratch_bytes(const AxmMoeDesc* desc, size_t* bytes) {
+  if (int rc = validate_route(desc)) return rc;
+  if (bytes == nullptr) return fail(AXM_ERR_ARGUMENT, "bytes is null");
+  if (desc->router_dtype != AXM_ROUTER_FP32 && desc->router_dtype != AXM_ROUTER_BF16)
+    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", desc->router_dtype);
+  const RouterTcPlan p = router_tc_plan(desc);
+  *bytes = p.ok ? p.scratch_bytes : 0;
+  return AXM_OK;
+}
+
+namespace axm {
+int launch_router_auto(const AxmMoeDesc* desc, const void* x, const void* router_w, const float* router_bias,
+                       float* logits, int32_t* topk_idx, float* topk_gate, int32_t* block_counts,
+                       void* scratch, size_t scratch_bytes, int32_t* status, void* stream, bool* used_tc) {
+  if (used_tc) *used_tc = false;
+  if (int rc = validate_route(desc)) return rc;
+  if (!x || !router_w || !topk_idx || !topk_gate || !block_counts)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_router_ws: null pointer");
+  if (desc->router_dtype != AXM_ROUTER_FP32 && desc->router_dtype != AXM_ROUTER_BF16)
+    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", desc->router_dtype);
+  const RouterTcPlan p = router_tc_plan(desc);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(scratch)) & 15) == 0;
+  if (!p.ok || scratch == nullptr || scratch_bytes < p.scratch_bytes || !aligned || desc->tokens == 0)
+    return axm_moe_router(desc, x, router_w, router_bias, logits, topk_idx, topk_gate, block_counts, stream);
+  if (int rc = require_device()) return rc;
+  if (used_tc) *used_tc = true;
+  return launch_router_tc(desc, p, x, router_w, router_bias, logits, topk_idx, topk_gate, block_counts,
+                          scratch, status, static_cast<cudaStream_t>(stream));
+}
+}  // namespace axm
+
+extern "C" int axm_moe_router_ws(const AxmMoeDesc* desc, const void* x, const void* router_w,
+                                 const float* router_bias, float* logits, int32_t* topk_idx,
+                                 float* topk_gate, int32_t* block_counts, void* scratch,
+                                 size_t scratch_bytes, int32_t* status, void* stream) {
+  return launch_router_auto(desc, x, router_w, router_bias, logits, topk_idx, topk_gate, block_counts, scratch,
+                            scratch_bytes, status, stream, nullptr);
 }
 
 extern "C" int axm_moe_route_from_logits(const AxmMoeDesc* desc, const float* logits,

@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 
 from . import (AXM_ERR_TIMEOUT, FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A,
-               AxmError, EpLayout, check, current_stream, load, make_desc, ptr)
+               AxmError, EpLayout, check, current_stream, load, make_desc, ptr, router_scratch_bytes)
 
 
 class CudaStages:
@@ -30,11 +30,17 @@ class CudaStages:
 
     def __init__(self):
         self.lib = load()
+        self.router_scratch = None   # split router weights of the tensor-core router, sized on first use
 
     def router(self, desc, x, w, logits, idx, gate, block_counts):
-        check(self.lib.axm_moe_router(ctypes.byref(desc), ptr(x), ptr(w["router_w"]),
-                                      ptr(w.get("router_bias")), ptr(logits), ptr(idx), ptr(gate),
-                                      ptr(block_counts), current_stream()))
+        need = router_scratch_bytes(desc)
+        if need and (self.router_scratch is None or self.router_scratch.numel() < need
+                     or self.router_scratch.device != x.device):
+            self.router_scratch = torch.empty(need, dtype=torch.uint8, device=x.device)
+        check(self.lib.axm_moe_router_ws(ctypes.byref(desc), ptr(x), ptr(w["router_w"]),
+                                         ptr(w.get("router_bias")), ptr(logits), ptr(idx), ptr(gate),
+                                         ptr(block_counts), ptr(self.router_scratch) if need else None,
+                                         need, None, current_stream()))
 
     def permute(self, desc, x, idx, block_counts, histogram, offsets, row_src, slot_dst, x_perm):
         check(self.lib.axm_moe_permute(ctypes.byref(desc), ptr(x), ptr(idx), ptr(block_counts),

@@ -12,17 +12,29 @@ def desc_for(axm, cfg, router_dtype=None, flags=None, tokens=None):
                          axm.FLAG_RESIDUAL if flags is None else flags)
 
 
-def run_router(axm, desc, x, wr, bias=None):
+def run_router(axm, desc, x, wr, bias=None, tensor_core=True):
+    """The fused router: with scratch (tensor-core kernel where the shape allows it) or, with
+    tensor_core=False, through axm_moe_router (CUDA-core kernel)."""
     lib = axm.load()
     T, E, k = desc.tokens, desc.num_experts, desc.top_k
     dev = x.device
-    logits = torch.empty(T, E, dtype=torch.float32, device=dev)
-    idx = torch.empty(T, k, dtype=torch.int32, device=dev)
+    logits = torch.full((T, E), float("nan"), dtype=torch.float32, device=dev)
+    idx = torch.full((T, k), -1, dtype=torch.int32, device=dev)
     gate = torch.empty(T, k, dtype=torch.float32, device=dev)
-    bc = torch.empty(axm.ROUTE_BLOCKS, E, dtype=torch.int32, device=dev)
-    axm.check(lib.axm_moe_router(ctypes.byref(desc), axm.ptr(x), axm.ptr(wr), axm.ptr(bias),
-                                 axm.ptr(logits), axm.ptr(idx), axm.ptr(gate), axm.ptr(bc),
-                                 axm.current_stream()))
+    bc = torch.full((axm.ROUTE_BLOCKS, E), 12345, dtype=torch.int32, device=dev)
+    if tensor_core:
+        need = axm.router_scratch_bytes(desc)
+        scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=dev)
+        status = torch.zeros(1, dtype=torch.int32, device=dev)
+        axm.check(lib.axm_moe_router_ws(ctypes.byref(desc), axm.ptr(x), axm.ptr(wr), axm.ptr(bias),
+                                        axm.ptr(logits), axm.ptr(idx), axm.ptr(gate), axm.ptr(bc),
+                                        axm.ptr(scratch), need, axm.ptr(status), axm.current_stream()))
+        torch.cuda.synchronize()
+        assert int(status.item()) == 0, f"router reported a timed-out wait: {int(status.item())}"
+    else:
+        axm.check(lib.axm_moe_router(ctypes.byref(desc), axm.ptr(x), axm.ptr(wr), axm.ptr(bias),
+                                     axm.ptr(logits), axm.ptr(idx), axm.ptr(gate), axm.ptr(bc),
+                                     axm.current_stream()))
     return logits, idx, gate, bc
 
 

@@ -54,7 +54,12 @@ def test_workspace_size_and_launch_count(axm):
     rows = 4096 * 2
     assert n >= 2 * rows * (2048 + 5632 + 2048)
     assert n % 256 == 0
-    assert axm.load().axm_moe_forward_launches(ctypes.byref(d)) == 5
+    # router (with its weight-preparation kernel on the tensor-core path), permute, two GEMMs, combine
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(d)) == 6
+    assert axm.router_scratch_bytes(d) == 3 * 16 * 2048 * 2      # three bf16 terms of 16 padded experts
+    wide = axm.make_desc(4096, 2048, 5632, 128, 2)                 # 3 * 128 columns exceed one MMA
+    assert axm.router_scratch_bytes(wide) == 0
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(wide)) == 5
     d0 = axm.make_desc(0, 2048, 5632, 8, 2)
     assert axm.load().axm_moe_forward_launches(ctypes.byref(d0)) == 0
 

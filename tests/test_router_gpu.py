@@ -42,18 +42,42 @@ CASES = [
 
 @pytest.mark.parametrize("name,tokens,kw", CASES)
 @pytest.mark.parametrize("router_bf16", [False, True])
-def test_fused_router(axm, workloads, oracle, cuda_device, name, tokens, kw, router_bf16):
+@pytest.mark.parametrize("kernel", ["tensor-core", "cuda-core"])
+def test_fused_router(axm, workloads, oracle, cuda_device, name, tokens, kw, router_bf16, kernel):
+    """Both forms of the fused router: the streaming tcgen05 kernel (taken whenever the caller
+    lends scratch and terms * E <= 256) and the CUDA-core kernel behind axm_moe_router."""
+    if kernel == "cuda-core" and name == "C3":
+        pytest.skip("the CUDA-core kernel is covered on the smaller shapes")
     cfg = workloads.scaled(workloads.CONFIGS[name], tokens=tokens, **kw)
     x, w = workloads.make_inputs(cfg, router_bf16=router_bf16)
     xd, wd = x.to(cuda_device), helpers.to_dev(w, cuda_device)
     desc = helpers.desc_for(axm, cfg, axm.ROUTER_BF16 if router_bf16 else axm.ROUTER_FP32)
-    logits, idx, gate, bc = helpers.run_router(axm, desc, xd, wd["router_w"], wd.get("router_bias"))
+    logits, idx, gate, bc = helpers.run_router(axm, desc, xd, wd["router_w"], wd.get("router_bias"),
+                                               tensor_core=(kernel == "tensor-core"))
     torch.cuda.synchronize()
     z = oracle.router_logits(x, w["router_w"], w.get("router_bias"))
     zl = logits.cpu().numpy()
     # summation order differs by design (tree vs sequential): |dz| <= 1e-4 * max(1, |z|)
     assert (np.abs(zl - z) <= 1e-4 * np.maximum(1.0, np.abs(z))).all()
     check_routing(oracle, zl, idx, gate, bc, cfg.top_k)
+    # the per-block counts are what the permute kernel places rows by: block b covers tokens
+    # [b * T / 296, (b + 1) * T / 296)
+    gi = idx.cpu().numpy()
+    T = cfg.tokens
+    bounds = [(b * T) // axm.ROUTE_BLOCKS for b in range(axm.ROUTE_BLOCKS + 1)]
+    bcn = bc.cpu().numpy()
+    for b in (0, 1, 147, 294, 295):
+        want = np.bincount(gi[bounds[b]:bounds[b + 1]].ravel(), minlength=cfg.num_experts)
+        assert (bcn[b] == want).all(), f"block {b}"
+    # same tokens in a different batch: identical logits bits (the reduction order over
+    # d_model does not depend on the batch), hence identical routing
+    if T >= 300:
+        half = workloads.scaled(cfg, tokens=T // 3)
+        d2 = helpers.desc_for(axm, half, axm.ROUTER_BF16 if router_bf16 else axm.ROUTER_FP32)
+        l2, i2, g2, _ = helpers.run_router(axm, d2, xd[T // 3:2 * (T // 3)].contiguous(), wd["router_w"],
+                                           wd.get("router_bias"), tensor_core=(kernel == "tensor-core"))
+        assert torch.equal(l2.view(torch.int32), logits[T // 3:2 * (T // 3)].view(torch.int32))
+        assert torch.equal(i2, idx[T // 3:2 * (T // 3)])
 
 
 def test_route_from_logits_ties_and_extremes(axm, workloads, oracle, cuda_device):
