@@ -255,6 +255,10 @@ def main():
                     help="override the workload's token count (e.g. 16 for a decode-sized batch)")
     ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
+    ap.add_argument("--ep-host-chunks", type=int, default=2,
+                    help="N > 1: parts the host-buffer call cuts each rank's tokens into")
+    ap.add_argument("--ep-stages", action="store_true",
+                    help="p2p transport: the stage-by-stage sequence from Python instead of axm_moe_ep_forward")
     ap.add_argument("--ep-return", default="copy", choices=["fused", "copy"],
                     help="p2p transport: expert rows returned from the down GEMM's epilogue, or "
                          "by a separate copy kernel")
@@ -316,13 +320,17 @@ def main():
         del w
         if args.ep_transport == "p2p":
             layer = ep.ExpertParallelMoeP2P(wloc, tl, cfg.num_experts, k,
-                                            fused_return=(args.ep_return == "fused"))
+                                            fused_return=(args.ep_return == "fused"),
+                                            c_layer=not args.ep_stages)
         else:
             layer = ep.ExpertParallelMoe(wloc, tl, cfg.num_experts, k)
         out = torch.empty_like(x_local)
         step = lambda: layer.forward(x_local, out)
-        # router, permute, two GEMMs, combine (+ dispatch, segments, return, wait with p2p)
-        launches_per_step = (9 if args.ep_transport == "p2p" else 5) + \
+        # p2p behind axm_moe_ep_forward: router (+ its preparation kernel), permute fused with the
+        # dispatch, segment tables, gate/up GEMM, down GEMM in two halves, two return copies, wait,
+        # combine.  nccl: router, permute, two GEMMs, combine plus library collectives.
+        c_layer = getattr(layer, "c_layer", False)
+        launches_per_step = (10 if c_layer else (9 if args.ep_transport == "p2p" else 5)) + \
             (1 if axm.router_scratch_bytes(layer.desc_route) else 0)
     del x
     torch.cuda.empty_cache()
@@ -417,6 +425,9 @@ def main():
             torch.cuda.current_stream().synchronize()
     elif world == 1:
         e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out)
+    elif getattr(layer, "c_layer", False):
+        # host buffers through axm_moe_ep_forward_host: two pipelined parts per rank
+        e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out, chunks=args.ep_host_chunks)
     else:
         def e2e_step():
             d_x.copy_(h_x, non_blocking=True)
@@ -492,11 +503,16 @@ def main():
         acc = {}
         reps = 10
         for _ in range(reps):
-            evs = []
-            layer.forward(x_local, out, events=evs)
-            torch.cuda.synchronize()
-            for (_, a), (n, b) in zip(evs[:-1], evs[1:]):
-                acc[n] = acc.get(n, 0.0) + a.elapsed_time(b) / reps
+            if getattr(layer, "c_layer", False):
+                _, ms = layer.forward_profiled(x_local, out)
+                for n, v in ms.items():
+                    acc[n] = acc.get(n, 0.0) + v / reps
+            else:
+                evs = []
+                layer.forward(x_local, out, events=evs)
+                torch.cuda.synchronize()
+                for (_, a), (n, b) in zip(evs[:-1], evs[1:]):
+                    acc[n] = acc.get(n, 0.0) + a.elapsed_time(b) / reps
         ep_stages = {n: {"ms": v} for n, v in acc.items()}
         ep_stages["rows_received_rank0"] = layer.last_rows_received
 

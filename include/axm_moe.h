@@ -429,6 +429,8 @@ typedef struct AxmEpLayout {
   int32_t num_shared;       /* shared experts, run on the local tokens */
   int32_t tokens_local;
   int64_t off_flags, off_counts, off_recv, off_oback; /* byte offsets inside a region */
+  void* local_region;       /* this rank's own region (= peers[rank]), readable by the host code of
+                             * axm_moe_ep_forward; the stage entry points below do not use it */
 } AxmEpLayout;
 
 /* Fills the offsets / sizes of `layout` and returns the bytes one region needs:
@@ -475,6 +477,66 @@ AXM_API int axm_ep_signal_return(const AxmEpLayout* layout, uint32_t step, void*
  * on the return buffer). */
 AXM_API int axm_ep_wait_return(const AxmEpLayout* layout, uint32_t step, int32_t* status,
                                void* stream);
+
+/* ---- the expert-parallel layer as one call ------------------------------------------
+ * axm_moe_ep_forward runs, for this rank's tokens (desc->tokens = T_local; desc->num_experts
+ * = E over all ranks), router -> permute fused with the dispatch (rows are stored straight
+ * into the owners' receive buffers) -> segment tables -> gate/up GEMM -> down GEMM in two
+ * halves, the rows of the first half returning to their source ranks while the second half
+ * is computed -> wait for the returned rows -> combine.  Everything is enqueued on `stream`
+ * (plus an internal side stream for the overlapped return, joined before the call's last
+ * kernels); no host synchronisation.  `layout` as for the stage calls, with local_region set;
+ * layout->slots and cap are what the regions were SIZED for, the call may carry fewer tokens.
+ * `step` starts at 1 and grows by one per call on every rank alike.
+ * The workspace is private to the rank; its first *zero_bytes bytes must be zero before the
+ * first call (counters) and are left zero by every call.  The status word (first int32 of
+ * the workspace, axm_moe_ep_status_word) is sticky: a bounded wait that gave up stores a
+ * non-zero code and nothing clears it but the caller.
+ * No reference counterpart: the engine is single-GPU. */
+typedef struct AxmEpTensors {
+  const void* x;            /* [T_local][D] bf16 */
+  const void* router_w;     /* [D][E], replicated */
+  const float* router_bias; /* [E] or NULL */
+  const void* w_gate;       /* [E / world][D][F]: this rank's experts */
+  const void* w_up;
+  const void* w_down;       /* [E / world][F][D] */
+  const void* shared_gate;  /* [S][D][F] replicated, or NULL */
+  const void* shared_up;
+  const void* shared_down;
+  float* logits;            /* [T_local][E], optional */
+  int32_t* topk_idx;        /* [T_local][k], optional */
+  float* topk_gate;         /* [T_local][k], optional */
+  int32_t* histogram;       /* [E]: this rank's tokens per expert, optional */
+  void* y;                  /* [T_local][D] bf16, optional */
+  void* out;                /* [T_local][D] bf16 */
+} AxmEpTensors;
+
+AXM_API int axm_moe_ep_workspace_bytes(const AxmEpLayout* layout, const AxmMoeDesc* desc, size_t* bytes,
+                                       size_t* zero_bytes);
+AXM_API int axm_moe_ep_forward(const AxmEpLayout* layout, const AxmMoeDesc* desc,
+                               const AxmEpTensors* tensors, void* workspace, size_t workspace_bytes,
+                               uint32_t step, void* stream);
+/* Device addresses of the sticky status word and of the number of rows this rank received
+ * in the last call (either pointer may be NULL). */
+AXM_API int axm_moe_ep_status_word(const AxmEpLayout* layout, const AxmMoeDesc* desc, void* workspace,
+                                   int32_t** status, int32_t** rows_received);
+/* axm_moe_ep_forward with CUDA events between its phases; synchronises the stream and returns
+ * seven device times in milliseconds: router, permute + dispatch, wait for rows + segment
+ * tables, gate/up GEMM, down GEMM (both halves; the first half's return runs underneath),
+ * return of the second half, wait for returned rows + combine.  A measuring aid. */
+AXM_API int axm_moe_ep_forward_profiled(const AxmEpLayout* layout, const AxmMoeDesc* desc,
+                                        const AxmEpTensors* tensors, void* workspace,
+                                        size_t workspace_bytes, uint32_t step, void* stream,
+                                        float* stage_ms);
+/* The same layer for activations in (pinned) host memory, mirroring the engine's host wrapper
+ * (core/src/ai.cpp:593-623): the rank's tokens are cut into `chunks` equal parts (1..8, the
+ * same on every rank; each part is one exchange step), part c + 1 is copied in and part c - 1
+ * copied out while part c is computed.  d_x / d_out: device staging buffers of T_local * D
+ * bf16.  *step is the first step number to use and is advanced by `chunks`.  Synchronises. */
+AXM_API int axm_moe_ep_forward_host(const AxmEpLayout* layout, const AxmMoeDesc* desc,
+                                    const AxmEpTensors* tensors, const void* h_x, void* h_out, void* d_x,
+                                    void* d_out, void* workspace, size_t workspace_bytes, int32_t chunks,
+                                    uint32_t* step, void* stream);
 
 /* Number of token blocks the router splits T into (rows of block_counts). */
 #define AXM_ROUTE_BLOCKS 296

@@ -55,7 +55,14 @@ class EpLayout(ctypes.Structure):
     _fields_ = ([("peers", ctypes.c_void_p)] +
                 [(n, ctypes.c_int32) for n in ("rank", "world", "num_experts", "d_model", "slots",
                                                "cap", "num_shared", "tokens_local")] +
-                [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")])
+                [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")] +
+                [("local_region", ctypes.c_void_p)])
+
+
+class EpTensors(ctypes.Structure):
+    _fields_ = [(n, ctypes.c_void_p) for n in (
+        "x", "router_w", "router_bias", "w_gate", "w_up", "w_down", "shared_gate", "shared_up",
+        "shared_down", "logits", "topk_idx", "topk_gate", "histogram", "y", "out")]
 
 
 class MoeTrain(ctypes.Structure):
@@ -127,6 +134,12 @@ def load():
                                               vp, vp, i32, vp, vp, vp]
     lib.axm_ep_return.argtypes = [lp, u32, vp, vp, vp, vp, vp]
     lib.axm_ep_wait_return.argtypes = [lp, u32, vp, vp]
+    ept = ctypes.POINTER(EpTensors)
+    lib.axm_moe_ep_workspace_bytes.argtypes = [lp, dp, ctypes.POINTER(sz), ctypes.POINTER(sz)]
+    lib.axm_moe_ep_forward.argtypes = [lp, dp, ept, vp, sz, u32, vp]
+    lib.axm_moe_ep_status_word.argtypes = [lp, dp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
+    lib.axm_moe_ep_forward_profiled.argtypes = [lp, dp, ept, vp, sz, u32, vp, ctypes.POINTER(ctypes.c_float)]
+    lib.axm_moe_ep_forward_host.argtypes = [lp, dp, ept, vp, vp, vp, vp, vp, sz, i32, ctypes.POINTER(u32), vp]
     lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     cp = ctypes.POINTER(MoeCheckpoint)
     lib.axm_moe_checkpoint_save.argtypes = [ctypes.c_char_p, dp, cp]

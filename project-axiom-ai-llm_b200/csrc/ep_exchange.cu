@@ -157,6 +157,163 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
   }
 }
 
+// Permute and dispatch in one kernel: the placement of axm_moe_permute (histogram, exclusive
+// scan, stable ranks: rows of an expert ordered by token, then slot) with the rows written
+// straight into the owners' receive buffers instead of a local x_perm that a second kernel
+// would read back.  One CTA per router block, like the permute kernel.  Block 0 posts this
+// rank's counts to all peers as soon as they are known; every block then waits for the
+// peers' counts (bounded), derives where this rank's rows of each expert start in the
+// owner's buffer, places its tokens and copies each row once per selected expert with
+// 16-byte stores (local for this rank's own experts, over NVLink otherwise).  slot_dst and
+// row_src describe the LOCAL expert-contiguous order (row r of this rank's virtual x_perm),
+// which is also the row of the return buffer where the expert output of that slot lands.
+constexpr int kFusedTokSub = 128;
+constexpr int kFusedMaxE = 256;
+__global__ void __launch_bounds__(kEpThreads)
+ep_permute_dispatch_kernel(EpArgs a, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx,
+                           const int32_t* __restrict__ block_counts, int32_t* __restrict__ histogram,
+                           int32_t* __restrict__ offsets, int32_t* __restrict__ row_src,
+                           int32_t* __restrict__ slot_dst, int32_t* __restrict__ done_counter, int T, int k,
+                           int hist_accumulate) {
+  __shared__ int total_s[kFusedMaxE];
+  __shared__ int run_s[kFusedMaxE];      // next free LOCAL row per expert for this block
+  __shared__ int scan_s[kFusedMaxE + 1];  // local offsets
+  __shared__ int base_s[kFusedMaxE];      // row in the owner's receive buffer of my first row of expert e
+  __shared__ int dst_s[kFusedTokSub * 8];  // destination row in the owner's buffer
+  __shared__ unsigned char own_s[kFusedTokSub * 8];  // owner rank
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int b = blockIdx.x, E = a.E;
+
+  for (int e = tid; e < E; e += kEpThreads) {
+    total_s[e] = 0;
+    run_s[e] = 0;
+  }
+  __syncthreads();
+  const int n_cells = AXM_ROUTE_BLOCKS * E;
+  for (int i = tid; i < n_cells; i += kEpThreads) {
+    const int bb = i / E, e = i - bb * E;
+    const int c = block_counts[i];
+    if (c != 0) {
+      atomicAdd(&total_s[e], c);
+      if (bb < b) atomicAdd(&run_s[e], c);
+    }
+  }
+  __syncthreads();
+  if (warp == 0) {
+    int carry = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + lane;
+      const int v = e < E ? total_s[e] : 0;
+      int incl = v;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += n;
+      }
+      if (e < E) scan_s[e] = carry + incl - v;
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (lane == 0) scan_s[E] = carry;
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += kEpThreads) run_s[e] += scan_s[e];
+  if (b == 0) {
+    // publish: local outputs, and my counts into every peer's table (row = my rank)
+    for (int e = tid; e <= E; e += kEpThreads) {
+      if (offsets != nullptr) offsets[e] = scan_s[e];
+      if (e < E && histogram != nullptr) histogram[e] = (hist_accumulate ? histogram[e] : 0) + total_s[e];
+    }
+    for (int i = tid; i < E * a.G; i += kEpThreads) {
+      const int g = i / E, e = i - g * E;
+      int32_t* table = reinterpret_cast<int32_t*>(a.peers[g] + a.off_counts);
+      table[a.rank * E + e] = total_s[e];
+    }
+    __threadfence_system();
+    __syncthreads();
+    if (tid < a.G) store_release_sys(flag_ptr(a, tid, 0, a.rank), a.step);
+  }
+  wait_all_sources(a, 0, 11);
+  {
+    const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
+    for (int e = tid; e < E; e += kEpThreads) {
+      const int e_first = (e / a.El) * a.El;
+      int base = 0;
+      for (int s = 0; s < a.G; ++s) {
+        const int32_t* row = table + s * E;
+        for (int q = e_first; q < e; ++q) base += __ldcg(row + q);
+        if (s < a.rank) base += __ldcg(row + e);
+      }
+      base_s[e] = base;
+    }
+  }
+  __syncthreads();
+
+  const int t_begin = (int)(((long long)b * T) / AXM_ROUTE_BLOCKS);
+  const int t_end = (int)(((long long)(b + 1) * T) / AXM_ROUTE_BLOCKS);
+  const int chunks = a.D / 8;
+  for (int ts = t_begin; ts < t_end; ts += kFusedTokSub) {
+    const int nt = min(kFusedTokSub, t_end - ts);
+    const int n_ent = nt * k;
+    if (warp == 0) {
+      for (int c0 = 0; c0 < n_ent; c0 += 32) {
+        const int i = c0 + lane;
+        const bool live = i < n_ent;
+        const int e = live ? topk_idx[(size_t)ts * k + i] : -1;
+        const unsigned peers = __match_any_sync(0xffffffffu, e);
+        const int rank_in = __popc(peers & ((1u << lane) - 1u));
+        int local_row = -1;
+        if (live) {
+          local_row = run_s[e] + rank_in;
+          dst_s[i] = base_s[e] + (local_row - scan_s[e]);
+          own_s[i] = (unsigned char)(e / a.El);
+        }
+        __syncwarp();
+        if (live && rank_in == __popc(peers) - 1) run_s[e] += rank_in + 1;
+        __syncwarp();
+        if (live) {
+          const size_t slot = (size_t)ts * k + i;
+          if (slot_dst != nullptr) slot_dst[slot] = local_row;
+          if (row_src != nullptr) row_src[local_row] = (int32_t)slot;
+        }
+      }
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nt; tt += kEpThreads / 32) {
+      const uint4* src = reinterpret_cast<const uint4*>(x + (size_t)(ts + tt) * a.D);
+      for (int c0 = 0; c0 < chunks; c0 += 128) {
+        uint4 v[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const int c = c0 + j * 32 + lane;
+          if (c < chunks) v[j] = __ldg(src + c);
+        }
+        for (int i = 0; i < k; ++i) {
+          const int dst_row = dst_s[tt * k + i];
+          if (dst_row < 0 || dst_row >= a.cap) continue;  // never write outside the receive buffer
+          uint4* dstp = reinterpret_cast<uint4*>(a.peers[own_s[tt * k + i]] + a.off_recv) + (size_t)dst_row * chunks;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int c = c0 + j * 32 + lane;
+            if (c < chunks) dstp[c] = v[j];
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+  // when every block is done, tell every owner that my rows have landed
+  __threadfence_system();
+  __syncthreads();
+  if (tid == 0) {
+    const int prev = atomicAdd(done_counter, 1);
+    if (prev == (int)gridDim.x - 1) {
+      *done_counter = 0;
+      __threadfence_system();
+      for (int o = 0; o < a.G; ++o) store_release_sys(flag_ptr(a, o, 1, a.rank), a.step);
+    }
+  }
+}
+
 // One block.  The receive buffer is expert-major: all sources' rows of local expert 0
 // (source 0 first), then of expert 1, ...  Two tables over that buffer, both indexed
 // j * G + s (local expert j, source rank s), which is also ascending row order:
@@ -171,7 +328,8 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
 __global__ void __launch_bounds__(kEpThreads)
 ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
                    AxmSegment* __restrict__ ret_segments, AxmRemoteOut* __restrict__ remote_out,
-                   int32_t* __restrict__ rows_received) {
+                   int32_t* __restrict__ rows_received, AxmSegment* __restrict__ seg_halves,
+                   int32_t* __restrict__ split_rows) {
   __shared__ int rows_s[kEpMaxRanks * 64];
   __shared__ int start_s[kEpMaxRanks * 64];
   wait_all_sources(a, 1, 12);
@@ -196,6 +354,7 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
       sg.rows = a.T_local;
       sg.expert = (a.El + s) | AXM_SEG_ALT_A;
       segments[n + s] = sg;
+      if (seg_halves != nullptr) seg_halves[2 * a.El + s] = sg;  // projected with the second halves
       if (remote_out != nullptr) {
         AxmRemoteOut ro;
         ro.base = nullptr;  // shared experts stay in the local output buffer
@@ -233,6 +392,22 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
       sg.a_row0 = start_s[first];
       sg.out_row0 = start_s[first];
       sg.rows = (s == 0) ? end - start_s[first] : 0;
+      // The same rows as two segments per expert, cut at a multiple of 256 rows (a pair of
+      // m-tiles) near the middle: the down projection of the first halves can be returned
+      // while the second halves are still being computed.  seg_halves: [2][El].
+      if (seg_halves != nullptr && s == 0) {
+        const int rows = end - start_s[first];
+        const int pairs = (rows + 255) / 256;
+        int cut = ((pairs + 1) / 2) * 256;
+        if (cut > rows) cut = rows;
+        AxmSegment ha = sg, hb = sg;
+        ha.rows = cut;
+        hb.a_row0 = hb.out_row0 = start_s[first] + cut;
+        hb.rows = rows - cut;
+        seg_halves[j] = ha;
+        seg_halves[a.El + j] = hb;
+        if (split_rows != nullptr) split_rows[j] = start_s[first] + cut;
+      }
     }
     segments[i] = sg;
   }
@@ -240,7 +415,10 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
 
 __global__ void __launch_bounds__(kEpThreads)
 ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
-                 const float* __restrict__ o, int32_t* __restrict__ done_counter) {
+                 const float* __restrict__ o, int32_t* __restrict__ done_counter,
+                 const int32_t* __restrict__ split_rows, int half, int signal) {
+  // half: -1 = all rows; 0 = rows of each local expert before split_rows[j]; 1 = the rest.
+  // signal: flag the sources when done (the last of the launches that cover a step).
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int warps_total = gridDim.x * (kEpThreads / 32);
   const int chunks = a.D / 4;  // 16-byte pieces of an fp32 row
@@ -253,6 +431,10 @@ ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
       if (seg < n) sg = ret_segments[seg];
     }
     if (seg >= n) break;
+    if (half >= 0) {
+      const int cut = split_rows[seg / a.G];  // entries are ordered (local expert, source)
+      if ((half == 0) != (r < cut)) continue;
+    }
     const int dst_row = sg.a_row0 + (r - sg.out_row0);
     if (dst_row >= a.slots) continue;
     const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)r * a.D);
@@ -269,7 +451,7 @@ ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
   }
   __threadfence_system();
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (signal && threadIdx.x == 0) {
     int prev = atomicAdd(done_counter, 1);
     if (prev == (int)gridDim.x - 1) {
       *done_counter = 0;
@@ -321,6 +503,39 @@ static EpArgs make_args(const AxmEpLayout* l, uint32_t step, int32_t* status) {
   return a;
 }
 
+int launch_ep_permute_dispatch(const AxmEpLayout* l, uint32_t step, const void* x, const int32_t* topk_idx,
+                               const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                               int32_t* row_src, int32_t* slot_dst, int32_t* done_counter, int T, int k,
+                               int hist_accumulate, int32_t* status, cudaStream_t st) {
+  if (int rc = validate_ep(l)) return rc;
+  if (l->num_experts > kFusedMaxE) return fail(AXM_ERR_ARGUMENT, "num_experts %d > %d", l->num_experts, kFusedMaxE);
+  EpArgs a = make_args(l, step, status);
+  ep_permute_dispatch_kernel<<<AXM_ROUTE_BLOCKS, kEpThreads, 0, st>>>(
+      a, static_cast<const __nv_bfloat16*>(x), topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
+      done_counter, T, k, hist_accumulate);
+  return check_launch("ep_permute_dispatch_kernel");
+}
+
+int launch_ep_segments_split(const AxmEpLayout* l, uint32_t step, AxmSegment* segments, AxmSegment* ret_segments,
+                             int32_t* rows_received, AxmSegment* seg_halves, int32_t* split_rows,
+                             int32_t* status, cudaStream_t st) {
+  if (int rc = validate_ep(l)) return rc;
+  EpArgs a = make_args(l, step, status);
+  ep_segments_kernel<<<1, kEpThreads, 0, st>>>(a, segments, ret_segments, nullptr, rows_received, seg_halves,
+                                              split_rows);
+  return check_launch("ep_segments_kernel");
+}
+
+int launch_ep_return_half(const AxmEpLayout* l, uint32_t step, const AxmSegment* ret_segments, const void* o,
+                          int32_t* done_counter, const int32_t* split_rows, int half, int signal,
+                          int32_t* status, cudaStream_t st) {
+  if (int rc = validate_ep(l)) return rc;
+  EpArgs a = make_args(l, step, status);
+  ep_return_kernel<<<2 * sm_count(), kEpThreads, 0, st>>>(a, ret_segments, static_cast<const float*>(o),
+                                                         done_counter, split_rows, half, signal);
+  return check_launch("ep_return_kernel");
+}
+
 }  // namespace axm
 
 using namespace axm;
@@ -369,7 +584,8 @@ extern "C" int axm_ep_segments(const AxmEpLayout* layout, uint32_t step, AxmSegm
   if (int rc = require_device()) return rc;
   EpArgs a = make_args(layout, step, status);
   ep_segments_kernel<<<1, kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(a, segments, ret_segments,
-                                                                             remote_out, rows_received);
+                                                                             remote_out, rows_received, nullptr,
+                                                                             nullptr);
   return check_launch("ep_segments_kernel");
 }
 
@@ -381,7 +597,7 @@ extern "C" int axm_ep_return(const AxmEpLayout* layout, uint32_t step,
   if (int rc = require_device()) return rc;
   EpArgs a = make_args(layout, step, status);
   ep_return_kernel<<<2 * sm_count(), kEpThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      a, ret_segments, static_cast<const float*>(o), scratch + 1);
+      a, ret_segments, static_cast<const float*>(o), scratch + 1, nullptr, -1, 1);
   return check_launch("ep_return_kernel");
 }
 

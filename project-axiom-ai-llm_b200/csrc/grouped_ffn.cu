@@ -381,7 +381,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
                           const void* w_gate, const void* w_up, const void* w_down,
                           const void* shared_gate, const void* shared_up, const void* shared_down,
                           void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                          cudaEvent_t between, void* save_g, void* save_u);
+                          cudaEvent_t between, void* save_g, void* save_u, int phases);
 
 bool use_2sm_kernels() {
   static int v = -1;
@@ -424,16 +424,39 @@ static int make_map_3d(CUtensorMap* m, const void* base, uint64_t experts, uint6
   return AXM_OK;
 }
 
+// phases: bit 0 = gate/up projection with the SiLU*mul epilogue (writes h), bit 1 = down
+// projection (reads h, writes o).  Callers that overlap other work with the down projection
+// launch the two separately, with different segment tables if they like.
+int launch_expert_ffn_phases(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
+                             int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
+                             const void* w_gate, const void* w_up, const void* w_down,
+                             const void* shared_gate, const void* shared_up, const void* shared_down,
+                             void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
+                             cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u,
+                             int phases);
+
 int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
                       int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
                       const void* w_gate, const void* w_up, const void* w_down,
                       const void* shared_gate, const void* shared_up, const void* shared_down,
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                       cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u) {
+  return launch_expert_ffn_phases(d, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate, w_up, w_down,
+                                  shared_gate, shared_up, shared_down, h, o, rows_total, status, st, between,
+                                  remote, save_g, save_u, 3);
+}
+
+int launch_expert_ffn_phases(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
+                             int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
+                             const void* w_gate, const void* w_up, const void* w_down,
+                             const void* shared_gate, const void* shared_up, const void* shared_down,
+                             void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
+                             cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u,
+                             int phases) {
   if (remote == nullptr && use_2sm_kernels())
     return launch_expert_ffn_2sm(d, x_perm, a_rows, x_alt, alt_rows, segments, num_segments, w_gate, w_up,
                                  w_down, shared_gate, shared_up, shared_down, h, o, rows_total, status, st,
-                                 between, save_g, save_u);
+                                 between, save_g, save_u, phases);
   if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
   CUtensorMap a1, a1_alt, g, u, g_sh, u_sh, a2, dn, dn_sh;
@@ -486,9 +509,12 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
   ga.h_ld = (int)h_ld;
   ga.lo_off = exact ? F : 0;
   ga.two_term = 0;
-  grouped_gemm_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
-  if ((rc = check_launch("grouped_gemm_kernel<swiglu>"))) return rc;
+  if (phases & 1) {
+    grouped_gemm_kernel<true><<<grid, kGemmThreads, kGemmSmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
+    if ((rc = check_launch("grouped_gemm_kernel<swiglu>"))) return rc;
+  }
   if (between != nullptr) cudaEventRecord(between, st);
+  if (!(phases & 2)) return AXM_OK;
   ga.n_total = D;
   ga.k_total = F;
   ga.out = o;

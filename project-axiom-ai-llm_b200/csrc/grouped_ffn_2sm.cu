@@ -545,7 +545,7 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
                           const void* w_gate, const void* w_up, const void* w_down,
                           const void* shared_gate, const void* shared_up, const void* shared_down,
                           void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
-                          cudaEvent_t between, void* save_g, void* save_u) {
+                          cudaEvent_t between, void* save_g, void* save_u, int phases) {
   const int grid = grid_2sm();
   if (grid < 0) return grid;  // status, message already set
   if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
@@ -589,9 +589,12 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.out = h;
   ga.save_g = static_cast<__nv_bfloat16*>(save_g);
   ga.save_u = static_cast<__nv_bfloat16*>(save_u);
-  grouped_gemm_2sm_kernel<kModeSwiGLU><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
-  if ((rc = check_launch("grouped_gemm_2sm_kernel<swiglu>"))) return rc;
+  if (phases & 1) {
+    grouped_gemm_2sm_kernel<kModeSwiGLU><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
+    if ((rc = check_launch("grouped_gemm_2sm_kernel<swiglu>"))) return rc;
+  }
   if (between != nullptr) cudaEventRecord(between, st);
+  if (!(phases & 2)) return AXM_OK;
   ga.n_total = D;
   ga.k_total = F;
   ga.out = o;

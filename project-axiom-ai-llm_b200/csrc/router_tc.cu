@@ -46,12 +46,13 @@ constexpr int kRtThreads = 192;     // warp 0: TMA producer, warp 1: MMA issuer,
 constexpr int kRtMaxStages = 8;
 constexpr int kRtTileRows = 128;
 constexpr int kRtABytes = kRtTileRows * BK * 2;   // 16 KiB
-constexpr int kRtStageBudget = 96 * 1024;         // two CTAs per SM
+constexpr int kRtStageBudget = 100 * 1024;        // two CTAs per SM
 
 struct __align__(8) RouterTcShared {
   uint64_t full[kRtMaxStages];
   uint64_t empty[kRtMaxStages];
   uint64_t tmem_full;
+  uint64_t exch_full;   // 128 arrivals: every row of this CTA's slice of the tile, from every CTA of the cluster
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -69,8 +70,11 @@ struct RouterTcArgs {
   int n_cols;      // terms * epad: N of the MMA
   int stages;
   int stage_bytes; // A tile + B tile, a multiple of 1024
-  int tmem_cols;   // power of two >= max(32, n_cols)
-  int tile_bytes;  // bytes of the region shared by the pipeline stages and the exchange buffer
+  int nacc;        // accumulators the k-steps rotate through (1, 2 or 4)
+  int tmem_cols;   // power of two >= max(32, nacc * n_cols)
+  int exch_bytes;  // bytes of the exchange buffer [CS][128 / CS][epad + 4] floats, 16-byte multiple
+  int tile_bytes;  // bytes of the region shared by the pipeline stages and, later, exchange buffer + logits
+  int skip_b;      // measuring aid: do not load the weight tiles (results are then meaningless)
 };
 
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -103,6 +107,32 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
         "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
       : "r"(taddr)
       : "memory");
+}
+__device__ __forceinline__ void rt_mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded wait on a barrier whose arrivals come from other CTAs of the cluster.
+__device__ __forceinline__ bool rt_mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t addr = smem_u32(bar);
+  long long t0 = clock64();
+  while (true) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}"
+        : "=r"(ok)
+        : "r"(addr), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
 }
 __device__ __forceinline__ void epilogue_bar_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 
@@ -141,6 +171,18 @@ router_prep_kernel(const WT* __restrict__ w, __nv_bfloat16* __restrict__ bt, int
   }
 }
 
+#ifdef AXM_RT_TRACE
+__device__ long long* g_rt_trace = nullptr;
+__device__ __forceinline__ unsigned long long rt_gtime() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define RT_MARK(i) do { if (g_rt_trace != nullptr && threadIdx.x == 64) g_rt_trace[(size_t)blockIdx.x * 16 + (i)] = (long long)rt_gtime(); } while (0)
+#else
+#define RT_MARK(i) do { } while (0)
+#endif
+
 // ---- the router ---------------------------------------------------------------------------
 template <int CS>
 __global__ void __launch_bounds__(kRtThreads)
@@ -150,20 +192,23 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  // After the reduction loop the stage memory is reused: exchange buffer [CS][RP][epad + 4]
+  // floats, then this CTA's logits [RP][E + 1].
+  float* exch = reinterpret_cast<float*>(tiles);
+  float* z_s = reinterpret_cast<float*>(tiles + a.exch_bytes);
   RouterTcShared* sh = reinterpret_cast<RouterTcShared*>(tiles + a.tile_bytes);
-  float* z_s = reinterpret_cast<float*>(sh + 1);  // [RP][E + 1]
-  float* exch = reinterpret_cast<float*>(tiles);  // [CS][RP][n_cols + 4], reuses the stages after the loop
 
+  RT_MARK(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = CS > 1 ? rt_cluster_rank() : 0u;
   const int tile = blockIdx.x / CS;
   const int row0 = tile * kRtTileRows;
   const int kb_total = (a.D + BK - 1) / BK;
-  const int kb_per = (kb_total + CS - 1) / CS;
-  const int kb_begin = (int)rank * kb_per;
-  const int kb_count = max(0, min(kb_total, kb_begin + kb_per) - kb_begin);
+  // Which 64-wide blocks of d_model this CTA reduces over: rank, rank + CS, ...  The CTAs of a
+  // cluster run in step, so together they ask HBM for CS adjacent 128-byte pieces of a row.
+  const int kb_count = max(0, (kb_total - (int)rank + CS - 1) / CS);
   const int EP = a.E + 1;
-  const int xld = a.n_cols + 4;  // row pitch of the exchange buffer in floats (conflict-free 16-byte stores)
+  const int xld = a.epad + 4;  // row pitch of the exchange buffer in floats (conflict-free 16-byte stores)
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < a.stages; ++i) {
@@ -171,22 +216,29 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       mbar_init(&sh->empty[i], 1);
     }
     mbar_init(&sh->tmem_full, 1);
+    mbar_init(&sh->exch_full, kRtTileRows);  // one arrival per row of the tile slice this CTA owns, from every CTA
     sh->abort_flag = 0;
     fence_barrier_init();
     tma_prefetch_desc(&tm_x);
     tma_prefetch_desc(&tm_b);
   }
   __syncthreads();
-  if (warp == 1) {
-    __syncwarp();
-    tmem_alloc(&sh->tmem_base, (uint32_t)a.tmem_cols);
-    tmem_relinquish();
+  // The producer warp starts requesting tiles at once; tensor memory is allocated meanwhile
+  // and only the MMA and epilogue warps (160 threads, named barrier 2) wait for its address.
+  uint32_t tmem_base = 0;
+  if (warp >= 1) {
+    if (warp == 1) {
+      tmem_alloc(&sh->tmem_base, (uint32_t)a.tmem_cols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    asm volatile("bar.sync 2, 160;" ::: "memory");
+    tc_fence_after();
+    tmem_base = sh->tmem_base;
   }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = sh->tmem_base;
   volatile int* abort_flag = &sh->abort_flag;
+  const uint32_t stage_tx = (uint32_t)(kRtABytes + (a.skip_b ? 0 : a.n_cols * BK * 2));
+  RT_MARK(1);
 
   if (warp == 0) {
     // ---- TMA producer -----------------------------------------------------------------
@@ -195,20 +247,22 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       // requested before the wait, the weight tiles of those stages after it
       const int early = min(a.stages, kb_count);
       for (int i = 0; i < early; ++i) {
-        mbar_expect_tx(&sh->full[i], (uint32_t)(kRtABytes + a.n_cols * BK * 2));
-        tma_load_2d(tiles + (size_t)i * a.stage_bytes, &tm_x, &sh->full[i], (kb_begin + i) * BK, row0);
+        mbar_expect_tx(&sh->full[i], stage_tx);
+        tma_load_2d(tiles + (size_t)i * a.stage_bytes, &tm_x, &sh->full[i], ((int)rank + i * CS) * BK, row0);
       }
       griddep_wait();
-      for (int i = 0; i < early; ++i)
-        tma_load_2d(tiles + (size_t)i * a.stage_bytes + kRtABytes, &tm_b, &sh->full[i], (kb_begin + i) * BK, 0);
+      if (!a.skip_b)
+        for (int i = 0; i < early; ++i)
+          tma_load_2d(tiles + (size_t)i * a.stage_bytes + kRtABytes, &tm_b, &sh->full[i],
+                      ((int)rank + i * CS) * BK, 0);
       int stage = early == a.stages ? 0 : early;
       uint32_t phase = early == a.stages ? 1u : 0u;
       for (int i = early; i < kb_count; ++i) {
         if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) break;
         unsigned char* sa = tiles + (size_t)stage * a.stage_bytes;
-        mbar_expect_tx(&sh->full[stage], (uint32_t)(kRtABytes + a.n_cols * BK * 2));
-        tma_load_2d(sa, &tm_x, &sh->full[stage], (kb_begin + i) * BK, row0);
-        tma_load_2d(sa + kRtABytes, &tm_b, &sh->full[stage], (kb_begin + i) * BK, 0);
+        mbar_expect_tx(&sh->full[stage], stage_tx);
+        tma_load_2d(sa, &tm_x, &sh->full[stage], ((int)rank + i * CS) * BK, row0);
+        if (!a.skip_b) tma_load_2d(sa + kRtABytes, &tm_b, &sh->full[stage], ((int)rank + i * CS) * BK, 0);
         if (++stage == a.stages) {
           stage = 0;
           phase ^= 1u;
@@ -217,10 +271,14 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------
+    // Successive 16-wide k-steps go to `nacc` different accumulators in turn: an MMA that adds
+    // to the accumulator the previous one is still writing would wait for it, and with so few
+    // columns per instruction that latency, not the HBM stream, would set the pace.
     if (lane == 0) {
       const uint32_t idesc = rt_instr_desc(a.n_cols);
       int stage = 0;
       uint32_t phase = 0;
+      int ks = 0;
       bool ok = true;
       for (int i = 0; i < kb_count; ++i) {
         if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
@@ -232,8 +290,9 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         const uint64_t da = make_smem_desc(sa, 16, 1024);
         const uint64_t db = make_smem_desc(sa + kRtABytes, 16, 1024);
 #pragma unroll
-        for (int j = 0; j < BK / UMMA_K; ++j)
-          tc_mma_bf16(tmem_base, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (i > 0 || j > 0) ? 1u : 0u);
+        for (int j = 0; j < BK / UMMA_K; ++j, ++ks)
+          tc_mma_bf16(tmem_base + (uint32_t)((ks % a.nacc) * a.n_cols), da + (uint64_t)(j * 2),
+                      db + (uint64_t)(j * 2), idesc, ks >= a.nacc ? 1u : 0u);
         tc_commit(&sh->empty[stage]);
         if (++stage == a.stages) {
           stage = 0;
@@ -244,64 +303,82 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
   }
 
-  // ---- epilogue warps: wait for this CTA's accumulator ---------------------------------
-  const bool epi = warp >= 2;
-  const int quad = warp & 3;
-  bool acc_ok = true;
-  if (epi && kb_count > 0) {
-    acc_ok = __all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, 0u, abort_flag));
-    tc_fence_after();
-  }
-  // Every CTA of the cluster has finished reading its pipeline stages once all threads are
-  // here (the accumulator is complete, so every load it consumed has landed): the stage
-  // memory of all CTAs may now receive the exchanged partial sums.
-  __syncthreads();  // the warps' lanes walk together again before the aligned cluster barrier
-  if (CS > 1) rt_cluster_sync();
-
-  if (epi) {
-    const int r = quad * 32 + lane;  // accumulator row (TMEM lane) = token row0 + r
-    const int owner = r / RP, lr = r - owner * RP;
-    const uint32_t dst_local = smem_u32(exch + ((size_t)rank * RP + lr) * xld);
-    const uint32_t dst = CS > 1 ? rt_map_to_cta(dst_local, (uint32_t)owner) : dst_local;
-    const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-    for (int c0 = 0; c0 < a.n_cols; c0 += 16) {
-      uint32_t v[16];
-      if (kb_count > 0 && acc_ok) {
-        tmem_ld16(t_addr + (uint32_t)c0, v);
-        tmem_ld_wait();
-      } else {
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = 0u;  // a slice without k-blocks contributes zero
-      }
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        rt_st_cluster_v4(dst + (uint32_t)(c0 + 4 * q) * 4u, v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+  if (warp >= 2) {
+    // ---- epilogue: 128 threads, thread = accumulator row ----------------------------------
+    const int quad = warp & 3;
+    bool acc_ok = true;
+    if (kb_count > 0) {
+      acc_ok = __all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, 0u, abort_flag));
+      tc_fence_after();
     }
-    tc_fence_before();
-  }
-  __syncthreads();
-  if (CS > 1) rt_cluster_sync();
-
-  if (epi) {
+    RT_MARK(2);
+    // One cluster barrier per kernel: a thread arrives when its part of the reduction loop is
+    // over (for these warps: the accumulator is complete, so every tile this CTA requested has
+    // landed and been read).  Once it completes, the stage memory of every CTA of the cluster
+    // is free to receive the partial sums.
+    if (CS > 1) {
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
+    RT_MARK(3);
+    {
+      // this CTA's partial logits of row r: sum over its accumulators of (hi + mid) + lo,
+      // 16 experts at a time, stored into the row's owner
+      const int r = quad * 32 + lane;
+      const int owner = r / RP, lr = r - owner * RP;
+      const uint32_t dst_local = smem_u32(exch + ((size_t)rank * RP + lr) * xld);
+      const uint32_t dst = CS > 1 ? rt_map_to_cta(dst_local, (uint32_t)owner) : dst_local;
+      const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+      const int used = (kb_count > 0 && acc_ok) ? min(a.nacc, kb_count * (BK / UMMA_K)) : 0;
+      for (int c0 = 0; c0 < a.epad; c0 += 16) {
+        float part[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) part[j] = 0.0f;
+        for (int ac = 0; ac < used; ++ac) {
+          uint32_t hi[16], mid[16], lo[16];
+          const uint32_t col = t_addr + (uint32_t)(ac * a.n_cols + c0);
+          tmem_ld16(col, hi);
+          if (a.terms == 3) {
+            tmem_ld16(col + (uint32_t)a.epad, mid);
+            tmem_ld16(col + (uint32_t)(2 * a.epad), lo);
+          }
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            float v = __uint_as_float(hi[j]);
+            if (a.terms == 3) v = (v + __uint_as_float(mid[j])) + __uint_as_float(lo[j]);
+            part[j] += v;
+          }
+        }
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          rt_st_cluster_v4(dst + (uint32_t)(c0 + 4 * q) * 4u, __float_as_uint(part[4 * q]),
+                           __float_as_uint(part[4 * q + 1]), __float_as_uint(part[4 * q + 2]),
+                           __float_as_uint(part[4 * q + 3]));
+      }
+      tc_fence_before();
+      // tell the owner that this row's slice has landed (release at cluster scope orders the stores)
+      const uint32_t bar_local = smem_u32(&sh->exch_full);
+      rt_mbar_arrive_cluster(CS > 1 ? rt_map_to_cta(bar_local, (uint32_t)owner) : bar_local);
+    }
+    RT_MARK(4);
+    const bool got_all = __all_sync(0xffffffffu, rt_mbar_wait_cluster(&sh->exch_full, 0u, abort_flag));
+    RT_MARK(5);
     griddep_wait();  // the count table was zeroed by the preparation kernel
     const int et = (warp - 2) * 32 + lane;  // 0..127
     const int t_first = row0 + (int)rank * RP;
-    const int rows_here = max(0, min(RP, a.T - t_first));
-    // z = sum over slices (in slice order) of (hi + mid) + lo, then + bias
+    const int rows_here = got_all ? max(0, min(RP, a.T - t_first)) : 0;
+    // z = sum over the CTAs' slices in rank order, then + bias
     for (int i = et; i < rows_here * a.E; i += 128) {
       const int lr = i / a.E, e = i - lr * a.E;
       float z = 0.0f;
 #pragma unroll
-      for (int s = 0; s < CS; ++s) {
-        const float* p = exch + ((size_t)s * RP + lr) * xld + e;
-        float part = p[0];
-        if (a.terms == 3) part = (part + p[a.epad]) + p[2 * a.epad];
-        z += part;
-      }
+      for (int s = 0; s < CS; ++s) z += exch[((size_t)s * RP + lr) * xld + e];
       if (a.bias != nullptr) z += __ldg(a.bias + e);
       z_s[lr * EP + e] = z;
       if (a.logits_out != nullptr) a.logits_out[(size_t)t_first * a.E + i] = z;
     }
+    RT_MARK(6);
     epilogue_bar_sync();
     if (et < rows_here) {
       const int t = t_first + et;
@@ -309,10 +386,20 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       route_one_token<kRouteMaxK>(z_s + et * EP, a.E, a.k, a.topk_idx + (size_t)t * a.k,
                                   a.topk_gate + (size_t)t * a.k, a.block_counts + (size_t)b * a.E);
     }
+    RT_MARK(7);
+  } else {
+    __syncwarp();
+    if (CS > 1) {
+      asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+      asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    }
   }
 
   // ---- teardown ------------------------------------------------------------------------
+  // Nobody stores into this CTA's shared memory any more: its exchange barrier has seen all
+  // 128 arrivals (or a wait gave up and the status word says so).
   __syncthreads();
+  RT_MARK(8);
   if (sh->abort_flag != 0) {
     long long t0 = clock64();
     while (clock64() - t0 < 4000000LL) {
@@ -345,16 +432,22 @@ RouterTcPlan router_tc_plan(const AxmMoeDesc* d) {
   if (!router_tc_enabled() || p.n_cols > 256 || d->d_model % 8 != 0) return p;  // ok = false
   const int b_bytes = (p.n_cols * BK * 2 + 1023) / 1024 * 1024;
   p.stage_bytes = kRtABytes + b_bytes;
-  p.stages = kRtStageBudget / p.stage_bytes;
-  p.stages = p.stages < 2 ? 2 : (p.stages > kRtMaxStages ? kRtMaxStages : p.stages);
   const int kb_total = (d->d_model + BK - 1) / BK;
   p.cs = kb_total >= 16 ? 4 : (kb_total >= 4 ? 2 : 1);  // a function of D alone
+  p.nacc = 4 * p.n_cols <= 256 ? 4 : (2 * p.n_cols <= 256 ? 2 : 1);
+  p.exch_bytes = kRtTileRows * (p.epad + 4) * 4;
+  p.stages = kRtStageBudget / p.stage_bytes;
+  p.stages = p.stages < 2 ? 2 : (p.stages > kRtMaxStages ? kRtMaxStages : p.stages);
+  p.skip_b = 0;
+  if (const char* e = getenv("AXM_RT_STAGES")) { int v = atoi(e); if (v >= 2 && v <= kRtMaxStages) p.stages = v; }
+  if (const char* e = getenv("AXM_RT_CS")) { int v = atoi(e); if (v == 1 || v == 2 || v == 4) p.cs = v; }
+  if (const char* e = getenv("AXM_RT_NACC")) { int v = atoi(e); if ((v == 1 || v == 2 || v == 4) && v * p.n_cols <= 512) p.nacc = v; }
+  if (const char* e = getenv("AXM_RT_NOB")) p.skip_b = atoi(e) != 0;
   p.tmem_cols = 32;
-  while (p.tmem_cols < p.n_cols) p.tmem_cols *= 2;
-  const int exch_bytes = kRtTileRows * (p.n_cols + 4) * 4;
-  p.tile_bytes = p.stages * p.stage_bytes > exch_bytes ? p.stages * p.stage_bytes : (exch_bytes + 1023) / 1024 * 1024;
-  p.smem_bytes = 1024 + (size_t)p.tile_bytes + sizeof(RouterTcShared) +
-                 sizeof(float) * (size_t)(kRtTileRows / p.cs) * (d->num_experts + 1);
+  while (p.tmem_cols < p.nacc * p.n_cols) p.tmem_cols *= 2;
+  const int after_loop = p.exch_bytes + 4 * (kRtTileRows / p.cs) * (d->num_experts + 1);
+  p.tile_bytes = p.stages * p.stage_bytes > after_loop ? p.stages * p.stage_bytes : (after_loop + 1023) / 1024 * 1024;
+  p.smem_bytes = 1024 + (size_t)p.tile_bytes + sizeof(RouterTcShared);
   p.scratch_bytes = ((size_t)p.n_cols * d->d_model * 2 + 255) & ~(size_t)255;
   p.ok = p.smem_bytes <= 227u * 1024u;
   return p;
@@ -436,8 +529,11 @@ int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, 
   a.n_cols = p.n_cols;
   a.stages = p.stages;
   a.stage_bytes = p.stage_bytes;
+  a.nacc = p.nacc;
   a.tmem_cols = p.tmem_cols;
+  a.exch_bytes = p.exch_bytes;
   a.tile_bytes = p.tile_bytes;
+  a.skip_b = p.skip_b;
   const int tiles = (T + kRtTileRows - 1) / kRtTileRows;
   switch (p.cs) {
     case 4: return launch_router_tc_cs<4>(p, mx, mb, a, tiles, st);
@@ -447,3 +543,9 @@ int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, 
 }
 
 }  // namespace axm
+
+#ifdef AXM_RT_TRACE
+extern "C" __attribute__((visibility("default"))) int axm_debug_set_router_trace(long long* p) {
+  return (int)cudaMemcpyToSymbol(axm::g_rt_trace, &p, sizeof(p));
+}
+#endif

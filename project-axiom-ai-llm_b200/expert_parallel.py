@@ -21,8 +21,8 @@ import ctypes
 import torch
 import torch.distributed as dist
 
-from . import (AXM_ERR_TIMEOUT, FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A,
-               AxmError, EpLayout, check, current_stream, load, make_desc, ptr, router_scratch_bytes)
+from . import (AXM_ERR_TIMEOUT, FLAG_H_EXACT, FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A,
+               AxmError, EpLayout, EpTensors, check, current_stream, load, make_desc, ptr, router_scratch_bytes)
 
 
 class CudaStages:
@@ -197,9 +197,13 @@ class ExpertParallelMoeP2P:
     """
 
     def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, residual=True,
-                 fused_return=False):
+                 fused_return=False, c_layer=True, h_exact=False):
         import torch.distributed._symmetric_memory as symm_mem
         self.fused_return = fused_return
+        # c_layer: the whole call behind axm_moe_ep_forward (permute fused with the dispatch,
+        # return overlapped with the second half of the down projection); otherwise the
+        # stage-by-stage sequence below, which the fused-return variant also uses
+        self.c_layer = c_layer and not fused_return
         self.lib = load()
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
@@ -216,10 +220,11 @@ class ExpertParallelMoeP2P:
         self.S = 0 if local_weights.get("shared_gate") is None else local_weights["shared_gate"].shape[0]
         self.Tl = tokens_local
         rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
-        flags = FLAG_RESIDUAL if residual else 0
+        flags = (FLAG_RESIDUAL if residual else 0) | (FLAG_H_EXACT if h_exact else 0)
         self.desc_route = make_desc(tokens_local, D, F, num_experts, top_k, 0, rdt, flags)
         self.desc_ffn = make_desc(tokens_local, D, F, self.El, min(top_k, self.El), self.S, rdt, flags)
         self.desc_comb = make_desc(tokens_local, D, F, num_experts, top_k, self.S, rdt, flags)
+        self.desc_layer = make_desc(tokens_local, D, F, num_experts, top_k, self.S, rdt, flags)
         dev, i32, bf = self.dev, torch.int32, torch.bfloat16
         n_slots = tokens_local * top_k
         self.slots = n_slots
@@ -240,6 +245,7 @@ class ExpertParallelMoeP2P:
         self.layout.rank = self.rank
         self.layout.num_shared = self.S
         self.layout.tokens_local = tokens_local
+        self.layout.local_region = self.region.data_ptr()
         lo = self.layout
         self.recv = self.region[lo.off_recv:lo.off_recv + 2 * self.cap * D].view(bf).view(self.cap, D)
         self.o_back = self.region[lo.off_oback:lo.off_oback + 4 * n_slots * D].view(
@@ -254,16 +260,30 @@ class ExpertParallelMoeP2P:
         self.row_src = torch.empty(n_slots, dtype=i32, device=dev)
         self.slot_dst = torch.empty(n_slots, dtype=i32, device=dev)
         self.x_perm = torch.empty(n_slots, D, dtype=bf, device=dev)
-        self.h = torch.empty(self.rows_total, F, dtype=bf, device=dev)
-        self.o = torch.empty(self.rows_total, D, dtype=torch.float32, device=dev)
         self.y = torch.empty(tokens_local, D, dtype=bf, device=dev)
+        self.step = 0
+        if self.c_layer:
+            nb, zb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+            check(self.lib.axm_moe_ep_workspace_bytes(ctypes.byref(self.layout), ctypes.byref(self.desc_layer),
+                                                      ctypes.byref(nb), ctypes.byref(zb)))
+            self.workspace = torch.empty(nb.value, dtype=torch.uint8, device=dev)
+            self.workspace[:zb.value].zero_()
+            ps, pr = ctypes.c_void_p(), ctypes.c_void_p()
+            check(self.lib.axm_moe_ep_status_word(ctypes.byref(self.layout), ctypes.byref(self.desc_layer),
+                                                  ptr(self.workspace), ctypes.byref(ps), ctypes.byref(pr)))
+            base = self.workspace.data_ptr()
+            self.status = self.workspace[ps.value - base:ps.value - base + 4].view(i32)
+            self.rows_received = self.workspace[pr.value - base:pr.value - base + 4].view(i32)
+            self.rows_received.zero_()
+            return
+        self.h = torch.empty(self.rows_total, F * (2 if h_exact else 1), dtype=bf, device=dev)
+        self.o = torch.empty(self.rows_total, D, dtype=torch.float32, device=dev)
         self.status = torch.zeros(1, dtype=i32, device=dev)
         self.scratch = torch.zeros(2, dtype=i32, device=dev)
         self.segments = torch.zeros(self.n_seg, 4, dtype=i32, device=dev)
         self.ret_segments = torch.zeros(self.world * self.El, 4, dtype=i32, device=dev)
         self.remote_out = torch.zeros(self.n_seg, 2, dtype=torch.int64, device=dev)
         self.rows_received = torch.zeros(1, dtype=i32, device=dev)
-        self.step = 0
 
     @property
     def last_rows_received(self):
@@ -281,7 +301,54 @@ class ExpertParallelMoeP2P:
             raise AxmError(AXM_ERR_TIMEOUT, f"a bounded device-side wait gave up (kernel code {code}) "
                                             f"on rank {self.rank}")
 
+    def ep_tensors(self, x, out):
+        w, S = self.w, self.S
+        return EpTensors(
+            x.data_ptr(), w["router_w"].data_ptr(),
+            None if w.get("router_bias") is None else w["router_bias"].data_ptr(),
+            w["w_gate"].data_ptr(), w["w_up"].data_ptr(), w["w_down"].data_ptr(),
+            w["shared_gate"].data_ptr() if S else None, w["shared_up"].data_ptr() if S else None,
+            w["shared_down"].data_ptr() if S else None, self.logits.data_ptr(), self.idx.data_ptr(),
+            self.gate.data_ptr(), self.histogram.data_ptr(), self.y.data_ptr(), out.data_ptr())
+
+    def forward_profiled(self, x, out=None):
+        """forward() with device times of its seven phases (synchronises): returns (out, {name: ms})."""
+        assert self.c_layer
+        if out is None:
+            out = torch.empty_like(x)
+        self.step += 1
+        t = self.ep_tensors(x, out)
+        ms = (ctypes.c_float * 7)()
+        check(self.lib.axm_moe_ep_forward_profiled(
+            ctypes.byref(self.layout), ctypes.byref(self.desc_layer), ctypes.byref(t), ptr(self.workspace),
+            self.workspace.numel(), self.step, current_stream(), ms))
+        names = ["router", "permute + dispatch (peer stores)", "wait rows + segments", "gate/up GEMM",
+                 "down GEMM (first half returning underneath)", "return of the second half",
+                 "wait return + combine"]
+        return out, dict(zip(names, list(ms)))
+
+    def forward_host(self, h_x, h_out, d_x, d_out, chunks=2):
+        """Activations in pinned host memory, copies pipelined with the exchange steps; synchronises."""
+        assert self.c_layer
+        t = self.ep_tensors(d_x, d_out)
+        step = ctypes.c_uint32(self.step + 1)
+        check(self.lib.axm_moe_ep_forward_host(
+            ctypes.byref(self.layout), ctypes.byref(self.desc_layer), ctypes.byref(t), ptr(h_x), ptr(h_out),
+            ptr(d_x), ptr(d_out), ptr(self.workspace), self.workspace.numel(), chunks, ctypes.byref(step),
+            current_stream()))
+        self.step = step.value - 1
+        return h_out
+
     def forward(self, x, out=None, events=None):
+        if self.c_layer:
+            if out is None:
+                out = torch.empty_like(x)
+            self.step += 1
+            t = self.ep_tensors(x, out)
+            check(self.lib.axm_moe_ep_forward(ctypes.byref(self.layout), ctypes.byref(self.desc_layer),
+                                              ctypes.byref(t), ptr(self.workspace), self.workspace.numel(),
+                                              self.step, current_stream()))
+            return out
         st, lib, lo = self.stages, self.lib, ctypes.byref(self.layout)
 
         def mark(name):

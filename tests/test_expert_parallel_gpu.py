@@ -44,15 +44,32 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         if transport == "nccl":
             layer = ep.ExpertParallelMoe(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
                                          cfg.top_k)
-        else:   # own peer-memory kernels; return fused into the down GEMM or as a copy kernel
+        elif transport == "c-layer":   # the whole call behind axm_moe_ep_forward (the default)
+            layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), tl, cfg.num_experts, cfg.top_k)
+            assert layer.c_layer
+        else:   # stage by stage; return fused into the down GEMM or as a copy kernel
             layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
-                                            cfg.top_k, fused_return=(transport == "p2p"))
-        out = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous()).clone()
+                                            cfg.top_k, fused_return=(transport == "p2p"), c_layer=False)
+        x_local = x[rank * tl:(rank + 1) * tl].contiguous()
+        out = layer.forward(x_local).clone()
         for _ in range(3):      # buffers and flags are reused call after call
-            out2 = layer.forward(x[rank * tl:(rank + 1) * tl].contiguous())
+            out2 = layer.forward(x_local)
         torch.cuda.synchronize()
         assert int(layer.status.item()) == 0
         assert torch.equal(out, out2)
+        if transport == "c-layer":
+            layer.check_status()
+            # the host-buffer form, in one piece and in three pipelined parts, gives the same bytes
+            h_x = x_local.cpu().pin_memory()
+            h_out = torch.empty_like(h_x).pin_memory()
+            d_x, d_out = torch.empty_like(x_local), torch.empty_like(x_local)
+            for chunks in (1, 3):
+                h_out.zero_()
+                layer.forward_host(h_x, h_out, d_x, d_out, chunks=chunks)
+                assert torch.equal(h_out, out.cpu()), f"host call in {chunks} part(s)"
+            out3, ms = layer.forward_profiled(x_local)
+            assert torch.equal(out3, out) and len(ms) == 7
+            layer.check_status()
         if rank == 0:
             single = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
             ref, _ = single.forward(x)
@@ -66,7 +83,7 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["nccl", "p2p", "p2p-copy"])
+@pytest.mark.parametrize("transport", ["c-layer", "nccl", "p2p", "p2p-copy"])
 @pytest.mark.parametrize("name,tokens", [("C1", 64), ("C2", 1024), ("C4", 2048)])
 def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens, transport):
     world = min(torch.cuda.device_count(), 4) if name == "C4" else 2
