@@ -65,7 +65,7 @@ __device__ __forceinline__ void route_one_token(float* z, int E, int k, int32_t*
 // ---- tensor-core router (router_tc.cu): launch plan and host entry ------------------------
 struct RouterTcPlan {
   bool ok;          // false: this shape is served by the CUDA-core kernel
-  int epad, terms, n_cols, stages, stage_bytes, nacc, tmem_cols, exch_bytes, tile_bytes, cs, skip_b;
+  int epad, terms, n_cols, stages, stage_bytes, tmem_cols, exch_bytes, tile_bytes, cs;
   size_t smem_bytes, scratch_bytes;
 };
 RouterTcPlan router_tc_plan(const AxmMoeDesc* d);

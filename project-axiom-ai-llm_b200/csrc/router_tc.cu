@@ -18,15 +18,17 @@
 // (N = 3 * Epad, Epad = E rounded up to 16), so one tcgen05.mma per 16 k produces all
 // three partial products and the epilogue adds them.  bf16 router weights use one term.
 //
-// Work split: one thread-block cluster of CS CTAs (1, 2 or 4) per tile; CTA r of the
-// cluster reduces over the r-th slice of D, so 2 to 4 CTAs per SM keep 100+ KB of x in
-// flight per SM even for a few thousand tokens.  CS depends on D only, never on the
+// Work split: one thread-block cluster of CS CTAs (1, 2 or 4) per tile, each reducing over
+// its share of D, so that two CTAs per SM keep 100+ KB of x in flight per SM even for a few
+// thousand tokens.  CS depends on the layer's shape only, never on the
 // number of tokens: a token's logits have the same summation order whatever batch it is
-// in (expert-parallel ranks and the single-GPU layer must route identically).  After the
-// reduction loop the CTAs exchange their partial accumulators through distributed shared
-// memory (plain st.shared::cluster stores, two cluster barriers); CTA r then owns rows
-// [r * 128 / CS, (r + 1) * 128 / CS) of the tile: it adds the slices in slice order, adds
-// the bias, writes the logits and routes one token per thread.
+// in (expert-parallel ranks and the single-GPU layer must route identically).  CTA r takes
+// the 64-wide blocks r, r + CS, ... of d_model.  After the reduction loop one cluster barrier
+// makes every CTA's stage memory reusable; each thread adds its row's three terms and stores
+// the row's partial logits into the CTA that owns the row (plain st.shared::cluster stores,
+// then an arrival on the owner's mbarrier); CTA r owns rows [r * 128 / CS, (r + 1) * 128 / CS)
+// of the tile: it adds the slices in rank order, adds the bias, writes the logits and routes
+// one token per thread.
 //
 // Per-block expert counts for the permute kernel go to block_counts with integer atomics
 // (order-independent, hence deterministic); the preparation kernel zeroes the table.
@@ -70,11 +72,9 @@ struct RouterTcArgs {
   int n_cols;      // terms * epad: N of the MMA
   int stages;
   int stage_bytes; // A tile + B tile, a multiple of 1024
-  int nacc;        // accumulators the k-steps rotate through (1, 2 or 4)
-  int tmem_cols;   // power of two >= max(32, nacc * n_cols)
+  int tmem_cols;   // power of two >= max(32, n_cols)
   int exch_bytes;  // bytes of the exchange buffer [CS][128 / CS][epad + 4] floats, 16-byte multiple
   int tile_bytes;  // bytes of the region shared by the pipeline stages and, later, exchange buffer + logits
-  int skip_b;      // measuring aid: do not load the weight tiles (results are then meaningless)
 };
 
 __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
@@ -171,18 +171,6 @@ router_prep_kernel(const WT* __restrict__ w, __nv_bfloat16* __restrict__ bt, int
   }
 }
 
-#ifdef AXM_RT_TRACE
-__device__ long long* g_rt_trace = nullptr;
-__device__ __forceinline__ unsigned long long rt_gtime() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-#define RT_MARK(i) do { if (g_rt_trace != nullptr && threadIdx.x == 64) g_rt_trace[(size_t)blockIdx.x * 16 + (i)] = (long long)rt_gtime(); } while (0)
-#else
-#define RT_MARK(i) do { } while (0)
-#endif
-
 // ---- the router ---------------------------------------------------------------------------
 template <int CS>
 __global__ void __launch_bounds__(kRtThreads)
@@ -197,8 +185,6 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   float* exch = reinterpret_cast<float*>(tiles);
   float* z_s = reinterpret_cast<float*>(tiles + a.exch_bytes);
   RouterTcShared* sh = reinterpret_cast<RouterTcShared*>(tiles + a.tile_bytes);
-
-  RT_MARK(0);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = CS > 1 ? rt_cluster_rank() : 0u;
   const int tile = blockIdx.x / CS;
@@ -237,8 +223,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     tmem_base = sh->tmem_base;
   }
   volatile int* abort_flag = &sh->abort_flag;
-  const uint32_t stage_tx = (uint32_t)(kRtABytes + (a.skip_b ? 0 : a.n_cols * BK * 2));
-  RT_MARK(1);
+  const uint32_t stage_tx = (uint32_t)(kRtABytes + a.n_cols * BK * 2);
 
   if (warp == 0) {
     // ---- TMA producer -----------------------------------------------------------------
@@ -251,10 +236,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         tma_load_2d(tiles + (size_t)i * a.stage_bytes, &tm_x, &sh->full[i], ((int)rank + i * CS) * BK, row0);
       }
       griddep_wait();
-      if (!a.skip_b)
-        for (int i = 0; i < early; ++i)
-          tma_load_2d(tiles + (size_t)i * a.stage_bytes + kRtABytes, &tm_b, &sh->full[i],
-                      ((int)rank + i * CS) * BK, 0);
+      for (int i = 0; i < early; ++i)
+        tma_load_2d(tiles + (size_t)i * a.stage_bytes + kRtABytes, &tm_b, &sh->full[i], ((int)rank + i * CS) * BK, 0);
       int stage = early == a.stages ? 0 : early;
       uint32_t phase = early == a.stages ? 1u : 0u;
       for (int i = early; i < kb_count; ++i) {
@@ -262,7 +245,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         unsigned char* sa = tiles + (size_t)stage * a.stage_bytes;
         mbar_expect_tx(&sh->full[stage], stage_tx);
         tma_load_2d(sa, &tm_x, &sh->full[stage], ((int)rank + i * CS) * BK, row0);
-        if (!a.skip_b) tma_load_2d(sa + kRtABytes, &tm_b, &sh->full[stage], ((int)rank + i * CS) * BK, 0);
+        tma_load_2d(sa + kRtABytes, &tm_b, &sh->full[stage], ((int)rank + i * CS) * BK, 0);
         if (++stage == a.stages) {
           stage = 0;
           phase ^= 1u;
@@ -271,14 +254,10 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     }
   } else if (warp == 1) {
     // ---- MMA issuer -------------------------------------------------------------------
-    // Successive 16-wide k-steps go to `nacc` different accumulators in turn: an MMA that adds
-    // to the accumulator the previous one is still writing would wait for it, and with so few
-    // columns per instruction that latency, not the HBM stream, would set the pace.
     if (lane == 0) {
       const uint32_t idesc = rt_instr_desc(a.n_cols);
       int stage = 0;
       uint32_t phase = 0;
-      int ks = 0;
       bool ok = true;
       for (int i = 0; i < kb_count; ++i) {
         if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
@@ -290,9 +269,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         const uint64_t da = make_smem_desc(sa, 16, 1024);
         const uint64_t db = make_smem_desc(sa + kRtABytes, 16, 1024);
 #pragma unroll
-        for (int j = 0; j < BK / UMMA_K; ++j, ++ks)
-          tc_mma_bf16(tmem_base + (uint32_t)((ks % a.nacc) * a.n_cols), da + (uint64_t)(j * 2),
-                      db + (uint64_t)(j * 2), idesc, ks >= a.nacc ? 1u : 0u);
+        for (int j = 0; j < BK / UMMA_K; ++j)
+          tc_mma_bf16(tmem_base, da + (uint64_t)(j * 2), db + (uint64_t)(j * 2), idesc, (i > 0 || j > 0) ? 1u : 0u);
         tc_commit(&sh->empty[stage]);
         if (++stage == a.stages) {
           stage = 0;
@@ -311,7 +289,6 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       acc_ok = __all_sync(0xffffffffu, mbar_wait(&sh->tmem_full, 0u, abort_flag));
       tc_fence_after();
     }
-    RT_MARK(2);
     // One cluster barrier per kernel: a thread arrives when its part of the reduction loop is
     // over (for these warps: the accumulator is complete, so every tile this CTA requested has
     // landed and been read).  Once it completes, the stage memory of every CTA of the cluster
@@ -320,23 +297,22 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
       asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
     }
-    RT_MARK(3);
     {
-      // this CTA's partial logits of row r: sum over its accumulators of (hi + mid) + lo,
-      // 16 experts at a time, stored into the row's owner
+      // this CTA's partial logits of row r, (hi + mid) + lo, 16 experts at a time, stored into
+      // the row's owner
       const int r = quad * 32 + lane;
       const int owner = r / RP, lr = r - owner * RP;
       const uint32_t dst_local = smem_u32(exch + ((size_t)rank * RP + lr) * xld);
       const uint32_t dst = CS > 1 ? rt_map_to_cta(dst_local, (uint32_t)owner) : dst_local;
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
-      const int used = (kb_count > 0 && acc_ok) ? min(a.nacc, kb_count * (BK / UMMA_K)) : 0;
+      const bool have = kb_count > 0 && acc_ok;  // a CTA without k-blocks contributes zeros
       for (int c0 = 0; c0 < a.epad; c0 += 16) {
         float part[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) part[j] = 0.0f;
-        for (int ac = 0; ac < used; ++ac) {
+        if (have) {
           uint32_t hi[16], mid[16], lo[16];
-          const uint32_t col = t_addr + (uint32_t)(ac * a.n_cols + c0);
+          const uint32_t col = t_addr + (uint32_t)c0;
           tmem_ld16(col, hi);
           if (a.terms == 3) {
             tmem_ld16(col + (uint32_t)a.epad, mid);
@@ -347,7 +323,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
           for (int j = 0; j < 16; ++j) {
             float v = __uint_as_float(hi[j]);
             if (a.terms == 3) v = (v + __uint_as_float(mid[j])) + __uint_as_float(lo[j]);
-            part[j] += v;
+            part[j] = v;
           }
         }
 #pragma unroll
@@ -361,9 +337,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const uint32_t bar_local = smem_u32(&sh->exch_full);
       rt_mbar_arrive_cluster(CS > 1 ? rt_map_to_cta(bar_local, (uint32_t)owner) : bar_local);
     }
-    RT_MARK(4);
     const bool got_all = __all_sync(0xffffffffu, rt_mbar_wait_cluster(&sh->exch_full, 0u, abort_flag));
-    RT_MARK(5);
     griddep_wait();  // the count table was zeroed by the preparation kernel
     const int et = (warp - 2) * 32 + lane;  // 0..127
     const int t_first = row0 + (int)rank * RP;
@@ -378,7 +352,6 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       z_s[lr * EP + e] = z;
       if (a.logits_out != nullptr) a.logits_out[(size_t)t_first * a.E + i] = z;
     }
-    RT_MARK(6);
     epilogue_bar_sync();
     if (et < rows_here) {
       const int t = t_first + et;
@@ -386,7 +359,6 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       route_one_token<kRouteMaxK>(z_s + et * EP, a.E, a.k, a.topk_idx + (size_t)t * a.k,
                                   a.topk_gate + (size_t)t * a.k, a.block_counts + (size_t)b * a.E);
     }
-    RT_MARK(7);
   } else {
     __syncwarp();
     if (CS > 1) {
@@ -399,7 +371,6 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   // Nobody stores into this CTA's shared memory any more: its exchange barrier has seen all
   // 128 arrivals (or a wait gave up and the status word says so).
   __syncthreads();
-  RT_MARK(8);
   if (sh->abort_flag != 0) {
     long long t0 = clock64();
     while (clock64() - t0 < 4000000LL) {
@@ -433,18 +404,16 @@ RouterTcPlan router_tc_plan(const AxmMoeDesc* d) {
   const int b_bytes = (p.n_cols * BK * 2 + 1023) / 1024 * 1024;
   p.stage_bytes = kRtABytes + b_bytes;
   const int kb_total = (d->d_model + BK - 1) / BK;
-  p.cs = kb_total >= 16 ? 4 : (kb_total >= 4 ? 2 : 1);  // a function of D alone
-  p.nacc = 4 * p.n_cols <= 256 ? 4 : (2 * p.n_cols <= 256 ? 2 : 1);
+  // CTAs per cluster = slices of d_model: a function of the layer's shape alone, never of the
+  // token count.  Four slices where the exchange is cheap (few columns); with many experts the
+  // epilogue (exchange, per-token top-k over E) weighs more than the stream and two are faster
+  // (measured at T 16384, D 2048, E 64: 31 us against 45).
+  p.cs = kb_total >= 16 && p.n_cols <= 64 ? 4 : (kb_total >= 4 ? 2 : 1);
   p.exch_bytes = kRtTileRows * (p.epad + 4) * 4;
   p.stages = kRtStageBudget / p.stage_bytes;
   p.stages = p.stages < 2 ? 2 : (p.stages > kRtMaxStages ? kRtMaxStages : p.stages);
-  p.skip_b = 0;
-  if (const char* e = getenv("AXM_RT_STAGES")) { int v = atoi(e); if (v >= 2 && v <= kRtMaxStages) p.stages = v; }
-  if (const char* e = getenv("AXM_RT_CS")) { int v = atoi(e); if (v == 1 || v == 2 || v == 4) p.cs = v; }
-  if (const char* e = getenv("AXM_RT_NACC")) { int v = atoi(e); if ((v == 1 || v == 2 || v == 4) && v * p.n_cols <= 512) p.nacc = v; }
-  if (const char* e = getenv("AXM_RT_NOB")) p.skip_b = atoi(e) != 0;
   p.tmem_cols = 32;
-  while (p.tmem_cols < p.nacc * p.n_cols) p.tmem_cols *= 2;
+  while (p.tmem_cols < p.n_cols) p.tmem_cols *= 2;
   const int after_loop = p.exch_bytes + 4 * (kRtTileRows / p.cs) * (d->num_experts + 1);
   p.tile_bytes = p.stages * p.stage_bytes > after_loop ? p.stages * p.stage_bytes : (after_loop + 1023) / 1024 * 1024;
   p.smem_bytes = 1024 + (size_t)p.tile_bytes + sizeof(RouterTcShared);
@@ -529,11 +498,9 @@ int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, 
   a.n_cols = p.n_cols;
   a.stages = p.stages;
   a.stage_bytes = p.stage_bytes;
-  a.nacc = p.nacc;
   a.tmem_cols = p.tmem_cols;
   a.exch_bytes = p.exch_bytes;
   a.tile_bytes = p.tile_bytes;
-  a.skip_b = p.skip_b;
   const int tiles = (T + kRtTileRows - 1) / kRtTileRows;
   switch (p.cs) {
     case 4: return launch_router_tc_cs<4>(p, mx, mb, a, tiles, st);
@@ -544,8 +511,3 @@ int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, 
 
 }  // namespace axm
 
-#ifdef AXM_RT_TRACE
-extern "C" __attribute__((visibility("default"))) int axm_debug_set_router_trace(long long* p) {
-  return (int)cudaMemcpyToSymbol(axm::g_rt_trace, &p, sizeof(p));
-}
-#endif
