@@ -521,9 +521,12 @@ AXM_API int axm_moe_ep_forward(const AxmEpLayout* layout, const AxmMoeDesc* desc
 AXM_API int axm_moe_ep_status_word(const AxmEpLayout* layout, const AxmMoeDesc* desc, void* workspace,
                                    int32_t** status, int32_t** rows_received);
 /* axm_moe_ep_forward with CUDA events between its phases; synchronises the stream and returns
- * seven device times in milliseconds: router, permute + dispatch, wait for rows + segment
+ * device times in milliseconds: router, permute + dispatch, wait for rows + segment
  * tables, gate/up GEMM, down GEMM (both halves; the first half's return runs underneath),
- * return of the second half, wait for returned rows + combine.  A measuring aid. */
+ * return of the second half, wait for returned rows + combine; stage_ms[7] and [8] are the
+ * start and the end of the first half's return copy (side stream), counted from the start
+ * of the down GEMM (both 0 when the return is not split).  stage_ms holds 9 floats.  A
+ * measuring aid. */
 AXM_API int axm_moe_ep_forward_profiled(const AxmEpLayout* layout, const AxmMoeDesc* desc,
                                         const AxmEpTensors* tensors, void* workspace,
                                         size_t workspace_bytes, uint32_t step, void* stream,

@@ -134,6 +134,11 @@ __device__ __forceinline__ void tma_store_3d(const void* tmap, const void* src, 
                "r"(smem_u32(src)), "r"(x), "r"(y), "r"(z)
                : "memory");
 }
+__device__ __forceinline__ void tma_store_2d(const void* tmap, const void* src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(tmap),
+               "r"(smem_u32(src)), "r"(x), "r"(y)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit_group() {
   asm volatile("cp.async.bulk.commit_group;" ::: "memory");
 }

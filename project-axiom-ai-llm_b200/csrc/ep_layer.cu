@@ -142,7 +142,11 @@ EpPipe* ep_pipe() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   EpPipe& p = pipes[dev];
   if (!p.ok) {
-    if (cudaStreamCreateWithFlags(&p.side, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+    // the side stream carries small copy kernels that must get onto the SMs beside a persistent
+    // GEMM that becomes runnable at the same moment: highest priority
+    int prio_lo = 0, prio_hi = 0;
+    if (cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithPriority(&p.side, cudaStreamNonBlocking, prio_hi) != cudaSuccess) return nullptr;
     if (cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     cudaEvent_t* evs[] = {&p.half_done, &p.side_done, &p.start};
@@ -157,7 +161,8 @@ EpPipe* ep_pipe() {
   return &p;
 }
 
-// ev: optional 8 timing events recorded between the phases (0 = start ... 7 = end)
+// ev: optional 10 timing events: 0..7 recorded on the caller's stream between the phases
+// (0 = start ... 7 = end), 8 and 9 on the side stream around the first half's return copy
 int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const AxmEpTensors* t, void* workspace,
                     size_t workspace_bytes, uint32_t step, void* stream, cudaEvent_t* ev) {
   if (int rc = validate_ep_layer(layout, desc)) return rc;
@@ -234,9 +239,11 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
     if ((rc = ffn(w.seg_halves, El, 2))) return rc;
     AXM_CUDA(cudaEventRecord(pipe->half_done, st));
     AXM_CUDA(cudaStreamWaitEvent(pipe->side, pipe->half_done, 0));
+    if (ev) cudaEventRecord(ev[8], pipe->side);
     if ((rc = launch_ep_return_half(&l, step, w.ret_segments, w.o, w.scratch + 1, w.split_rows, 0, 0, w.status,
                                     pipe->side)))
       return rc;
+    if (ev) cudaEventRecord(ev[9], pipe->side);
     AXM_CUDA(cudaEventRecord(pipe->side_done, pipe->side));
     if ((rc = ffn(w.seg_halves + El, El + S, 2))) return rc;
     mark(5);
@@ -291,18 +298,25 @@ extern "C" int axm_moe_ep_forward_profiled(const AxmEpLayout* layout, const AxmM
                                            const AxmEpTensors* tensors, void* workspace, size_t workspace_bytes,
                                            uint32_t step, void* stream, float* stage_ms) {
   if (stage_ms == nullptr) return fail(AXM_ERR_ARGUMENT, "stage_ms is null");
-  for (int i = 0; i < 7; ++i) stage_ms[i] = 0.0f;
-  cudaEvent_t ev[8];
-  for (int i = 0; i < 8; ++i)
+  for (int i = 0; i < 9; ++i) stage_ms[i] = 0.0f;
+  cudaEvent_t ev[10];
+  for (int i = 0; i < 10; ++i)
     if (cudaEventCreate(&ev[i]) != cudaSuccess) return fail(AXM_ERR_LAUNCH, "cudaEventCreate failed");
   int rc = ep_forward_impl(layout, desc, tensors, workspace, workspace_bytes, step, stream, ev);
   if (rc == AXM_OK) {
     cudaError_t e = cudaStreamSynchronize(static_cast<cudaStream_t>(stream));
     if (e != cudaSuccess) rc = fail(AXM_ERR_LAUNCH, "synchronise: %s", cudaGetErrorString(e));
-    else
+    else {
       for (int i = 0; i < 7; ++i) cudaEventElapsedTime(&stage_ms[i], ev[i], ev[i + 1]);
+      // the overlapped copy: when it started and ended, counted from the start of the down GEMM
+      if (cudaEventQuery(ev[8]) == cudaSuccess && cudaEventQuery(ev[9]) == cudaSuccess) {
+        cudaEventElapsedTime(&stage_ms[7], ev[4], ev[8]);
+        cudaEventElapsedTime(&stage_ms[8], ev[4], ev[9]);
+      }
+      cudaGetLastError();
+    }
   }
-  for (int i = 0; i < 8; ++i) cudaEventDestroy(ev[i]);
+  for (int i = 0; i < 10; ++i) cudaEventDestroy(ev[i]);
   return rc;
 }
 

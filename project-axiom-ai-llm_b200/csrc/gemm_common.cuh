@@ -102,6 +102,10 @@ int encode_tensor_map(CUtensorMap* m, const void* base, int rank, const uint64_t
 int encode_tensor_map_f32(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
                           const uint64_t* strides_bytes, const uint32_t* box);
 
+// bf16 map with 64-byte swizzle (box inner extent 32 elements): the epilogue blocks of the dH kernel.
+int encode_tensor_map_sw64(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box);
+
 // Two-SM (cta_group::2) kernels are the default; AXM_GEMM_2SM=0 selects the one-SM kernels.
 bool use_2sm_kernels();
 // Input-gradient GEMM of the backward pass on CTA pairs (grouped_ffn_2sm.cu).

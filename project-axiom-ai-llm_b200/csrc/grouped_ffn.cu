@@ -350,7 +350,8 @@ static EncodeTiledFn encode_fn() {
 }
 
 static int encode_tensor_map_typed(CUtensorMap* m, CUtensorMapDataType type, const void* base, int rank,
-                                   const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box) {
+                                   const uint64_t* dims, const uint64_t* strides_bytes, const uint32_t* box,
+                                   CUtensorMapSwizzle swizzle = CU_TENSOR_MAP_SWIZZLE_128B) {
   if (encode_fn() == nullptr) return fail(AXM_ERR_DEVICE, "cuTensorMapEncodeTiled entry point not found");
   cuuint64_t d[3], st[2];
   cuuint32_t b[3], es[3] = {1, 1, 1};
@@ -360,7 +361,7 @@ static int encode_tensor_map_typed(CUtensorMap* m, CUtensorMapDataType type, con
     if (i + 1 < rank) st[i] = strides_bytes[i];
   }
   CUresult r = encode_fn()(m, type, (cuuint32_t)rank, const_cast<void*>(base),
-                           d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
                            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(AXM_ERR_ARGUMENT, "cuTensorMapEncodeTiled(rank %d) failed: %d", rank, (int)r);
   return AXM_OK;
@@ -369,6 +370,12 @@ static int encode_tensor_map_typed(CUtensorMap* m, CUtensorMapDataType type, con
 int encode_tensor_map(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
                       const uint64_t* strides_bytes, const uint32_t* box) {
   return encode_tensor_map_typed(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box);
+}
+
+int encode_tensor_map_sw64(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,
+                           const uint64_t* strides_bytes, const uint32_t* box) {
+  return encode_tensor_map_typed(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, base, rank, dims, strides_bytes, box,
+                                 CU_TENSOR_MAP_SWIZZLE_64B);
 }
 
 int encode_tensor_map_f32(CUtensorMap* m, const void* base, int rank, const uint64_t* dims,

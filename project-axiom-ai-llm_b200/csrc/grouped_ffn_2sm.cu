@@ -50,6 +50,9 @@ struct Gemm2Args {
   int two_term;
 };
 
+constexpr int kStagesDh = 5;  // operand stages of kModeDH (one stage's room goes to its epilogue blocks)
+constexpr int kDhSlots = 3;   // 4 KiB slots (g / dG block + u / dU block) per epilogue warp
+
 // fp32 accumulate, bf16 A (K-major) and B (MN-major), N = 256, M = 256 over the pair
 constexpr uint32_t kInstrDesc2 = (1u << 4) | (1u << 7) | (1u << 10) | (0u << 15) | (1u << 16) |
                                  ((uint32_t)(UMMA_N >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
@@ -110,19 +113,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
 grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_alt,
                         const __grid_constant__ CUtensorMap tm_b0, const __grid_constant__ CUtensorMap tm_b1,
                         const __grid_constant__ CUtensorMap tm_b0_sh, const __grid_constant__ CUtensorMap tm_b1_sh,
+                        const __grid_constant__ CUtensorMap tm_g, const __grid_constant__ CUtensorMap tm_u,
+                        const __grid_constant__ CUtensorMap tm_dg, const __grid_constant__ CUtensorMap tm_du,
                         Gemm2Args args) {
   constexpr bool kSwiGLU = kMode == kModeSwiGLU;
   constexpr bool kDX = kMode == kModeDX;
   constexpr bool kDH = kMode == kModeDH;
   constexpr bool kBKmajor = kDX || kDH;  // weights read K-major: one box of 64 k x 128 columns per CTA
+  // kModeDH gives one operand stage to the epilogue's g / u / dG / dU blocks
+  constexpr int kSt = kDH ? kStagesDh : kStages2;
   extern __shared__ unsigned char smem_raw[];
   // both CTAs of a pair compute the same offsets, so their tiles sit at the same place
   unsigned char* tiles = reinterpret_cast<unsigned char*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
-  GemmShared2* sh = reinterpret_cast<GemmShared2*>(tiles + (size_t)kStages2 * kStageBytes2);
-  // kModeDH: 4 KiB per epilogue warp behind the control block
+  GemmShared2* sh = reinterpret_cast<GemmShared2*>(tiles + (size_t)kSt * kStageBytes2);
+  // kModeDH: behind the control block, 1024-byte aligned, per epilogue warp kDhSlots slots of
+  // 4 KiB (a 32 x 32 bf16 block of g / dG and one of u / dU, filled and drained by TMA with
+  // 64-byte swizzle), then one mbarrier per warp and slot
   unsigned char* staging = reinterpret_cast<unsigned char*>(
-      (reinterpret_cast<uintptr_t>(sh + 1) + 127) & ~static_cast<uintptr_t>(127));
+      (reinterpret_cast<uintptr_t>(sh + 1) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint64_t* dh_bars = reinterpret_cast<uint64_t*>(staging + (size_t)4 * kDhSlots * 4096);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -140,9 +150,16 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 
   for (int s = threadIdx.x; s < nseg; s += kGemmThreads) sh->seg[s] = args.segments[s];
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kStages2; ++i) {
+    for (int i = 0; i < kSt; ++i) {
       mbar_init(&sh->full[i], 1);
       mbar_init(&sh->empty[i], 1);
+    }
+    if (kDH) {
+      for (int i = 0; i < 4 * kDhSlots; ++i) mbar_init(&dh_bars[i], 1);
+      tma_prefetch_desc(&tm_g);
+      tma_prefetch_desc(&tm_u);
+      tma_prefetch_desc(&tm_dg);
+      tma_prefetch_desc(&tm_du);
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(&sh->tmem_full[i], 1);
@@ -241,7 +258,7 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
             tma2_load_3d(sb, mb, bar, n_col, kk, e);
             tma2_load_3d(sb + kBChunkBytes, mb, bar, n_col + 64, kk, e);
           }
-          if (++stage == kStages2) {
+          if (++stage == kSt) {
             stage = 0;
             phase ^= 1u;
           }
@@ -282,7 +299,7 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           // free this stage in both CTAs once the MMAs that read it are done
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 0));
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 1));
-          if (++stage == kStages2) {
+          if (++stage == kSt) {
             stage = 0;
             phase ^= 1u;
           }
@@ -299,11 +316,35 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     const int quad = warp & 3;
     int acc = 0;
     uint32_t acc_phase = 0;
+    uint32_t dh_issued = 0, dh_used = 0;  // kModeDH: blocks of g / u requested (lane 0) and consumed
     const uint32_t leader_tmem_empty0 = map_to_cta(smem_u32(&sh->tmem_empty[0]), 0);
     const uint32_t leader_tmem_empty1 = map_to_cta(smem_u32(&sh->tmem_empty[1]), 0);
     for (int unit = cluster_id; unit < total_units; unit += num_clusters) {
       const UnitCoord uc = decode_unit(sh, n_tiles, unit, (int)rank);
       const AxmSegment sg = sh->seg[uc.seg];
+      // kModeDH: this warp's 32 rows of the tile, and the loads of its first two blocks of g / u,
+      // requested before the accumulator is waited for
+      const int dh_row0 = sg.out_row0 + uc.m_tile * BM + quad * 32;
+      const int dh_rows_left = uc.live ? sg.rows - (uc.m_tile * BM + quad * 32) : 0;
+      const bool dh_full = dh_rows_left >= 32;
+      const int dh_n0 = uc.n_tile * BN_OUT;
+      auto dh_valid = [&](int jb) { return dh_rows_left > 0 && dh_n0 + jb * 32 < args.n_total; };
+      auto dh_issue = [&](int jb) {  // lane 0 only; blocks are issued in the order they are used
+        const int slot = (int)(dh_issued % kDhSlots);
+        unsigned char* dst = staging + (size_t)(((warp - 2) & 3) * kDhSlots + slot) * 4096;
+        uint64_t* bar = &dh_bars[((warp - 2) & 3) * kDhSlots + slot];
+        mbar_expect_tx(bar, 4096);
+        tma_load_2d(dst, &tm_g, bar, dh_n0 + jb * 32, dh_row0);
+        tma_load_2d(dst + 2048, &tm_u, bar, dh_n0 + jb * 32, dh_row0);
+        ++dh_issued;
+      };
+      if constexpr (kDH) {
+        if (dh_full && lane == 0) {
+          bulk_wait_read();  // the previous tile's last stores have read their slots
+          if (dh_valid(0)) dh_issue(0);
+          if (dh_valid(1)) dh_issue(1);
+        }
+      }
       if (!__all_sync(0xffffffffu, mbar_wait(&sh->tmem_full[acc], acc_phase, abort_flag))) break;
       tc_fence_after();
       const int row_in_seg = uc.m_tile * BM + quad * 32 + lane;
@@ -314,86 +355,91 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       if constexpr (kDH) {
         // The SwiGLU derivative with the saved g, u: dG = dH u s (1 + g (1 - s)), dU = dH g s,
         // s = sigmoid(g) (core/src/CUDA/kernel/swiglu.cu:34-55 of the reference engine).
-        // g, u, dG, dU move between global memory and the warp's staging block in row-contiguous
-        // 64-byte runs; piece p of a 32 x 32 bf16 block: row p / 4, 16-byte piece p % 4, in shared
-        // memory at row * 64 + ((piece ^ (row / 2 % 4)) * 16 (no bank conflicts either way).  The
-        // pieces of the next 32 columns are fetched while the current ones are worked on.
-        unsigned char* g_s = staging + (size_t)((warp - 2) & 3) * 4096;
-        unsigned char* u_s = g_s + 2048;
-        const int rows_left = uc.live ? sg.rows - (uc.m_tile * BM + quad * 32) : 0;
-        const size_t block_elem = (size_t)(sg.out_row0 + uc.m_tile * BM + quad * 32) * args.n_total + n0;
-        auto piece_ok = [&](int p, int c0) {
-          return (p >> 2) < rows_left && c0 < BN_OUT && n0 + c0 + (p & 3) * 8 < args.n_total;
-        };
-        auto piece_elem = [&](int p, int c0) { return block_elem + (size_t)(p >> 2) * args.n_total + c0 + (p & 3) * 8; };
+        // g and u come in, and dG and dU go out, as 32 x 32 bf16 blocks moved by TMA (64-byte
+        // swizzle: 16-byte piece q of row r sits at r * 64 + ((q ^ (r / 2 % 4)) * 16, so a lane
+        // reading its own row meets no bank conflict): the epilogue warps issue no global loads
+        // or stores of their own.  Each warp owns kDhSlots slots; the loads run two blocks ahead.
+        unsigned char* slots = staging + (size_t)((warp - 2) & 3) * kDhSlots * 4096;
         auto piece_smem = [&](int row, int piece) { return row * 64 + ((piece ^ ((row >> 1) & 3)) << 4); };
-        uint4 g_next[4], u_next[4];
-        auto fetch_gu = [&](int c0) {
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int p = lane + 32 * i;
-            g_next[i] = make_uint4(0, 0, 0, 0);
-            u_next[i] = make_uint4(0, 0, 0, 0);
-            if (piece_ok(p, c0)) {
-              g_next[i] = __ldg(reinterpret_cast<const uint4*>(args.save_g + piece_elem(p, c0)));
-              u_next[i] = __ldg(reinterpret_cast<const uint4*>(args.save_u + piece_elem(p, c0)));
-            }
-          }
-        };
-        if (uc.live) {
-          fetch_gu(0);
 #pragma unroll 1
-          for (int c0 = 0; c0 < BN_OUT; c0 += 32) {
-            uint32_t v[32];
-            __syncwarp();  // the previous block's read-back is done; also rejoins the warp for tcgen05.ld
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int p = lane + 32 * i;
-              *reinterpret_cast<uint4*>(g_s + piece_smem(p >> 2, p & 3)) = g_next[i];
-              *reinterpret_cast<uint4*>(u_s + piece_smem(p >> 2, p & 3)) = u_next[i];
-            }
-            fetch_gu(c0 + 32);
+        for (int jb = 0; jb < BN_OUT / 32; ++jb) {
+          if (!dh_valid(jb)) break;  // columns ascend: nothing valid follows
+          const int slot = (int)(dh_used % kDhSlots);
+          unsigned char* g_s = slots + (size_t)slot * 4096;
+          unsigned char* u_s = g_s + 2048;
+          const int c0 = jb * 32;
+          uint32_t v[32];
+          if (dh_full) {
+            if (!__all_sync(0xffffffffu, mbar_wait(&dh_bars[((warp - 2) & 3) * kDhSlots + slot],
+                                                   (dh_used / kDhSlots) & 1u, abort_flag)))
+              break;
+          } else {
+            // a block with fewer than 32 rows of the segment (segments not padded to 32 rows):
+            // the lane fetches its own row, and stores it itself below
             __syncwarp();
-            tmem_ld32(t_addr + c0, v);
-            tmem_ld_wait();
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
-              uint4* gp = reinterpret_cast<uint4*>(g_s + piece_smem(lane, q));
-              uint4* up = reinterpret_cast<uint4*>(u_s + piece_smem(lane, q));
-              const uint4 gv = *gp;
-              const uint4 uv = *up;
-              const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
-              const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
-              uint32_t dgw[4], duw[4];
-#pragma unroll
-              for (int pp = 0; pp < 4; ++pp) {
-                float r0[2], r1[2];
-#pragma unroll
-                for (int hh = 0; hh < 2; ++hh) {
-                  const float gval = hh ? bf16_hi(gw[pp]) : bf16_lo(gw[pp]);
-                  const float uval = hh ? bf16_hi(uw[pp]) : bf16_lo(uw[pp]);
-                  const float dh = __uint_as_float(v[q * 8 + pp * 2 + hh]);
-                  const float sg_ = __fdividef(1.0f, 1.0f + __expf(-gval));
-                  r0[hh] = dh * uval * (sg_ * (1.0f + gval * (1.0f - sg_)));  // dG
-                  r1[hh] = dh * gval * sg_;                                    // dU
-                }
-                dgw[pp] = pack_bf16(r0[0], r0[1]);
-                duw[pp] = pack_bf16(r1[0], r1[1]);
+              uint4 gv = make_uint4(0, 0, 0, 0), uv = make_uint4(0, 0, 0, 0);
+              if (lane < dh_rows_left && n0 + c0 + q * 8 < args.n_total) {
+                const size_t el = (size_t)(dh_row0 + lane) * args.n_total + n0 + c0 + q * 8;
+                gv = __ldg(reinterpret_cast<const uint4*>(args.save_g + el));
+                uv = __ldg(reinterpret_cast<const uint4*>(args.save_u + el));
               }
+              *reinterpret_cast<uint4*>(g_s + piece_smem(lane, q)) = gv;
+              *reinterpret_cast<uint4*>(u_s + piece_smem(lane, q)) = uv;
+            }
+          }
+          __syncwarp();
+          tmem_ld32(t_addr + c0, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4* gp = reinterpret_cast<uint4*>(g_s + piece_smem(lane, q));
+            uint4* up = reinterpret_cast<uint4*>(u_s + piece_smem(lane, q));
+            const uint4 gv = *gp;
+            const uint4 uv = *up;
+            const uint32_t gw[4] = {gv.x, gv.y, gv.z, gv.w};
+            const uint32_t uw[4] = {uv.x, uv.y, uv.z, uv.w};
+            uint32_t dgw[4], duw[4];
+#pragma unroll
+            for (int pp = 0; pp < 4; ++pp) {
+              float r0[2], r1[2];
+#pragma unroll
+              for (int hh = 0; hh < 2; ++hh) {
+                const float gval = hh ? bf16_hi(gw[pp]) : bf16_lo(gw[pp]);
+                const float uval = hh ? bf16_hi(uw[pp]) : bf16_lo(uw[pp]);
+                const float dh = __uint_as_float(v[q * 8 + pp * 2 + hh]);
+                const float sg_ = __fdividef(1.0f, 1.0f + __expf(-gval));
+                r0[hh] = dh * uval * (sg_ * (1.0f + gval * (1.0f - sg_)));  // dG
+                r1[hh] = dh * gval * sg_;                                    // dU
+              }
+              dgw[pp] = pack_bf16(r0[0], r0[1]);
+              duw[pp] = pack_bf16(r1[0], r1[1]);
+            }
+            if (dh_full) {
               *gp = make_uint4(dgw[0], dgw[1], dgw[2], dgw[3]);  // in place: the lane's own row
               *up = make_uint4(duw[0], duw[1], duw[2], duw[3]);
+            } else if (lane < dh_rows_left && n0 + c0 + q * 8 < args.n_total) {
+              const size_t el = (size_t)(dh_row0 + lane) * args.n_total + n0 + c0 + q * 8;
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out) + el) = make_uint4(dgw[0], dgw[1], dgw[2], dgw[3]);
+              *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out1) + el) = make_uint4(duw[0], duw[1], duw[2], duw[3]);
             }
+          }
+          if (dh_full) {
+            fence_proxy_async();  // the stores below read these bytes through the async proxy
             __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int p = lane + 32 * i;
-              if (piece_ok(p, c0)) {
-                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out) + piece_elem(p, c0)) =
-                    *reinterpret_cast<const uint4*>(g_s + piece_smem(p >> 2, p & 3));
-                *reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(args.out1) + piece_elem(p, c0)) =
-                    *reinterpret_cast<const uint4*>(u_s + piece_smem(p >> 2, p & 3));
+            if (lane == 0) {
+              // the slot two blocks ahead is the one block jb - 1 was stored from: that store
+              // was issued a whole block ago and has read its bytes
+              if (jb + 2 < BN_OUT / 32 && dh_valid(jb + 2)) {
+                bulk_wait_read();
+                dh_issue(jb + 2);
               }
+              tma_store_2d(&tm_dg, g_s, n0 + c0, dh_row0);
+              tma_store_2d(&tm_du, u_s, n0 + c0, dh_row0);
+              bulk_commit_group();
             }
+            ++dh_used;
           }
         }
       } else if (uc.live) {
@@ -470,6 +516,7 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    if (kDH && lane == 0) bulk_wait_all();  // the last dG / dU blocks have left shared memory
   }
 
   // ---- drain: nobody leaves while the peer may still touch its shared memory or TMEM -----
@@ -590,7 +637,8 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.save_g = static_cast<__nv_bfloat16*>(save_g);
   ga.save_u = static_cast<__nv_bfloat16*>(save_u);
   if (phases & 1) {
-    grouped_gemm_2sm_kernel<kModeSwiGLU><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, ga);
+    grouped_gemm_2sm_kernel<kModeSwiGLU><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a1, a1_alt, g, u, g_sh, u_sh, a1,
+                                                                                      a1, a1, a1, ga);
     if ((rc = check_launch("grouped_gemm_2sm_kernel<swiglu>"))) return rc;
   }
   if (between != nullptr) cudaEventRecord(between, st);
@@ -602,7 +650,8 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.save_u = nullptr;
   ga.out1 = nullptr;
   ga.two_term = exact ? 1 : 0;
-  grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2_lo, dn, dn, dn_sh, dn_sh, ga);
+  grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2_lo, dn, dn, dn_sh, dn_sh, a2,
+                                                                                  a2, a2, a2, ga);
   return check_launch("grouped_gemm_2sm_kernel<down>");
 }
 
@@ -617,7 +666,8 @@ static int map2_weights_kmajor(CUtensorMap* m, const void* base, uint64_t expert
 
 // dH = dO . Wd[e]^T with the SwiGLU derivative in the epilogue: dG, dU (bf16) from the saved g, u.
 // AXM_ERR_DEVICE when pairs cannot be scheduled, so that the caller can fall back.
-constexpr size_t kGemm2DhSmemBytes = kGemm2SmemBytes + 128 + 4 * 4096;
+constexpr size_t kGemm2DhSmemBytes = 1024 + (size_t)kStagesDh * kStageBytes2 + sizeof(GemmShared2) + 1024 +
+                                     (size_t)4 * kDhSlots * 4096 + 8 * 4 * kDhSlots;
 static_assert(kGemm2DhSmemBytes <= 227u * 1024u, "shared memory of the pair dH kernel");
 
 int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t num_segments,
@@ -631,10 +681,20 @@ int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   if (grid < 0) return grid;
   if (grid < 2) return fail(AXM_ERR_DEVICE, "two-SM clusters cannot be scheduled on this device");
   const int D = d->d_model, F = d->d_ff, E = d->num_experts;
-  CUtensorMap m_do, m_wd;
+  CUtensorMap m_do, m_wd, m_g, m_u, m_dg, m_du;
   int rc;
   if ((rc = map2_rows(&m_do, d_o, (uint64_t)rows_total, D))) return rc;
   if ((rc = map2_weights_kmajor(&m_wd, w_down, E, F, D))) return rc;
+  {
+    // 32 x 32 bf16 blocks of the [rows][F] tensors the epilogue reads and writes, 64-byte swizzle
+    const uint64_t dims[2] = {(uint64_t)F, (uint64_t)rows_total};
+    const uint64_t strides[1] = {(uint64_t)F * 2};
+    const uint32_t box[2] = {32, 32};
+    if ((rc = encode_tensor_map_sw64(&m_g, g, 2, dims, strides, box))) return rc;
+    if ((rc = encode_tensor_map_sw64(&m_u, u, 2, dims, strides, box))) return rc;
+    if ((rc = encode_tensor_map_sw64(&m_dg, d_g, 2, dims, strides, box))) return rc;
+    if ((rc = encode_tensor_map_sw64(&m_du, d_u, 2, dims, strides, box))) return rc;
+  }
   Gemm2Args ga;
   ga.segments = segments;
   ga.num_segments = num_segments;
@@ -650,7 +710,7 @@ int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.lo_off = 0;
   ga.two_term = 0;
   grouped_gemm_2sm_kernel<kModeDH><<<grid, kGemmThreads, kGemm2DhSmemBytes, st>>>(m_do, m_do, m_wd, m_wd, m_wd,
-                                                                                  m_wd, ga);
+                                                                                  m_wd, m_g, m_u, m_dg, m_du, ga);
   return check_launch("grouped_gemm_2sm_kernel<dH>");
 }
 
@@ -688,7 +748,7 @@ int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.lo_off = 0;
   ga.two_term = 0;
   grouped_gemm_2sm_kernel<kModeDX><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(m_dg, m_du, m_wg, m_wu, m_wg,
-                                                                                m_wu, ga);
+                                                                                m_wu, m_dg, m_dg, m_dg, m_dg, ga);
   return check_launch("grouped_gemm_2sm_kernel<dX>");
 }
 

@@ -318,13 +318,14 @@ class ExpertParallelMoeP2P:
             out = torch.empty_like(x)
         self.step += 1
         t = self.ep_tensors(x, out)
-        ms = (ctypes.c_float * 7)()
+        ms = (ctypes.c_float * 9)()
         check(self.lib.axm_moe_ep_forward_profiled(
             ctypes.byref(self.layout), ctypes.byref(self.desc_layer), ctypes.byref(t), ptr(self.workspace),
             self.workspace.numel(), self.step, current_stream(), ms))
         names = ["router", "permute + dispatch (peer stores)", "wait rows + segments", "gate/up GEMM",
                  "down GEMM (first half returning underneath)", "return of the second half",
-                 "wait return + combine"]
+                 "wait return + combine", "first half's return starts (after down GEMM start)",
+                 "first half's return ends (after down GEMM start)"]
         return out, dict(zip(names, list(ms)))
 
     def forward_host(self, h_x, h_out, d_x, d_out, chunks=2):
