@@ -127,7 +127,11 @@ AXM_API int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* tensors
  * RMSNorm at forward_pass.cu:404-461) but then adds the NORMALISED activations as the
  * residual and leaves the block's hidden state untouched; this entry point wires the
  * residual to the block input, which is what a pre-norm block means.  gamma is fp32 [D]
- * or NULL (ones).  x_norm is a caller buffer of T*D bf16 that receives RMSNorm(x). */
+ * or NULL (ones).  x_norm is a caller buffer of T*D bf16 that receives RMSNorm(x), or NULL:
+ * then the normalisation is folded into the reads of the router and of the permute kernel
+ * (one statistics pass stores 1/rms per token, nothing normalised is written to memory; same
+ * bits as the two-kernel form).  The folded form needs num_shared == 0 and a shape the
+ * tensor-core router serves (AXM_ERR_ARGUMENT otherwise).  eps > 0. */
 AXM_API int axm_moe_forward_prenorm(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
                                     const float* gamma, float eps, void* x_norm, void* workspace,
                                     size_t workspace_bytes, void* stream);

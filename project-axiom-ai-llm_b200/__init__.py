@@ -241,7 +241,8 @@ class MoeLayer:
         return out, self.histogram
 
     def forward_prenorm(self, x, gamma, eps, x_norm, out=None):
-        """out = x + MoE(RMSNorm(x)); x_norm receives the normalised activations."""
+        """out = x + MoE(RMSNorm(x)); x_norm receives the normalised activations (None: the
+        normalisation is folded into the router's and the permute kernel's reads)."""
         if out is None:
             out = torch.empty_like(x)
         t = self.tensors(x, out)

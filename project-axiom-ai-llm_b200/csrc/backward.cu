@@ -311,10 +311,6 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
   }
 }
 
-int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
-                   const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
-                   int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
-                   int32_t* status, cudaStream_t st, int row_align);
 int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
                       int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
                       const void* w_gate, const void* w_up, const void* w_down,

@@ -31,6 +31,15 @@ int ensure_dynamic_smem(const void* kernel, size_t bytes, SmemLimitCache* cache,
 int validate_route(const AxmMoeDesc* d);
 int validate_perm(const AxmMoeDesc* d);
 
+// The permute kernel (permute.cu).  segments / status optional; row_align > 1 pads every expert's
+// rows to that multiple with zero rows; norm_rstd / norm_gamma: pre-norm form, the rows written to
+// x_perm are bf16(x * norm_rstd[t] * gamma) (gamma NULL: ones).
+int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
+                   const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
+                   int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
+                   int32_t* status, cudaStream_t st, int row_align, const float* norm_rstd = nullptr,
+                   const float* norm_gamma = nullptr);
+
 #define AXM_CUDA(call)                                              \
   do {                                                              \
     if (int axm_rc_ = ::axm::cuda_status((call), #call)) return axm_rc_; \

@@ -510,9 +510,9 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   a.out0 = d_g;
   a.out1 = d_u;
   rc = AXM_ERR_DEVICE;
-  static const bool dh_pairs = [] {  // opt-in until it has run against the tests on hardware
+  static const bool dh_pairs = [] {  // CTA pairs with TMA-moved epilogue blocks by default; AXM_DH_2SM=0 opts out
     const char* e = getenv("AXM_DH_2SM");
-    return e != nullptr && e[0] == '1';
+    return !(e != nullptr && e[0] == '0');
   }();
   if (dh_pairs && use_2sm_kernels())
     rc = launch_bwd_dh_2sm(desc, segments, num_segments, rows_total, d_o, w_down, g, u, d_g, d_u, status, st);

@@ -107,10 +107,6 @@ int ensure_dynamic_smem(const void* kernel, size_t bytes, SmemLimitCache* cache,
   return AXM_OK;
 }
 
-int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
-                   const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
-                   int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
-                   int32_t* status, cudaStream_t st, int row_align);
 int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, const void* x_alt,
                       int32_t alt_rows, const AxmSegment* segments, int32_t num_segments,
                       const void* w_gate, const void* w_up, const void* w_down,
@@ -136,6 +132,7 @@ struct Workspace {
   void* o;
   void* router_scratch;  // split, transposed router weights of the tensor-core router (may be empty)
   size_t router_scratch_bytes;
+  float* rstd;           // [T] per-token 1/rms of the fused pre-norm call
   size_t bytes;
 };
 
@@ -165,6 +162,7 @@ static Workspace carve(const AxmMoeDesc* d, void* base) {
   w.router_scratch_bytes = 0;
   axm_moe_router_scratch_bytes(d, &w.router_scratch_bytes);
   w.router_scratch = take(w.router_scratch_bytes);
+  w.rstd = static_cast<float*>(take(sizeof(float) * T));
   w.bytes = off;
   return w;
 }
@@ -219,11 +217,17 @@ extern "C" int axm_moe_status_word(const AxmMoeDesc* desc, void* workspace, int3
   return AXM_OK;
 }
 
+static int launch_rms_stats(const void* x, float* rstd, int tokens, int d_model, float eps, cudaStream_t st);
+
 // residual_src: what the combine adds to y (t->x for the plain layer; the un-normalised
 // block input when x is the output of a preceding RMSNorm).
+// norm_gamma / norm_eps (norm_eps > 0): fused pre-norm form - t->x is the un-normalised block
+// input; one statistics pass stores 1/rms per token, the router and the permute kernel apply
+// the normalisation as they read x, nothing normalised is written to memory.
 static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* workspace,
                         size_t workspace_bytes, void* stream, cudaEvent_t* ev,
-                        const void* residual_src = nullptr) {
+                        const void* residual_src = nullptr, const float* norm_gamma = nullptr,
+                        float norm_eps = 0.0f) {
   if (int rc = validate_forward(desc)) return rc;
   if (t == nullptr) return fail(AXM_ERR_ARGUMENT, "tensors is null");
   if (desc->tokens == 0) return AXM_OK;  // empty input: nothing to enqueue
@@ -249,12 +253,26 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
 
   if (ev) cudaEventRecord(ev[0], st);
   bool router_cleared_status = false;  // the tensor-core router's preparation kernel clears the word
-  int rc = launch_router_auto(desc, t->x, t->router_w, t->router_bias, logits, idx, gate, w.block_counts,
-                              w.router_scratch, w.router_scratch_bytes, w.status, stream, &router_cleared_status);
+  int rc;
+  const float* rstd = nullptr;
+  if (norm_eps > 0.0f) {
+    const RouterTcPlan plan = router_tc_plan(desc);
+    if (!plan.ok || w.router_scratch_bytes < plan.scratch_bytes || (reinterpret_cast<uintptr_t>(t->x) & 15) != 0)
+      return fail(AXM_ERR_ARGUMENT, "the fused pre-norm form needs the tensor-core router (at most 80 experts with "
+                                    "fp32 router weights, 16-byte aligned x); pass x_norm to run the two-kernel form");
+    if ((rc = launch_rms_stats(t->x, w.rstd, T, desc->d_model, norm_eps, st))) return rc;
+    rstd = w.rstd;
+    rc = launch_router_tc(desc, plan, t->x, t->router_w, t->router_bias, logits, idx, gate, w.block_counts,
+                          w.router_scratch, w.status, st, rstd, norm_gamma);
+    router_cleared_status = true;
+  } else {
+    rc = launch_router_auto(desc, t->x, t->router_w, t->router_bias, logits, idx, gate, w.block_counts,
+                            w.router_scratch, w.router_scratch_bytes, w.status, stream, &router_cleared_status);
+  }
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[1], st);
   rc = launch_permute(desc, t->x, idx, w.block_counts, t->histogram, offsets, row_src, slot_dst,
-                      w.x_perm, w.segments, router_cleared_status ? nullptr : w.status, st, 1);
+                      w.x_perm, w.segments, router_cleared_status ? nullptr : w.status, st, 1, rstd, norm_gamma);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[2], st);
   rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
@@ -277,10 +295,13 @@ extern "C" int axm_moe_forward(const AxmMoeDesc* desc, const AxmMoeTensors* t, v
 
 // y[t, :] = bf16(x[t, :] * rsqrt(mean(x[t, :]^2) + eps) * gamma).  One warp per token:
 // the row stays in registers between the sum of squares and the scaling.
+// kWrite = false: only rstd[t] = rsqrt(mean(x[t]^2) + eps) is stored (same sum order, hence the
+// same bits, as in the writing form); the router and the permute kernel then apply it on load.
 constexpr int kNormMaxChunks = 16;  // 16-byte pieces per lane kept in registers (D <= 4096)
+template <bool kWrite>
 __global__ void __launch_bounds__(256)
 rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ gamma,
-               __nv_bfloat16* __restrict__ y, int T, int D, float eps) {
+               __nv_bfloat16* __restrict__ y, float* __restrict__ rstd_out, int T, int D, float eps) {
   const int lane = threadIdx.x & 31;
   const int warps = gridDim.x * (blockDim.x >> 5);
   const int chunks = D / 8;
@@ -311,6 +332,10 @@ rmsnorm_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ ga
 #pragma unroll
     for (int s = 16; s > 0; s >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, s);
     const float rstd = rsqrtf(ss / (float)D + eps);
+    if (!kWrite) {
+      if (lane == 0) rstd_out[t] = rstd;
+      continue;
+    }
     uint4* out = reinterpret_cast<uint4*>(y + (size_t)t * D);
     auto scale = [&](uint4 u, int c) {
       const uint32_t w4[4] = {u.x, u.y, u.z, u.w};
@@ -340,16 +365,33 @@ extern "C" int axm_moe_rmsnorm(const void* x, const float* gamma, void* y, int32
   if (int rc = require_device()) return rc;
   int blocks = (tokens + 7) / 8;
   if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
-  rmsnorm_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(y), tokens, d_model, eps);
+  rmsnorm_kernel<true><<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(x), gamma, static_cast<__nv_bfloat16*>(y), nullptr, tokens, d_model, eps);
   return check_launch("rmsnorm_kernel");
+}
+
+// rstd[t] alone (device buffer of `tokens` floats): the statistics pass of the fused pre-norm call.
+static int launch_rms_stats(const void* x, float* rstd, int tokens, int d_model, float eps, cudaStream_t st) {
+  int blocks = (tokens + 7) / 8;
+  if (blocks > 8 * sm_count()) blocks = 8 * sm_count();
+  rmsnorm_kernel<false><<<blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x), nullptr, nullptr, rstd, tokens,
+                                                d_model, eps);
+  return check_launch("rmsnorm_kernel(stats)");
 }
 
 extern "C" int axm_moe_forward_prenorm(const AxmMoeDesc* desc, const AxmMoeTensors* t, const float* gamma,
                                        float eps, void* x_norm, void* workspace, size_t workspace_bytes,
                                        void* stream) {
   if (int rc = validate_forward(desc)) return rc;
-  if (!t || !t->x || !x_norm) return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_prenorm: null pointer");
+  if (!t || !t->x) return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_prenorm: null pointer");
+  if (!(eps > 0.0f)) return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_prenorm: eps must be positive");
+  if (x_norm == nullptr) {
+    // fused form: the normalised activations are never written; shared experts would need them
+    // as a GEMM operand in memory
+    if (desc->num_shared > 0)
+      return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_prenorm without x_norm does not take shared experts");
+    return forward_impl(desc, t, workspace, workspace_bytes, stream, nullptr, t->x, gamma, eps);
+  }
   if (x_norm == t->out) return fail(AXM_ERR_ARGUMENT, "x_norm must not alias out");
   if (int rc = axm_moe_rmsnorm(t->x, gamma, x_norm, desc->tokens, desc->d_model, eps, stream)) return rc;
   AxmMoeTensors tt = *t;

@@ -29,7 +29,8 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
                int32_t* __restrict__ offsets, int32_t* __restrict__ row_src,
                int32_t* __restrict__ slot_dst, __nv_bfloat16* __restrict__ x_perm,
                AxmSegment* __restrict__ segments, int32_t* __restrict__ status, int T, int D,
-               int E, int k, int S, int hist_accumulate, int row_align) {
+               int E, int k, int S, int hist_accumulate, int row_align,
+               const float* __restrict__ norm_rstd, const float* __restrict__ norm_gamma) {
   __shared__ int total_s[kMaxE];
   __shared__ int run_s[kMaxE];   // next free row per expert for this block
   __shared__ int scan_s[kMaxE + 1];
@@ -155,6 +156,26 @@ permute_kernel(const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ 
             int c = c0 + j * 32 + lane;
             if (c < chunks) v[j] = __ldg(src + c);
           }
+          if (norm_rstd != nullptr) {
+            // pre-norm form: the rows dispatched are RMSNorm(x), formed here exactly as the
+            // RMSNorm kernel forms them, bf16(x * rstd * gamma)
+            const float rs = __ldg(norm_rstd + ts + tt);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int c = c0 + j * 32 + lane;
+              if (c < chunks) {
+                const uint32_t w4[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+                uint32_t r4[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                  const int d = c * 8 + 2 * q;
+                  const float g0 = norm_gamma ? __ldg(norm_gamma + d) : 1.0f, g1 = norm_gamma ? __ldg(norm_gamma + d + 1) : 1.0f;
+                  r4[q] = pack_bf16(bf16_lo(w4[q]) * rs * g0, bf16_hi(w4[q]) * rs * g1);
+                }
+                v[j] = make_uint4(r4[0], r4[1], r4[2], r4[3]);
+              }
+            }
+          }
           for (int i = 0; i < k; ++i) {
             uint4* dstp = reinterpret_cast<uint4*>(x_perm + (size_t)dst_s[tt * k + i] * D);
 #pragma unroll
@@ -279,12 +300,13 @@ static void launch_combine(int blocks, cudaStream_t st, const void* x, const voi
 int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
                    const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
                    int32_t* row_src, int32_t* slot_dst, void* x_perm, AxmSegment* segments,
-                   int32_t* status, cudaStream_t st, int row_align) {
+                   int32_t* status, cudaStream_t st, int row_align, const float* norm_rstd,
+                   const float* norm_gamma) {
   permute_kernel<<<AXM_ROUTE_BLOCKS, kPermThreads, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), topk_idx, block_counts, histogram, offsets, row_src,
       slot_dst, static_cast<__nv_bfloat16*>(x_perm), segments, status, d->tokens, d->d_model,
       d->num_experts, d->top_k, d->num_shared, (d->flags & AXM_FLAG_HIST_ACCUMULATE) ? 1 : 0,
-      row_align < 1 ? 1 : row_align);
+      row_align < 1 ? 1 : row_align, norm_rstd, norm_gamma);
   return check_launch("permute_kernel");
 }
 
@@ -315,7 +337,7 @@ extern "C" int axm_moe_permute(const AxmMoeDesc* desc, const void* x, const int3
   if (x_perm != nullptr && x == nullptr) return fail(AXM_ERR_ARGUMENT, "axm_moe_permute: x_perm without x");
   if (int rc = require_device()) return rc;
   return launch_permute(desc, x, topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
-                        x_perm, nullptr, nullptr, static_cast<cudaStream_t>(stream), 1);
+                        x_perm, nullptr, nullptr, static_cast<cudaStream_t>(stream), 1, nullptr, nullptr);
 }
 
 extern "C" int axm_moe_permute_padded(const AxmMoeDesc* desc, const void* x, const int32_t* topk_idx,
@@ -329,7 +351,7 @@ extern "C" int axm_moe_permute_padded(const AxmMoeDesc* desc, const void* x, con
   if (row_align < 1 || row_align > 1024) return fail(AXM_ERR_ARGUMENT, "row_align %d not in 1..1024", row_align);
   if (int rc = require_device()) return rc;
   return launch_permute(desc, x, topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
-                        x_perm, segments, nullptr, static_cast<cudaStream_t>(stream), row_align);
+                        x_perm, segments, nullptr, static_cast<cudaStream_t>(stream), row_align, nullptr, nullptr);
 }
 
 extern "C" int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* offsets,

@@ -74,8 +74,11 @@ RouterTcPlan router_tc_plan(const AxmMoeDesc* d);
 int launch_router_auto(const AxmMoeDesc* desc, const void* x, const void* router_w, const float* router_bias,
                        float* logits, int32_t* topk_idx, float* topk_gate, int32_t* block_counts,
                        void* scratch, size_t scratch_bytes, int32_t* status, void* stream, bool* used_tc);
+// norm_rstd / norm_gamma: pre-norm form (the router sees bf16(x * rstd[t] * gamma) without it
+// being materialised); both NULL for the plain form.
 int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, const void* router_w,
                      const float* bias, float* logits, int32_t* idx, float* gate, int32_t* block_counts,
-                     void* scratch, int32_t* status, cudaStream_t st);
+                     void* scratch, int32_t* status, cudaStream_t st, const float* norm_rstd = nullptr,
+                     const float* norm_gamma = nullptr);
 
 }  // namespace axm

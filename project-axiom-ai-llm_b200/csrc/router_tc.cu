@@ -60,6 +60,13 @@ struct __align__(8) RouterTcShared {
 };
 
 struct RouterTcArgs {
+  // Pre-norm form: the router sees RMSNorm(x) without anybody having written it to memory.
+  // norm_rstd[t] = rsqrt(mean(x[t]^2) + eps); the epilogue warps then load x themselves,
+  // form bf16(x * rstd * gamma) exactly as the RMSNorm kernel does and store it in the layout
+  // the tensor core reads; the TMA producer only brings the weight tiles.  NULL: x by TMA.
+  const __nv_bfloat16* x;
+  const float* norm_rstd;
+  const float* norm_gamma;  // [D] or NULL (ones)
   const float* bias;
   float* logits_out;
   int32_t* topk_idx;
@@ -198,7 +205,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < a.stages; ++i) {
-      mbar_init(&sh->full[i], 1);
+      mbar_init(&sh->full[i], a.norm_rstd != nullptr ? 129 : 1);  // + the 128 loading threads
       mbar_init(&sh->empty[i], 1);
     }
     mbar_init(&sh->tmem_full, 1);
@@ -223,7 +230,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
     tmem_base = sh->tmem_base;
   }
   volatile int* abort_flag = &sh->abort_flag;
-  const uint32_t stage_tx = (uint32_t)(kRtABytes + a.n_cols * BK * 2);
+  const bool by_warps = a.norm_rstd != nullptr;  // activation tiles produced by the epilogue warps
+  const uint32_t stage_tx = (uint32_t)((by_warps ? 0 : kRtABytes) + a.n_cols * BK * 2);
 
   if (warp == 0) {
     // ---- TMA producer -----------------------------------------------------------------
@@ -233,7 +241,8 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
       const int early = min(a.stages, kb_count);
       for (int i = 0; i < early; ++i) {
         mbar_expect_tx(&sh->full[i], stage_tx);
-        tma_load_2d(tiles + (size_t)i * a.stage_bytes, &tm_x, &sh->full[i], ((int)rank + i * CS) * BK, row0);
+        if (!by_warps)
+          tma_load_2d(tiles + (size_t)i * a.stage_bytes, &tm_x, &sh->full[i], ((int)rank + i * CS) * BK, row0);
       }
       griddep_wait();
       for (int i = 0; i < early; ++i)
@@ -244,7 +253,7 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
         if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) break;
         unsigned char* sa = tiles + (size_t)stage * a.stage_bytes;
         mbar_expect_tx(&sh->full[stage], stage_tx);
-        tma_load_2d(sa, &tm_x, &sh->full[stage], ((int)rank + i * CS) * BK, row0);
+        if (!by_warps) tma_load_2d(sa, &tm_x, &sh->full[stage], ((int)rank + i * CS) * BK, row0);
         tma_load_2d(sa + kRtABytes, &tm_b, &sh->full[stage], ((int)rank + i * CS) * BK, 0);
         if (++stage == a.stages) {
           stage = 0;
@@ -282,6 +291,57 @@ router_tc_kernel(const __grid_constant__ CUtensorMap tm_x, const __grid_constant
   }
 
   if (warp >= 2) {
+    // ---- pre-norm form: these warps produce the activation tiles -----------------------------
+    // A row's 128 bytes of a k-block are loaded by eight neighbouring lanes (16 bytes each),
+    // scaled and rounded like the RMSNorm kernel, and stored with the 128-byte swizzle of the
+    // tensor-core layout: 16-byte piece c of row r at r * 128 + ((c ^ (r & 7)) * 16).
+    if (by_warps) {
+      const int lt = (warp - 2) * 32 + lane;
+      const int c = lt & 7, rsub = lt >> 3;  // piece of the row, row within a group of 16
+      const int chunks = a.D / 8;
+      float rstd[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int r = row0 + rsub + 16 * j;
+        rstd[j] = r < a.T ? __ldg(a.norm_rstd + r) : 0.0f;
+      }
+      auto fetch = [&](int i, uint4 (&v)[8]) {
+        const int piece = ((int)rank + i * CS) * 8 + c;  // 16-byte piece index inside a row of x
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = row0 + rsub + 16 * j;
+          v[j] = make_uint4(0, 0, 0, 0);
+          if (r < a.T && piece < chunks) v[j] = __ldg(reinterpret_cast<const uint4*>(a.x + (size_t)r * a.D) + piece);
+        }
+      };
+      uint4 cur[8], nxt[8];
+      if (kb_count > 0) fetch(0, cur);
+      for (int i = 0; i < kb_count; ++i) {
+        if (i + 1 < kb_count) fetch(i + 1, nxt);
+        const int stage = i % a.stages;
+        const uint32_t use = (uint32_t)(i / a.stages);
+        if (!__all_sync(0xffffffffu, mbar_wait(&sh->empty[stage], (use & 1u) ^ 1u, abort_flag))) break;
+        unsigned char* sa = tiles + (size_t)stage * a.stage_bytes;
+        const int d0 = (((int)rank + i * CS) * 8 + c) * 8;  // first of this lane's eight columns
+        float gm[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) gm[q] = (a.norm_gamma != nullptr && d0 + q < a.D) ? __ldg(a.norm_gamma + d0 + q) : 1.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = rsub + 16 * j;
+          const uint32_t w4[4] = {cur[j].x, cur[j].y, cur[j].z, cur[j].w};
+          uint32_t o4[4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            o4[q] = pack_bf16(bf16_lo(w4[q]) * rstd[j] * gm[2 * q], bf16_hi(w4[q]) * rstd[j] * gm[2 * q + 1]);
+          *reinterpret_cast<uint4*>(sa + r * 128 + ((c ^ (r & 7)) << 4)) = make_uint4(o4[0], o4[1], o4[2], o4[3]);
+        }
+        fence_proxy_async();  // the tensor core reads these bytes through the async proxy
+        mbar_arrive(&sh->full[stage]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+      }
+    }
     // ---- epilogue: 128 threads, thread = accumulator row ----------------------------------
     const int quad = warp & 3;
     bool acc_ok = true;
@@ -454,7 +514,8 @@ static int launch_router_tc_cs(const RouterTcPlan& p, const CUtensorMap& mx, con
 // Returns AXM_OK after enqueueing the preparation and router kernels.
 int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, const void* router_w,
                      const float* bias, float* logits, int32_t* idx, float* gate, int32_t* block_counts,
-                     void* scratch, int32_t* status, cudaStream_t st) {
+                     void* scratch, int32_t* status, cudaStream_t st, const float* norm_rstd,
+                     const float* norm_gamma) {
   const int T = d->tokens, D = d->d_model, E = d->num_experts;
   CUtensorMap mx, mb;
   {
@@ -483,6 +544,9 @@ int launch_router_tc(const AxmMoeDesc* d, const RouterTcPlan& p, const void* x, 
                                                               status, D, E, p.epad, n_counts);
   if (int rc = check_launch("router_prep_kernel")) return rc;
   RouterTcArgs a;
+  a.x = static_cast<const __nv_bfloat16*>(x);
+  a.norm_rstd = norm_rstd;
+  a.norm_gamma = norm_gamma;
   a.bias = bias;
   a.logits_out = logits;
   a.topk_idx = idx;

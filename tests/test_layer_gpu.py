@@ -298,3 +298,12 @@ def test_prenorm_call_site(axm, workloads, oracle, cuda_device, name, tokens, wi
     out_ref = (x.cpu()[lo:hi].float() + y_ref[lo:hi].float()).bfloat16()   # residual = block input
     helpers.assert_close_out(out[lo:hi], out_ref, y_ref[lo:hi], what="out = x + MoE(RMSNorm(x))")
     assert not torch.equal(out[lo:hi].cpu(), (xc[lo:hi].float() + y_ref[lo:hi].float()).bfloat16())
+    # the folded form (no x_norm buffer: one statistics pass, the normalisation applied as the
+    # router and the permute kernel read x) gives the same bits as the two-kernel form
+    logits2, idx2, gate2 = layer.logits.clone(), layer.topk_idx.clone(), layer.topk_gate.clone()
+    y2 = layer.y.clone()
+    out_f = layer.forward_prenorm(x, gamma, eps, None)
+    assert layer.status() == 0
+    assert torch.equal(layer.logits.view(torch.int32), logits2.view(torch.int32))
+    assert torch.equal(layer.topk_idx, idx2) and torch.equal(layer.topk_gate.view(torch.int32), gate2.view(torch.int32))
+    assert torch.equal(layer.y, y2) and torch.equal(out_f, out)
