@@ -297,6 +297,8 @@ typedef struct AxmMoeTrain {
   float* d_w_gate;          /* [E][D][F] fp32; the three expert gradients together or none */
   float* d_w_up;            /* [E][D][F] fp32 */
   float* d_w_down;          /* [E][F][D] fp32 */
+  float* d_router_bias;     /* [E] fp32 gradient of router_bias (sum over tokens of the logit
+                             * gradients), optional; NULL leaves the bias untrained */
 } AxmMoeTrain;
 
 AXM_API int axm_moe_train_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes);

@@ -70,7 +70,7 @@ class MoeTrain(ctypes.Structure):
                                                 "w_down", "out", "aux_loss", "histogram")] +
                 [("aux_alpha", ctypes.c_float)] +
                 [(n, ctypes.c_void_p) for n in ("d_out", "d_x", "d_router_w", "d_w_gate", "d_w_up",
-                                                "d_w_down")])
+                                                "d_w_down", "d_router_bias")])
 
 
 class MoeCheckpoint(ctypes.Structure):
@@ -304,6 +304,8 @@ class MoeTrainLayer:
         self.histogram = torch.zeros(E, dtype=torch.int32, device=dev)
         self.d_x = torch.empty(tokens, D, dtype=f32, device=dev)
         self.d_router_w = torch.empty(D, E, dtype=f32, device=dev)
+        self.d_router_bias = (torch.empty(E, dtype=f32, device=dev)
+                              if weights.get("router_bias") is not None else None)
         self.weight_grads = weight_grads
         if weight_grads:
             self.d_w_gate = torch.empty(E, D, F, dtype=f32, device=dev)
@@ -321,7 +323,8 @@ class MoeTrainLayer:
             self.out.data_ptr(), self.aux.data_ptr(), self.histogram.data_ptr(), self.aux_alpha,
             None if d_out is None else d_out.data_ptr(), self.d_x.data_ptr(),
             self.d_router_w.data_ptr(), self.d_w_gate.data_ptr() if g else None,
-            self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None)
+            self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None,
+            None if self.d_router_bias is None else self.d_router_bias.data_ptr())
 
     def forward(self, x):
         t = self.tensors(x, None)
@@ -340,6 +343,8 @@ class MoeTrainLayer:
         self.forward(x)
         self.backward(x, d_out)
         grads = {"d_x": self.d_x, "d_router_w": self.d_router_w}
+        if self.d_router_bias is not None:
+            grads["d_router_bias"] = self.d_router_bias
         if self.weight_grads:
             grads.update(d_w_gate=self.d_w_gate, d_w_up=self.d_w_up, d_w_down=self.d_w_down)
         return self.out, self.aux, grads

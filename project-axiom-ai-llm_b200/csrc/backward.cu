@@ -154,6 +154,29 @@ router_bwd_kernel(const float* __restrict__ logits, const int32_t* __restrict__ 
   for (int e = 0; e < E; ++e) dz[(size_t)t * E + e] = p[e] * (dp[e] - pd);
 }
 
+// Gradient of the router bias: d_bias[e] = sum_t dz[t, e] (the bias is added to the logits).
+// Two passes with a fixed order: kBiasChunks blocks sum their token ranges, one block adds the
+// partial sums in chunk order.  Deterministic.
+constexpr int kBiasChunks = 64;
+__global__ void __launch_bounds__(256)
+dbias_partial_kernel(const float* __restrict__ dz, float* __restrict__ partial, int T, int E) {
+  const int c = blockIdx.x;
+  const int t0 = (int)(((long long)c * T) / kBiasChunks), t1 = (int)(((long long)(c + 1) * T) / kBiasChunks);
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float acc = 0.0f;
+    for (int t = t0; t < t1; ++t) acc += dz[(size_t)t * E + e];
+    partial[(size_t)c * E + e] = acc;
+  }
+}
+__global__ void __launch_bounds__(256)
+dbias_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_bias, int E) {
+  for (int e = threadIdx.x; e < E; e += blockDim.x) {
+    float acc = 0.0f;
+    for (int c = 0; c < kBiasChunks; ++c) acc += partial[(size_t)c * E + e];
+    d_bias[e] = acc;
+  }
+}
+
 // dWr[d, e] = sum_t x[t, d] * dz[t, e].  grid (ceil(D / 128), chunks): a thread owns one d
 // and sums its chunk of tokens in order into partial[chunk][d][e]; dwr_reduce adds the
 // chunks in order.  Deterministic.
@@ -504,6 +527,12 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
     return rc;
   router_bwd_kernel<<<(T + rb_threads - 1) / rb_threads, rb_threads, sm, st>>>(
       w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, T, E, k);
+  if (t->d_router_bias != nullptr) {
+    // the auxiliary-loss partial sums of the forward pass are no longer needed: their room
+    // ([296][E] floats) holds the [64][E] partial sums
+    dbias_partial_kernel<<<kBiasChunks, 256, 0, st>>>(w.dz, w.aux_partial, T, E);
+    dbias_reduce_kernel<<<1, 256, 0, st>>>(w.aux_partial, t->d_router_bias, E);
+  }
   if (t->d_router_w != nullptr) {
     dim3 grid((D + 127) / 128, kDwrChunks);
     dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), w.dz,

@@ -127,3 +127,29 @@ def test_full_size_c5_step_matches_oracle(axm, workloads, oracle, cuda_device):
     lo, hi = 4000, 4064
     y_ref, out_ref = oracle.forward(x, w, idx, gates, h_bf16=True, tok_range=(lo, hi))
     helpers.assert_close_out(out[lo:hi], out_ref[lo:hi], y_ref[lo:hi], what="training forward out (slice)")
+
+
+def test_router_bias_is_trained(axm, workloads, oracle, cuda_device):
+    """With a router bias (added to the logits before the softmax) the backward pass also
+    returns its gradient, the sum over tokens of the logit gradients; the other gradients see
+    the bias through the routing and the probabilities."""
+    cfg = workloads.scaled(workloads.CONFIGS["C4"], tokens=200, d_model=128, d_ff=256, num_experts=16, top_k=3,
+                           num_shared=0)
+    alpha = 0.01
+    x, w = workloads.make_inputs(cfg)
+    assert w.get("router_bias") is not None
+    dY = torch.randn(cfg.tokens, cfg.d_model, generator=torch.Generator().manual_seed(11))
+    wd = helpers.to_dev(w, cuda_device)
+    layer = axm.MoeTrainLayer(wd, cfg.tokens, cfg.top_k, aux_alpha=alpha)
+    xd, dYd = x.to(cuda_device), dY.to(cuda_device)
+    out, aux, grads = layer.step(xd, dYd)
+    torch.cuda.synchronize()
+    desc = axm.make_desc(cfg.tokens, cfg.d_model, cfg.d_ff, cfg.num_experts, cfg.top_k)
+    logits, idx_d, gate_d, _ = helpers.run_router(axm, desc, xd, wd["router_w"], wd["router_bias"])
+    zl = logits.cpu().numpy()
+    idx, gates = idx_d.cpu().numpy(), gate_d.cpu().numpy()
+    _, _, probs, _, _ = oracle.route(zl, cfg.top_k)
+    ref = oracle.backward(x, w, idx, gates, probs, dY.numpy(), alpha=alpha)
+    close(grads["d_router_bias"], ref["dlogits"].sum(0), "d_router_bias")
+    close(grads["d_router_w"], ref["dWr"], "dWr with a router bias")
+    close(grads["d_x"].cpu() - dY, ref["dX"] - dY.numpy(), "dX with a router bias")
