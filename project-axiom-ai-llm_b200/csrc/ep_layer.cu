@@ -1,8 +1,9 @@
 // The expert-parallel layer behind the C ABI: one call per rank and layer enqueues
 //   router -> permute + dispatch (rows stored straight into the owners' receive buffers)
-//   -> segment tables -> gate/up GEMM -> down GEMM in two halves, the first half's rows
-//   travelling back to their source ranks while the second half is computed
-//   -> wait for the rows coming back -> combine.
+//   -> segment tables -> gate/up GEMM -> down GEMM -> return of the expert rows to their
+//   source ranks -> wait for the rows coming back -> combine.
+// (Optionally the down GEMM runs in two halves with the first half's rows travelling back
+// while the second half is computed; see split_return below.)
 // The reference engine is single-GPU (no communication library anywhere in core/src); this is
 // the sharded form of its forward_mixture_experts (core/src/CUDA/kernel/moe_router.cu:205-320)
 // with the host logic in C++: validation before any launch, caller-provided workspace, all
@@ -181,7 +182,11 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   if (int rc = require_device()) return rc;
 
   static const int fused_dispatch = env_flag("AXM_EP_FUSED_DISPATCH", 1);
-  static const int split_return = env_flag("AXM_EP_SPLIT_RETURN", 1);
+  // Off by default.  Measured on 8 GPUs (T 8192, D 4096, E 8, F 14336): the first half's copy
+  // does run under the second half's GEMM (98 - 135 us after the down projection starts), but two
+  // launches of 64 tile pairs on 74 CTA pairs take 205 us where one launch of 128 takes 180, and
+  // the ranks drift further apart: 0.774 ms per step against 0.690.  AXM_EP_SPLIT_RETURN=1 enables it.
+  static const int split_return = env_flag("AXM_EP_SPLIT_RETURN", 0);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k, S = desc->num_shared;
   const int G = layout->world, El = E / G;
