@@ -255,8 +255,9 @@ def main():
                     help="override the workload's token count (e.g. 16 for a decode-sized batch)")
     ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
-    ap.add_argument("--ep-host-chunks", type=int, default=2,
-                    help="N > 1: parts the host-buffer call cuts each rank's tokens into")
+    ap.add_argument("--ep-host-chunks", type=int, default=1,
+                    help="N > 1: parts the host-buffer call cuts each rank's tokens into (every part is a "
+                         "whole exchange step, whose fixed cost outweighs the hidden copies at 8 GPUs)")
     ap.add_argument("--ep-stages", action="store_true",
                     help="p2p transport: the stage-by-stage sequence from Python instead of axm_moe_ep_forward")
     ap.add_argument("--ep-return", default="copy", choices=["fused", "copy"],
@@ -327,10 +328,10 @@ def main():
         out = torch.empty_like(x_local)
         step = lambda: layer.forward(x_local, out)
         # p2p behind axm_moe_ep_forward: router (+ its preparation kernel), permute fused with the
-        # dispatch, segment tables, gate/up GEMM, down GEMM in two halves, two return copies, wait,
-        # combine.  nccl: router, permute, two GEMMs, combine plus library collectives.
+        # dispatch, segment tables, gate/up GEMM, down GEMM, return copy, wait, combine.
+        # nccl: router, permute, two GEMMs, combine plus library collectives.
         c_layer = getattr(layer, "c_layer", False)
-        launches_per_step = (10 if c_layer else (9 if args.ep_transport == "p2p" else 5)) + \
+        launches_per_step = (8 if c_layer else (9 if args.ep_transport == "p2p" else 5)) + \
             (1 if axm.router_scratch_bytes(layer.desc_route) else 0)
     del x
     torch.cuda.empty_cache()
@@ -426,7 +427,7 @@ def main():
     elif world == 1:
         e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out)
     elif getattr(layer, "c_layer", False):
-        # host buffers through axm_moe_ep_forward_host: two pipelined parts per rank
+        # host buffers through axm_moe_ep_forward_host
         e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out, chunks=args.ep_host_chunks)
     else:
         def e2e_step():

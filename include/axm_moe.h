@@ -487,11 +487,11 @@ AXM_API int axm_ep_wait_return(const AxmEpLayout* layout, uint32_t step, int32_t
 /* ---- the expert-parallel layer as one call ------------------------------------------
  * axm_moe_ep_forward runs, for this rank's tokens (desc->tokens = T_local; desc->num_experts
  * = E over all ranks), router -> permute fused with the dispatch (rows are stored straight
- * into the owners' receive buffers) -> segment tables -> gate/up GEMM -> down GEMM in two
- * halves, the rows of the first half returning to their source ranks while the second half
- * is computed -> wait for the returned rows -> combine.  Everything is enqueued on `stream`
- * (plus an internal side stream for the overlapped return, joined before the call's last
- * kernels); no host synchronisation.  `layout` as for the stage calls, with local_region set;
+ * into the owners' receive buffers) -> segment tables -> gate/up GEMM -> down GEMM -> return
+ * of the expert rows -> wait for the returned rows -> combine.  Everything is enqueued on
+ * `stream`; no host synchronisation.  (With AXM_EP_SPLIT_RETURN=1 in the environment the down
+ * GEMM runs in two halves and the first half's rows return on an internal side stream while
+ * the second half is computed; measured slower on 8 GPUs, so it is off by default.)  `layout` as for the stage calls, with local_region set;
  * layout->slots and cap are what the regions were SIZED for, the call may carry fewer tokens.
  * `step` starts at 1 and grows by one per call on every rank alike.
  * The workspace is private to the rank; its first *zero_bytes bytes must be zero before the
@@ -528,8 +528,8 @@ AXM_API int axm_moe_ep_status_word(const AxmEpLayout* layout, const AxmMoeDesc* 
                                    int32_t** status, int32_t** rows_received);
 /* axm_moe_ep_forward with CUDA events between its phases; synchronises the stream and returns
  * device times in milliseconds: router, permute + dispatch, wait for rows + segment
- * tables, gate/up GEMM, down GEMM (both halves; the first half's return runs underneath),
- * return of the second half, wait for returned rows + combine; stage_ms[7] and [8] are the
+ * tables, gate/up GEMM, down GEMM, return copy (of the second half when the return is
+ * split), wait for returned rows + combine; stage_ms[7] and [8] are the
  * start and the end of the first half's return copy (side stream), counted from the start
  * of the down GEMM (both 0 when the return is not split).  stage_ms holds 9 floats.  A
  * measuring aid. */

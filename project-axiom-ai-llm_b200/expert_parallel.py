@@ -200,9 +200,8 @@ class ExpertParallelMoeP2P:
                  fused_return=False, c_layer=True, h_exact=False):
         import torch.distributed._symmetric_memory as symm_mem
         self.fused_return = fused_return
-        # c_layer: the whole call behind axm_moe_ep_forward (permute fused with the dispatch,
-        # return overlapped with the second half of the down projection); otherwise the
-        # stage-by-stage sequence below, which the fused-return variant also uses
+        # c_layer: the whole call behind axm_moe_ep_forward (permute fused with the dispatch);
+        # otherwise the stage-by-stage sequence below, which the fused-return variant also uses
         self.c_layer = c_layer and not fused_return
         self.lib = load()
         self.group = group if group is not None else dist.group.WORLD
@@ -323,12 +322,14 @@ class ExpertParallelMoeP2P:
             ctypes.byref(self.layout), ctypes.byref(self.desc_layer), ctypes.byref(t), ptr(self.workspace),
             self.workspace.numel(), self.step, current_stream(), ms))
         names = ["router", "permute + dispatch (peer stores)", "wait rows + segments", "gate/up GEMM",
-                 "down GEMM (first half returning underneath)", "return of the second half",
-                 "wait return + combine", "first half's return starts (after down GEMM start)",
-                 "first half's return ends (after down GEMM start)"]
-        return out, dict(zip(names, list(ms)))
+                 "down GEMM", "return (peer stores)", "wait return + combine"]
+        stages = dict(zip(names, list(ms)[:7]))
+        if ms[8] > 0:   # the split return (AXM_EP_SPLIT_RETURN=1): when the first half's copy ran
+            stages["first half's return: start after down GEMM start"] = ms[7]
+            stages["first half's return: end after down GEMM start"] = ms[8]
+        return out, stages
 
-    def forward_host(self, h_x, h_out, d_x, d_out, chunks=2):
+    def forward_host(self, h_x, h_out, d_x, d_out, chunks=1):
         """Activations in pinned host memory, copies pipelined with the exchange steps; synchronises."""
         assert self.c_layer
         t = self.ep_tensors(d_x, d_out)

@@ -68,7 +68,7 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
                 layer.forward_host(h_x, h_out, d_x, d_out, chunks=chunks)
                 assert torch.equal(h_out, out.cpu()), f"host call in {chunks} part(s)"
             out3, ms = layer.forward_profiled(x_local)
-            assert torch.equal(out3, out) and len(ms) == 9
+            assert torch.equal(out3, out) and len(ms) >= 7
             layer.check_status()
         if rank == 0:
             single = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
