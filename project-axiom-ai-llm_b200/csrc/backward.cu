@@ -177,70 +177,84 @@ dbias_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_bia
   }
 }
 
-// dWr[d, e] = sum_t x[t, d] * dz[t, e].  grid (ceil(D / 128), chunks): a thread owns one d
-// and sums its chunk of tokens in order into partial[chunk][d][e]; dwr_reduce adds the
-// chunks in order.  Deterministic.
+// dWr[d, e] = sum_t x[t, d] * dz[t, e].  grid (ceil(D / 256), chunks): a thread sums its chunk of
+// tokens in order; dwr_reduce adds the chunks in order.  Deterministic.
 constexpr int kDwrChunks = 128;
+// A thread owns two adjacent d (one 4-byte load per token, a warp reads 128 contiguous bytes of the
+// row) and EC experts; eight tokens per trip keep eight loads in flight.  The partial sums are laid
+// out [chunk][e][d], so that neighbouring threads write neighbouring words.
 template <int EC>
 __global__ void __launch_bounds__(128)
 dwr_partial_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ dz,
                    float* __restrict__ partial, int T, int D, int E) {
-  const int d = blockIdx.x * 128 + threadIdx.x;
+  const int d = (blockIdx.x * 128 + threadIdx.x) * 2;
   const int c = blockIdx.y;
   const int t0 = (int)(((long long)c * T) / kDwrChunks), t1 = (int)(((long long)(c + 1) * T) / kDwrChunks);
+  if (d >= D) return;  // D is a multiple of 8: a thread's two columns are both inside or both outside
   for (int e0 = 0; e0 < E; e0 += EC) {
-    float acc[EC];
+    float acc0[EC], acc1[EC];
 #pragma unroll
-    for (int j = 0; j < EC; ++j) acc[j] = 0.0f;
-    if (d < D) {
-      // four tokens per trip: their activation loads are independent and overlap; the
-      // token's logit gradients (the same address for the whole warp) come as float4
-      int t = t0;
-      const bool vec = (E & 3) == 0 && e0 + EC <= E;
-      for (; t + 3 < t1; t += 4) {
-        float xv[4];
+    for (int j = 0; j < EC; ++j) acc0[j] = acc1[j] = 0.0f;
+    const bool vec = (E & 3) == 0 && e0 + EC <= E;
+    int t = t0;
+    for (; t + 7 < t1; t += 8) {
+      uint32_t xv[8];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) xv[q] = __bfloat162float(x[(size_t)(t + q) * D + d]);
+      for (int q = 0; q < 8; ++q) xv[q] = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)(t + q) * D + d));
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float* z = dz + (size_t)(t + q) * E + e0;
-          if (vec) {
+      for (int q = 0; q < 8; ++q) {
+        const float x0 = bf16_lo(xv[q]), x1 = bf16_hi(xv[q]);
+        const float* z = dz + (size_t)(t + q) * E + e0;
+        if (vec) {
 #pragma unroll
-            for (int j4 = 0; j4 < EC / 4; ++j4) {
-              const float4 zz = __ldg(reinterpret_cast<const float4*>(z) + j4);
-              acc[4 * j4 + 0] = fmaf(xv[q], zz.x, acc[4 * j4 + 0]);
-              acc[4 * j4 + 1] = fmaf(xv[q], zz.y, acc[4 * j4 + 1]);
-              acc[4 * j4 + 2] = fmaf(xv[q], zz.z, acc[4 * j4 + 2]);
-              acc[4 * j4 + 3] = fmaf(xv[q], zz.w, acc[4 * j4 + 3]);
+          for (int j4 = 0; j4 < EC / 4; ++j4) {
+            const float4 zz = __ldg(reinterpret_cast<const float4*>(z) + j4);
+            const float zv[4] = {zz.x, zz.y, zz.z, zz.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              acc0[4 * j4 + i] = fmaf(x0, zv[i], acc0[4 * j4 + i]);
+              acc1[4 * j4 + i] = fmaf(x1, zv[i], acc1[4 * j4 + i]);
             }
-          } else {
-#pragma unroll
-            for (int j = 0; j < EC; ++j)
-              if (e0 + j < E) acc[j] = fmaf(xv[q], __ldg(z + j), acc[j]);
           }
+        } else {
+#pragma unroll
+          for (int j = 0; j < EC; ++j)
+            if (e0 + j < E) {
+              const float zv = __ldg(z + j);
+              acc0[j] = fmaf(x0, zv, acc0[j]);
+              acc1[j] = fmaf(x1, zv, acc1[j]);
+            }
         }
       }
-      for (; t < t1; ++t) {
-        const float xv = __bfloat162float(x[(size_t)t * D + d]);
-        const float* z = dz + (size_t)t * E + e0;
-#pragma unroll
-        for (int j = 0; j < EC; ++j)
-          if (e0 + j < E) acc[j] = fmaf(xv, __ldg(z + j), acc[j]);
-      }
     }
-    if (d < D)
+    for (; t < t1; ++t) {
+      const uint32_t xv = __ldg(reinterpret_cast<const uint32_t*>(x + (size_t)t * D + d));
+      const float x0 = bf16_lo(xv), x1 = bf16_hi(xv);
+      const float* z = dz + (size_t)t * E + e0;
 #pragma unroll
       for (int j = 0; j < EC; ++j)
-        if (e0 + j < E) partial[((size_t)c * D + d) * E + e0 + j] = acc[j];
+        if (e0 + j < E) {
+          const float zv = __ldg(z + j);
+          acc0[j] = fmaf(x0, zv, acc0[j]);
+          acc1[j] = fmaf(x1, zv, acc1[j]);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < EC; ++j)
+      if (e0 + j < E)
+        *reinterpret_cast<float2*>(partial + ((size_t)c * E + e0 + j) * D + d) = make_float2(acc0[j], acc1[j]);
   }
 }
 
-__global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_wr, int n) {
+// d_wr[d][e] = sum over the chunks, in chunk order, of partial[chunk][e][d].
+__global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_wr, int D, int E) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
+  if (i >= D * E) return;
+  const int e = i / D, d = i - e * D;
   float acc = 0.0f;
-  for (int c = 0; c < kDwrChunks; ++c) acc += partial[(size_t)c * n + i];
-  d_wr[i] = acc;
+#pragma unroll 16
+  for (int c = 0; c < kDwrChunks; ++c) acc += __ldg(partial + ((size_t)c * E + e) * D + d);  // loads ahead, adds in order
+  d_wr[(size_t)d * E + e] = acc;
 }
 
 // dX[t, d] = dOut[t, d] (residual) + sum_i dXp[slot_dst[t, i], d] + sum_e Wr[d, e] * dz[t, e].
@@ -534,10 +548,10 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
     dbias_reduce_kernel<<<1, 256, 0, st>>>(w.aux_partial, t->d_router_bias, E);
   }
   if (t->d_router_w != nullptr) {
-    dim3 grid((D + 127) / 128, kDwrChunks);
+    dim3 grid((D / 2 + 127) / 128, kDwrChunks);
     dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), w.dz,
                                                  w.dwr_partial, T, D, E);
-    dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(w.dwr_partial, t->d_router_w, D * E);
+    dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(w.dwr_partial, t->d_router_w, D, E);
   }
   dim3 fgrid((D + d_tile - 1) / d_tile, 1);
   // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory)
