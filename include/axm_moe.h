@@ -437,11 +437,6 @@ typedef struct AxmEpLayout {
   int64_t off_flags, off_counts, off_recv, off_oback; /* byte offsets inside a region */
   void* local_region;       /* this rank's own region (= peers[rank]), readable by the host code of
                              * axm_moe_ep_forward; the stage entry points below do not use it */
-  int64_t off_o;            /* 0, or the byte offset of the expert-output rows [o_rows][D] fp32 inside
-                             * a region (axm_ep_region_add_outputs): the source ranks' combine then reads
-                             * the rows where the owner's down GEMM wrote them, and no return copy runs */
-  int32_t o_rows;
-  int32_t reserved;
 } AxmEpLayout;
 
 /* Fills the offsets / sizes of `layout` and returns the bytes one region needs:
@@ -449,13 +444,6 @@ typedef struct AxmEpLayout {
  * return buffer [slots][D] fp32. */
 AXM_API int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d_model,
                                 int32_t slots, int32_t cap, AxmEpLayout* layout, size_t* bytes);
-
-/* Appends room for the down projection's output rows to a region laid out by
- * axm_ep_region_bytes (*bytes in: the region's size so far; out: the new size).  o_rows must cover
- * cap + num_shared * tokens_local.  With it axm_moe_ep_forward lets every rank's combine kernel
- * fetch the expert rows of its tokens straight from the owners' memory (plain 16-byte peer loads
- * after a flag says the owner's GEMM is done) instead of having the owners copy them back. */
-AXM_API int axm_ep_region_add_outputs(AxmEpLayout* layout, int32_t o_rows, size_t* bytes);
 
 /* Dispatch: posts this rank's per-expert counts (from `offsets`, [E+1]) to all
  * peers, waits for theirs, copies the permuted rows (x_perm [slots][D] bf16) into

@@ -56,8 +56,7 @@ class EpLayout(ctypes.Structure):
                 [(n, ctypes.c_int32) for n in ("rank", "world", "num_experts", "d_model", "slots",
                                                "cap", "num_shared", "tokens_local")] +
                 [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")] +
-                [("local_region", ctypes.c_void_p), ("off_o", ctypes.c_int64), ("o_rows", ctypes.c_int32),
-                 ("reserved", ctypes.c_int32)])
+                [("local_region", ctypes.c_void_p)])
 
 
 class EpTensors(ctypes.Structure):
@@ -128,7 +127,6 @@ def load():
     lib.axm_moe_expert_ffn_backward.argtypes = [dp, vp, i32, i32] + [vp] * 16
     lp, u32 = ctypes.POINTER(EpLayout), ctypes.c_uint32
     lib.axm_ep_region_bytes.argtypes = [i32, i32, i32, i32, i32, lp, ctypes.POINTER(sz)]
-    lib.axm_ep_region_add_outputs.argtypes = [lp, i32, ctypes.POINTER(sz)]
     lib.axm_ep_dispatch.argtypes = [lp, u32, vp, vp, vp, vp, vp]
     lib.axm_ep_segments.argtypes = [lp, u32, vp, vp, vp, vp, vp, vp]
     lib.axm_ep_signal_return.argtypes = [lp, u32, vp]

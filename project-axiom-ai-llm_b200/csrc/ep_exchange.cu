@@ -46,7 +46,6 @@ struct EpArgs {
   int S, T_local;       // shared experts, local tokens
   uint32_t step;
   long long off_counts, off_flags, off_recv, off_oback;  // byte offsets inside a region
-  long long off_o;      // expert-output rows inside a region (0: not there)
   int32_t* status;
 };
 
@@ -174,8 +173,8 @@ __global__ void __launch_bounds__(kEpThreads)
 ep_permute_dispatch_kernel(EpArgs a, const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ topk_idx,
                            const int32_t* __restrict__ block_counts, int32_t* __restrict__ histogram,
                            int32_t* __restrict__ offsets, int32_t* __restrict__ row_src,
-                           int32_t* __restrict__ slot_dst, int32_t* __restrict__ slot_loc,
-                           int32_t* __restrict__ done_counter, int T, int k, int hist_accumulate) {
+                           int32_t* __restrict__ slot_dst, int32_t* __restrict__ done_counter, int T, int k,
+                           int hist_accumulate) {
   __shared__ int total_s[kFusedMaxE];
   __shared__ int run_s[kFusedMaxE];      // next free LOCAL row per expert for this block
   __shared__ int scan_s[kFusedMaxE + 1];  // local offsets
@@ -275,8 +274,6 @@ ep_permute_dispatch_kernel(EpArgs a, const __nv_bfloat16* __restrict__ x, const 
           const size_t slot = (size_t)ts * k + i;
           if (slot_dst != nullptr) slot_dst[slot] = local_row;
           if (row_src != nullptr) row_src[local_row] = (int32_t)slot;
-          // where the expert output of this slot will be: owner rank and row in its buffers
-          if (slot_loc != nullptr) slot_loc[slot] = (int32_t)(((uint32_t)(e / a.El) << 26) | (uint32_t)dst_s[i]);
         }
       }
     }
@@ -502,129 +499,21 @@ static EpArgs make_args(const AxmEpLayout* l, uint32_t step, int32_t* status) {
   a.off_flags = l->off_flags;
   a.off_recv = l->off_recv;
   a.off_oback = l->off_oback;
-  a.off_o = l->off_o;
   a.status = status;
   return a;
 }
 
 int launch_ep_permute_dispatch(const AxmEpLayout* l, uint32_t step, const void* x, const int32_t* topk_idx,
                                const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
-                               int32_t* row_src, int32_t* slot_dst, int32_t* slot_loc, int32_t* done_counter,
-                               int T, int k, int hist_accumulate, int32_t* status, cudaStream_t st) {
+                               int32_t* row_src, int32_t* slot_dst, int32_t* done_counter, int T, int k,
+                               int hist_accumulate, int32_t* status, cudaStream_t st) {
   if (int rc = validate_ep(l)) return rc;
   if (l->num_experts > kFusedMaxE) return fail(AXM_ERR_ARGUMENT, "num_experts %d > %d", l->num_experts, kFusedMaxE);
-  if (slot_loc != nullptr && l->cap >= (1 << 26)) return fail(AXM_ERR_ARGUMENT, "receive buffer of %d rows too large", l->cap);
   EpArgs a = make_args(l, step, status);
   ep_permute_dispatch_kernel<<<AXM_ROUTE_BLOCKS, kEpThreads, 0, st>>>(
       a, static_cast<const __nv_bfloat16*>(x), topk_idx, block_counts, histogram, offsets, row_src, slot_dst,
-      slot_loc, done_counter, T, k, hist_accumulate);
+      done_counter, T, k, hist_accumulate);
   return check_launch("ep_permute_dispatch_kernel");
-}
-
-// The combine kernel of permute.cu with the k expert rows of a token fetched from where their
-// owners' down GEMMs wrote them: row slot_loc & (2^26 - 1) of rank slot_loc >> 26, plain 16-byte
-// loads that bypass L1 (peer memory is coherent at its home L2).  Shared experts' rows are local.
-template <int K>
-__global__ void __launch_bounds__(256)
-combine_remote_kernel(EpArgs a, const __nv_bfloat16* __restrict__ x, const float* __restrict__ o_shared,
-                      const int32_t* __restrict__ slot_loc, const float* __restrict__ topk_gate,
-                      __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ out, int T, int D, int S,
-                      int residual) {
-  const int chunks = D / 8;
-  const long long total = (long long)T * chunks;
-  for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
-       g += (long long)gridDim.x * blockDim.x) {
-    const int t = (int)(g / chunks);
-    const int c = (int)(g - (long long)t * chunks);
-    float gw[K];
-    float4 va[K], vb[K];
-#pragma unroll
-    for (int i = 0; i < K; ++i) {
-      const uint32_t loc = (uint32_t)__ldg(slot_loc + (size_t)t * K + i);
-      gw[i] = __ldg(topk_gate + (size_t)t * K + i);
-      const float4* row = reinterpret_cast<const float4*>(a.peers[loc >> 26] + a.off_o) +
-                          (size_t)(loc & 0x3ffffffu) * (D / 4) + 2 * c;
-      va[i] = __ldcg(row);
-      vb[i] = __ldcg(row + 1);
-    }
-    uint4 xv = make_uint4(0, 0, 0, 0);
-    if (residual) xv = __ldg(reinterpret_cast<const uint4*>(x + (size_t)t * D) + c);
-    float acc[8];
-#pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = 0.0f;
-#pragma unroll
-    for (int i = 0; i < K; ++i) {
-      acc[0] = fmaf(gw[i], va[i].x, acc[0]);
-      acc[1] = fmaf(gw[i], va[i].y, acc[1]);
-      acc[2] = fmaf(gw[i], va[i].z, acc[2]);
-      acc[3] = fmaf(gw[i], va[i].w, acc[3]);
-      acc[4] = fmaf(gw[i], vb[i].x, acc[4]);
-      acc[5] = fmaf(gw[i], vb[i].y, acc[5]);
-      acc[6] = fmaf(gw[i], vb[i].z, acc[6]);
-      acc[7] = fmaf(gw[i], vb[i].w, acc[7]);
-    }
-    for (int s = 0; s < S; ++s) {
-      const float4* row = reinterpret_cast<const float4*>(o_shared + ((size_t)s * T + t) * D) + 2 * c;
-      const float4 p = __ldcg(row), q = __ldcg(row + 1);
-      acc[0] += p.x;
-      acc[1] += p.y;
-      acc[2] += p.z;
-      acc[3] += p.w;
-      acc[4] += q.x;
-      acc[5] += q.y;
-      acc[6] += q.z;
-      acc[7] += q.w;
-    }
-    uint4 yv;
-    yv.x = pack_bf16(acc[0], acc[1]);
-    yv.y = pack_bf16(acc[2], acc[3]);
-    yv.z = pack_bf16(acc[4], acc[5]);
-    yv.w = pack_bf16(acc[6], acc[7]);
-    if (y != nullptr) reinterpret_cast<uint4*>(y + (size_t)t * D)[c] = yv;
-    if (residual) {
-      uint4 rr;
-      rr.x = pack_bf16(bf16_lo(xv.x) + bf16_lo(yv.x), bf16_hi(xv.x) + bf16_hi(yv.x));
-      rr.y = pack_bf16(bf16_lo(xv.y) + bf16_lo(yv.y), bf16_hi(xv.y) + bf16_hi(yv.y));
-      rr.z = pack_bf16(bf16_lo(xv.z) + bf16_lo(yv.z), bf16_hi(xv.z) + bf16_hi(yv.z));
-      rr.w = pack_bf16(bf16_lo(xv.w) + bf16_lo(yv.w), bf16_hi(xv.w) + bf16_hi(yv.w));
-      reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = rr;
-    } else {
-      reinterpret_cast<uint4*>(out + (size_t)t * D)[c] = yv;
-    }
-  }
-}
-
-int launch_ep_combine_remote(const AxmEpLayout* l, uint32_t step, const AxmMoeDesc* d, const void* x,
-                             const float* o_shared, const int32_t* slot_loc, const float* topk_gate, void* y,
-                             void* out, cudaStream_t st) {
-  if (int rc = validate_ep(l)) return rc;
-  if (d->tokens == 0) return AXM_OK;
-  EpArgs a = make_args(l, step, nullptr);
-  const long long total = (long long)d->tokens * (d->d_model / 8);
-  int blocks = (int)((total + 255) / 256);
-  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
-  const int residual = (d->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
-  auto xb = static_cast<const __nv_bfloat16*>(x);
-  auto yb = static_cast<__nv_bfloat16*>(y);
-  auto ob = static_cast<__nv_bfloat16*>(out);
-  switch (d->top_k) {
-#define AXM_CR_CASE(K)                                                                                          \
-  case K:                                                                                                       \
-    combine_remote_kernel<K><<<blocks, 256, 0, st>>>(a, xb, o_shared, slot_loc, topk_gate, yb, ob, d->tokens, \
-                                                     d->d_model, d->num_shared, residual);                      \
-    break;
-    AXM_CR_CASE(1)
-    AXM_CR_CASE(2)
-    AXM_CR_CASE(3)
-    AXM_CR_CASE(4)
-    AXM_CR_CASE(5)
-    AXM_CR_CASE(6)
-    AXM_CR_CASE(7)
-    AXM_CR_CASE(8)
-#undef AXM_CR_CASE
-    default: return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..8", d->top_k);
-  }
-  return check_launch("combine_remote_kernel");
 }
 
 int launch_ep_segments_split(const AxmEpLayout* l, uint32_t step, AxmSegment* segments, AxmSegment* ret_segments,
@@ -672,20 +561,7 @@ extern "C" int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d
   layout->d_model = d_model;
   layout->slots = slots;
   layout->cap = cap;
-  layout->off_o = 0;
-  layout->o_rows = 0;
-  layout->reserved = 0;
   *bytes = (size_t)off;
-  return AXM_OK;
-}
-
-extern "C" int axm_ep_region_add_outputs(AxmEpLayout* layout, int32_t o_rows, size_t* bytes) {
-  if (!layout || !bytes) return fail(AXM_ERR_ARGUMENT, "axm_ep_region_add_outputs: null pointer");
-  if (o_rows <= 0 || layout->d_model <= 0) return fail(AXM_ERR_ARGUMENT, "axm_ep_region_add_outputs: bad sizes");
-  const size_t off = (*bytes + 255) & ~static_cast<size_t>(255);
-  layout->off_o = (int64_t)off;
-  layout->o_rows = o_rows;
-  *bytes = (off + (size_t)4 * o_rows * layout->d_model + 255) & ~static_cast<size_t>(255);
   return AXM_OK;
 }
 

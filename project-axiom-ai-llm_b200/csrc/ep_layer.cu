@@ -25,11 +25,8 @@ int launch_expert_ffn_phases(const AxmMoeDesc* d, const void* x_perm, int32_t a_
                              int phases);
 int launch_ep_permute_dispatch(const AxmEpLayout* l, uint32_t step, const void* x, const int32_t* topk_idx,
                                const int32_t* block_counts, int32_t* histogram, int32_t* offsets,
-                               int32_t* row_src, int32_t* slot_dst, int32_t* slot_loc, int32_t* done_counter,
-                               int T, int k, int hist_accumulate, int32_t* status, cudaStream_t st);
-int launch_ep_combine_remote(const AxmEpLayout* l, uint32_t step, const AxmMoeDesc* d, const void* x,
-                             const float* o_shared, const int32_t* slot_loc, const float* topk_gate, void* y,
-                             void* out, cudaStream_t st);
+                               int32_t* row_src, int32_t* slot_dst, int32_t* done_counter, int T, int k,
+                               int hist_accumulate, int32_t* status, cudaStream_t st);
 int launch_ep_segments_split(const AxmEpLayout* l, uint32_t step, AxmSegment* segments, AxmSegment* ret_segments,
                              int32_t* rows_received, AxmSegment* seg_halves, int32_t* split_rows,
                              int32_t* status, cudaStream_t st);
@@ -52,7 +49,6 @@ struct EpWs {
   int32_t* offsets;
   int32_t* row_src;
   int32_t* slot_dst;
-  int32_t* slot_loc;         // owner rank and row there of every slot's expert output
   AxmSegment* segments;      // [G * El + S]
   AxmSegment* ret_segments;  // [G * El]
   AxmSegment* seg_halves;    // [2 * El + S]
@@ -88,7 +84,6 @@ EpWs carve_ep(const AxmEpLayout* l, const AxmMoeDesc* d, void* base) {
   w.offsets = static_cast<int32_t*>(take(4 * (E + 1)));
   w.row_src = static_cast<int32_t*>(take(4 * T * k));
   w.slot_dst = static_cast<int32_t*>(take(4 * T * k));
-  w.slot_loc = static_cast<int32_t*>(take(4 * T * k));
   w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (G * El + S)));
   w.ret_segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * G * El));
   w.seg_halves = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (2 * El + S)));
@@ -187,9 +182,6 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   if (int rc = require_device()) return rc;
 
   static const int fused_dispatch = env_flag("AXM_EP_FUSED_DISPATCH", 1);
-  // Pull form of the return: the region holds the expert-output rows (axm_ep_region_add_outputs),
-  // the owners only flag "my GEMM is done", and each rank's combine fetches its rows from them.
-  static const int pull_env = env_flag("AXM_EP_PULL_COMBINE", 1);
   // Off by default.  Measured on 8 GPUs (T 8192, D 4096, E 8, F 14336): the first half's copy
   // does run under the second half's GEMM (98 - 135 us after the down projection starts), but two
   // launches of 64 tile pairs on 74 CTA pairs take 205 us where one launch of 128 takes 180, and
@@ -202,10 +194,7 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   l.slots = T * k;
   l.tokens_local = T;
   l.num_shared = S;
-  const int rows_needed = layout->cap + S * T;
-  const bool pull = pull_env && fused_dispatch && layout->off_o > 0 && layout->o_rows >= rows_needed;
-  EpPipe* pipe = (split_return && !pull) ? ep_pipe() : nullptr;
-  void* o_buf = pull ? static_cast<void*>(static_cast<char*>(layout->local_region) + layout->off_o) : w.o;
+  EpPipe* pipe = split_return ? ep_pipe() : nullptr;
 
   float* logits = t->logits ? t->logits : w.logits;
   int32_t* idx = t->topk_idx ? t->topk_idx : w.topk_idx;
@@ -226,8 +215,8 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   mark(1);
   if (fused_dispatch) {
     rc = launch_ep_permute_dispatch(&l, step, t->x, idx, w.block_counts, t->histogram, w.offsets, w.row_src,
-                                    w.slot_dst, pull ? w.slot_loc : nullptr, w.scratch, T, k,
-                                    (desc->flags & AXM_FLAG_HIST_ACCUMULATE) ? 1 : 0, w.status, st);
+                                    w.slot_dst, w.scratch, T, k, (desc->flags & AXM_FLAG_HIST_ACCUMULATE) ? 1 : 0,
+                                    w.status, st);
     if (rc) return rc;
   } else {
     if ((rc = axm_moe_permute(&d_route, t->x, idx, w.block_counts, t->histogram, w.offsets, w.row_src, w.slot_dst,
@@ -244,7 +233,7 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   const void* o_back = static_cast<const char*>(layout->local_region) + layout->off_oback;
   auto ffn = [&](const AxmSegment* segs, int n, int phases) {
     return launch_expert_ffn_phases(&d_ffn, recv, l.cap, t->x, T, segs, n, t->w_gate, t->w_up, t->w_down,
-                                    t->shared_gate, t->shared_up, t->shared_down, w.h, o_buf, rows_total, w.status,
+                                    t->shared_gate, t->shared_up, t->shared_down, w.h, w.o, rows_total, w.status,
                                     st, nullptr, nullptr, nullptr, nullptr, phases);
   };
   if ((rc = ffn(w.segments, n_seg, 1))) return rc;
@@ -269,16 +258,13 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   } else {
     if ((rc = ffn(w.segments, n_seg, 2))) return rc;
     mark(5);
-    if (pull) rc = axm_ep_signal_return(&l, step, stream);  // "my rows are where the sources will look"
-    else rc = axm_ep_return(&l, step, w.ret_segments, w.o, w.scratch, w.status, stream);
-    if (rc) return rc;
+    if ((rc = axm_ep_return(&l, step, w.ret_segments, w.o, w.scratch, w.status, stream))) return rc;
   }
   mark(6);
   if ((rc = axm_ep_wait_return(&l, step, w.status, stream))) return rc;
   AxmMoeDesc d_comb = *desc;
-  const float* o_shared = S > 0 ? static_cast<const float*>(o_buf) + (size_t)l.cap * D : nullptr;
-  if (pull) rc = launch_ep_combine_remote(&l, step, &d_comb, t->x, o_shared, w.slot_loc, gate, t->y, t->out, st);
-  else rc = axm_moe_combine(&d_comb, t->x, o_back, o_shared, w.slot_dst, gate, t->y, t->out, stream);
+  const float* o_shared = S > 0 ? static_cast<const float*>(w.o) + (size_t)l.cap * D : nullptr;
+  rc = axm_moe_combine(&d_comb, t->x, o_back, o_shared, w.slot_dst, gate, t->y, t->out, stream);
   mark(7);
   return rc;
 }

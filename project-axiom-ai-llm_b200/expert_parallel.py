@@ -235,11 +235,6 @@ class ExpertParallelMoeP2P:
         nbytes = ctypes.c_size_t(0)
         check(self.lib.axm_ep_region_bytes(self.world, num_experts, D, n_slots, self.cap,
                                            ctypes.byref(self.layout), ctypes.byref(nbytes)))
-        if self.c_layer:
-            # room for the down projection's output rows inside the region: the combine of every
-            # rank then fetches its rows from the owners and no return copy runs
-            check(self.lib.axm_ep_region_add_outputs(ctypes.byref(self.layout), self.rows_total,
-                                                     ctypes.byref(nbytes)))
         self.region = symm_mem.empty(nbytes.value, dtype=torch.uint8, device=dev)
         self.handle = symm_mem.rendezvous(self.region, self.group)
         self.region.zero_()
