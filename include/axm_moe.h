@@ -437,6 +437,10 @@ typedef struct AxmEpLayout {
   int64_t off_flags, off_counts, off_recv, off_oback; /* byte offsets inside a region */
   void* local_region;       /* this rank's own region (= peers[rank]), readable by the host code of
                              * axm_moe_ep_forward; the stage entry points below do not use it */
+  int32_t row_align;        /* 0 or 1: rows packed.  64: training layout - every local expert's run in the
+                             * receive buffer starts at a multiple of 64 rows and is followed by zero rows
+                             * up to the next multiple; cap must then hold slots * world + 63 * (E / world) */
+  int32_t reserved;
 } AxmEpLayout;
 
 /* Fills the offsets / sizes of `layout` and returns the bytes one region needs:
@@ -522,6 +526,32 @@ AXM_API int axm_moe_ep_workspace_bytes(const AxmEpLayout* layout, const AxmMoeDe
 AXM_API int axm_moe_ep_forward(const AxmEpLayout* layout, const AxmMoeDesc* desc,
                                const AxmEpTensors* tensors, void* workspace, size_t workspace_bytes,
                                uint32_t step, void* stream);
+/* ---- training step of the expert-parallel layer -------------------------------------------
+ * The sharded form of axm_moe_forward_train / axm_moe_backward; no reference counterpart (the
+ * engine is single-GPU and its backward covers the dense FFN only,
+ * core/src/CUDA/kernel/backward_pass.cu:1701-2005).  AxmMoeTrain is read per rank: x, out,
+ * d_out, d_x cover this rank's desc->tokens tokens; w_gate / w_up / w_down and their gradients
+ * cover this rank's E / world experts; router_w and router_bias are replicated.
+ * Two exchange regions of equal size are needed, both with row_align = 64 and
+ * cap >= slots * world + 63 * (E / world): `layout` carries the forward rows and keeps them
+ * until the backward pass has read them, `bwd_layout` carries the gradient rows.  The same
+ * `step` is passed to the forward and the backward call of one training step; it grows by one
+ * per training step on every rank alike.  tokens_global is the token count over all ranks.
+ * Left to the caller (sums over the ranks of replicated quantities): d_router_w, d_router_bias
+ * and aux_loss hold this rank's share.  Expert weight gradients are complete on their rank.
+ * The workspace holds the saved activations between the two calls; its leading zero_bytes must
+ * be zero before the first call. */
+AXM_API int axm_moe_ep_train_workspace_bytes(const AxmEpLayout* layout, const AxmMoeDesc* desc, size_t* bytes,
+                                             size_t* zero_bytes);
+AXM_API int axm_moe_ep_forward_train(const AxmEpLayout* layout, const AxmMoeDesc* desc,
+                                     const AxmMoeTrain* tensors, int32_t tokens_global, void* workspace,
+                                     size_t workspace_bytes, uint32_t step, void* stream);
+AXM_API int axm_moe_ep_backward(const AxmEpLayout* layout, const AxmEpLayout* bwd_layout,
+                                const AxmMoeDesc* desc, const AxmMoeTrain* tensors, int32_t tokens_global,
+                                void* workspace, size_t workspace_bytes, uint32_t step, void* stream);
+AXM_API int axm_moe_ep_train_status_word(const AxmEpLayout* layout, const AxmMoeDesc* desc, void* workspace,
+                                         int32_t** status, int32_t** rows_received);
+
 /* Device addresses of the sticky status word and of the number of rows this rank received
  * in the last call (either pointer may be NULL). */
 AXM_API int axm_moe_ep_status_word(const AxmEpLayout* layout, const AxmMoeDesc* desc, void* workspace,

@@ -56,7 +56,8 @@ class EpLayout(ctypes.Structure):
                 [(n, ctypes.c_int32) for n in ("rank", "world", "num_experts", "d_model", "slots",
                                                "cap", "num_shared", "tokens_local")] +
                 [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")] +
-                [("local_region", ctypes.c_void_p)])
+                [("local_region", ctypes.c_void_p), ("row_align", ctypes.c_int32),
+                 ("reserved", ctypes.c_int32)])
 
 
 class EpTensors(ctypes.Structure):
@@ -140,6 +141,10 @@ def load():
     lib.axm_moe_ep_status_word.argtypes = [lp, dp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.axm_moe_ep_forward_profiled.argtypes = [lp, dp, ept, vp, sz, u32, vp, ctypes.POINTER(ctypes.c_float)]
     lib.axm_moe_ep_forward_host.argtypes = [lp, dp, ept, vp, vp, vp, vp, vp, sz, i32, ctypes.POINTER(u32), vp]
+    lib.axm_moe_ep_train_workspace_bytes.argtypes = [lp, dp, ctypes.POINTER(sz), ctypes.POINTER(sz)]
+    lib.axm_moe_ep_forward_train.argtypes = [lp, dp, tp, i32, vp, sz, u32, vp]
+    lib.axm_moe_ep_backward.argtypes = [lp, lp, dp, tp, i32, vp, sz, u32, vp]
+    lib.axm_moe_ep_train_status_word.argtypes = [lp, dp, vp, ctypes.POINTER(vp), ctypes.POINTER(vp)]
     lib.axm_moe_route_dispatch_noalloc.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp]
     cp = ctypes.POINTER(MoeCheckpoint)
     lib.axm_moe_checkpoint_save.argtypes = [ctypes.c_char_p, dp, cp]

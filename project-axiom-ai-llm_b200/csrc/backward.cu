@@ -355,6 +355,87 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                       cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u);
 
+// ---- pieces of the backward pass that run where the tokens live (shared with the
+// expert-parallel training step, ep_train.cu) ------------------------------------------
+size_t dwr_partial_floats(int D, int E) { return (size_t)kDwrChunks * D * E; }
+
+int launch_aux_partial(const float* logits, float* partial, int T, int E, cudaStream_t st) {
+  const size_t sm = sizeof(float) * kAuxThreads * (E + 1);
+  static SmemLimitCache aux_cache = {};
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(aux_partial_kernel), sm, &aux_cache, "aux_partial_kernel"))
+    return rc;
+  aux_partial_kernel<<<AXM_ROUTE_BLOCKS, kAuxThreads, sm, st>>>(logits, partial, T, E);
+  return check_launch("aux_partial_kernel");
+}
+
+static int finalize_tile(int E) { return E <= 64 ? 512 : 128; }
+
+// Raises the dynamic shared-memory limits of router_bwd_kernel and bwd_finalize_kernel.
+int bwd_source_limits(int E, int router_dtype) {
+  const int rb_threads = router_bwd_threads(E);
+  const size_t sm = sizeof(float) * (size_t)rb_threads * 2 * (E + 1);
+  static SmemLimitCache rb_cache = {};
+  int rc;
+  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_bwd_kernel), sm, &rb_cache, "router_bwd_kernel")))
+    return rc;
+  const size_t fsm = sizeof(float) * (size_t)E * finalize_tile(E);
+  static SmemLimitCache cache32 = {}, cache16 = {};
+  if (router_dtype == AXM_ROUTER_FP32)
+    return ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<float>), fsm, &cache32, "bwd_finalize_kernel");
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<__nv_bfloat16>), fsm, &cache16, "bwd_finalize_kernel");
+}
+
+// d_o[r] = bf16(gate * dOut[token of r]) and d_gate[slot] = <dOut[t], o[r]> over the rows
+// [0, offsets[E]) of the expert-contiguous order (row_src[r] < 0: zero row).
+int launch_bwd_prepare(const float* d_out, const float* o, const int32_t* row_src, const float* gate,
+                       const int32_t* offsets, void* d_o, float* d_gate, int D, int E, int k, cudaStream_t st) {
+  bwd_prepare_kernel<<<4 * sm_count(), 256, 0, st>>>(d_out, o, row_src, gate, offsets,
+                                                     static_cast<__nv_bfloat16*>(d_o), d_gate, D, E, k);
+  return check_launch("bwd_prepare_kernel");
+}
+
+// Gate gradients -> logit gradients -> router bias / weight gradients -> dX, over desc->tokens
+// tokens.  bias_partial holds at least [64][E] floats, dwr_partial dwr_partial_floats(D, E).
+// bwd_source_limits must have succeeded for this E and router dtype.
+int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const float* logits,
+                           const int32_t* topk_idx, const float* d_gate, const float* aux_coef, float* dz,
+                           float* bias_partial, float* dwr_partial, const float* d_xp, const int32_t* slot_dst,
+                           cudaStream_t st) {
+  const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
+  const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
+  const int rb_threads = router_bwd_threads(E);
+  const size_t sm = sizeof(float) * (size_t)rb_threads * 2 * (E + 1);
+  const int d_tile = finalize_tile(E);
+  const size_t fsm = sizeof(float) * (size_t)E * d_tile;
+  router_bwd_kernel<<<(T + rb_threads - 1) / rb_threads, rb_threads, sm, st>>>(logits, topk_idx, d_gate, aux_coef,
+                                                                              dz, T, E, k);
+  if (t->d_router_bias != nullptr) {
+    dbias_partial_kernel<<<kBiasChunks, 256, 0, st>>>(dz, bias_partial, T, E);
+    dbias_reduce_kernel<<<1, 256, 0, st>>>(bias_partial, t->d_router_bias, E);
+  }
+  if (t->d_router_w != nullptr) {
+    dim3 grid((D / 2 + 127) / 128, kDwrChunks);
+    dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), dz, dwr_partial, T, D, E);
+    dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(dwr_partial, t->d_router_w, D, E);
+  }
+  dim3 fgrid((D + d_tile - 1) / d_tile, 1);
+  // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory)
+  int per_sm = (int)((200u * 1024u) / (fsm + 1024));
+  per_sm = per_sm < 1 ? 1 : (per_sm > 12 ? 12 : per_sm);
+  fgrid.y = (unsigned)((per_sm * sm_count() + fgrid.x - 1) / fgrid.x);
+  if ((int)fgrid.y > T) fgrid.y = T;
+  if (desc->router_dtype == AXM_ROUTER_FP32) {
+    auto kern = bwd_finalize_kernel<float>;
+    kern<<<fgrid, 128, fsm, st>>>(t->d_out, d_xp, slot_dst, static_cast<const float*>(t->router_w), dz, t->d_x, T, D,
+                                  E, k, residual, d_tile);
+  } else {
+    auto kern = bwd_finalize_kernel<__nv_bfloat16>;
+    kern<<<fgrid, 128, fsm, st>>>(t->d_out, d_xp, slot_dst, static_cast<const __nv_bfloat16*>(t->router_w), dz,
+                                  t->d_x, T, D, E, k, residual, d_tile);
+  }
+  return check_launch("backward");
+}
+
 constexpr int kTrainAlign = 64;
 
 struct TrainWs {
@@ -487,11 +568,7 @@ extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* 
   if ((rc = axm_moe_combine(desc, t->x, w.o, nullptr, w.slot_dst, w.topk_gate, nullptr, t->out, stream)))
     return rc;
   // auxiliary loss and the constants its gradient needs
-  const size_t sm = sizeof(float) * kAuxThreads * (E + 1);
-  static SmemLimitCache aux_cache = {};
-  if (int rc2 = ensure_dynamic_smem(reinterpret_cast<const void*>(aux_partial_kernel), sm, &aux_cache, "aux_partial_kernel"))
-    return rc2;
-  aux_partial_kernel<<<AXM_ROUTE_BLOCKS, kAuxThreads, sm, st>>>(w.logits, w.aux_partial, T, E);
+  if (int rc2 = launch_aux_partial(w.logits, w.aux_partial, T, E, st)) return rc2;
   aux_final_kernel<<<1, 256, 0, st>>>(w.aux_partial, w.counts, w.aux_coef, t->aux_loss, T, E, k,
                                       t->aux_alpha);
   if (t->histogram != nullptr)
@@ -508,69 +585,21 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   if (int rc = check_ws(desc, workspace, workspace_bytes, &w)) return rc;
   if (int rc = require_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
-  const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
+  const int D = desc->d_model, E = desc->num_experts, k = desc->top_k;
 
   // Shared-memory limits of the two router-gradient kernels are settled before anything is
   // launched, so that a refusal leaves no half-finished backward pass behind.
-  const int rb_threads = router_bwd_threads(E);
-  const size_t sm = sizeof(float) * (size_t)rb_threads * 2 * (E + 1);
-  static SmemLimitCache rb_cache = {};
   int rc;
-  if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_bwd_kernel), sm, &rb_cache, "router_bwd_kernel")))
+  if ((rc = bwd_source_limits(E, desc->router_dtype))) return rc;
+  if ((rc = launch_bwd_prepare(t->d_out, static_cast<const float*>(w.o), w.row_src, w.topk_gate, w.offsets, w.d_o,
+                               w.d_gate, D, E, k, st)))
     return rc;
-  const int d_tile = E <= 64 ? 512 : 128;
-  const size_t fsm = sizeof(float) * (size_t)E * d_tile;
-  {
-    static SmemLimitCache cache32 = {}, cache16 = {};
-    if (desc->router_dtype == AXM_ROUTER_FP32)
-      rc = ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<float>), fsm, &cache32, "bwd_finalize_kernel");
-    else
-      rc = ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<__nv_bfloat16>), fsm, &cache16, "bwd_finalize_kernel");
-    if (rc) return rc;
-  }
-
-  bwd_prepare_kernel<<<4 * sm_count(), 256, 0, st>>>(t->d_out, static_cast<const float*>(w.o), w.row_src,
-                                                     w.topk_gate, w.offsets,
-                                                     static_cast<__nv_bfloat16*>(w.d_o), w.d_gate, D, E, k);
-  rc = check_launch("bwd_prepare_kernel");
-  if (rc) return rc;
   if ((rc = axm_moe_expert_ffn_backward(desc, w.segments, E, w.rows_max, w.x_perm, w.h, w.g, w.u, w.d_o,
                                         t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.d_xp,
                                         t->d_w_gate, t->d_w_up, t->d_w_down, w.status, stream)))
     return rc;
-  router_bwd_kernel<<<(T + rb_threads - 1) / rb_threads, rb_threads, sm, st>>>(
-      w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, T, E, k);
-  if (t->d_router_bias != nullptr) {
-    // the auxiliary-loss partial sums of the forward pass are no longer needed: their room
-    // ([296][E] floats) holds the [64][E] partial sums
-    dbias_partial_kernel<<<kBiasChunks, 256, 0, st>>>(w.dz, w.aux_partial, T, E);
-    dbias_reduce_kernel<<<1, 256, 0, st>>>(w.aux_partial, t->d_router_bias, E);
-  }
-  if (t->d_router_w != nullptr) {
-    dim3 grid((D / 2 + 127) / 128, kDwrChunks);
-    dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), w.dz,
-                                                 w.dwr_partial, T, D, E);
-    dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(w.dwr_partial, t->d_router_w, D, E);
-  }
-  dim3 fgrid((D + d_tile - 1) / d_tile, 1);
-  // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory)
-  int per_sm = (int)((200u * 1024u) / (fsm + 1024));
-  per_sm = per_sm < 1 ? 1 : (per_sm > 12 ? 12 : per_sm);
-  fgrid.y = (unsigned)((per_sm * sm_count() + fgrid.x - 1) / fgrid.x);
-  if ((int)fgrid.y > T) fgrid.y = T;
-  if (desc->router_dtype == AXM_ROUTER_FP32) {
-    auto kern = bwd_finalize_kernel<float>;
-    kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
-                                  static_cast<const float*>(t->router_w), w.dz, t->d_x, T, D, E, k,
-                                  residual, d_tile);
-  } else {
-    auto kern = bwd_finalize_kernel<__nv_bfloat16>;
-    kern<<<fgrid, 128, fsm, st>>>(t->d_out, static_cast<const float*>(w.d_xp), w.slot_dst,
-                                  static_cast<const __nv_bfloat16*>(t->router_w), w.dz, t->d_x, T, D, E,
-                                  k, residual, d_tile);
-  }
-  return check_launch("backward");
+  return launch_bwd_source_tail(desc, t, w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, w.aux_partial,
+                                w.dwr_partial, static_cast<const float*>(w.d_xp), w.slot_dst, st);
 }
 
 // ---- optimizer step for the MoE weights ---------------------------------------------

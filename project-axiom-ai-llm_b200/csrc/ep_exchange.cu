@@ -44,6 +44,7 @@ struct EpArgs {
   int slots;            // T_local * k
   int cap;              // rows the receive buffer holds
   int S, T_local;       // shared experts, local tokens
+  int align;            // every local expert's run in the receive buffer starts at a multiple of this
   uint32_t step;
   long long off_counts, off_flags, off_recv, off_oback;  // byte offsets inside a region
   int32_t* status;
@@ -83,6 +84,22 @@ __device__ __forceinline__ void wait_all_sources(const EpArgs& a, int kind, int 
   __syncthreads();
 }
 
+__device__ __forceinline__ int round_up_rows(int v, int align) { return (v + align - 1) / align * align; }
+
+// Row of `owner_first .. e`'s receive buffer where the rows that rank `rank` sends to expert e
+// start: the (aligned) runs of the owner's earlier experts, then the rows lower ranks send to e.
+__device__ __forceinline__ int dispatch_base(const EpArgs& a, const int32_t* table, int e) {
+  const int e_first = (e / a.El) * a.El;  // the owner's first expert
+  int base = 0;
+  for (int q = e_first; q < e; ++q) {
+    int tot = 0;
+    for (int s = 0; s < a.G; ++s) tot += __ldcg(table + s * a.E + q);
+    base += round_up_rows(tot, a.align);
+  }
+  for (int s = 0; s < a.rank; ++s) base += __ldcg(table + s * a.E + e);
+  return base;
+}
+
 constexpr int kEpThreads = 256;
 constexpr int kEpMaxRanks = 64;
 constexpr int kEpMaxExperts = 4096;  // 64 ranks x 64 experts per rank
@@ -112,16 +129,7 @@ ep_dispatch_kernel(EpArgs a, const int32_t* __restrict__ offsets,
   //    the rows that lower ranks send to this expert
   const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
   for (int e = tid; e <= a.E; e += kEpThreads) off_s[e] = offsets[e];
-  for (int e = tid; e < a.E; e += kEpThreads) {
-    const int e_first = (e / a.El) * a.El;  // the owner's first expert
-    int base = 0;
-    for (int s = 0; s < a.G; ++s) {
-      const int32_t* row = table + s * a.E;
-      for (int q = e_first; q < e; ++q) base += __ldcg(row + q);
-      if (s < a.rank) base += __ldcg(row + e);
-    }
-    dst_base[e] = base;
-  }
+  for (int e = tid; e < a.E; e += kEpThreads) dst_base[e] = dispatch_base(a, table, e);
   __syncthreads();
   // 4. copy: one warp per row, 16-byte pieces, plain stores into the owner's memory
   const int warp = tid >> 5, lane = tid & 31;
@@ -235,16 +243,7 @@ ep_permute_dispatch_kernel(EpArgs a, const __nv_bfloat16* __restrict__ x, const 
   wait_all_sources(a, 0, 11);
   {
     const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
-    for (int e = tid; e < E; e += kEpThreads) {
-      const int e_first = (e / a.El) * a.El;
-      int base = 0;
-      for (int s = 0; s < a.G; ++s) {
-        const int32_t* row = table + s * E;
-        for (int q = e_first; q < e; ++q) base += __ldcg(row + q);
-        if (s < a.rank) base += __ldcg(row + e);
-      }
-      base_s[e] = base;
-    }
+    for (int e = tid; e < E; e += kEpThreads) base_s[e] = dispatch_base(a, table, e);
   }
   __syncthreads();
 
@@ -343,6 +342,7 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
   if (threadIdx.x == 0) {
     int acc = 0;
     for (int i = 0; i < n; ++i) {
+      if (i % a.G == 0) acc = round_up_rows(acc, a.align);  // a new expert's run
       start_s[i] = acc;
       acc += rows_s[i];
     }
@@ -388,7 +388,9 @@ ep_segments_kernel(EpArgs a, AxmSegment* __restrict__ segments,
       remote_out[i] = ro;
     } else {
       const int first = j * a.G;  // the expert's run starts where its source 0 starts
-      const int end = (j + 1 < a.El) ? start_s[first + a.G] : start_s[n - 1] + rows_s[n - 1];
+      // with an alignment the run is padded to a whole number of aligned blocks (zero rows)
+      const int end = (j + 1 < a.El) ? start_s[first + a.G]
+                                     : round_up_rows(start_s[n - 1] + rows_s[n - 1], a.align);
       sg.a_row0 = start_s[first];
       sg.out_row0 = start_s[first];
       sg.rows = (s == 0) ? end - start_s[first] : 0;
@@ -431,6 +433,7 @@ ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
       if (seg < n) sg = ret_segments[seg];
     }
     if (seg >= n) break;
+    if (r < sg.out_row0) continue;  // a padding row between two experts' runs (training layout)
     if (half >= 0) {
       const int cut = split_rows[seg / a.G];  // entries are ordered (local expert, source)
       if ((half == 0) != (r < cut)) continue;
@@ -463,6 +466,30 @@ ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
 
 __global__ void ep_wait_return_kernel(EpArgs a) { wait_all_sources(a, 2, 13); }
 
+// Training layout (align > 1): zero the padding rows between one local expert's last row and
+// the next aligned start in a [cap][D] bf16 buffer laid out like the receive buffer.  Runs after
+// ep_segments_kernel on the same stream (the counts are complete then).  grid (El, parts).
+__global__ void __launch_bounds__(kEpThreads)
+ep_zero_pad_kernel(EpArgs a, __nv_bfloat16* __restrict__ buf) {
+  const int32_t* table = reinterpret_cast<const int32_t*>(a.peers[a.rank] + a.off_counts);
+  const int j = blockIdx.x;
+  int start = 0, tot = 0;
+  for (int q = 0; q <= j; ++q) {
+    start += round_up_rows(tot, a.align);
+    tot = 0;
+    for (int s = 0; s < a.G; ++s) tot += __ldcg(table + s * a.E + a.rank * a.El + q);
+  }
+  const int pad0 = start + tot;
+  int pad1 = start + round_up_rows(tot, a.align);
+  if (pad1 > a.cap) pad1 = a.cap;
+  const int chunks = a.D / 8;
+  const long long pieces = (long long)(pad1 > pad0 ? pad1 - pad0 : 0) * chunks;
+  uint4* dst = reinterpret_cast<uint4*>(buf + (size_t)pad0 * a.D);
+  for (long long i = (long long)blockIdx.y * kEpThreads + threadIdx.x; i < pieces;
+       i += (long long)gridDim.y * kEpThreads)
+    dst[i] = make_uint4(0u, 0u, 0u, 0u);
+}
+
 // After a down GEMM that stored its rows into the sources' return buffers itself:
 // the kernel boundary has made those stores visible; tell every source.
 __global__ void ep_signal_return_kernel(EpArgs a) {
@@ -479,6 +506,7 @@ static int validate_ep(const AxmEpLayout* l) {
   if (l->num_experts / l->world > 64) return fail(AXM_ERR_ARGUMENT, "more than 64 experts per rank");
   if (l->d_model <= 0 || l->d_model % 8 != 0) return fail(AXM_ERR_ARGUMENT, "d_model %d not a multiple of 8", l->d_model);
   if (l->slots < 0 || l->cap < 0) return fail(AXM_ERR_ARGUMENT, "negative row count");
+  if (l->row_align < 0 || l->row_align > 1024) return fail(AXM_ERR_ARGUMENT, "row_align %d not in 0..1024", l->row_align);
   return AXM_OK;
 }
 
@@ -494,6 +522,7 @@ static EpArgs make_args(const AxmEpLayout* l, uint32_t step, int32_t* status) {
   a.cap = l->cap;
   a.S = l->num_shared;
   a.T_local = l->tokens_local;
+  a.align = l->row_align > 1 ? l->row_align : 1;
   a.step = step;
   a.off_counts = l->off_counts;
   a.off_flags = l->off_flags;
@@ -536,6 +565,15 @@ int launch_ep_return_half(const AxmEpLayout* l, uint32_t step, const AxmSegment*
   return check_launch("ep_return_kernel");
 }
 
+// Zero rows behind every local expert's run in `buf` ([cap][D] bf16, receive-buffer layout).
+int launch_ep_zero_pad(const AxmEpLayout* l, uint32_t step, void* buf, cudaStream_t st) {
+  if (int rc = validate_ep(l)) return rc;
+  if (l->row_align <= 1) return AXM_OK;
+  EpArgs a = make_args(l, step, nullptr);
+  ep_zero_pad_kernel<<<dim3(a.El, 8), kEpThreads, 0, st>>>(a, static_cast<__nv_bfloat16*>(buf));
+  return check_launch("ep_zero_pad_kernel");
+}
+
 }  // namespace axm
 
 using namespace axm;
@@ -561,6 +599,8 @@ extern "C" int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d
   layout->d_model = d_model;
   layout->slots = slots;
   layout->cap = cap;
+  layout->row_align = 1;
+  layout->reserved = 0;
   *bytes = (size_t)off;
   return AXM_OK;
 }

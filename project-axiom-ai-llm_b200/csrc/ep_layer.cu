@@ -34,6 +34,34 @@ int launch_ep_return_half(const AxmEpLayout* l, uint32_t step, const AxmSegment*
                           int32_t* done_counter, const int32_t* split_rows, int half, int signal,
                           int32_t* status, cudaStream_t st);
 
+// Arguments of one expert-parallel layer call against the exchange layout (also used by ep_train.cu).
+int validate_ep_layer(const AxmEpLayout* l, const AxmMoeDesc* d) {
+  if (l == nullptr || d == nullptr) return fail(AXM_ERR_ARGUMENT, "layout or desc is null");
+  if (l->world <= 0 || l->world > 64 || l->rank < 0 || l->rank >= l->world)
+    return fail(AXM_ERR_ARGUMENT, "rank %d / world %d out of range", l->rank, l->world);
+  if (d->tokens < 0) return fail(AXM_ERR_ARGUMENT, "tokens %d negative", d->tokens);
+  if (d->d_model <= 0 || d->d_ff <= 0 || d->d_model % 8 || d->d_ff % 8)
+    return fail(AXM_ERR_ARGUMENT, "d_model %d and d_ff %d must be positive multiples of 8", d->d_model, d->d_ff);
+  if (d->num_experts <= 0 || d->num_experts > 256 || d->num_experts % l->world != 0)
+    return fail(AXM_ERR_ARGUMENT, "num_experts %d must be in 1..256 and a multiple of world %d", d->num_experts,
+                l->world);
+  if (d->num_experts / l->world > 64) return fail(AXM_ERR_ARGUMENT, "more than 64 experts per rank");
+  if (d->top_k <= 0 || d->top_k > 8 || d->top_k > d->num_experts)
+    return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..min(num_experts, 8)", d->top_k);
+  if (d->num_shared < 0 || d->num_shared > 8) return fail(AXM_ERR_ARGUMENT, "num_shared %d not in 0..8", d->num_shared);
+  if (d->router_dtype != AXM_ROUTER_BF16 && d->router_dtype != AXM_ROUTER_FP32)
+    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", d->router_dtype);
+  if (l->num_experts != d->num_experts || l->d_model != d->d_model)
+    return fail(AXM_ERR_ARGUMENT, "layout was sized for %d experts / d_model %d, desc says %d / %d", l->num_experts,
+                l->d_model, d->num_experts, d->d_model);
+  if ((long long)d->tokens * d->top_k > l->slots)
+    return fail(AXM_ERR_ARGUMENT, "%d tokens x top-%d exceed the %d slots the exchange region was sized for",
+                d->tokens, d->top_k, l->slots);
+  if ((long long)l->cap + (long long)d->num_shared * d->tokens > 0x7fffffffLL)
+    return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
+  return AXM_OK;
+}
+
 namespace {
 
 size_t up256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
@@ -96,33 +124,6 @@ EpWs carve_ep(const AxmEpLayout* l, const AxmMoeDesc* d, void* base) {
   w.router_scratch = take(w.router_scratch_bytes);
   w.bytes = off;
   return w;
-}
-
-int validate_ep_layer(const AxmEpLayout* l, const AxmMoeDesc* d) {
-  if (l == nullptr || d == nullptr) return fail(AXM_ERR_ARGUMENT, "layout or desc is null");
-  if (l->world <= 0 || l->world > 64 || l->rank < 0 || l->rank >= l->world)
-    return fail(AXM_ERR_ARGUMENT, "rank %d / world %d out of range", l->rank, l->world);
-  if (d->tokens < 0) return fail(AXM_ERR_ARGUMENT, "tokens %d negative", d->tokens);
-  if (d->d_model <= 0 || d->d_ff <= 0 || d->d_model % 8 || d->d_ff % 8)
-    return fail(AXM_ERR_ARGUMENT, "d_model %d and d_ff %d must be positive multiples of 8", d->d_model, d->d_ff);
-  if (d->num_experts <= 0 || d->num_experts > 256 || d->num_experts % l->world != 0)
-    return fail(AXM_ERR_ARGUMENT, "num_experts %d must be in 1..256 and a multiple of world %d", d->num_experts,
-                l->world);
-  if (d->num_experts / l->world > 64) return fail(AXM_ERR_ARGUMENT, "more than 64 experts per rank");
-  if (d->top_k <= 0 || d->top_k > 8 || d->top_k > d->num_experts)
-    return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..min(num_experts, 8)", d->top_k);
-  if (d->num_shared < 0 || d->num_shared > 8) return fail(AXM_ERR_ARGUMENT, "num_shared %d not in 0..8", d->num_shared);
-  if (d->router_dtype != AXM_ROUTER_BF16 && d->router_dtype != AXM_ROUTER_FP32)
-    return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", d->router_dtype);
-  if (l->num_experts != d->num_experts || l->d_model != d->d_model)
-    return fail(AXM_ERR_ARGUMENT, "layout was sized for %d experts / d_model %d, desc says %d / %d", l->num_experts,
-                l->d_model, d->num_experts, d->d_model);
-  if ((long long)d->tokens * d->top_k > l->slots)
-    return fail(AXM_ERR_ARGUMENT, "%d tokens x top-%d exceed the %d slots the exchange region was sized for",
-                d->tokens, d->top_k, l->slots);
-  if ((long long)l->cap + (long long)d->num_shared * d->tokens > 0x7fffffffLL)
-    return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
-  return AXM_OK;
 }
 
 int env_flag(const char* name, int dflt) {

@@ -22,7 +22,7 @@ import torch
 import torch.distributed as dist
 
 from . import (AXM_ERR_TIMEOUT, FLAG_H_EXACT, FLAG_RESIDUAL, ROUTER_BF16, ROUTER_FP32, ROUTE_BLOCKS, SEG_ALT_A,
-               AxmError, EpLayout, EpTensors, check, current_stream, load, make_desc, ptr, router_scratch_bytes)
+               AxmError, EpLayout, EpTensors, MoeTrain, check, current_stream, load, make_desc, ptr, router_scratch_bytes)
 
 
 class CudaStages:
@@ -398,3 +398,141 @@ class ExpertParallelMoeP2P:
         st.combine(self.desc_comb, x, self.o_back, o_shared, self.slot_dst, self.gate, self.y, out)
         mark("wait return + combine")
         return out
+
+
+class ExpertParallelTrainP2P:
+    """Training step of the sharded layer (csrc/ep_train.cu): forward with the activations kept
+    where they were produced, backward as the same exchange in reverse.  Two symmetric-memory
+    regions (forward rows / gradient rows), both in the 64-row training layout.
+
+    step(x_local, d_out_local) -> (out_local, aux_loss, grads): grads["d_x"] covers this rank's
+    tokens, d_w_gate / d_w_up / d_w_down this rank's experts; d_router_w, d_router_bias and the
+    auxiliary loss are summed over the ranks here (one small all-reduce each), because the router
+    is replicated.  GPU only."""
+
+    ALIGN = 64
+
+    def __init__(self, local_weights, tokens_local, num_experts, top_k, group=None, aux_alpha=0.01,
+                 weight_grads=True, tokens_global=None):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.lib = load()
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.w = local_weights
+        wr = local_weights["router_w"]
+        dev = self.dev = wr.device
+        D = wr.shape[0]
+        F = local_weights["w_gate"].shape[2]
+        self.E, self.k, self.D, self.F = num_experts, top_k, D, F
+        self.El = num_experts // self.world
+        assert self.El * self.world == num_experts and local_weights["w_gate"].shape[0] == self.El
+        self.Tl = tokens_local
+        self.tokens_global = tokens_global if tokens_global is not None else tokens_local * self.world
+        rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
+        self.desc = make_desc(tokens_local, D, F, num_experts, top_k, 0, rdt, FLAG_RESIDUAL)
+        n_slots = tokens_local * top_k
+        cap = n_slots * self.world + (self.ALIGN - 1) * self.El
+        self.cap = (cap + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        self.layouts, self.regions, self.handles = [], [], []
+        for _ in range(2):   # forward rows, gradient rows
+            lo = EpLayout()
+            nbytes = ctypes.c_size_t(0)
+            check(self.lib.axm_ep_region_bytes(self.world, num_experts, D, n_slots, self.cap,
+                                               ctypes.byref(lo), ctypes.byref(nbytes)))
+            region = symm_mem.empty(nbytes.value, dtype=torch.uint8, device=dev)
+            handle = symm_mem.rendezvous(region, self.group)
+            region.zero_()
+            lo.peers = handle.buffer_ptrs_dev
+            lo.rank = self.rank
+            lo.num_shared = 0
+            lo.tokens_local = tokens_local
+            lo.local_region = region.data_ptr()
+            lo.row_align = self.ALIGN
+            self.layouts.append(lo)
+            self.regions.append(region)
+            self.handles.append(handle)
+        torch.cuda.synchronize()
+        dist.barrier(self.group)
+        nb, zb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+        check(self.lib.axm_moe_ep_train_workspace_bytes(ctypes.byref(self.layouts[0]), ctypes.byref(self.desc),
+                                                        ctypes.byref(nb), ctypes.byref(zb)))
+        self.workspace = torch.empty(nb.value, dtype=torch.uint8, device=dev)
+        self.workspace[:zb.value].zero_()
+        ps, pr = ctypes.c_void_p(), ctypes.c_void_p()
+        check(self.lib.axm_moe_ep_train_status_word(ctypes.byref(self.layouts[0]), ctypes.byref(self.desc),
+                                                    ptr(self.workspace), ctypes.byref(ps), ctypes.byref(pr)))
+        base = self.workspace.data_ptr()
+        self.status = self.workspace[ps.value - base:ps.value - base + 4].view(torch.int32)
+        self.rows_received = self.workspace[pr.value - base:pr.value - base + 4].view(torch.int32)
+        self.rows_received.zero_()
+        f32 = torch.float32
+        self.out = torch.empty(tokens_local, D, dtype=torch.bfloat16, device=dev)
+        self.aux = torch.zeros(1, dtype=f32, device=dev)
+        self.histogram = torch.zeros(num_experts, dtype=torch.int32, device=dev)
+        self.d_x = torch.empty(tokens_local, D, dtype=f32, device=dev)
+        self.d_router_w = torch.empty(D, num_experts, dtype=f32, device=dev)
+        self.d_router_bias = (torch.empty(num_experts, dtype=f32, device=dev)
+                              if local_weights.get("router_bias") is not None else None)
+        self.weight_grads = weight_grads
+        if weight_grads:
+            self.d_w_gate = torch.empty(self.El, D, F, dtype=f32, device=dev)
+            self.d_w_up = torch.empty(self.El, D, F, dtype=f32, device=dev)
+            self.d_w_down = torch.empty(self.El, F, D, dtype=f32, device=dev)
+        self.aux_alpha = aux_alpha
+        self.step_no = 0
+
+    def check_status(self):
+        """Raises AxmError(AXM_ERR_TIMEOUT) if a bounded device-side wait gave up since the last check
+        (synchronises this rank's stream)."""
+        code = int(self.status.item())
+        if code != 0:
+            self.status.zero_()
+            raise AxmError(AXM_ERR_TIMEOUT, f"a bounded device-side wait gave up (kernel code {code}) "
+                                            f"on rank {self.rank}")
+
+    def tensors(self, x, d_out):
+        w, g = self.w, self.weight_grads
+        return MoeTrain(
+            x.data_ptr(), w["router_w"].data_ptr(),
+            None if w.get("router_bias") is None else w["router_bias"].data_ptr(),
+            w["w_gate"].data_ptr(), w["w_up"].data_ptr(), w["w_down"].data_ptr(),
+            self.out.data_ptr(), self.aux.data_ptr(), self.histogram.data_ptr(), self.aux_alpha,
+            None if d_out is None else d_out.data_ptr(), self.d_x.data_ptr(),
+            self.d_router_w.data_ptr(), self.d_w_gate.data_ptr() if g else None,
+            self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None,
+            None if self.d_router_bias is None else self.d_router_bias.data_ptr())
+
+    def forward(self, x):
+        """Enqueues the forward pass; self.aux then holds this rank's share of the auxiliary loss."""
+        self.step_no += 1
+        t = self.tensors(x, None)
+        check(self.lib.axm_moe_ep_forward_train(ctypes.byref(self.layouts[0]), ctypes.byref(self.desc),
+                                                ctypes.byref(t), self.tokens_global, ptr(self.workspace),
+                                                self.workspace.numel(), self.step_no, current_stream()))
+        return self.out
+
+    def backward(self, x, d_out, reduce=True):
+        """Enqueues the backward pass of the last forward(); reduce=True adds the replicated
+        router's gradients (and the auxiliary loss) over the ranks."""
+        t = self.tensors(x, d_out)
+        check(self.lib.axm_moe_ep_backward(ctypes.byref(self.layouts[0]), ctypes.byref(self.layouts[1]),
+                                           ctypes.byref(self.desc), ctypes.byref(t), self.tokens_global,
+                                           ptr(self.workspace), self.workspace.numel(), self.step_no,
+                                           current_stream()))
+        if reduce:
+            dist.all_reduce(self.d_router_w, group=self.group)
+            if self.d_router_bias is not None:
+                dist.all_reduce(self.d_router_bias, group=self.group)
+            dist.all_reduce(self.aux, group=self.group)
+        return self.d_x
+
+    def step(self, x, d_out, reduce=True):
+        self.forward(x)
+        self.backward(x, d_out, reduce=reduce)
+        grads = {"d_x": self.d_x, "d_router_w": self.d_router_w}
+        if self.d_router_bias is not None:
+            grads["d_router_bias"] = self.d_router_bias
+        if self.weight_grads:
+            grads.update(d_w_gate=self.d_w_gate, d_w_up=self.d_w_up, d_w_down=self.d_w_down)
+        return self.out, self.aux, grads
