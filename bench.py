@@ -228,7 +228,7 @@ def workload_config(cfg, n_gpus):
     l2_note = ("inputs larger than L2 (expert weights "
                f"{cfg.weight_bytes / n_gpus / 1e9:.2f} GB per GPU); no flush")
     return {
-        "workload": f"{cfg.name}: MoE layer forward, T={cfg.tokens} d_model={cfg.d_model} "
+        "workload": f"{cfg.name}: MoE layer {'training step (forward + backward)' if cfg.training else 'forward'}, T={cfg.tokens} d_model={cfg.d_model} "
                     f"E={cfg.num_experts}+{cfg.num_shared} shared top-{cfg.top_k} d_ff={cfg.d_ff}, "
                     f"seed {cfg.seed}",
         "tokens": cfg.tokens, "d_model": cfg.d_model, "num_experts": cfg.num_experts,
@@ -297,8 +297,24 @@ def main():
 
     training = cfg.training
     if training and world > 1:
-        raise SystemExit("the training step (C5) is single-GPU in this build")
-    if training:
+        # the same step sharded: tokens and experts over the ranks, both exchanges by this library's
+        # peer-memory kernels, the replicated router's gradients summed with one small all-reduce each
+        ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
+        assert T % world == 0 and cfg.num_experts % world == 0
+        tl = T // world
+        x_local = x[rank * tl:(rank + 1) * tl].contiguous()
+        wloc = ep.shard_weights(w, rank, world)
+        del w
+        layer = ep.ExpertParallelTrainP2P(wloc, tl, cfg.num_experts, k, aux_alpha=cfg.aux_alpha)
+        d_out = torch.randn(T, D, device=dev, generator=torch.Generator(device=dev).manual_seed(cfg.seed))
+        d_out = d_out[rank * tl:(rank + 1) * tl].contiguous()
+        out = layer.out
+        step = lambda: layer.step(x_local, d_out)
+        # forward: router, permute + dispatch, segment tables (2), padding, two GEMMs, auxiliary loss (2),
+        # return, wait, combine; backward: prepare, dispatch, segment tables (2), padding, dH, dX, three
+        # weight-gradient GEMMs, return, wait, router gradient, dWr (2), dX assembly
+        launches_per_step = 12 + 16 + (1 if axm.router_scratch_bytes(layer.desc) else 0)
+    elif training:
         # forward (saving activations) + auxiliary loss + backward with all weight gradients
         layer = axm.MoeTrainLayer(w, T, k, aux_alpha=cfg.aux_alpha)
         x_local = x
@@ -451,8 +467,8 @@ def main():
     e2e_ms /= args.steps
     clocks = sampler.stop() if rank == 0 else None
     copy_bytes = h_x.numel() * 2 * world
-    h2d_bytes = copy_bytes + (h_dy.numel() * 4 if training else 0)
-    d2h_bytes = copy_bytes + (h_dx.numel() * 4 if training else 0)
+    h2d_bytes = copy_bytes + (h_dy.numel() * 4 * world if training else 0)
+    d2h_bytes = copy_bytes + (h_dx.numel() * 4 * world if training else 0)
 
     # ---- roofline of the dominant kernel (gate/up grouped GEMM) ---------------------
     roofline = None
@@ -465,7 +481,7 @@ def main():
                     "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                     "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
                     "traffic": None}
-        status = int(layer.workspace[:4].view(torch.int32).item())
+        status = int(layer.status.item()) if world > 1 else int(layer.workspace[:4].view(torch.int32).item())
         if status != 0:
             raise SystemExit(f"a GEMM kernel reported a timed-out wait (status {status})")
     elif world == 1:
@@ -500,7 +516,7 @@ def main():
             raise SystemExit(f"GEMM kernel reported a timed-out wait (status {status})")
 
     ep_stages = None
-    if world > 1:
+    if world > 1 and not training:
         acc = {}
         reps = 10
         for _ in range(reps):
@@ -519,7 +535,33 @@ def main():
 
     # ---- expert parallel: the answer itself, against the single-GPU layer ------------
     ep_check = None
-    if world > 1:
+    ep_failed = False
+    if world > 1 and training:
+        # the sharded training step against the single-GPU step on the same seeded batch: output
+        # and input gradient bit for bit
+        layer.check_status()
+        layer.step(x_local, d_out)
+        mine = [layer.out.clone(), layer.d_x.clone()]
+        gathered = []
+        for t_ in mine:
+            parts = [torch.empty_like(t_) for _ in range(world)] if rank == 0 else None
+            dist.gather(t_, parts, dst=0)
+            gathered.append(parts)
+        verdict = torch.zeros(1, dtype=torch.int32, device=dev)
+        if rank == 0:
+            xs, ws = wl.make_inputs(cfg, device=dev)
+            dy = torch.randn(T, D, device=dev, generator=torch.Generator(device=dev).manual_seed(cfg.seed))
+            single = axm.MoeTrainLayer(ws, T, k, aux_alpha=cfg.aux_alpha, weight_grads=False)
+            single.step(xs, dy)
+            torch.cuda.synchronize()
+            same = (torch.equal(torch.cat(gathered[0]), single.out) and
+                    torch.equal(torch.cat(gathered[1]), single.d_x))
+            ep_check = "bit-equal (out, d_x)" if same else "MISMATCH"
+            verdict[0] = 0 if same else 1
+            del single, ws, xs, dy, gathered
+        dist.broadcast(verdict, src=0)
+        ep_failed = int(verdict.item()) != 0
+    elif world > 1:
         if hasattr(layer, "check_status"):
             layer.check_status()
         out_final = layer.forward(x_local, out).clone()
@@ -540,8 +582,6 @@ def main():
             del single, ws, xs, ref_out, gathered
         dist.broadcast(verdict, src=0)
         ep_failed = int(verdict.item()) != 0
-    else:
-        ep_failed = False
 
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu_baseline and not training:
@@ -571,6 +611,8 @@ def main():
             line["roofline"] = roofline
         if stages is not None:
             line["stages"] = stages
+        if world > 1 and training:
+            line["config"]["ep_transport"] = "p2p"
         if ep_stages is not None:
             line["stages_rank0"] = ep_stages
             line["config"]["ep_transport"] = args.ep_transport
