@@ -478,8 +478,9 @@ def main():
         fl = 3.0 * cfg.gemm_flops
         tf = fl / (ms_step * 1e-3) / 1e12
         roofline = {"kernel": "all grouped GEMMs of the training step (whole-step time)",
-                    "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
-                    "frac": tf / peaks["bf16_tflops"], "peak_source": peaks["source"] + " (burst)",
+                    "bound": "tensor", "achieved": tf, "peak": peaks["bf16_tflops"] * world, "unit": "TFLOP/s",
+                    "frac": tf / (peaks["bf16_tflops"] * world),
+                    "peak_source": peaks["source"] + (" (burst)" if world == 1 else f" (burst) x {world} GPUs"),
                     "traffic": None}
         status = int(layer.status.item()) if world > 1 else int(layer.workspace[:4].view(torch.int32).item())
         if status != 0:
@@ -516,6 +517,24 @@ def main():
             raise SystemExit(f"GEMM kernel reported a timed-out wait (status {status})")
 
     ep_stages = None
+    if world > 1 and training:
+        # forward and backward halves of the sharded step (rank 0's events; each includes waiting for peers)
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        acc = [0.0, 0.0]
+        reps = 10
+        for _ in range(reps):
+            barrier()
+            ev[0].record()
+            layer.forward(x_local)
+            ev[1].record()
+            layer.backward(x_local, d_out)
+            ev[2].record()
+            torch.cuda.synchronize()
+            acc[0] += ev[0].elapsed_time(ev[1]) / reps
+            acc[1] += ev[1].elapsed_time(ev[2]) / reps
+        ep_stages = {"forward (saves activations, auxiliary loss)": {"ms": acc[0]},
+                     "backward (incl. three small all-reduces)": {"ms": acc[1]},
+                     "rows_received_rank0": int(layer.rows_received.item())}
     if world > 1 and not training:
         acc = {}
         reps = 10
@@ -613,7 +632,9 @@ def main():
             line["stages"] = stages
         if world > 1 and training:
             line["config"]["ep_transport"] = "p2p"
-        if ep_stages is not None:
+        if ep_stages is not None and training:
+            line["stages_rank0"] = ep_stages
+        elif ep_stages is not None:
             line["stages_rank0"] = ep_stages
             line["config"]["ep_transport"] = args.ep_transport
             if args.ep_transport == "p2p":
