@@ -299,6 +299,13 @@ typedef struct AxmMoeTrain {
   float* d_w_down;          /* [E][F][D] fp32 */
   float* d_router_bias;     /* [E] fp32 gradient of router_bias (sum over tokens of the logit
                              * gradients), optional; NULL leaves the bias untrained */
+  const void* shared_gate;  /* [S][D][F] bf16: shared experts (desc->num_shared > 0), applied to every
+                             * token with weight 1 as in the forward call */
+  const void* shared_up;    /* [S][D][F] bf16 */
+  const void* shared_down;  /* [S][F][D] bf16 */
+  float* d_shared_gate;     /* [S][D][F] fp32: given exactly when the routed experts' gradients are */
+  float* d_shared_up;       /* [S][D][F] fp32 */
+  float* d_shared_down;     /* [S][F][D] fp32 */
 } AxmMoeTrain;
 
 AXM_API int axm_moe_train_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes);

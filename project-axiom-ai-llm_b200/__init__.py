@@ -71,7 +71,9 @@ class MoeTrain(ctypes.Structure):
                                                 "w_down", "out", "aux_loss", "histogram")] +
                 [("aux_alpha", ctypes.c_float)] +
                 [(n, ctypes.c_void_p) for n in ("d_out", "d_x", "d_router_w", "d_w_gate", "d_w_up",
-                                                "d_w_down", "d_router_bias")])
+                                                "d_w_down", "d_router_bias", "shared_gate", "shared_up",
+                                                "shared_down", "d_shared_gate", "d_shared_up",
+                                                "d_shared_down")])
 
 
 class MoeCheckpoint(ctypes.Structure):
@@ -298,7 +300,8 @@ class MoeTrainLayer:
         D, E = wr.shape
         F = weights["w_gate"].shape[2]
         rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
-        self.desc = make_desc(tokens, D, F, E, top_k, 0, rdt, FLAG_RESIDUAL)
+        S = self.S = 0 if weights.get("shared_gate") is None else weights["shared_gate"].shape[0]
+        self.desc = make_desc(tokens, D, F, E, top_k, S, rdt, FLAG_RESIDUAL)
         dev = torch.device(device)
         n = ctypes.c_size_t(0)
         check(self.lib.axm_moe_train_workspace_bytes(ctypes.byref(self.desc), ctypes.byref(n)))
@@ -316,6 +319,10 @@ class MoeTrainLayer:
             self.d_w_gate = torch.empty(E, D, F, dtype=f32, device=dev)
             self.d_w_up = torch.empty(E, D, F, dtype=f32, device=dev)
             self.d_w_down = torch.empty(E, F, D, dtype=f32, device=dev)
+            if S:
+                self.d_shared_gate = torch.empty(S, D, F, dtype=f32, device=dev)
+                self.d_shared_up = torch.empty(S, D, F, dtype=f32, device=dev)
+                self.d_shared_down = torch.empty(S, F, D, dtype=f32, device=dev)
         self.aux_alpha = aux_alpha
 
     def tensors(self, x, d_out):
@@ -329,7 +336,12 @@ class MoeTrainLayer:
             None if d_out is None else d_out.data_ptr(), self.d_x.data_ptr(),
             self.d_router_w.data_ptr(), self.d_w_gate.data_ptr() if g else None,
             self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None,
-            None if self.d_router_bias is None else self.d_router_bias.data_ptr())
+            None if self.d_router_bias is None else self.d_router_bias.data_ptr(),
+            w["shared_gate"].data_ptr() if self.S else None, w["shared_up"].data_ptr() if self.S else None,
+            w["shared_down"].data_ptr() if self.S else None,
+            self.d_shared_gate.data_ptr() if g and self.S else None,
+            self.d_shared_up.data_ptr() if g and self.S else None,
+            self.d_shared_down.data_ptr() if g and self.S else None)
 
     def forward(self, x):
         t = self.tensors(x, None)
@@ -352,4 +364,7 @@ class MoeTrainLayer:
             grads["d_router_bias"] = self.d_router_bias
         if self.weight_grads:
             grads.update(d_w_gate=self.d_w_gate, d_w_up=self.d_w_up, d_w_down=self.d_w_down)
+            if self.S:
+                grads.update(d_shared_gate=self.d_shared_gate, d_shared_up=self.d_shared_up,
+                             d_shared_down=self.d_shared_down)
         return self.out, self.aux, grads

@@ -270,7 +270,7 @@ __global__ void __launch_bounds__(128)
 bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d_xp,
                     const int32_t* __restrict__ slot_dst, const WT* __restrict__ wr,
                     const float* __restrict__ dz, float* __restrict__ d_x, int T, int D, int E, int k,
-                    int residual, int d_tile) {
+                    int residual, int d_tile, int S, int shared_row0, int shared_stride) {
   extern __shared__ __align__(16) float w_s[];  // [E][d_tile]
   const int d0 = blockIdx.x * d_tile;
   // a warp fills 32 consecutive d of one expert: no bank conflicts; the strided reads of
@@ -302,6 +302,19 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
         const int r = __ldg(slot_dst + (size_t)tq[q] * k + i);
         v[q] = __ldg(reinterpret_cast<const float4*>(d_xp + (size_t)r * D) + c);
       }
+#pragma unroll
+      for (int q = 0; q < kFinTokens; ++q) {
+        acc[q].x += v[q].x;
+        acc[q].y += v[q].y;
+        acc[q].z += v[q].z;
+        acc[q].w += v[q].w;
+      }
+    }
+    for (int s = 0; s < S; ++s) {  // shared experts: row shared_row0 + s * shared_stride + t of d_xp
+      float4 v[kFinTokens];
+#pragma unroll
+      for (int q = 0; q < kFinTokens; ++q)
+        v[q] = __ldg(reinterpret_cast<const float4*>(d_xp + ((size_t)shared_row0 + (size_t)s * shared_stride + tq[q]) * D) + c);
 #pragma unroll
       for (int q = 0; q < kFinTokens; ++q) {
         acc[q].x += v[q].x;
@@ -400,7 +413,7 @@ int launch_bwd_prepare(const float* d_out, const float* o, const int32_t* row_sr
 int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const float* logits,
                            const int32_t* topk_idx, const float* d_gate, const float* aux_coef, float* dz,
                            float* bias_partial, float* dwr_partial, const float* d_xp, const int32_t* slot_dst,
-                           cudaStream_t st) {
+                           cudaStream_t st, int S, int shared_row0, int shared_stride) {
   const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
   const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
   const int rb_threads = router_bwd_threads(E);
@@ -427,16 +440,64 @@ int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const f
   if (desc->router_dtype == AXM_ROUTER_FP32) {
     auto kern = bwd_finalize_kernel<float>;
     kern<<<fgrid, 128, fsm, st>>>(t->d_out, d_xp, slot_dst, static_cast<const float*>(t->router_w), dz, t->d_x, T, D,
-                                  E, k, residual, d_tile);
+                                  E, k, residual, d_tile, S, shared_row0, shared_stride);
   } else {
     auto kern = bwd_finalize_kernel<__nv_bfloat16>;
     kern<<<fgrid, 128, fsm, st>>>(t->d_out, d_xp, slot_dst, static_cast<const __nv_bfloat16*>(t->router_w), dz,
-                                  t->d_x, T, D, E, k, residual, d_tile);
+                                  t->d_x, T, D, E, k, residual, d_tile, S, shared_row0, shared_stride);
   }
   return check_launch("backward");
 }
 
 constexpr int kTrainAlign = 64;
+
+int launch_combine_strided(const AxmMoeDesc* desc, const void* x, const void* o, const void* o_shared,
+                           int shared_stride, const int32_t* slot_dst, const float* topk_gate, void* y, void* out,
+                           cudaStream_t st);
+
+// Shared experts in the training layout: every shared expert s gets its own copy of the token
+// rows at rows [row0 + s * Tp, row0 + s * Tp + T) of x_perm, followed by zero rows up to Tp (a
+// multiple of 64), and one ordinary segment {a_row0 = out_row0 = row0 + s * Tp, rows = Tp,
+// expert = s} behind the routed experts' segments.  With that every backward kernel treats a
+// shared expert like a routed one that received all tokens.
+__global__ void __launch_bounds__(256)
+train_shared_rows_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ x_perm,
+                         AxmSegment* __restrict__ segments, int T, int Tp, int D, int E, int S, int row0) {
+  if (blockIdx.x == 0 && (int)threadIdx.x < S) {
+    AxmSegment sg;
+    sg.a_row0 = sg.out_row0 = row0 + (int)threadIdx.x * Tp;
+    sg.rows = Tp;
+    sg.expert = threadIdx.x;
+    segments[E + threadIdx.x] = sg;
+  }
+  const int chunks = D / 8;
+  const long long total = (long long)Tp * chunks;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / chunks), c = (int)(i - (long long)t * chunks);
+    const uint4 v = t < T ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)t * D) + c) : make_uint4(0u, 0u, 0u, 0u);
+    for (int s = 0; s < S; ++s)
+      reinterpret_cast<uint4*>(x_perm + ((size_t)row0 + (size_t)s * Tp + t) * D)[c] = v;
+  }
+}
+
+// Upstream gradient of the shared experts' rows: d_o[row0 + s * Tp + t] = bf16(dOut[t]) (they
+// enter the output with weight 1), zero rows behind the tokens.
+__global__ void __launch_bounds__(256)
+bwd_prepare_shared_kernel(const float* __restrict__ d_out, __nv_bfloat16* __restrict__ d_o, int T, int Tp, int D,
+                          int S, int row0) {
+  const int chunks = D / 4;
+  const long long total = (long long)Tp * chunks;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / chunks), c = (int)(i - (long long)t * chunks);
+    uint2 v = make_uint2(0u, 0u);
+    if (t < T) {
+      const float4 a = __ldg(reinterpret_cast<const float4*>(d_out + (size_t)t * D) + c);
+      v = make_uint2(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w));
+    }
+    for (int s = 0; s < S; ++s)
+      reinterpret_cast<uint2*>(d_o + ((size_t)row0 + (size_t)s * Tp + t) * D)[c] = v;
+  }
+}
 
 struct TrainWs {
   int32_t* status;
@@ -457,7 +518,9 @@ struct TrainWs {
   void *x_perm, *g, *u, *h, *o, *d_o, *d_g, *d_u, *d_xp;
   void* router_scratch;
   size_t router_scratch_bytes;
-  int rows_max;
+  int rows_max;     // rows of every row buffer: routed rows (padded) + shared experts' rows
+  int shared_row0;  // first row of shared expert 0 (a fixed place behind the routed rows)
+  int shared_rows;  // rows per shared expert: the tokens padded to a multiple of 64
   size_t bytes;
 };
 
@@ -469,9 +532,13 @@ static TrainWs carve_train(const AxmMoeDesc* d, void* base) {
     off += (n + 255) & ~static_cast<size_t>(255);
     return p;
   };
-  const size_t T = d->tokens, D = d->d_model, F = d->d_ff, E = d->num_experts, k = d->top_k;
-  const size_t R = (T * k + (kTrainAlign - 1) * E + kTrainAlign - 1) / kTrainAlign * kTrainAlign;
+  const size_t T = d->tokens, D = d->d_model, F = d->d_ff, E = d->num_experts, k = d->top_k, S = d->num_shared;
+  const size_t R0 = (T * k + (kTrainAlign - 1) * E + kTrainAlign - 1) / kTrainAlign * kTrainAlign;
+  const size_t Tp = (T + kTrainAlign - 1) / kTrainAlign * kTrainAlign;
+  const size_t R = R0 + S * Tp;
   w.rows_max = (int)R;
+  w.shared_row0 = (int)R0;
+  w.shared_rows = (int)Tp;
   w.status = static_cast<int32_t*>(take(4));
   w.logits = static_cast<float*>(take(4 * T * E));
   w.topk_idx = static_cast<int32_t*>(take(4 * T * k));
@@ -479,9 +546,9 @@ static TrainWs carve_train(const AxmMoeDesc* d, void* base) {
   w.block_counts = static_cast<int32_t*>(take(4 * AXM_ROUTE_BLOCKS * E));
   w.counts = static_cast<int32_t*>(take(4 * E));
   w.offsets = static_cast<int32_t*>(take(4 * (E + 1)));
-  w.row_src = static_cast<int32_t*>(take(4 * R));
+  w.row_src = static_cast<int32_t*>(take(4 * R0));
   w.slot_dst = static_cast<int32_t*>(take(4 * T * k));
-  w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * E));
+  w.segments = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (E + S)));
   w.aux_partial = static_cast<float*>(take(4 * AXM_ROUTE_BLOCKS * E));
   w.aux_coef = static_cast<float*>(take(4 * E));
   w.d_gate = static_cast<float*>(take(4 * T * k));
@@ -512,10 +579,10 @@ static int validate_train(const AxmMoeDesc* d) {
     return fail(AXM_ERR_ARGUMENT, "num_experts %d not in 1..256", d->num_experts);
   if (d->top_k <= 0 || d->top_k > 8 || d->top_k > d->num_experts)
     return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..min(num_experts, 8)", d->top_k);
-  if (d->num_shared != 0) return fail(AXM_ERR_ARGUMENT, "the training step does not take shared experts");
+  if (d->num_shared < 0 || d->num_shared > 8) return fail(AXM_ERR_ARGUMENT, "num_shared %d not in 0..8", d->num_shared);
   if (d->router_dtype != AXM_ROUTER_BF16 && d->router_dtype != AXM_ROUTER_FP32)
     return fail(AXM_ERR_ARGUMENT, "router_dtype %d unknown", d->router_dtype);
-  if ((long long)d->tokens * d->top_k + 64LL * d->num_experts > 0x7fffffffLL)
+  if ((long long)d->tokens * d->top_k + 64LL * d->num_experts + ((long long)d->tokens + 64) * d->num_shared > 0x7fffffffLL)
     return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
   return AXM_OK;
 }
@@ -544,14 +611,17 @@ extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* 
   if (int rc = validate_train(desc)) return rc;
   if (!t || !t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->out)
     return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_train: x, router_w, w_gate, w_up, w_down, out are required");
+  if (desc->num_shared > 0 && (!t->shared_gate || !t->shared_up || !t->shared_down))
+    return fail(AXM_ERR_ARGUMENT, "num_shared > 0 needs shared_gate, shared_up and shared_down");
   TrainWs w;
   if (int rc = check_ws(desc, workspace, workspace_bytes, &w)) return rc;
   if (int rc = require_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int T = desc->tokens, E = desc->num_experts, k = desc->top_k;
+  const int T = desc->tokens, E = desc->num_experts, k = desc->top_k, S = desc->num_shared;
   AxmMoeDesc d = *desc;
   // ws.counts holds this call's counts; the saved h of the training layout is one bf16 term
   d.flags &= ~(AXM_FLAG_HIST_ACCUMULATE | AXM_FLAG_H_EXACT);
+  d.num_shared = 0;  // the routed part; the shared experts follow as ordinary segments of their own
   bool router_cleared_status = false;
   int rc = launch_router_auto(&d, t->x, t->router_w, t->router_bias, w.logits, w.topk_idx, w.topk_gate,
                               w.block_counts, w.router_scratch, w.router_scratch_bytes, w.status, stream,
@@ -565,7 +635,23 @@ extern "C" int axm_moe_forward_train(const AxmMoeDesc* desc, const AxmMoeTrain* 
                               t->w_down, nullptr, nullptr, nullptr, w.h, w.o, w.rows_max, w.status, st,
                               nullptr, nullptr, w.g, w.u)))
     return rc;
-  if ((rc = axm_moe_combine(desc, t->x, w.o, nullptr, w.slot_dst, w.topk_gate, nullptr, t->out, stream)))
+  if (S > 0) {
+    train_shared_rows_kernel<<<2 * sm_count(), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x),
+                                                             static_cast<__nv_bfloat16*>(w.x_perm), w.segments, T,
+                                                             w.shared_rows, desc->d_model, E, S, w.shared_row0);
+    AxmMoeDesc ds = d;
+    ds.num_experts = S;
+    ds.top_k = 1;
+    if ((rc = launch_expert_ffn(&ds, w.x_perm, w.rows_max, nullptr, 0, w.segments + E, S, t->shared_gate,
+                                t->shared_up, t->shared_down, nullptr, nullptr, nullptr, w.h, w.o, w.rows_max,
+                                w.status, st, nullptr, nullptr, w.g, w.u)))
+      return rc;
+  }
+  AxmMoeDesc dc = *desc;
+  dc.flags &= ~(AXM_FLAG_HIST_ACCUMULATE | AXM_FLAG_H_EXACT);
+  const float* o_shared = S > 0 ? static_cast<const float*>(w.o) + (size_t)w.shared_row0 * desc->d_model : nullptr;
+  if ((rc = launch_combine_strided(&dc, t->x, w.o, o_shared, w.shared_rows, w.slot_dst, w.topk_gate, nullptr, t->out,
+                                   st)))
     return rc;
   // auxiliary loss and the constants its gradient needs
   if (int rc2 = launch_aux_partial(w.logits, w.aux_partial, T, E, st)) return rc2;
@@ -581,6 +667,16 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   if (int rc = validate_train(desc)) return rc;
   if (!t || !t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->d_out || !t->d_x)
     return fail(AXM_ERR_ARGUMENT, "axm_moe_backward: x, weights, d_out and d_x are required");
+  const int S = desc->num_shared;
+  if (S > 0) {
+    if (!t->shared_gate || !t->shared_up || !t->shared_down)
+      return fail(AXM_ERR_ARGUMENT, "num_shared > 0 needs shared_gate, shared_up and shared_down");
+    const bool routed = t->d_w_gate || t->d_w_up || t->d_w_down;
+    const bool shared_all = t->d_shared_gate && t->d_shared_up && t->d_shared_down;
+    const bool shared_any = t->d_shared_gate || t->d_shared_up || t->d_shared_down;
+    if (routed != shared_any || shared_any != shared_all)
+      return fail(AXM_ERR_ARGUMENT, "shared experts' weight gradients: all three exactly when the routed experts' are given");
+  }
   TrainWs w;
   if (int rc = check_ws(desc, workspace, workspace_bytes, &w)) return rc;
   if (int rc = require_device()) return rc;
@@ -594,12 +690,27 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
   if ((rc = launch_bwd_prepare(t->d_out, static_cast<const float*>(w.o), w.row_src, w.topk_gate, w.offsets, w.d_o,
                                w.d_gate, D, E, k, st)))
     return rc;
-  if ((rc = axm_moe_expert_ffn_backward(desc, w.segments, E, w.rows_max, w.x_perm, w.h, w.g, w.u, w.d_o,
+  AxmMoeDesc dr = *desc;
+  dr.num_shared = 0;  // the routed experts; the shared ones follow as experts of their own
+  if ((rc = axm_moe_expert_ffn_backward(&dr, w.segments, E, w.rows_max, w.x_perm, w.h, w.g, w.u, w.d_o,
                                         t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.d_xp,
                                         t->d_w_gate, t->d_w_up, t->d_w_down, w.status, stream)))
     return rc;
+  if (S > 0) {
+    bwd_prepare_shared_kernel<<<2 * sm_count(), 256, 0, st>>>(t->d_out, static_cast<__nv_bfloat16*>(w.d_o),
+                                                              desc->tokens, w.shared_rows, D, S, w.shared_row0);
+    AxmMoeDesc ds = *desc;
+    ds.num_experts = S;
+    ds.num_shared = 0;
+    ds.top_k = 1;
+    if ((rc = axm_moe_expert_ffn_backward(&ds, w.segments + E, S, w.rows_max, w.x_perm, w.h, w.g, w.u, w.d_o,
+                                          t->shared_gate, t->shared_up, t->shared_down, w.d_g, w.d_u, w.d_xp,
+                                          t->d_shared_gate, t->d_shared_up, t->d_shared_down, w.status, stream)))
+      return rc;
+  }
   return launch_bwd_source_tail(desc, t, w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, w.aux_partial,
-                                w.dwr_partial, static_cast<const float*>(w.d_xp), w.slot_dst, st);
+                                w.dwr_partial, static_cast<const float*>(w.d_xp), w.slot_dst, st, S, w.shared_row0,
+                                w.shared_rows);
 }
 
 // ---- optimizer step for the MoE weights ---------------------------------------------

@@ -50,7 +50,7 @@ int launch_bwd_prepare(const float* d_out, const float* o, const int32_t* row_sr
 int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const float* logits,
                            const int32_t* topk_idx, const float* d_gate, const float* aux_coef, float* dz,
                            float* bias_partial, float* dwr_partial, const float* d_xp, const int32_t* slot_dst,
-                           cudaStream_t st);
+                           cudaStream_t st, int S, int shared_row0, int shared_stride);
 
 namespace {
 
@@ -345,5 +345,5 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
   if ((rc = axm_ep_return(&lb, step, w.ret_segments, w.o, w.scratch, w.status, stream))) return rc;
   if ((rc = axm_ep_wait_return(&lb, step, w.status, stream))) return rc;
   return launch_bwd_source_tail(&c.d_route, t, w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, w.aux_partial,
-                                w.dwr_partial, dxp_back, w.slot_dst, st);
+                                w.dwr_partial, dxp_back, w.slot_dst, st, 0, 0, 0);
 }

@@ -219,7 +219,7 @@ __global__ void __launch_bounds__(256)
 combine_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ o,
                const float* __restrict__ o_shared, const int32_t* __restrict__ slot_dst,
                const float* __restrict__ topk_gate, __nv_bfloat16* __restrict__ y,
-               __nv_bfloat16* __restrict__ out, int T, int D, int S, int residual) {
+               __nv_bfloat16* __restrict__ out, int T, int D, int S, int residual, int shared_stride) {
   const int chunks = D / 8;
   const long long total = (long long)T * chunks;
   for (long long g = (long long)blockIdx.x * blockDim.x + threadIdx.x; g < total;
@@ -257,7 +257,7 @@ combine_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ o,
       acc[7] = fmaf(gw[i], vb[i].w, acc[7]);
     }
     for (int s = 0; s < S; ++s) {
-      const float4* row = reinterpret_cast<const float4*>(o_shared + ((size_t)s * T + t) * D) + 2 * c;
+      const float4* row = reinterpret_cast<const float4*>(o_shared + ((size_t)s * shared_stride + t) * D) + 2 * c;
       float4 a = __ldg(row), b = __ldg(row + 1);
       acc[0] += a.x;
       acc[1] += a.y;
@@ -290,11 +290,11 @@ combine_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict__ o,
 template <int K>
 static void launch_combine(int blocks, cudaStream_t st, const void* x, const void* o,
                            const void* o_shared, const int32_t* slot_dst, const float* topk_gate,
-                           void* y, void* out, const AxmMoeDesc* d, int residual) {
+                           void* y, void* out, const AxmMoeDesc* d, int residual, int shared_stride) {
   combine_kernel<K><<<blocks, 256, 0, st>>>(
       static_cast<const __nv_bfloat16*>(x), static_cast<const float*>(o),
       static_cast<const float*>(o_shared), slot_dst, topk_gate, static_cast<__nv_bfloat16*>(y),
-      static_cast<__nv_bfloat16*>(out), d->tokens, d->d_model, d->num_shared, residual);
+      static_cast<__nv_bfloat16*>(out), d->tokens, d->d_model, d->num_shared, residual, shared_stride);
 }
 
 int launch_permute(const AxmMoeDesc* d, const void* x, const int32_t* topk_idx,
@@ -324,6 +324,41 @@ int validate_perm(const AxmMoeDesc* d) {
   if ((long long)d->tokens * d->top_k + (long long)d->tokens * d->num_shared > 0x7fffffffLL)
     return fail(AXM_ERR_ARGUMENT, "row count overflows int32");
   return AXM_OK;
+}
+}  // namespace axm
+
+namespace axm {
+// Combine with the shared experts' rows `shared_stride` rows apart ([S][shared_stride][D] fp32; the
+// public entry point passes the token count, the training layout its padded token count).
+int launch_combine_strided(const AxmMoeDesc* desc, const void* x, const void* o, const void* o_shared,
+                           int shared_stride, const int32_t* slot_dst, const float* topk_gate, void* y, void* out,
+                           cudaStream_t st) {
+  if (int rc = validate_perm(desc)) return rc;
+  if (!o || !slot_dst || !topk_gate || !out) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: null pointer");
+  const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
+  if (residual && !x) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: residual without x");
+  if (desc->num_shared > 0 && !o_shared) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: shared experts without o_shared");
+  if (desc->tokens == 0) return AXM_OK;
+  if (int rc = require_device()) return rc;
+  long long total = (long long)desc->tokens * (desc->d_model / 8);
+  int blocks = (int)((total + 255) / 256);
+  int cap = sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  switch (desc->top_k) {
+#define AXM_COMBINE_CASE(K) \
+  case K: launch_combine<K>(blocks, st, x, o, o_shared, slot_dst, topk_gate, y, out, desc, residual, shared_stride); break;
+    AXM_COMBINE_CASE(1)
+    AXM_COMBINE_CASE(2)
+    AXM_COMBINE_CASE(3)
+    AXM_COMBINE_CASE(4)
+    AXM_COMBINE_CASE(5)
+    AXM_COMBINE_CASE(6)
+    AXM_COMBINE_CASE(7)
+    AXM_COMBINE_CASE(8)
+#undef AXM_COMBINE_CASE
+    default: return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..8", desc->top_k);
+  }
+  return check_launch("combine_kernel");
 }
 }  // namespace axm
 
@@ -367,31 +402,6 @@ extern "C" int axm_moe_build_segments(const AxmMoeDesc* desc, const int32_t* off
 extern "C" int axm_moe_combine(const AxmMoeDesc* desc, const void* x, const void* o,
                                const void* o_shared, const int32_t* slot_dst,
                                const float* topk_gate, void* y, void* out, void* stream) {
-  if (int rc = validate_perm(desc)) return rc;
-  if (!o || !slot_dst || !topk_gate || !out) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: null pointer");
-  const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
-  if (residual && !x) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: residual without x");
-  if (desc->num_shared > 0 && !o_shared) return fail(AXM_ERR_ARGUMENT, "axm_moe_combine: shared experts without o_shared");
-  if (desc->tokens == 0) return AXM_OK;
-  if (int rc = require_device()) return rc;
-  long long total = (long long)desc->tokens * (desc->d_model / 8);
-  int blocks = (int)((total + 255) / 256);
-  int cap = sm_count() * 16;
-  if (blocks > cap) blocks = cap;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  switch (desc->top_k) {
-#define AXM_COMBINE_CASE(K) \
-  case K: launch_combine<K>(blocks, st, x, o, o_shared, slot_dst, topk_gate, y, out, desc, residual); break;
-    AXM_COMBINE_CASE(1)
-    AXM_COMBINE_CASE(2)
-    AXM_COMBINE_CASE(3)
-    AXM_COMBINE_CASE(4)
-    AXM_COMBINE_CASE(5)
-    AXM_COMBINE_CASE(6)
-    AXM_COMBINE_CASE(7)
-    AXM_COMBINE_CASE(8)
-#undef AXM_COMBINE_CASE
-    default: return fail(AXM_ERR_ARGUMENT, "top_k %d not in 1..8", desc->top_k);
-  }
-  return check_launch("combine_kernel");
+  return launch_combine_strided(desc, x, o, o_shared, desc ? desc->tokens : 0, slot_dst, topk_gate, y, out,
+                                static_cast<cudaStream_t>(stream));
 }

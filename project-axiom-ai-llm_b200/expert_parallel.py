@@ -501,7 +501,8 @@ class ExpertParallelTrainP2P:
             None if d_out is None else d_out.data_ptr(), self.d_x.data_ptr(),
             self.d_router_w.data_ptr(), self.d_w_gate.data_ptr() if g else None,
             self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None,
-            None if self.d_router_bias is None else self.d_router_bias.data_ptr())
+            None if self.d_router_bias is None else self.d_router_bias.data_ptr(),
+            None, None, None, None, None, None)
 
     def forward(self, x):
         """Enqueues the forward pass; self.aux then holds this rank's share of the auxiliary loss."""

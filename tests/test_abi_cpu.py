@@ -44,7 +44,7 @@ def test_struct_sizes_match_header(axm):
     assert ctypes.sizeof(axm.MoeDesc) == 32
     assert ctypes.sizeof(axm.MoeTensors) == 18 * 8
     assert ctypes.sizeof(axm.Segment) == 16
-    assert ctypes.sizeof(axm.MoeTrain) == 17 * 8       # 16 pointers and one float, padded
+    assert ctypes.sizeof(axm.MoeTrain) == 23 * 8       # 22 pointers and one float, padded
     assert ctypes.sizeof(axm.EpLayout) == 8 + 8 * 4 + 4 * 8 + 8 + 2 * 4
     assert ctypes.sizeof(axm.EpTensors) == 15 * 8
 

@@ -153,3 +153,58 @@ def test_router_bias_is_trained(axm, workloads, oracle, cuda_device):
     close(grads["d_router_bias"], ref["dlogits"].sum(0), "d_router_bias")
     close(grads["d_router_w"], ref["dWr"], "dWr with a router bias")
     close(grads["d_x"].cpu() - dY, ref["dX"] - dY.numpy(), "dX with a router bias")
+
+
+def test_train_step_with_shared_experts(axm, workloads, oracle, cuda_device):
+    """Shared experts (every token, weight 1) in the training step.  The oracle's backward covers
+    routed experts; a shared expert is the same arithmetic with every token routed to it at gate 1,
+    so the reference is the routed backward plus, per shared expert, the backward of a one-expert
+    top-1 layer with unit gates and probabilities (its router gradient vanishes identically)."""
+    cfg = workloads.scaled(workloads.CONFIGS["C4"], tokens=200, d_model=128, d_ff=256, num_experts=16, top_k=3,
+                           num_shared=2)
+    alpha = 0.01
+    x, w = workloads.make_inputs(cfg)
+    S = cfg.num_shared
+    assert w["shared_gate"].shape[0] == S
+    dY = torch.randn(cfg.tokens, cfg.d_model, generator=torch.Generator().manual_seed(12))
+    wd = helpers.to_dev(w, cuda_device)
+    layer = axm.MoeTrainLayer(wd, cfg.tokens, cfg.top_k, aux_alpha=alpha)
+    xd, dYd = x.to(cuda_device), dY.to(cuda_device)
+    out, aux, grads = layer.step(xd, dYd)
+    keep = {k: v.clone() for k, v in grads.items()}
+    out2, _, grads2 = layer.step(xd, dYd)           # buffers reused; deterministic
+    torch.cuda.synchronize()
+    assert int(layer.workspace[:4].view(torch.int32).item()) == 0
+    for k_, v in keep.items():
+        assert torch.equal(v, grads2[k_]), k_
+
+    desc = axm.make_desc(cfg.tokens, cfg.d_model, cfg.d_ff, cfg.num_experts, cfg.top_k)
+    logits, idx_d, gate_d, _ = helpers.run_router(axm, desc, xd, wd["router_w"], wd["router_bias"])
+    zl = logits.cpu().numpy()
+    idx, gates = idx_d.cpu().numpy(), gate_d.cpu().numpy()
+    _, _, probs, _, _ = oracle.route(zl, cfg.top_k)
+
+    # forward: the oracle applies the shared experts itself; the inference layer gives the same bytes
+    y_ref, out_ref = oracle.forward(x, w, idx, gates, h_bf16=True)
+    helpers.assert_close_out(out, out_ref, y_ref, what="training forward out with shared experts")
+    inf = axm.MoeLayer(wd, cfg.tokens, cfg.top_k)
+    out_inf, _ = inf.forward(xd)
+    assert torch.equal(out_inf, out2)
+
+    routed = {k_: v for k_, v in w.items() if not k_.startswith("shared_")}
+    ones = np.ones((cfg.tokens, 1), np.float32)
+    zero_idx = np.zeros((cfg.tokens, 1), np.int32)
+    for act_bf16, factor in ((False, 1.0), (True, 0.5)):
+        ref = oracle.backward(x, routed, idx, gates, probs, dY.numpy(), alpha=alpha, act_bf16=act_bf16)
+        dx_ref = ref["dX"] - dY.numpy()
+        for s in range(S):
+            ws = {"router_w": torch.zeros(cfg.d_model, 1), "w_gate": w["shared_gate"][s:s + 1],
+                  "w_up": w["shared_up"][s:s + 1], "w_down": w["shared_down"][s:s + 1]}
+            rs = oracle.backward(x, ws, zero_idx, ones, ones, dY.numpy(), alpha=0.0, act_bf16=act_bf16)
+            dx_ref = dx_ref + (rs["dX"] - dY.numpy())
+            close(grads["d_shared_gate"][s], rs["dWg"][0], f"d_shared_gate[{s}] (bf16 points {act_bf16})", factor)
+            close(grads["d_shared_up"][s], rs["dWu"][0], f"d_shared_up[{s}] (bf16 points {act_bf16})", factor)
+            close(grads["d_shared_down"][s], rs["dWd"][0], f"d_shared_down[{s}] (bf16 points {act_bf16})", factor)
+        close(grads["d_x"].cpu() - dY, dx_ref, f"dX with shared experts (bf16 points {act_bf16})", factor)
+        for gname, oname in (("d_router_w", "dWr"), ("d_w_gate", "dWg"), ("d_w_up", "dWu"), ("d_w_down", "dWd")):
+            close(grads[gname], ref[oname], f"{oname} beside shared experts (bf16 points {act_bf16})", factor)
