@@ -433,13 +433,29 @@ def main():
         h_dx = torch.empty_like(h_dy).pin_memory()
         d_dy = torch.empty_like(d_out)
 
+        copy_in, copy_out = torch.cuda.Stream(), torch.cuda.Stream()
+        ev_dy, ev_fwd, ev_free = torch.cuda.Event(), torch.cuda.Event(), torch.cuda.Event()
+
         def e2e_step():
+            # the upstream gradient comes in while the forward pass runs, the output goes out while
+            # the backward pass runs; x in and d_x out are the exposed copies
+            cur = torch.cuda.current_stream()
+            ev_free.record(cur)                  # the previous step's reads of d_dy are done
+            copy_in.wait_event(ev_free)
             d_x.copy_(h_x, non_blocking=True)
-            d_dy.copy_(h_dy, non_blocking=True)
-            layer.step(d_x, d_dy)
-            h_out.copy_(layer.out, non_blocking=True)
+            with torch.cuda.stream(copy_in):
+                d_dy.copy_(h_dy, non_blocking=True)
+                ev_dy.record(copy_in)
+            layer.forward(d_x)
+            ev_fwd.record(cur)
+            copy_out.wait_event(ev_fwd)
+            with torch.cuda.stream(copy_out):
+                h_out.copy_(layer.out, non_blocking=True)
+            cur.wait_event(ev_dy)
+            layer.backward(d_x, d_dy)
             h_dx.copy_(layer.d_x, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            cur.synchronize()
+            copy_out.synchronize()
     elif world == 1:
         e2e_step = lambda: layer.forward_host(h_x, h_out, d_x, out)
     elif getattr(layer, "c_layer", False):
@@ -465,6 +481,30 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
     e2e_ms /= args.steps
+    # ---- the same with a run of batches in flight: axm_moe_forward_host_batches ------------
+    e2e_stream = None
+    if world == 1 and not training:
+        n_b = max(2, min(args.steps, 64))
+        h_x_b = torch.empty_like(h_x).pin_memory()
+        h_x_b.copy_(h_x)
+        h_out_b = torch.empty_like(h_out).pin_memory()
+        d_x2 = torch.empty(2 * T, D, dtype=torch.bfloat16, device=dev)
+        d_out2 = torch.empty_like(d_x2)
+        h_xs = [h_x if i % 2 == 0 else h_x_b for i in range(n_b)]
+        h_outs = [h_out if i % 2 == 0 else h_out_b for i in range(n_b)]
+        layer.forward_host_batches(h_xs[:3], h_outs[:3], d_x2, d_out2)
+        barrier()
+        e0.record()
+        layer.forward_host_batches(h_xs, h_outs, d_x2, d_out2)
+        e1.record()
+        barrier()
+        es_ms = e0.elapsed_time(e1) / n_b
+        e2e_stream = {"value": T / (es_ms / 1000.0), "unit": "tokens/s", "ms_per_step": es_ms, "batches": n_b,
+                      "h2d_bytes_per_step": h_x.numel() * 2, "d2h_bytes_per_step": h_x.numel() * 2,
+                      "what": "one call over a run of host batches, double-buffered on the device: every "
+                              "batch is copied in, computed and copied out inside the timed region, batch "
+                              "i + 1's copy in and batch i - 1's copy out overlap batch i's compute"}
+        del d_x2, d_out2
     clocks = sampler.stop() if rank == 0 else None
     copy_bytes = h_x.numel() * 2 * world
     h2d_bytes = copy_bytes + (h_dy.numel() * 4 * world if training else 0)
@@ -647,6 +687,8 @@ def main():
             line["sustained"] = sustained
         if h_exact is not None:
             line["h_exact"] = h_exact
+        if e2e_stream is not None:
+            line["e2e_stream"] = e2e_stream
         if ep_check is not None:
             line["ep_check"] = ep_check
         print(json.dumps(line), flush=True)

@@ -160,6 +160,20 @@ AXM_API int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors* te
                                  const void* h_x, void* h_out, void* d_x, void* d_out,
                                  void* workspace, size_t workspace_bytes, void* stream);
 
+/* A run of n_batches (<= 64) batches from pinned host memory, double-buffered on the device:
+ * batch i + 1 is copied in while batch i is computed and batch i - 1 is copied out, so in
+ * steady state a batch costs the longer of its compute and its copies.  Every batch is one
+ * axm_moe_forward over desc->tokens tokens (same bytes out).  h_x[i] / h_out[i]: [T][D] bf16
+ * host buffers; d_x2, d_out2: device buffers of two batches each; workspace: the layer's
+ * workspace plus 256 bytes.  Per-token outputs in `tensors` must be NULL (histogram is allowed
+ * and follows AXM_FLAG_HIST_ACCUMULATE).  Synchronises before returning.  The reference's call
+ * site copies nothing (device-resident activations, core/src/CUDA/kernel/forward_pass.cu:1585-1598);
+ * this is for hosts that feed the layer from host memory. */
+AXM_API int axm_moe_forward_host_batches(const AxmMoeDesc* desc, const AxmMoeTensors* tensors,
+                                         const void* const* h_x, void* const* h_out, int32_t n_batches,
+                                         void* d_x2, void* d_out2, void* workspace,
+                                         size_t workspace_bytes, void* stream);
+
 /* Device address of the int32 status word inside a workspace.  The GEMM kernels
  * store a non-zero code there when one of their bounded waits gives up; a
  * caller that synchronises can read it back.  No reference counterpart (the

@@ -109,6 +109,8 @@ def load():
     lib.axm_moe_forward_prenorm.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, ctypes.c_float, vp, vp, sz, vp]
     lib.axm_moe_rmsnorm.argtypes = [vp, vp, vp, i32, i32, ctypes.c_float, vp]
     lib.axm_moe_forward_host.argtypes = [dp, ctypes.POINTER(MoeTensors), vp, vp, vp, vp, vp, sz, vp]
+    lib.axm_moe_forward_host_batches.argtypes = [dp, ctypes.POINTER(MoeTensors), ctypes.POINTER(vp),
+                                                 ctypes.POINTER(vp), i32, vp, vp, vp, sz, vp]
     lib.axm_moe_status_word.argtypes = [dp, vp, ctypes.POINTER(vp)]
     lib.axm_moe_router.argtypes = [dp, vp, vp, vp, vp, vp, vp, vp, vp]
     lib.axm_moe_router_scratch_bytes.argtypes = [dp, ctypes.POINTER(sz)]
@@ -212,7 +214,8 @@ class MoeLayer:
         self.desc = make_desc(tokens, D, F, E, top_k, S, rdt, flags)
         self.T, self.D, self.F, self.E, self.k, self.S = tokens, D, F, E, top_k, S
         self.device = torch.device(device)
-        self.workspace = torch.empty(max(workspace_bytes(self.desc), 256), dtype=torch.uint8,
+        # 256 spare bytes: the batch pipeline keeps one status word per batch behind the workspace
+        self.workspace = torch.empty(max(workspace_bytes(self.desc), 256) + 256, dtype=torch.uint8,
                                      device=self.device)
         dev = self.device
         self.logits = torch.empty(tokens, E, dtype=torch.float32, device=dev)
@@ -278,6 +281,20 @@ class MoeLayer:
             ctypes.byref(self.desc), ctypes.byref(t), ptr(h_x), ptr(h_out), ptr(d_x), ptr(d_out),
             ptr(self.workspace), self.workspace.numel(), current_stream()))
         return h_out
+
+    def forward_host_batches(self, h_xs, h_outs, d_x2, d_out2):
+        """A run of batches from pinned host memory, double-buffered on the device (batch i + 1
+        comes in while batch i is computed and batch i - 1 goes out); synchronises."""
+        n = len(h_xs)
+        assert n == len(h_outs) and d_x2.shape[0] == 2 * self.T and d_out2.shape[0] == 2 * self.T
+        t = self.tensors(d_x2, d_out2)
+        t.logits = t.topk_idx = t.topk_gate = t.offsets = t.row_src = t.slot_dst = t.y = None
+        xs = (ctypes.c_void_p * n)(*[h.data_ptr() for h in h_xs])
+        outs = (ctypes.c_void_p * n)(*[h.data_ptr() for h in h_outs])
+        check(self.lib.axm_moe_forward_host_batches(
+            ctypes.byref(self.desc), ctypes.byref(t), xs, outs, n, ptr(d_x2), ptr(d_out2),
+            ptr(self.workspace), self.workspace.numel(), current_stream()))
+        return h_outs
 
     def status(self):
         """Reads the workspace status word (synchronises)."""

@@ -424,6 +424,7 @@ constexpr int kHostChunksMax = 8;
 struct HostPipe {
   cudaStream_t in = nullptr, out = nullptr;
   cudaEvent_t arrived[kHostChunksMax] = {}, done[kHostChunksMax] = {}, start = nullptr;
+  cudaEvent_t copied[2] = {};  // batch pipeline: the copy out of slot b has read its device buffer
   bool ok = false;
 };
 HostPipe* host_pipe() {
@@ -435,6 +436,8 @@ HostPipe* host_pipe() {
     if (cudaStreamCreateWithFlags(&p.in, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaStreamCreateWithFlags(&p.out, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
     if (cudaEventCreateWithFlags(&p.start, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    for (int i = 0; i < 2; ++i)
+      if (cudaEventCreateWithFlags(&p.copied[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
     for (int i = 0; i < kHostChunksMax; ++i) {
       if (cudaEventCreateWithFlags(&p.arrived[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
       if (cudaEventCreateWithFlags(&p.done[i], cudaEventDisableTiming) != cudaSuccess) return nullptr;
@@ -600,5 +603,71 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
   if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "pipelined host call: %s", cudaGetErrorString(e));
   for (int c = 0; c < chunks; ++c)
     if (status[c] != 0) return fail(AXM_ERR_TIMEOUT, "a bounded wait in GEMM kernel %d gave up", status[c]);
+  return AXM_OK;
+}
+
+// A run of batches from host memory, double-buffered on the device: batch i + 1 comes in over
+// PCIe while batch i is computed and batch i - 1 goes out, so in steady state a batch costs the
+// longer of its compute and its copies instead of their sum.  Every batch is a complete layer
+// call over desc->tokens tokens (same arithmetic as axm_moe_forward).  d_x2 and d_out2 hold two
+// batches each; the workspace is one layer workspace plus 256 bytes.  Optional per-token outputs
+// in `t` (logits, indices, gates, permutation) are refused: they would describe the last batch
+// only.  Synchronises before returning.
+extern "C" int axm_moe_forward_host_batches(const AxmMoeDesc* desc, const AxmMoeTensors* t,
+                                            const void* const* h_x, void* const* h_out, int32_t n_batches,
+                                            void* d_x2, void* d_out2, void* workspace, size_t workspace_bytes,
+                                            void* stream) {
+  if (int rc = validate_forward(desc)) return rc;
+  if (!t || !h_x || !h_out || !d_x2 || !d_out2)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_host_batches: null pointer");
+  if (n_batches < 0 || n_batches > 64) return fail(AXM_ERR_ARGUMENT, "n_batches %d not in 0..64", n_batches);
+  if (t->logits || t->topk_idx || t->topk_gate || t->offsets || t->row_src || t->slot_dst || t->y)
+    return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_host_batches: per-token outputs are not kept per batch");
+  for (int i = 0; i < n_batches; ++i)
+    if (!h_x[i] || !h_out[i]) return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_host_batches: batch %d has a null buffer", i);
+  if (d_x2 == d_out2) return fail(AXM_ERR_ARGUMENT, "axm_moe_forward_host_batches: d_x2 and d_out2 must differ");
+  if (n_batches == 0 || desc->tokens == 0) return AXM_OK;
+  const size_t ws_bytes = carve(desc, nullptr).bytes;
+  if (workspace == nullptr || (reinterpret_cast<uintptr_t>(workspace) & 255) != 0 || workspace_bytes < ws_bytes + 256)
+    return fail(AXM_ERR_WORKSPACE, "workspace is null, not 256-byte aligned or smaller than %zu bytes", ws_bytes + 256);
+  if (int rc = require_device()) return rc;
+  HostPipe* pipe = host_pipe();
+  if (pipe == nullptr) return fail(AXM_ERR_LAUNCH, "could not create the copy streams");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const size_t batch_bytes = (size_t)desc->tokens * desc->d_model * 2;
+  int32_t* status_all = reinterpret_cast<int32_t*>(static_cast<char*>(workspace) + ws_bytes);  // [64]
+  AXM_CUDA(cudaEventRecord(pipe->start, st));
+  AXM_CUDA(cudaStreamWaitEvent(pipe->in, pipe->start, 0));
+  AXM_CUDA(cudaStreamWaitEvent(pipe->out, pipe->start, 0));
+  for (int i = 0; i < n_batches; ++i) {
+    const int b = i & 1;
+    char* dx = static_cast<char*>(d_x2) + (size_t)b * batch_bytes;
+    char* dout = static_cast<char*>(d_out2) + (size_t)b * batch_bytes;
+    // slot b's input was last read by the layer call of batch i - 2
+    if (i >= 2) AXM_CUDA(cudaStreamWaitEvent(pipe->in, pipe->done[b], 0));
+    AXM_CUDA(cudaMemcpyAsync(dx, h_x[i], batch_bytes, cudaMemcpyHostToDevice, pipe->in));
+    AXM_CUDA(cudaEventRecord(pipe->arrived[b], pipe->in));
+    AXM_CUDA(cudaStreamWaitEvent(st, pipe->arrived[b], 0));
+    // slot b's output was last read by the copy out of batch i - 2
+    if (i >= 2) AXM_CUDA(cudaStreamWaitEvent(st, pipe->copied[b], 0));
+    AxmMoeTensors tt = *t;
+    tt.x = dx;
+    tt.out = dout;
+    if (int rc = axm_moe_forward(desc, &tt, workspace, ws_bytes, stream)) return rc;
+    AXM_CUDA(cudaMemcpyAsync(status_all + i, carve(desc, workspace).status, sizeof(int32_t), cudaMemcpyDeviceToDevice, st));
+    AXM_CUDA(cudaEventRecord(pipe->done[b], st));
+    AXM_CUDA(cudaStreamWaitEvent(pipe->out, pipe->done[b], 0));
+    AXM_CUDA(cudaMemcpyAsync(h_out[i], dout, batch_bytes, cudaMemcpyDeviceToHost, pipe->out));
+    AXM_CUDA(cudaEventRecord(pipe->copied[b], pipe->out));
+  }
+  int32_t status[64] = {};
+  cudaError_t e = cudaStreamSynchronize(pipe->out);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(pipe->in);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e == cudaSuccess) e = cudaMemcpy(status, status_all, sizeof(int32_t) * n_batches, cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(AXM_ERR_LAUNCH, "batch pipeline: %s", cudaGetErrorString(e));
+  for (int i = 0; i < n_batches; ++i)
+    if (status[i] != 0) return fail(AXM_ERR_TIMEOUT, "a bounded wait in GEMM kernel %d gave up (batch %d)", status[i], i);
   return AXM_OK;
 }

@@ -189,6 +189,44 @@ def test_forward_host_matches_forward(axm, workloads, cuda_device, tokens):
         assert torch.equal(h_out, out.cpu()) and torch.equal(layer.histogram, hist)
 
 
+def test_host_batches_pipeline_matches_forward(axm, workloads, cuda_device):
+    """Five different batches through the double-buffered host pipeline: every batch's bytes equal
+    the device-resident call's, whichever of the two device slots it went through; the argument
+    checks happen before any copy."""
+    import ctypes
+    cfg = workloads.scaled(workloads.CONFIGS["C2"], tokens=1536)
+    x, w = workloads.make_inputs(cfg, device=cuda_device)
+    layer = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+    g = torch.Generator(device=cuda_device).manual_seed(77)
+    xs = [x] + [torch.randn(cfg.tokens, cfg.d_model, device=cuda_device, generator=g).to(torch.bfloat16)
+                for _ in range(4)]
+    want = [layer.forward(xi)[0].clone().cpu() for xi in xs]
+    h_xs = [xi.cpu().pin_memory() for xi in xs]
+    h_outs = [torch.zeros_like(h).pin_memory() for h in h_xs]
+    d_x2 = torch.empty(2 * cfg.tokens, cfg.d_model, dtype=torch.bfloat16, device=cuda_device)
+    d_out2 = torch.empty_like(d_x2)
+    for n in (5, 1, 2):
+        for h in h_outs:
+            h.zero_()
+        layer.forward_host_batches(h_xs[:n], h_outs[:n], d_x2, d_out2)
+        for i in range(n):
+            assert torch.equal(h_outs[i], want[i]), f"batch {i} of {n}"
+    assert layer.status() == 0
+    # refusals: per-token outputs requested, too many batches, a null batch pointer
+    t = layer.tensors(d_x2, d_out2)
+    ptrs = (ctypes.c_void_p * 2)(h_xs[0].data_ptr(), h_xs[1].data_ptr())
+    outs = (ctypes.c_void_p * 2)(h_outs[0].data_ptr(), h_outs[1].data_ptr())
+    call = lambda tt, xs_, n: layer.lib.axm_moe_forward_host_batches(
+        ctypes.byref(layer.desc), ctypes.byref(tt), xs_, outs, n, axm.ptr(d_x2), axm.ptr(d_out2),
+        axm.ptr(layer.workspace), layer.workspace.numel(), axm.current_stream())
+    assert call(t, ptrs, 2) == axm.AXM_ERR_ARGUMENT          # logits etc. still set
+    t.logits = t.topk_idx = t.topk_gate = t.offsets = t.row_src = t.slot_dst = t.y = None
+    assert call(t, ptrs, 65) == axm.AXM_ERR_ARGUMENT
+    bad = (ctypes.c_void_p * 2)(h_xs[0].data_ptr(), None)
+    assert call(t, bad, 2) == axm.AXM_ERR_ARGUMENT
+    assert call(t, ptrs, 2) == axm.AXM_OK
+
+
 def test_empty_input(axm, workloads, cuda_device):
     cfg = workloads.scaled(workloads.CONFIGS["C1"], tokens=0)
     _, w = workloads.make_inputs(workloads.scaled(cfg, tokens=1), device=cuda_device)
