@@ -298,7 +298,7 @@ def main():
     training = cfg.training
     if training and world > 1:
         # the same step sharded: tokens and experts over the ranks, both exchanges by this library's
-        # peer-memory kernels, the replicated router's gradients summed with one small all-reduce each
+        # peer-memory kernels, the replicated router's gradients summed with one small all-reduce
         ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
         assert T % world == 0 and cfg.num_experts % world == 0
         tl = T // world
@@ -573,7 +573,7 @@ def main():
             acc[0] += ev[0].elapsed_time(ev[1]) / reps
             acc[1] += ev[1].elapsed_time(ev[2]) / reps
         ep_stages = {"forward (saves activations, auxiliary loss)": {"ms": acc[0]},
-                     "backward (incl. three small all-reduces)": {"ms": acc[1]},
+                     "backward (incl. the all-reduce of the router gradients)": {"ms": acc[1]},
                      "rows_received_rank0": int(layer.rows_received.item())}
     if world > 1 and not training:
         acc = {}

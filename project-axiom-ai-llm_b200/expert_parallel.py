@@ -407,8 +407,8 @@ class ExpertParallelTrainP2P:
 
     step(x_local, d_out_local) -> (out_local, aux_loss, grads): grads["d_x"] covers this rank's
     tokens, d_w_gate / d_w_up / d_w_down this rank's experts; d_router_w, d_router_bias and the
-    auxiliary loss are summed over the ranks here (one small all-reduce each), because the router
-    is replicated.  GPU only."""
+    auxiliary loss are summed over the ranks here (they share one buffer: one small all-reduce),
+    because the router is replicated.  GPU only."""
 
     ALIGN = 64
 
@@ -468,12 +468,16 @@ class ExpertParallelTrainP2P:
         self.rows_received.zero_()
         f32 = torch.float32
         self.out = torch.empty(tokens_local, D, dtype=torch.bfloat16, device=dev)
-        self.aux = torch.zeros(1, dtype=f32, device=dev)
+        # the three quantities that are summed over the ranks live in one buffer: one all-reduce
+        has_bias = local_weights.get("router_bias") is not None
+        n_wr = D * num_experts
+        n_wr_pad = (n_wr + 3) // 4 * 4                    # keeps the bias gradient 16-byte aligned
+        self.replicated = torch.zeros(n_wr_pad + (num_experts if has_bias else 0) + 1, dtype=f32, device=dev)
+        self.d_router_w = self.replicated[:n_wr].view(D, num_experts)
+        self.d_router_bias = self.replicated[n_wr_pad:n_wr_pad + num_experts] if has_bias else None
+        self.aux = self.replicated[-1:]
         self.histogram = torch.zeros(num_experts, dtype=torch.int32, device=dev)
         self.d_x = torch.empty(tokens_local, D, dtype=f32, device=dev)
-        self.d_router_w = torch.empty(D, num_experts, dtype=f32, device=dev)
-        self.d_router_bias = (torch.empty(num_experts, dtype=f32, device=dev)
-                              if local_weights.get("router_bias") is not None else None)
         self.weight_grads = weight_grads
         if weight_grads:
             self.d_w_gate = torch.empty(self.El, D, F, dtype=f32, device=dev)
@@ -522,10 +526,7 @@ class ExpertParallelTrainP2P:
                                            ptr(self.workspace), self.workspace.numel(), self.step_no,
                                            current_stream()))
         if reduce:
-            dist.all_reduce(self.d_router_w, group=self.group)
-            if self.d_router_bias is not None:
-                dist.all_reduce(self.d_router_bias, group=self.group)
-            dist.all_reduce(self.aux, group=self.group)
+            dist.all_reduce(self.replicated, group=self.group)
         return self.d_x
 
     def step(self, x, d_out, reduce=True):
