@@ -265,23 +265,35 @@ __global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __re
 // for the whole block (broadcast).
 constexpr int kFinTokens = 4;
 
-template <typename WT>
+// ER > 0: E == ER and the thread keeps its 4 x ER router weights in registers (no shared memory);
+// ER == 0: any E, the block's weight slice sits in shared memory.
+template <typename WT, int ER>
 __global__ void __launch_bounds__(128)
 bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d_xp,
                     const int32_t* __restrict__ slot_dst, const WT* __restrict__ wr,
                     const float* __restrict__ dz, float* __restrict__ d_x, int T, int D, int E, int k,
                     int residual, int d_tile, int S, int shared_row0, int shared_stride) {
-  extern __shared__ __align__(16) float w_s[];  // [E][d_tile]
+  extern __shared__ __align__(16) float w_s[];  // [E][d_tile] (ER == 0)
   const int d0 = blockIdx.x * d_tile;
-  // a warp fills 32 consecutive d of one expert: no bank conflicts; the strided reads of
-  // Wr stay in L1/L2 (the slice is E * d_tile elements)
-  for (int i = threadIdx.x; i < E * d_tile; i += blockDim.x) {
-    const int e = i / d_tile, dd = i - e * d_tile;
-    w_s[i] = d0 + dd < D ? (float)wr[(size_t)(d0 + dd) * E + e] : 0.0f;
+  if (ER == 0) {
+    // a warp fills 32 consecutive d of one expert: no bank conflicts; the strided reads of
+    // Wr stay in L1/L2 (the slice is E * d_tile elements)
+    for (int i = threadIdx.x; i < E * d_tile; i += blockDim.x) {
+      const int e = i / d_tile, dd = i - e * d_tile;
+      w_s[i] = d0 + dd < D ? (float)wr[(size_t)(d0 + dd) * E + e] : 0.0f;
+    }
+    __syncthreads();
   }
-  __syncthreads();
   const int dl = threadIdx.x * 4;
   if (dl >= d_tile || d0 + dl >= D) return;
+  float4 w_r[ER > 0 ? ER : 1];
+  if (ER > 0) {  // D is a multiple of 8: the thread's four d are all inside
+#pragma unroll
+    for (int e = 0; e < ER; ++e) {
+      const WT* row = wr + (size_t)(d0 + dl) * ER + e;
+      w_r[e] = make_float4((float)row[0], (float)row[ER], (float)row[2 * ER], (float)row[3 * ER]);
+    }
+  }
   const int c = (d0 + dl) / 4;
   const int t0 = (int)(((long long)blockIdx.y * T) / gridDim.y);
   const int t1 = (int)(((long long)(blockIdx.y + 1) * T) / gridDim.y);
@@ -324,13 +336,28 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
       }
     }
     auto add_e = [&](int e, int q, float zv) {
-      const float4 wv = *reinterpret_cast<const float4*>(w_s + e * d_tile + dl);
+      const float4 wv = ER > 0 ? w_r[e] : *reinterpret_cast<const float4*>(w_s + e * d_tile + dl);
       rt[q].x = fmaf(wv.x, zv, rt[q].x);
       rt[q].y = fmaf(wv.y, zv, rt[q].y);
       rt[q].z = fmaf(wv.z, zv, rt[q].z);
       rt[q].w = fmaf(wv.w, zv, rt[q].w);
     };
-    if ((E & 3) == 0) {
+    if (ER > 0) {
+#pragma unroll
+      for (int e = 0; e < ER; e += 4) {
+        float4 zz[kFinTokens];
+#pragma unroll
+        for (int q = 0; q < kFinTokens; ++q)
+          zz[q] = __ldg(reinterpret_cast<const float4*>(dz + (size_t)tq[q] * ER + e));
+#pragma unroll
+        for (int q = 0; q < kFinTokens; ++q) {
+          add_e(e, q, zz[q].x);
+          add_e(e + 1, q, zz[q].y);
+          add_e(e + 2, q, zz[q].z);
+          add_e(e + 3, q, zz[q].w);
+        }
+      }
+    } else if ((E & 3) == 0) {
       for (int e = 0; e < E; e += 4) {
         float4 zz[kFinTokens];
 #pragma unroll
@@ -391,11 +418,12 @@ int bwd_source_limits(int E, int router_dtype) {
   int rc;
   if ((rc = ensure_dynamic_smem(reinterpret_cast<const void*>(router_bwd_kernel), sm, &rb_cache, "router_bwd_kernel")))
     return rc;
+  if (E == 8 || E == 16) return AXM_OK;  // weights in registers: no dynamic shared memory
   const size_t fsm = sizeof(float) * (size_t)E * finalize_tile(E);
   static SmemLimitCache cache32 = {}, cache16 = {};
   if (router_dtype == AXM_ROUTER_FP32)
-    return ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<float>), fsm, &cache32, "bwd_finalize_kernel");
-  return ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<__nv_bfloat16>), fsm, &cache16, "bwd_finalize_kernel");
+    return ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<float, 0>), fsm, &cache32, "bwd_finalize_kernel");
+  return ensure_dynamic_smem(reinterpret_cast<const void*>(bwd_finalize_kernel<__nv_bfloat16, 0>), fsm, &cache16, "bwd_finalize_kernel");
 }
 
 // d_o[r] = bf16(gate * dOut[token of r]) and d_gate[slot] = <dOut[t], o[r]> over the rows
@@ -429,22 +457,30 @@ int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const f
   if (t->d_router_w != nullptr) {
     dim3 grid((D / 2 + 127) / 128, kDwrChunks);
     dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), dz, dwr_partial, T, D, E);
-    dwr_reduce_kernel<<<(D * E + 255) / 256, 256, 0, st>>>(dwr_partial, t->d_router_w, D, E);
+    dwr_reduce_kernel<<<(D * E + 63) / 64, 64, 0, st>>>(dwr_partial, t->d_router_w, D, E);  // many small blocks: the sums are latency-bound
   }
   dim3 fgrid((D + d_tile - 1) / d_tile, 1);
-  // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory)
-  int per_sm = (int)((200u * 1024u) / (fsm + 1024));
+  const bool in_regs = E == 8 || E == 16;
+  // one wave: as many blocks per SM as the weight slices fit (about 200 KB of shared memory);
+  // with the weights in registers, what the register file holds
+  int per_sm = in_regs ? 3 : (int)((200u * 1024u) / (fsm + 1024));
   per_sm = per_sm < 1 ? 1 : (per_sm > 12 ? 12 : per_sm);
   fgrid.y = (unsigned)((per_sm * sm_count() + fgrid.x - 1) / fgrid.x);
   if ((int)fgrid.y > T) fgrid.y = T;
+  auto launch = [&](auto kern, const auto* wr_typed, size_t smem) {
+    kern<<<fgrid, 128, smem, st>>>(t->d_out, d_xp, slot_dst, wr_typed, dz, t->d_x, T, D, E, k, residual, d_tile, S,
+                                   shared_row0, shared_stride);
+  };
   if (desc->router_dtype == AXM_ROUTER_FP32) {
-    auto kern = bwd_finalize_kernel<float>;
-    kern<<<fgrid, 128, fsm, st>>>(t->d_out, d_xp, slot_dst, static_cast<const float*>(t->router_w), dz, t->d_x, T, D,
-                                  E, k, residual, d_tile, S, shared_row0, shared_stride);
+    const float* w = static_cast<const float*>(t->router_w);
+    if (E == 8) launch(bwd_finalize_kernel<float, 8>, w, 0);
+    else if (E == 16) launch(bwd_finalize_kernel<float, 16>, w, 0);
+    else launch(bwd_finalize_kernel<float, 0>, w, fsm);
   } else {
-    auto kern = bwd_finalize_kernel<__nv_bfloat16>;
-    kern<<<fgrid, 128, fsm, st>>>(t->d_out, d_xp, slot_dst, static_cast<const __nv_bfloat16*>(t->router_w), dz,
-                                  t->d_x, T, D, E, k, residual, d_tile, S, shared_row0, shared_stride);
+    const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(t->router_w);
+    if (E == 8) launch(bwd_finalize_kernel<__nv_bfloat16, 8>, w, 0);
+    else if (E == 16) launch(bwd_finalize_kernel<__nv_bfloat16, 16>, w, 0);
+    else launch(bwd_finalize_kernel<__nv_bfloat16, 0>, w, fsm);
   }
   return check_launch("backward");
 }

@@ -13,9 +13,11 @@
 //             dXp and the three weight gradients of its own experts -> return of the fp32 dXp rows
 //             -> token's rank: router gradient, dX.
 //
-// Region A keeps the forward rows until the backward pass has used them; the return flag of the
-// backward step is raised only after the weight-gradient GEMMs, so a peer that runs ahead into
-// its next forward step cannot overwrite rows that are still being read here.
+// Region A keeps the forward rows until the backward pass has used them.  A peer that runs ahead
+// into its next forward step cannot overwrite them: it writes rows only after it has seen the
+// counts of ALL ranks for that step, and a rank posts its counts when its own stream gets there,
+// i.e. after its weight-gradient GEMMs.  That is why the dXp rows may travel home (and their flag
+// be raised) on a side stream while the weight gradients are still being computed.
 //
 // What the caller still reduces over the ranks (replicated parameters): d_router_w,
 // d_router_bias and the auxiliary loss are this rank's share; their sum over the ranks is the
@@ -23,6 +25,8 @@
 //
 // The reference engine is single-GPU and has no MoE backward (core/src/CUDA/kernel/
 // backward_pass.cu:1701-2005 covers the dense FFN); conventions as in backward.cu.
+#include <cstdlib>
+
 #include "router.cuh"
 
 namespace axm {
@@ -42,6 +46,11 @@ int launch_ep_segments_split(const AxmEpLayout* l, uint32_t step, AxmSegment* se
                              int32_t* rows_received, AxmSegment* seg_halves, int32_t* split_rows,
                              int32_t* status, cudaStream_t st);
 int launch_ep_zero_pad(const AxmEpLayout* l, uint32_t step, void* buf, cudaStream_t st);
+int launch_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegment* segments, int32_t num_segments,
+                               int32_t rows_total, const void* x_perm, const void* h, const void* g, const void* u,
+                               const void* d_o, const void* w_gate, const void* w_up, const void* w_down, void* d_g,
+                               void* d_u, void* d_xp, void* d_w_gate, void* d_w_up, void* d_w_down, int32_t* status,
+                               void* stream, int phases);
 size_t dwr_partial_floats(int D, int E);
 int launch_aux_partial(const float* logits, float* partial, int T, int E, cudaStream_t st);
 int bwd_source_limits(int E, int router_dtype);
@@ -180,6 +189,29 @@ __global__ void expert_segments_kernel(const AxmSegment* __restrict__ segments, 
                                        int El) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   if (j < El) out[j] = segments[j * G];
+}
+
+// High-priority side stream for the return of the dXp rows under the weight-gradient GEMMs,
+// created once per device and thread.
+struct TrainPipe {
+  cudaStream_t side = nullptr;
+  cudaEvent_t dx_done = nullptr, side_done = nullptr;
+  bool ok = false;
+};
+TrainPipe* train_pipe() {
+  static thread_local TrainPipe pipes[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  TrainPipe& p = pipes[dev];
+  if (!p.ok) {
+    int prio_lo = 0, prio_hi = 0;
+    if (cudaDeviceGetStreamPriorityRange(&prio_lo, &prio_hi) != cudaSuccess) return nullptr;
+    if (cudaStreamCreateWithPriority(&p.side, cudaStreamNonBlocking, prio_hi) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&p.dx_done, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    if (cudaEventCreateWithFlags(&p.side_done, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    p.ok = true;
+  }
+  return &p;
 }
 
 struct Call {
@@ -336,13 +368,33 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
     return rc;
   expert_segments_kernel<<<1, 64, 0, st>>>(w.segments, w.expert_segs, G, c.El);
   if ((rc = launch_ep_zero_pad(&lb, step, do_recv, st))) return rc;
-  if ((rc = axm_moe_expert_ffn_backward(&c.d_ffn, w.expert_segs, c.El, lb.cap, x_recv, w.h, w.g, w.u, do_recv,
-                                        t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.o, t->d_w_gate, t->d_w_up,
-                                        t->d_w_down, w.status, stream)))
+  // AXM_EP_TRAIN_OVERLAP=0 keeps everything on the caller's stream (return after the weight gradients)
+  static const bool overlap = [] {
+    const char* e = getenv("AXM_EP_TRAIN_OVERLAP");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  TrainPipe* pipe = (overlap && wgrad) ? train_pipe() : nullptr;
+  if ((rc = launch_expert_ffn_backward(&c.d_ffn, w.expert_segs, c.El, lb.cap, x_recv, w.h, w.g, w.u, do_recv,
+                                       t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.o, t->d_w_gate, t->d_w_up,
+                                       t->d_w_down, w.status, stream, pipe ? 1 : 3)))
     return rc;
-  // the flag that goes with these rows also tells the sources that their forward rows have been
-  // read (weight gradients included)
-  if ((rc = axm_ep_return(&lb, step, w.ret_segments, w.o, w.scratch, w.status, stream))) return rc;
+  if (pipe != nullptr) {
+    // The dXp rows go home on a side stream while the weight gradients are computed.  Raising the
+    // return flag before the weight gradients have read the forward rows is safe: a source writes
+    // new rows into this rank's receive buffer only after it has seen the counts of ALL ranks for
+    // the next step, and this rank posts its own only when its stream has reached that step.
+    AXM_CUDA(cudaEventRecord(pipe->dx_done, st));
+    AXM_CUDA(cudaStreamWaitEvent(pipe->side, pipe->dx_done, 0));
+    if ((rc = axm_ep_return(&lb, step, w.ret_segments, w.o, w.scratch, w.status, pipe->side))) return rc;
+    AXM_CUDA(cudaEventRecord(pipe->side_done, pipe->side));
+    if ((rc = launch_expert_ffn_backward(&c.d_ffn, w.expert_segs, c.El, lb.cap, x_recv, w.h, w.g, w.u, do_recv,
+                                         t->w_gate, t->w_up, t->w_down, w.d_g, w.d_u, w.o, t->d_w_gate, t->d_w_up,
+                                         t->d_w_down, w.status, stream, 2)))
+      return rc;
+    AXM_CUDA(cudaStreamWaitEvent(st, pipe->side_done, 0));
+  } else {
+    if ((rc = axm_ep_return(&lb, step, w.ret_segments, w.o, w.scratch, w.status, stream))) return rc;
+  }
   if ((rc = axm_ep_wait_return(&lb, step, w.status, stream))) return rc;
   return launch_bwd_source_tail(&c.d_route, t, w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, w.aux_partial,
                                 w.dwr_partial, dxp_back, w.slot_dst, st, 0, 0, 0);

@@ -466,13 +466,15 @@ static int launch_bwd(const CUtensorMap& a0, const CUtensorMap& a1, const CUtens
 
 using namespace axm;
 
-extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegment* segments,
-                                           int32_t num_segments, int32_t rows_total,
-                                           const void* x_perm, const void* h, const void* g,
-                                           const void* u, const void* d_o, const void* w_gate,
-                                           const void* w_up, const void* w_down, void* d_g, void* d_u,
-                                           void* d_xp, void* d_w_gate, void* d_w_up, void* d_w_down,
-                                           int32_t* status, void* stream) {
+namespace axm {
+// phases: bit 0 = the two input-gradient products (dH with the SwiGLU derivative, then dXp),
+// bit 1 = the three weight gradients.  The expert-parallel backward runs them as two calls so
+// that the dXp rows can travel home while the weight gradients are computed.
+int launch_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegment* segments, int32_t num_segments,
+                               int32_t rows_total, const void* x_perm, const void* h, const void* g, const void* u,
+                               const void* d_o, const void* w_gate, const void* w_up, const void* w_down, void* d_g,
+                               void* d_u, void* d_xp, void* d_w_gate, void* d_w_up, void* d_w_down, int32_t* status,
+                               void* stream, int phases) {
   if (desc == nullptr) return fail(AXM_ERR_ARGUMENT, "desc is null");
   const int D = desc->d_model, F = desc->d_ff, E = desc->num_experts;
   if (D <= 0 || F <= 0 || D % 8 || F % 8 || E <= 0)
@@ -509,6 +511,7 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   a.k_total = D;
   a.out0 = d_g;
   a.out1 = d_u;
+  if (phases & 1) {
   rc = AXM_ERR_DEVICE;
   static const bool dh_pairs = [] {  // CTA pairs with TMA-moved epilogue blocks by default; AXM_DH_2SM=0 opts out
     const char* e = getenv("AXM_DH_2SM");
@@ -530,7 +533,8 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   if (rc == AXM_ERR_DEVICE)  // pairs not wanted or not schedulable: the one-SM kernel
     rc = launch_bwd<kDX>(m_dg, m_du, m_wg, m_wu, a, st, "grouped_bwd_kernel<dX>");
   if (rc) return rc;
-  if (!wgrad) return AXM_OK;
+  }
+  if (!wgrad || !(phases & 2)) return AXM_OK;
 
   CUtensorMap k_h, k_do, k_x, k_dg, k_du;  // 64-row boxes: rows are the reduction index
   if ((rc = map_rows(&k_h, h, R, F, 64))) return rc;
@@ -558,4 +562,16 @@ extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegm
   if ((rc = wgrad_one(h, k_h, F, d_o, k_do, D, d_w_down, o_wd, "grouped_bwd_kernel<dWd>"))) return rc;  // h^T dO : [F][D]
   if ((rc = wgrad_one(x_perm, k_x, D, d_g, k_dg, F, d_w_gate, o_wg, "grouped_bwd_kernel<dWg>"))) return rc;  // x^T dG : [D][F]
   return wgrad_one(x_perm, k_x, D, d_u, k_du, F, d_w_up, o_wu, "grouped_bwd_kernel<dWu>");
+}
+}  // namespace axm
+
+extern "C" int axm_moe_expert_ffn_backward(const AxmMoeDesc* desc, const AxmSegment* segments,
+                                           int32_t num_segments, int32_t rows_total,
+                                           const void* x_perm, const void* h, const void* g,
+                                           const void* u, const void* d_o, const void* w_gate,
+                                           const void* w_up, const void* w_down, void* d_g, void* d_u,
+                                           void* d_xp, void* d_w_gate, void* d_w_up, void* d_w_down,
+                                           int32_t* status, void* stream) {
+  return axm::launch_expert_ffn_backward(desc, segments, num_segments, rows_total, x_perm, h, g, u, d_o, w_gate, w_up,
+                                         w_down, d_g, d_u, d_xp, d_w_gate, d_w_up, d_w_down, status, stream, 3);
 }
