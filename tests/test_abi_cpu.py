@@ -140,3 +140,62 @@ def test_adamw_argument_checks(axm):
     assert lib.axm_moe_adamw_step_engine(a, a, a, a, ctypes.c_void_p(0x10004), 64, 2048, 1e-3, 0.9, 0.95,
                                          1e-8, 0.0, 1, None) == axm.AXM_ERR_ARGUMENT
     assert lib.axm_moe_adamw_step(a, a, a, a, a, 0, 1e-3, 0.9, 0.95, 1e-8, 0.0, 1, None) == axm.AXM_OK
+
+
+def test_ep_training_layout_checks(axm):
+    """The sharded training step refuses, before any CUDA call, a layout that is not in the 64-row
+    training form, a receive buffer without room for the padding, shared experts, and a token
+    count over all ranks below this rank's."""
+    lib = axm.load()
+    world, E, D, F, T, k = 2, 8, 256, 512, 64, 2
+    slots = T * k
+
+    def layout(cap, align):
+        lo = axm.EpLayout()
+        n = ctypes.c_size_t(0)
+        assert lib.axm_ep_region_bytes(world, E, D, slots, cap, ctypes.byref(lo), ctypes.byref(n)) == axm.AXM_OK
+        assert lo.row_align == 1           # packed rows unless the caller asks for the training form
+        lo.rank, lo.row_align = 0, align
+        return lo
+
+    d = axm.make_desc(T, D, F, E, k)
+    nb, zb = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    need = slots * world + 63 * (E // world)
+    good = layout(need, 64)
+    assert lib.axm_moe_ep_train_workspace_bytes(ctypes.byref(good), ctypes.byref(d), ctypes.byref(nb),
+                                                ctypes.byref(zb)) == axm.AXM_OK
+    assert nb.value > 5 * 2 * need * F and 0 < zb.value <= 512
+    for bad in (layout(need, 1), layout(need - 1, 64)):
+        assert lib.axm_moe_ep_train_workspace_bytes(ctypes.byref(bad), ctypes.byref(d), ctypes.byref(nb),
+                                                    ctypes.byref(zb)) == axm.AXM_ERR_ARGUMENT
+    shared = axm.make_desc(T, D, F, E, k, num_shared=1)
+    assert lib.axm_moe_ep_train_workspace_bytes(ctypes.byref(good), ctypes.byref(shared), ctypes.byref(nb),
+                                                ctypes.byref(zb)) == axm.AXM_ERR_ARGUMENT
+    t = axm.MoeTrain()
+    assert lib.axm_moe_ep_forward_train(ctypes.byref(good), ctypes.byref(d), ctypes.byref(t), T - 1, None, 0, 1,
+                                        None) == axm.AXM_ERR_ARGUMENT
+    assert b"tokens_global" in lib.axm_last_error()
+    # the backward pass wants an exchange region of its own
+    good.peers = good.local_region = 0x10000
+    t2 = axm.MoeTrain(*([0x1000] * 9), 0.01, *([0x1000] * 7), *([None] * 6))
+    assert lib.axm_moe_ep_backward(ctypes.byref(good), ctypes.byref(good), ctypes.byref(d), ctypes.byref(t2), T * world,
+                                   ctypes.c_void_p(0x100000), 1 << 40, 1, None) == axm.AXM_ERR_ARGUMENT
+    assert b"region of its own" in lib.axm_last_error()
+
+
+def test_host_batches_argument_checks(axm):
+    lib = axm.load()
+    d = axm.make_desc(64, 256, 512, 8, 2)
+    a = 0x10000
+    t = axm.MoeTensors(*([a] * 18))
+    two = (ctypes.c_void_p * 2)(a, a)
+    call = lambda tt, xs, n, dx=a, dout=a + 4096, ws=a, nbytes=1 << 40: lib.axm_moe_forward_host_batches(
+        ctypes.byref(d), ctypes.byref(tt), xs, two, n, ctypes.c_void_p(dx), ctypes.c_void_p(dout),
+        ctypes.c_void_p(ws), nbytes, None)
+    assert call(t, two, 2) == axm.AXM_ERR_ARGUMENT and b"per-token outputs" in lib.axm_last_error()
+    t.logits = t.topk_idx = t.topk_gate = t.offsets = t.row_src = t.slot_dst = t.y = None
+    assert call(t, two, 65) == axm.AXM_ERR_ARGUMENT
+    assert call(t, (ctypes.c_void_p * 2)(a, None), 2) == axm.AXM_ERR_ARGUMENT
+    assert call(t, two, 2, dx=a, dout=a) == axm.AXM_ERR_ARGUMENT
+    assert call(t, two, 2, nbytes=1024) == axm.AXM_ERR_WORKSPACE
+    assert call(t, two, 0) == axm.AXM_OK          # nothing to do: no device needed
