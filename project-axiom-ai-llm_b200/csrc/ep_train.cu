@@ -83,6 +83,7 @@ struct EpTrainWs {
   AxmSegment* expert_segs;   // [El]: one segment per local expert, padded rows
   float* aux_partial;        // [296][E]; the backward pass reuses it for the bias partial sums
   float* aux_coef;           // [E]
+  int32_t* counts_global;    // [E]: tokens per expert over all ranks (from the count table)
   float* d_gate;             // [T * k]
   float* dz;                 // [T][E]
   float* dwr_partial;
@@ -122,6 +123,7 @@ EpTrainWs carve(const AxmEpLayout* l, const AxmMoeDesc* d, void* base) {
   w.expert_segs = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * El));
   w.aux_partial = static_cast<float*>(take(4 * (size_t)AXM_ROUTE_BLOCKS * E));
   w.aux_coef = static_cast<float*>(take(4 * E));
+  w.counts_global = static_cast<int32_t*>(take(4 * E));
   w.d_gate = static_cast<float*>(take(4 * T * k));
   w.dz = static_cast<float*>(take(4 * T * E));
   w.dwr_partial = static_cast<float*>(take(4 * dwr_partial_floats((int)D, (int)E)));
@@ -155,11 +157,22 @@ int validate_ep_train(const AxmEpLayout* l, const AxmMoeDesc* d, int32_t tokens_
   return AXM_OK;
 }
 
-// One block: f_e from the counts of all ranks (every rank's counts were posted into this rank's
-// table by the dispatch), the constant alpha * E * f_e / T that the router backward adds to
-// dp[t, e], and this rank's share of the loss alpha * E * sum_e f_e * P_e (P_e = mean over ALL
-// tokens; the share sums this rank's probabilities only).  T is the token count over all ranks.
-__global__ void aux_final_ep_kernel(const float* __restrict__ partial, const int32_t* __restrict__ table, int G,
+// counts[e] = tokens of all ranks routed to expert e (every rank's counts were posted into this
+// rank's table by the dispatch).  Runs before this rank's return flag lets a peer move on to a
+// step that rewrites the table.
+__global__ void global_counts_kernel(const int32_t* __restrict__ table, int G, int E, int32_t* __restrict__ counts) {
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= E) return;
+  int cnt = 0;
+  for (int s = 0; s < G; ++s) cnt += __ldcg(table + s * E + e);
+  counts[e] = cnt;
+}
+
+// One block: f_e from the counts of all ranks, the constant alpha * E * f_e / T that the router
+// backward adds to dp[t, e], and this rank's share of the loss alpha * E * sum_e f_e * P_e (P_e =
+// mean over ALL tokens; the share sums this rank's probabilities only).  T is the token count
+// over all ranks.
+__global__ void aux_final_ep_kernel(const float* __restrict__ partial, const int32_t* __restrict__ counts,
                                     float* __restrict__ aux_coef, float* __restrict__ aux_loss, int T, int E, int k,
                                     float alpha) {
   __shared__ float term[256];
@@ -169,9 +182,7 @@ __global__ void aux_final_ep_kernel(const float* __restrict__ partial, const int
     float P = 0.0f;
     for (int b = 0; b < AXM_ROUTE_BLOCKS; ++b) P += partial[(size_t)b * E + e];
     P /= (float)T;
-    int cnt = 0;
-    for (int s = 0; s < G; ++s) cnt += __ldcg(table + s * E + e);
-    const float f = (float)cnt / ((float)T * (float)k);
+    const float f = (float)counts[e] / ((float)T * (float)k);
     v = f * P;
     aux_coef[e] = alpha * (float)E * f / (float)T;
   }
@@ -302,17 +313,17 @@ extern "C" int axm_moe_ep_forward_train(const AxmEpLayout* layout, const AxmMoeD
                                      w.status, st)))
     return rc;
   expert_segments_kernel<<<1, 64, 0, st>>>(w.segments, w.expert_segs, G, c.El);
+  global_counts_kernel<<<(E + 63) / 64, 64, 0, st>>>(table, G, E, w.counts_global);
   if ((rc = launch_ep_zero_pad(&c.l, step, recv, st))) return rc;
   if ((rc = launch_expert_ffn(&c.d_ffn, recv, c.l.cap, nullptr, 0, w.expert_segs, c.El, t->w_gate, t->w_up,
                               t->w_down, nullptr, nullptr, nullptr, w.h, w.o, c.l.cap, w.status, st, nullptr,
                               nullptr, w.g, w.u)))
     return rc;
-  // the auxiliary-loss statistics read the count table: before this rank's return flag lets a
-  // peer move on to a step that rewrites it
-  if ((rc = launch_aux_partial(w.logits, w.aux_partial, T, E, st))) return rc;
-  aux_final_ep_kernel<<<1, 256, 0, st>>>(w.aux_partial, table, G, w.aux_coef, t->aux_loss, tokens_global, E, k,
-                                         t->aux_alpha);
   if ((rc = axm_ep_return(&c.l, step, w.ret_segments, w.o, w.scratch, w.status, stream))) return rc;
+  // the auxiliary-loss statistics fill the time in which the peers' rows come back
+  if ((rc = launch_aux_partial(w.logits, w.aux_partial, T, E, st))) return rc;
+  aux_final_ep_kernel<<<1, 256, 0, st>>>(w.aux_partial, w.counts_global, w.aux_coef, t->aux_loss, tokens_global, E, k,
+                                         t->aux_alpha);
   if ((rc = axm_ep_wait_return(&c.l, step, w.status, stream))) return rc;
   AxmMoeDesc d_comb = c.d_route;
   if ((rc = axm_moe_combine(&d_comb, t->x, o_back, nullptr, w.slot_dst, w.topk_gate, nullptr, t->out, stream)))
