@@ -255,7 +255,7 @@ def main():
                     help="override the workload's token count (e.g. 16 for a decode-sized batch)")
     ap.add_argument("--ep-transport", default="p2p", choices=["p2p", "nccl"],
                     help="N > 1: own peer-memory exchange kernels, or NCCL all-to-all")
-    ap.add_argument("--ep-host-chunks", type=int, default=1,
+    ap.add_argument("--ep-host-chunks", type=int, default=0,
                     help="N > 1: parts the host-buffer call cuts each rank's tokens into (every part is a "
                          "whole exchange step, whose fixed cost outweighs the hidden copies at 8 GPUs)")
     ap.add_argument("--ep-stages", action="store_true",

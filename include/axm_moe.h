@@ -591,8 +591,10 @@ AXM_API int axm_moe_ep_forward_profiled(const AxmEpLayout* layout, const AxmMoeD
 /* The same layer for activations in (pinned) host memory, mirroring the engine's host wrapper
  * (core/src/ai.cpp:593-623): the rank's tokens are cut into `chunks` equal parts (1..8, the
  * same on every rank; each part is one exchange step), part c + 1 is copied in and part c - 1
- * copied out while part c is computed.  d_x / d_out: device staging buffers of T_local * D
- * bf16.  *step is the first step number to use and is advanced by `chunks`.  Synchronises. */
+ * copied out while part c is computed.  chunks = 0 lets the library choose (two parts from 4096
+ * tokens per rank on, else one; every rank must then arrive at the same number).  d_x / d_out:
+ * device staging buffers of T_local * D bf16.  *step is the first step number to use and is
+ * advanced by the number of parts.  Synchronises. */
 AXM_API int axm_moe_ep_forward_host(const AxmEpLayout* layout, const AxmMoeDesc* desc,
                                     const AxmEpTensors* tensors, const void* h_x, void* h_out, void* d_x,
                                     void* d_out, void* workspace, size_t workspace_bytes, int32_t chunks,

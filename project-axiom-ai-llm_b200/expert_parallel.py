@@ -329,8 +329,9 @@ class ExpertParallelMoeP2P:
             stages["first half's return: end after down GEMM start"] = ms[8]
         return out, stages
 
-    def forward_host(self, h_x, h_out, d_x, d_out, chunks=1):
-        """Activations in pinned host memory, copies pipelined with the exchange steps; synchronises."""
+    def forward_host(self, h_x, h_out, d_x, d_out, chunks=0):
+        """Activations in pinned host memory, copies pipelined with the exchange steps; synchronises.
+        chunks = 0 leaves the number of parts to the library (two from 4096 tokens per rank on)."""
         assert self.c_layer
         t = self.ep_tensors(d_x, d_out)
         step = ctypes.c_uint32(self.step + 1)
