@@ -189,7 +189,8 @@ dwr_partial_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
                    float* __restrict__ partial, int T, int D, int E) {
   const int d = (blockIdx.x * 128 + threadIdx.x) * 2;
   const int c = blockIdx.y;
-  const int t0 = (int)(((long long)c * T) / kDwrChunks), t1 = (int)(((long long)(c + 1) * T) / kDwrChunks);
+  const int chunks = gridDim.y;  // at most kDwrChunks
+  const int t0 = (int)(((long long)c * T) / chunks), t1 = (int)(((long long)(c + 1) * T) / chunks);
   if (d >= D) return;  // D is a multiple of 8: a thread's two columns are both inside or both outside
   for (int e0 = 0; e0 < E; e0 += EC) {
     float acc0[EC], acc1[EC];
@@ -247,13 +248,14 @@ dwr_partial_kernel(const __nv_bfloat16* __restrict__ x, const float* __restrict_
 }
 
 // d_wr[d][e] = sum over the chunks, in chunk order, of partial[chunk][e][d].
-__global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_wr, int D, int E) {
+__global__ void dwr_reduce_kernel(const float* __restrict__ partial, float* __restrict__ d_wr, int D, int E,
+                                  int chunks) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= D * E) return;
   const int e = i / D, d = i - e * D;
   float acc = 0.0f;
 #pragma unroll 16
-  for (int c = 0; c < kDwrChunks; ++c) acc += __ldg(partial + ((size_t)c * E + e) * D + d);  // loads ahead, adds in order
+  for (int c = 0; c < chunks; ++c) acc += __ldg(partial + ((size_t)c * E + e) * D + d);  // loads ahead, adds in order
   d_wr[(size_t)d * E + e] = acc;
 }
 
@@ -455,9 +457,13 @@ int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const f
     dbias_reduce_kernel<<<1, 256, 0, st>>>(bias_partial, t->d_router_bias, E);
   }
   if (t->d_router_w != nullptr) {
-    dim3 grid((D / 2 + 127) / 128, kDwrChunks);
+    // about 64 tokens per chunk, at most kDwrChunks chunks: a small batch (a rank's share under
+    // expert parallelism) does not pay for 128 partial sums per element
+    int chunks = T / 64;
+    chunks = chunks < 8 ? 8 : (chunks > kDwrChunks ? kDwrChunks : chunks);
+    dim3 grid((D / 2 + 127) / 128, chunks);
     dwr_partial_kernel<16><<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(t->x), dz, dwr_partial, T, D, E);
-    dwr_reduce_kernel<<<(D * E + 63) / 64, 64, 0, st>>>(dwr_partial, t->d_router_w, D, E);  // many small blocks: the sums are latency-bound
+    dwr_reduce_kernel<<<(D * E + 63) / 64, 64, 0, st>>>(dwr_partial, t->d_router_w, D, E, chunks);  // many small blocks: the sums are latency-bound
   }
   dim3 fgrid((D + d_tile - 1) / d_tile, 1);
   const bool in_regs = E == 8 || E == 16;

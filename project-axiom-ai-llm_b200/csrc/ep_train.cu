@@ -160,8 +160,13 @@ int validate_ep_train(const AxmEpLayout* l, const AxmMoeDesc* d, int32_t tokens_
 // counts[e] = tokens of all ranks routed to expert e (every rank's counts were posted into this
 // rank's table by the dispatch).  Runs before this rank's return flag lets a peer move on to a
 // step that rewrites the table.
-__global__ void global_counts_kernel(const int32_t* __restrict__ table, int G, int E, int32_t* __restrict__ counts) {
-  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+// In the same launch: expert_segs[j] = the merged segment of local expert j (entry j * G of the
+// exchange table).  One block of 256 threads (E <= 256, at most 64 experts per rank).
+__global__ void train_tables_kernel(const int32_t* __restrict__ table, int G, int E, int32_t* __restrict__ counts,
+                                    const AxmSegment* __restrict__ segments, AxmSegment* __restrict__ expert_segs,
+                                    int El) {
+  const int e = threadIdx.x;
+  if (e < El) expert_segs[e] = segments[e * G];
   if (e >= E) return;
   int cnt = 0;
   for (int s = 0; s < G; ++s) cnt += __ldcg(table + s * E + e);
@@ -193,13 +198,6 @@ __global__ void aux_final_ep_kernel(const float* __restrict__ partial, const int
     for (int i = 0; i < E; ++i) acc += term[i];
     if (aux_loss != nullptr) *aux_loss = alpha * (float)E * acc;
   }
-}
-
-// expert_segs[j] = the merged segment of local expert j (entry j * G of the exchange table).
-__global__ void expert_segments_kernel(const AxmSegment* __restrict__ segments, AxmSegment* __restrict__ out, int G,
-                                       int El) {
-  const int j = blockIdx.x * blockDim.x + threadIdx.x;
-  if (j < El) out[j] = segments[j * G];
 }
 
 // High-priority side stream for the return of the dXp rows under the weight-gradient GEMMs,
@@ -312,8 +310,7 @@ extern "C" int axm_moe_ep_forward_train(const AxmEpLayout* layout, const AxmMoeD
   if ((rc = launch_ep_segments_split(&c.l, step, w.segments, w.ret_segments, w.rows_received, nullptr, nullptr,
                                      w.status, st)))
     return rc;
-  expert_segments_kernel<<<1, 64, 0, st>>>(w.segments, w.expert_segs, G, c.El);
-  global_counts_kernel<<<(E + 63) / 64, 64, 0, st>>>(table, G, E, w.counts_global);
+  train_tables_kernel<<<1, 256, 0, st>>>(table, G, E, w.counts_global, w.segments, w.expert_segs, c.El);
   if ((rc = launch_ep_zero_pad(&c.l, step, recv, st))) return rc;
   if ((rc = launch_expert_ffn(&c.d_ffn, recv, c.l.cap, nullptr, 0, w.expert_segs, c.El, t->w_gate, t->w_up,
                               t->w_down, nullptr, nullptr, nullptr, w.h, w.o, c.l.cap, w.status, st, nullptr,
@@ -354,7 +351,7 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
   if (int rc = require_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   EpTrainWs& w = c.w;
-  const int D = desc->d_model, E = desc->num_experts, k = desc->top_k, G = fwd_layout->world;
+  const int D = desc->d_model, E = desc->num_experts, k = desc->top_k;
   AxmEpLayout lb = *bwd_layout;
   lb.slots = c.l.slots;
   lb.tokens_local = c.l.tokens_local;
@@ -377,7 +374,7 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
   if ((rc = launch_ep_segments_split(&lb, step, w.segments, w.ret_segments, w.rows_received, nullptr, nullptr,
                                      w.status, st)))
     return rc;
-  expert_segments_kernel<<<1, 64, 0, st>>>(w.segments, w.expert_segs, G, c.El);
+  // w.expert_segs still holds the forward pass's one-segment-per-expert table
   if ((rc = launch_ep_zero_pad(&lb, step, do_recv, st))) return rc;
   // AXM_EP_TRAIN_OVERLAP=0 keeps everything on the caller's stream (return after the weight gradients)
   static const bool overlap = [] {
