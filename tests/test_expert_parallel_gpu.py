@@ -44,8 +44,9 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         if transport == "nccl":
             layer = ep.ExpertParallelMoe(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
                                          cfg.top_k)
-        elif transport == "c-layer":   # the whole call behind axm_moe_ep_forward (the default)
-            layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), tl, cfg.num_experts, cfg.top_k)
+        elif transport in ("c-layer", "c-layer-exact"):   # the whole call behind axm_moe_ep_forward (the default)
+            layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), tl, cfg.num_experts, cfg.top_k,
+                                            h_exact=(transport == "c-layer-exact"))
             assert layer.c_layer
         else:   # stage by stage; return fused into the down GEMM or as a copy kernel
             layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), tl, cfg.num_experts,
@@ -71,7 +72,7 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
             assert torch.equal(out3, out) and len(ms) >= 7
             layer.check_status()
         if rank == 0:
-            single = axm.MoeLayer(w, cfg.tokens, cfg.top_k)
+            single = axm.MoeLayer(w, cfg.tokens, cfg.top_k, h_exact=(transport == "c-layer-exact"))
             ref, _ = single.forward(x)
             torch.cuda.synchronize()
             torch.save({"ref": ref.cpu(), "hist": single.histogram.cpu()},
@@ -83,9 +84,11 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("transport", ["c-layer", "nccl", "p2p", "p2p-copy"])
+@pytest.mark.parametrize("transport", ["c-layer", "c-layer-exact", "nccl", "p2p", "p2p-copy"])
 @pytest.mark.parametrize("name,tokens", [("C1", 64), ("C2", 1024), ("C4", 2048)])
 def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens, transport):
+    if transport == "c-layer-exact" and name != "C2":
+        pytest.skip("the strict-tolerance mode under expert parallelism is covered on one shape")
     world = min(torch.cuda.device_count(), 4) if name == "C4" else 2
     mp.start_processes(_worker, args=(world, _free_port(), name, tokens, transport, str(tmp_path)),
                        nprocs=world, join=True, start_method="spawn")

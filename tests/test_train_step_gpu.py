@@ -155,13 +155,14 @@ def test_router_bias_is_trained(axm, workloads, oracle, cuda_device):
     close(grads["d_x"].cpu() - dY, ref["dX"] - dY.numpy(), "dX with a router bias")
 
 
-def test_train_step_with_shared_experts(axm, workloads, oracle, cuda_device):
+@pytest.mark.parametrize("tokens,shared", [(200, 2), (128, 1)])
+def test_train_step_with_shared_experts(axm, workloads, oracle, cuda_device, tokens, shared):
     """Shared experts (every token, weight 1) in the training step.  The oracle's backward covers
     routed experts; a shared expert is the same arithmetic with every token routed to it at gate 1,
     so the reference is the routed backward plus, per shared expert, the backward of a one-expert
     top-1 layer with unit gates and probabilities (its router gradient vanishes identically)."""
-    cfg = workloads.scaled(workloads.CONFIGS["C4"], tokens=200, d_model=128, d_ff=256, num_experts=16, top_k=3,
-                           num_shared=2)
+    cfg = workloads.scaled(workloads.CONFIGS["C4"], tokens=tokens, d_model=128, d_ff=256, num_experts=16, top_k=3,
+                           num_shared=shared)
     alpha = 0.01
     x, w = workloads.make_inputs(cfg)
     S = cfg.num_shared
