@@ -552,14 +552,16 @@ AXM_API int axm_moe_ep_forward(const AxmEpLayout* layout, const AxmMoeDesc* desc
  * engine is single-GPU and its backward covers the dense FFN only,
  * core/src/CUDA/kernel/backward_pass.cu:1701-2005).  AxmMoeTrain is read per rank: x, out,
  * d_out, d_x cover this rank's desc->tokens tokens; w_gate / w_up / w_down and their gradients
- * cover this rank's E / world experts; router_w and router_bias are replicated.
+ * cover this rank's E / world experts; router_w, router_bias and the shared experts are
+ * replicated (shared experts are applied to the rank's own tokens without communication).
  * Two exchange regions of equal size are needed, both with row_align = 64 and
  * cap >= slots * world + 63 * (E / world): `layout` carries the forward rows and keeps them
  * until the backward pass has read them, `bwd_layout` carries the gradient rows.  The same
  * `step` is passed to the forward and the backward call of one training step; it grows by one
  * per training step on every rank alike.  tokens_global is the token count over all ranks.
- * Left to the caller (sums over the ranks of replicated quantities): d_router_w, d_router_bias
- * and aux_loss hold this rank's share.  Expert weight gradients are complete on their rank.
+ * Left to the caller (sums over the ranks of replicated quantities): d_router_w, d_router_bias,
+ * d_shared_gate / d_shared_up / d_shared_down and aux_loss hold this rank's share.  Routed
+ * experts' weight gradients are complete on their rank.
  * The workspace holds the saved activations between the two calls; its leading zero_bytes must
  * be zero before the first call. */
 AXM_API int axm_moe_ep_train_workspace_bytes(const AxmEpLayout* layout, const AxmMoeDesc* desc, size_t* bytes,

@@ -274,7 +274,7 @@ __global__ void __launch_bounds__(128)
 bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d_xp,
                     const int32_t* __restrict__ slot_dst, const WT* __restrict__ wr,
                     const float* __restrict__ dz, float* __restrict__ d_x, int T, int D, int E, int k,
-                    int residual, int d_tile, int S, int shared_row0, int shared_stride) {
+                    int residual, int d_tile, int S, const float* __restrict__ d_xp_shared, int shared_stride) {
   extern __shared__ __align__(16) float w_s[];  // [E][d_tile] (ER == 0)
   const int d0 = blockIdx.x * d_tile;
   if (ER == 0) {
@@ -324,11 +324,11 @@ bwd_finalize_kernel(const float* __restrict__ d_out, const float* __restrict__ d
         acc[q].w += v[q].w;
       }
     }
-    for (int s = 0; s < S; ++s) {  // shared experts: row shared_row0 + s * shared_stride + t of d_xp
+    for (int s = 0; s < S; ++s) {  // shared experts: row s * shared_stride + t of d_xp_shared
       float4 v[kFinTokens];
 #pragma unroll
       for (int q = 0; q < kFinTokens; ++q)
-        v[q] = __ldg(reinterpret_cast<const float4*>(d_xp + ((size_t)shared_row0 + (size_t)s * shared_stride + tq[q]) * D) + c);
+        v[q] = __ldg(reinterpret_cast<const float4*>(d_xp_shared + ((size_t)s * shared_stride + tq[q]) * D) + c);
 #pragma unroll
       for (int q = 0; q < kFinTokens; ++q) {
         acc[q].x += v[q].x;
@@ -443,7 +443,7 @@ int launch_bwd_prepare(const float* d_out, const float* o, const int32_t* row_sr
 int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const float* logits,
                            const int32_t* topk_idx, const float* d_gate, const float* aux_coef, float* dz,
                            float* bias_partial, float* dwr_partial, const float* d_xp, const int32_t* slot_dst,
-                           cudaStream_t st, int S, int shared_row0, int shared_stride) {
+                           cudaStream_t st, int S, const float* d_xp_shared, int shared_stride) {
   const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k;
   const int residual = (desc->flags & AXM_FLAG_RESIDUAL) ? 1 : 0;
   const int rb_threads = router_bwd_threads(E);
@@ -475,7 +475,7 @@ int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const f
   if ((int)fgrid.y > T) fgrid.y = T;
   auto launch = [&](auto kern, const auto* wr_typed, size_t smem) {
     kern<<<fgrid, 128, smem, st>>>(t->d_out, d_xp, slot_dst, wr_typed, dz, t->d_x, T, D, E, k, residual, d_tile, S,
-                                   shared_row0, shared_stride);
+                                   d_xp_shared, shared_stride);
   };
   if (desc->router_dtype == AXM_ROUTER_FP32) {
     const float* w = static_cast<const float*>(t->router_w);
@@ -539,6 +539,20 @@ bwd_prepare_shared_kernel(const float* __restrict__ d_out, __nv_bfloat16* __rest
     for (int s = 0; s < S; ++s)
       reinterpret_cast<uint2*>(d_o + ((size_t)row0 + (size_t)s * Tp + t) * D)[c] = v;
   }
+}
+
+// Launchers of the two kernels above for callers outside this file (the expert-parallel training
+// step keeps the shared experts' rows in buffers of their own: row0 = 0, E = 0 there).
+int launch_train_shared_rows(const void* x, void* x_perm, AxmSegment* segments, int T, int Tp, int D, int E, int S,
+                             int row0, cudaStream_t st) {
+  train_shared_rows_kernel<<<2 * sm_count(), 256, 0, st>>>(static_cast<const __nv_bfloat16*>(x),
+                                                           static_cast<__nv_bfloat16*>(x_perm), segments, T, Tp, D, E, S,
+                                                           row0);
+  return check_launch("train_shared_rows_kernel");
+}
+int launch_bwd_prepare_shared(const float* d_out, void* d_o, int T, int Tp, int D, int S, int row0, cudaStream_t st) {
+  bwd_prepare_shared_kernel<<<2 * sm_count(), 256, 0, st>>>(d_out, static_cast<__nv_bfloat16*>(d_o), T, Tp, D, S, row0);
+  return check_launch("bwd_prepare_shared_kernel");
 }
 
 struct TrainWs {
@@ -751,8 +765,8 @@ extern "C" int axm_moe_backward(const AxmMoeDesc* desc, const AxmMoeTrain* t, vo
       return rc;
   }
   return launch_bwd_source_tail(desc, t, w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, w.aux_partial,
-                                w.dwr_partial, static_cast<const float*>(w.d_xp), w.slot_dst, st, S, w.shared_row0,
-                                w.shared_rows);
+                                w.dwr_partial, static_cast<const float*>(w.d_xp), w.slot_dst, st, S,
+                                static_cast<const float*>(w.d_xp) + (size_t)w.shared_row0 * D, w.shared_rows);
 }
 
 // ---- optimizer step for the MoE weights ---------------------------------------------

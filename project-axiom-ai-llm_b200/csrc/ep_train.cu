@@ -20,8 +20,10 @@
 // be raised) on a side stream while the weight gradients are still being computed.
 //
 // What the caller still reduces over the ranks (replicated parameters): d_router_w,
-// d_router_bias and the auxiliary loss are this rank's share; their sum over the ranks is the
-// gradient / the loss.  Expert weight gradients are complete on the rank that owns the expert.
+// d_router_bias, the shared experts' weight gradients and the auxiliary loss are this rank's
+// share; their sum over the ranks is the gradient / the loss.  Routed experts' weight gradients
+// are complete on the rank that owns the expert.  Shared experts (replicated) are applied to the
+// rank's own tokens without communication, forward and backward, in the gaps the exchange leaves.
 //
 // The reference engine is single-GPU and has no MoE backward (core/src/CUDA/kernel/
 // backward_pass.cu:1701-2005 covers the dense FFN); conventions as in backward.cu.
@@ -59,7 +61,13 @@ int launch_bwd_prepare(const float* d_out, const float* o, const int32_t* row_sr
 int launch_bwd_source_tail(const AxmMoeDesc* desc, const AxmMoeTrain* t, const float* logits,
                            const int32_t* topk_idx, const float* d_gate, const float* aux_coef, float* dz,
                            float* bias_partial, float* dwr_partial, const float* d_xp, const int32_t* slot_dst,
-                           cudaStream_t st, int S, int shared_row0, int shared_stride);
+                           cudaStream_t st, int S, const float* d_xp_shared, int shared_stride);
+int launch_train_shared_rows(const void* x, void* x_perm, AxmSegment* segments, int T, int Tp, int D, int E, int S,
+                             int row0, cudaStream_t st);
+int launch_bwd_prepare_shared(const float* d_out, void* d_o, int T, int Tp, int D, int S, int row0, cudaStream_t st);
+int launch_combine_strided(const AxmMoeDesc* desc, const void* x, const void* o, const void* o_shared,
+                           int shared_stride, const int32_t* slot_dst, const float* topk_gate, void* y, void* out,
+                           cudaStream_t st);
 
 namespace {
 
@@ -91,6 +99,15 @@ struct EpTrainWs {
   void *g, *u, *h;           // [cap][F] bf16, saved by the forward pass
   void *d_g, *d_u;           // [cap][F] bf16
   void* o;                   // [cap][D] fp32: expert rows (forward), dXp rows (backward)
+  // shared experts (replicated; they see this rank's tokens only): S runs of Tp rows each, Tp =
+  // the tokens padded to a multiple of 64
+  AxmSegment* shared_segs;   // [S]
+  void* xs;                  // [S * Tp][D] bf16: a copy of the token rows per shared expert
+  void *gs, *us, *hs;        // [S * Tp][F] bf16
+  void *dgs, *dus;           // [S * Tp][F] bf16
+  void* dos;                 // [S * Tp][D] bf16
+  void* os;                  // [S * Tp][D] fp32: outputs (forward), dXp rows (backward)
+  int shared_rows;           // Tp
   void* router_scratch;
   size_t router_scratch_bytes;
   size_t zero_bytes;
@@ -105,8 +122,9 @@ EpTrainWs carve(const AxmEpLayout* l, const AxmMoeDesc* d, void* base) {
     off += up256(n);
     return p;
   };
-  const size_t T = d->tokens, D = d->d_model, F = d->d_ff, E = d->num_experts, k = d->top_k;
+  const size_t T = d->tokens, D = d->d_model, F = d->d_ff, E = d->num_experts, k = d->top_k, S = d->num_shared;
   const size_t G = l->world, El = E / G, cap = (size_t)l->cap;
+  const size_t Tp = (T + kEpTrainAlign - 1) / kEpTrainAlign * kEpTrainAlign;
   w.status = static_cast<int32_t*>(take(4));
   w.scratch = static_cast<int32_t*>(take(8));
   w.zero_bytes = off;
@@ -134,6 +152,16 @@ EpTrainWs carve(const AxmEpLayout* l, const AxmMoeDesc* d, void* base) {
   w.d_g = take(2 * cap * F);
   w.d_u = take(2 * cap * F);
   w.o = take(4 * cap * D);
+  w.shared_rows = (int)Tp;
+  w.shared_segs = static_cast<AxmSegment*>(take(sizeof(AxmSegment) * (S ? S : 1)));
+  w.xs = take(2 * S * Tp * D);
+  w.gs = take(2 * S * Tp * F);
+  w.us = take(2 * S * Tp * F);
+  w.hs = take(2 * S * Tp * F);
+  w.dgs = take(2 * S * Tp * F);
+  w.dus = take(2 * S * Tp * F);
+  w.dos = take(2 * S * Tp * D);
+  w.os = take(4 * S * Tp * D);
   w.router_scratch_bytes = 0;
   axm_moe_router_scratch_bytes(d, &w.router_scratch_bytes);
   w.router_scratch = take(w.router_scratch_bytes);
@@ -144,7 +172,6 @@ EpTrainWs carve(const AxmEpLayout* l, const AxmMoeDesc* d, void* base) {
 int validate_ep_train(const AxmEpLayout* l, const AxmMoeDesc* d, int32_t tokens_global) {
   if (int rc = validate_ep_layer(l, d)) return rc;
   if (d->tokens <= 0) return fail(AXM_ERR_ARGUMENT, "tokens %d must be positive", d->tokens);
-  if (d->num_shared != 0) return fail(AXM_ERR_ARGUMENT, "the training step does not take shared experts");
   if (tokens_global < d->tokens)
     return fail(AXM_ERR_ARGUMENT, "tokens_global %d is smaller than this rank's %d tokens", tokens_global, d->tokens);
   if (l->row_align != kEpTrainAlign)
@@ -247,8 +274,9 @@ int prepare(const AxmEpLayout* layout, const AxmMoeDesc* desc, const AxmMoeTrain
   c->l = *layout;
   c->l.slots = desc->tokens * desc->top_k;
   c->l.tokens_local = desc->tokens;
-  c->l.num_shared = 0;
+  c->l.num_shared = 0;  // the exchange carries routed rows only; shared experts stay on their rank
   c->d_route = *desc;
+  c->d_route.num_shared = 0;
   // the saved h of the training layout is one bf16 term; the histogram is this call's
   c->d_route.flags &= ~(AXM_FLAG_HIST_ACCUMULATE | AXM_FLAG_H_EXACT);
   c->d_ffn = c->d_route;
@@ -292,6 +320,9 @@ extern "C" int axm_moe_ep_forward_train(const AxmEpLayout* layout, const AxmMoeD
   if (int rc = prepare(layout, desc, t, tokens_global, workspace, workspace_bytes, step, &c)) return rc;
   if (!t->x || !t->router_w || !t->w_gate || !t->w_up || !t->w_down || !t->out)
     return fail(AXM_ERR_ARGUMENT, "axm_moe_ep_forward_train: x, router_w, w_gate, w_up, w_down, out are required");
+  const int S = desc->num_shared;
+  if (S > 0 && (!t->shared_gate || !t->shared_up || !t->shared_down))
+    return fail(AXM_ERR_ARGUMENT, "num_shared > 0 needs shared_gate, shared_up and shared_down");
   if (int rc = require_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   EpTrainWs& w = c.w;
@@ -307,6 +338,19 @@ extern "C" int axm_moe_ep_forward_train(const AxmEpLayout* layout, const AxmMoeD
   if ((rc = launch_ep_permute_dispatch(&c.l, step, t->x, w.topk_idx, w.block_counts, t->histogram, w.offsets,
                                        w.row_src, w.slot_dst, w.scratch, T, k, 0, w.status, st)))
     return rc;
+  AxmMoeDesc d_shared = c.d_route;
+  d_shared.num_experts = S > 0 ? S : 1;
+  d_shared.top_k = 1;
+  if (S > 0) {
+    // the shared experts need this rank's tokens only: their GEMMs fill the time in which the
+    // routed rows of the peers arrive
+    if ((rc = launch_train_shared_rows(t->x, w.xs, w.shared_segs, T, w.shared_rows, desc->d_model, 0, S, 0, st)))
+      return rc;
+    if ((rc = launch_expert_ffn(&d_shared, w.xs, S * w.shared_rows, nullptr, 0, w.shared_segs, S, t->shared_gate,
+                                t->shared_up, t->shared_down, nullptr, nullptr, nullptr, w.hs, w.os,
+                                S * w.shared_rows, w.status, st, nullptr, nullptr, w.gs, w.us)))
+      return rc;
+  }
   if ((rc = launch_ep_segments_split(&c.l, step, w.segments, w.ret_segments, w.rows_received, nullptr, nullptr,
                                      w.status, st)))
     return rc;
@@ -323,7 +367,9 @@ extern "C" int axm_moe_ep_forward_train(const AxmEpLayout* layout, const AxmMoeD
                                          t->aux_alpha);
   if ((rc = axm_ep_wait_return(&c.l, step, w.status, stream))) return rc;
   AxmMoeDesc d_comb = c.d_route;
-  if ((rc = axm_moe_combine(&d_comb, t->x, o_back, nullptr, w.slot_dst, w.topk_gate, nullptr, t->out, stream)))
+  d_comb.num_shared = S;
+  if ((rc = launch_combine_strided(&d_comb, t->x, o_back, S > 0 ? w.os : nullptr, w.shared_rows, w.slot_dst,
+                                   w.topk_gate, nullptr, t->out, st)))
     return rc;
   return check_launch("ep_forward_train");
 }
@@ -348,6 +394,15 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
   const bool wgrad = t->d_w_gate || t->d_w_up || t->d_w_down;
   if (wgrad && !(t->d_w_gate && t->d_w_up && t->d_w_down))
     return fail(AXM_ERR_ARGUMENT, "weight gradients: give all three or none");
+  const int S = desc->num_shared;
+  if (S > 0) {
+    if (!t->shared_gate || !t->shared_up || !t->shared_down)
+      return fail(AXM_ERR_ARGUMENT, "num_shared > 0 needs shared_gate, shared_up and shared_down");
+    const bool shared_all = t->d_shared_gate && t->d_shared_up && t->d_shared_down;
+    const bool shared_any = t->d_shared_gate || t->d_shared_up || t->d_shared_down;
+    if (wgrad != shared_any || shared_any != shared_all)
+      return fail(AXM_ERR_ARGUMENT, "shared experts' weight gradients: all three exactly when the routed experts' are given");
+  }
   if (int rc = require_device()) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   EpTrainWs& w = c.w;
@@ -370,6 +425,18 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
                                st)))
     return rc;
   if ((rc = axm_ep_dispatch(&lb, step, w.offsets, w.d_o_local, w.scratch, w.status, stream))) return rc;
+  if (S > 0) {
+    // shared experts: local rows only (their weight gradients are this rank's share, like the
+    // router's); computed while the gradient rows of the peers arrive
+    AxmMoeDesc d_shared = c.d_route;
+    d_shared.num_experts = S;
+    d_shared.top_k = 1;
+    if ((rc = launch_bwd_prepare_shared(t->d_out, w.dos, desc->tokens, w.shared_rows, D, S, 0, st))) return rc;
+    if ((rc = launch_expert_ffn_backward(&d_shared, w.shared_segs, S, S * w.shared_rows, w.xs, w.hs, w.gs, w.us, w.dos,
+                                         t->shared_gate, t->shared_up, t->shared_down, w.dgs, w.dus, w.os,
+                                         t->d_shared_gate, t->d_shared_up, t->d_shared_down, w.status, stream, 3)))
+      return rc;
+  }
   // where the experts live: the same tables as in the forward pass (the counts are the same)
   if ((rc = launch_ep_segments_split(&lb, step, w.segments, w.ret_segments, w.rows_received, nullptr, nullptr,
                                      w.status, st)))
@@ -405,5 +472,6 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
   }
   if ((rc = axm_ep_wait_return(&lb, step, w.status, stream))) return rc;
   return launch_bwd_source_tail(&c.d_route, t, w.logits, w.topk_idx, w.d_gate, w.aux_coef, w.dz, w.aux_partial,
-                                w.dwr_partial, dxp_back, w.slot_dst, st, 0, 0, 0);
+                                w.dwr_partial, dxp_back, w.slot_dst, st, S, static_cast<const float*>(w.os),
+                                w.shared_rows);
 }

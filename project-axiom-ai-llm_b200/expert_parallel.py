@@ -431,7 +431,8 @@ class ExpertParallelTrainP2P:
         self.Tl = tokens_local
         self.tokens_global = tokens_global if tokens_global is not None else tokens_local * self.world
         rdt = ROUTER_FP32 if wr.dtype == torch.float32 else ROUTER_BF16
-        self.desc = make_desc(tokens_local, D, F, num_experts, top_k, 0, rdt, FLAG_RESIDUAL)
+        self.S = 0 if local_weights.get("shared_gate") is None else local_weights["shared_gate"].shape[0]
+        self.desc = make_desc(tokens_local, D, F, num_experts, top_k, self.S, rdt, FLAG_RESIDUAL)
         n_slots = tokens_local * top_k
         cap = n_slots * self.world + (self.ALIGN - 1) * self.El
         self.cap = (cap + self.ALIGN - 1) // self.ALIGN * self.ALIGN
@@ -484,6 +485,12 @@ class ExpertParallelTrainP2P:
             self.d_w_gate = torch.empty(self.El, D, F, dtype=f32, device=dev)
             self.d_w_up = torch.empty(self.El, D, F, dtype=f32, device=dev)
             self.d_w_down = torch.empty(self.El, F, D, dtype=f32, device=dev)
+            if self.S:      # replicated like the router: this rank's share, summed in backward()
+                self.d_shared = torch.empty(self.S * (2 * D * F + F * D), dtype=f32, device=dev)
+                n1 = self.S * D * F
+                self.d_shared_gate = self.d_shared[:n1].view(self.S, D, F)
+                self.d_shared_up = self.d_shared[n1:2 * n1].view(self.S, D, F)
+                self.d_shared_down = self.d_shared[2 * n1:].view(self.S, F, D)
         self.aux_alpha = aux_alpha
         self.step_no = 0
 
@@ -507,7 +514,11 @@ class ExpertParallelTrainP2P:
             self.d_router_w.data_ptr(), self.d_w_gate.data_ptr() if g else None,
             self.d_w_up.data_ptr() if g else None, self.d_w_down.data_ptr() if g else None,
             None if self.d_router_bias is None else self.d_router_bias.data_ptr(),
-            None, None, None, None, None, None)
+            w["shared_gate"].data_ptr() if self.S else None, w["shared_up"].data_ptr() if self.S else None,
+            w["shared_down"].data_ptr() if self.S else None,
+            self.d_shared_gate.data_ptr() if g and self.S else None,
+            self.d_shared_up.data_ptr() if g and self.S else None,
+            self.d_shared_down.data_ptr() if g and self.S else None)
 
     def forward(self, x):
         """Enqueues the forward pass; self.aux then holds this rank's share of the auxiliary loss."""
@@ -528,6 +539,8 @@ class ExpertParallelTrainP2P:
                                            current_stream()))
         if reduce:
             dist.all_reduce(self.replicated, group=self.group)
+            if self.S and self.weight_grads:
+                dist.all_reduce(self.d_shared, group=self.group)
         return self.d_x
 
     def step(self, x, d_out, reduce=True):
@@ -538,4 +551,7 @@ class ExpertParallelTrainP2P:
             grads["d_router_bias"] = self.d_router_bias
         if self.weight_grads:
             grads.update(d_w_gate=self.d_w_gate, d_w_up=self.d_w_up, d_w_down=self.d_w_down)
+            if self.S:
+                grads.update(d_shared_gate=self.d_shared_gate, d_shared_up=self.d_shared_up,
+                             d_shared_down=self.d_shared_down)
         return self.out, self.aux, grads

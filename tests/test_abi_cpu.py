@@ -144,8 +144,8 @@ def test_adamw_argument_checks(axm):
 
 def test_ep_training_layout_checks(axm):
     """The sharded training step refuses, before any CUDA call, a layout that is not in the 64-row
-    training form, a receive buffer without room for the padding, shared experts, and a token
-    count over all ranks below this rank's."""
+    training form, a receive buffer without room for the padding, and a token count over all ranks
+    below this rank's."""
     lib = axm.load()
     world, E, D, F, T, k = 2, 8, 256, 512, 64, 2
     slots = T * k
@@ -168,9 +168,11 @@ def test_ep_training_layout_checks(axm):
     for bad in (layout(need, 1), layout(need - 1, 64)):
         assert lib.axm_moe_ep_train_workspace_bytes(ctypes.byref(bad), ctypes.byref(d), ctypes.byref(nb),
                                                     ctypes.byref(zb)) == axm.AXM_ERR_ARGUMENT
-    shared = axm.make_desc(T, D, F, E, k, num_shared=1)
+    plain = nb.value
+    shared = axm.make_desc(T, D, F, E, k, num_shared=1)          # one replicated expert over this rank's tokens
     assert lib.axm_moe_ep_train_workspace_bytes(ctypes.byref(good), ctypes.byref(shared), ctypes.byref(nb),
-                                                ctypes.byref(zb)) == axm.AXM_ERR_ARGUMENT
+                                                ctypes.byref(zb)) == axm.AXM_OK
+    assert nb.value - plain >= 64 * (5 * 2 * F + (2 + 2 + 4) * D)    # its rows: x, g, u, h, dG, dU, dO, o
     t = axm.MoeTrain()
     assert lib.axm_moe_ep_forward_train(ctypes.byref(good), ctypes.byref(d), ctypes.byref(t), T - 1, None, 0, 1,
                                         None) == axm.AXM_ERR_ARGUMENT

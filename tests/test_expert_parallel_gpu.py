@@ -112,7 +112,11 @@ def _train_worker(rank, world, port, name, tokens, out_dir):
     dev = torch.device("cuda", rank)
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
-        cfg = wl.scaled(wl.CONFIGS[name], tokens=tokens)
+        if name == "C4-small":   # top-3 of 16 experts with a logit bias and two shared experts
+            cfg = wl.scaled(wl.CONFIGS["C4"], tokens=tokens, d_model=256, d_ff=512, num_experts=16, top_k=3,
+                            num_shared=2)
+        else:
+            cfg = wl.scaled(wl.CONFIGS[name], tokens=tokens)
         x, w = wl.make_inputs(cfg)          # CPU generator: identical on every rank
         g = torch.Generator().manual_seed(1234)
         d_out = torch.randn(cfg.tokens, cfg.d_model, generator=g, dtype=torch.float32)
@@ -144,12 +148,13 @@ def _train_worker(rank, world, port, name, tokens, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("name,tokens", [("C1", 64), ("C5", 1024), ("C5", 600)])
+@pytest.mark.parametrize("name,tokens", [("C1", 64), ("C5", 1024), ("C5", 600), ("C4-small", 600)])
 def test_expert_parallel_training_step_equals_single_gpu(tmp_path, name, tokens):
     """Forward and backward under expert parallelism against the single-GPU training step on the
     gathered batch.  The same rows meet the same weights in the same tile positions, so the output,
     dX and the expert weight gradients are bit-equal; the replicated router's gradients and the
-    auxiliary loss are sums over the ranks in another order (tolerance)."""
+    auxiliary loss are sums over the ranks in another order (tolerance), and so are the weight
+    gradients of shared experts, which every rank applies to its own tokens."""
     # the 16-expert shape runs on four GPUs where the box has them (4 experts per rank)
     world = 4 if (name == "C5" and tokens == 1024 and torch.cuda.device_count() >= 4) else 2
     mp.start_processes(_train_worker, args=(world, _free_port(), name, tokens, str(tmp_path)),
@@ -160,6 +165,11 @@ def test_expert_parallel_training_step_equals_single_gpu(tmp_path, name, tokens)
     assert torch.equal(torch.cat([p["d_x"] for p in parts]), ref["d_x"])
     for k in ("d_w_gate", "d_w_up", "d_w_down"):
         assert torch.equal(torch.cat([p[k] for p in parts]), ref[k]), k
+    for k in ("d_shared_gate", "d_shared_up", "d_shared_down"):   # replicated: summed over the ranks
+        if k in ref:
+            scale = ref[k].abs().max().item()
+            for p in parts:
+                assert (p[k] - ref[k]).abs().max().item() <= 1e-5 * max(scale, 1.0), k
     for p in parts:
         scale = ref["d_router_w"].abs().max().item()
         assert (p["d_router_w"] - ref["d_router_w"]).abs().max().item() <= 1e-5 * max(scale, 1.0)
