@@ -461,7 +461,9 @@ typedef struct AxmEpLayout {
   int32_t row_align;        /* 0 or 1: rows packed.  64: training layout - every local expert's run in the
                              * receive buffer starts at a multiple of 64 rows and is followed by zero rows
                              * up to the next multiple; cap must then hold slots * world + 63 * (E / world) */
-  int32_t reserved;
+  int32_t return_rows;      /* rows every rank's return buffer holds when `slots` carries one call's (smaller)
+                             * row count; 0: the same as slots.  Ranks may hold different numbers of tokens in
+                             * a call, so a rank bounds its stores into a peer's return buffer by this. */
 } AxmEpLayout;
 
 /* Fills the offsets / sizes of `layout` and returns the bytes one region needs:

@@ -57,7 +57,7 @@ class EpLayout(ctypes.Structure):
                                                "cap", "num_shared", "tokens_local")] +
                 [(n, ctypes.c_int64) for n in ("off_flags", "off_counts", "off_recv", "off_oback")] +
                 [("local_region", ctypes.c_void_p), ("row_align", ctypes.c_int32),
-                 ("reserved", ctypes.c_int32)])
+                 ("return_rows", ctypes.c_int32)])
 
 
 class EpTensors(ctypes.Structure):

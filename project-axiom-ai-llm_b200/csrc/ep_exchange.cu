@@ -41,7 +41,8 @@ struct EpArgs {
   char* const* peers;   // device array [G]: base of every rank's exchange region
   int rank, G, E, El;   // El = experts per rank
   int D;                // d_model
-  int slots;            // T_local * k
+  int slots;            // T_local * k of this call
+  int ret_rows;         // rows of a rank's return buffer (>= any rank's slots)
   int cap;              // rows the receive buffer holds
   int S, T_local;       // shared experts, local tokens
   int align;            // every local expert's run in the receive buffer starts at a multiple of this
@@ -439,7 +440,7 @@ ep_return_kernel(EpArgs a, const AxmSegment* __restrict__ ret_segments,
       if ((half == 0) != (r < cut)) continue;
     }
     const int dst_row = sg.a_row0 + (r - sg.out_row0);
-    if (dst_row >= a.slots) continue;
+    if (dst_row >= a.ret_rows) continue;  // the source's buffer, not this rank's row count
     const uint4* src = reinterpret_cast<const uint4*>(o + (size_t)r * a.D);
     uint4* dst = reinterpret_cast<uint4*>(a.peers[sg.expert] + a.off_oback) + (size_t)dst_row * chunks;
     for (int c0 = 0; c0 < chunks; c0 += 128) {
@@ -519,6 +520,7 @@ static EpArgs make_args(const AxmEpLayout* l, uint32_t step, int32_t* status) {
   a.El = l->num_experts / l->world;
   a.D = l->d_model;
   a.slots = l->slots;
+  a.ret_rows = l->return_rows > l->slots ? l->return_rows : l->slots;
   a.cap = l->cap;
   a.S = l->num_shared;
   a.T_local = l->tokens_local;
@@ -600,7 +602,7 @@ extern "C" int axm_ep_region_bytes(int32_t world, int32_t num_experts, int32_t d
   layout->slots = slots;
   layout->cap = cap;
   layout->row_align = 1;
-  layout->reserved = 0;
+  layout->return_rows = 0;
   *bytes = (size_t)off;
   return AXM_OK;
 }

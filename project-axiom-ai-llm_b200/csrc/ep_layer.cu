@@ -192,6 +192,7 @@ int ep_forward_impl(const AxmEpLayout* layout, const AxmMoeDesc* desc, const Axm
   const int T = desc->tokens, D = desc->d_model, E = desc->num_experts, k = desc->top_k, S = desc->num_shared;
   const int G = layout->world, El = E / G;
   AxmEpLayout l = *layout;  // this call's row counts (a chunk may hold fewer tokens than the region was sized for)
+  l.return_rows = layout->return_rows > layout->slots ? layout->return_rows : layout->slots;
   l.slots = T * k;
   l.tokens_local = T;
   l.num_shared = S;

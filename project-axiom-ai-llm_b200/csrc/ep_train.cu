@@ -272,6 +272,7 @@ int prepare(const AxmEpLayout* layout, const AxmMoeDesc* desc, const AxmMoeTrain
   if (step == 0) return fail(AXM_ERR_ARGUMENT, "step starts at 1 and grows by one per call");
   c->El = desc->num_experts / layout->world;
   c->l = *layout;
+  c->l.return_rows = layout->return_rows > layout->slots ? layout->return_rows : layout->slots;
   c->l.slots = desc->tokens * desc->top_k;
   c->l.tokens_local = desc->tokens;
   c->l.num_shared = 0;  // the exchange carries routed rows only; shared experts stay on their rank
@@ -408,6 +409,7 @@ extern "C" int axm_moe_ep_backward(const AxmEpLayout* fwd_layout, const AxmEpLay
   EpTrainWs& w = c.w;
   const int D = desc->d_model, E = desc->num_experts, k = desc->top_k;
   AxmEpLayout lb = *bwd_layout;
+  lb.return_rows = bwd_layout->return_rows > bwd_layout->slots ? bwd_layout->return_rows : bwd_layout->slots;
   lb.slots = c.l.slots;
   lb.tokens_local = c.l.tokens_local;
   lb.num_shared = 0;

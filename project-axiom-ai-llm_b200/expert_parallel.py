@@ -348,7 +348,13 @@ class ExpertParallelMoeP2P:
                 out = torch.empty_like(x)
             self.step += 1
             t = self.ep_tensors(x, out)
-            check(self.lib.axm_moe_ep_forward(ctypes.byref(self.layout), ctypes.byref(self.desc_layer),
+            desc = self.desc_layer
+            if x.shape[0] != self.Tl:
+                # fewer tokens than the regions were sized for (an uneven last batch; the ranks need
+                # not hold the same number): the call carries its own token count
+                assert x.shape[0] <= self.Tl
+                desc = make_desc(x.shape[0], self.D, self.F, self.E, self.k, self.S, desc.router_dtype, desc.flags)
+            check(self.lib.axm_moe_ep_forward(ctypes.byref(self.layout), ctypes.byref(desc),
                                               ctypes.byref(t), ptr(self.workspace), self.workspace.numel(),
                                               self.step, current_stream()))
             return out

@@ -84,6 +84,49 @@ def _worker(rank, world, port, name, tokens, transport, out_dir):
         dist.destroy_process_group()
 
 
+def _uneven_worker(rank, world, port, out_dir):
+    sys.path.insert(0, HERE)
+    import importlib
+    import conftest
+    axm = conftest.load_package()
+    wl = importlib.import_module("project_axiom_ai_llm_b200.workloads")
+    ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = wl.scaled(wl.CONFIGS["C2"], tokens=1024)
+        x, w = wl.make_inputs(cfg)
+        x, w = x.to(dev), {k: v.to(dev) for k, v in w.items()}
+        bounds = [0, 600, 1024]            # rank 0 holds 600 tokens, rank 1 the other 424
+        layer = ep.ExpertParallelMoeP2P(ep.shard_weights(w, rank, world), 600, cfg.num_experts, cfg.top_k)
+        xl = x[bounds[rank]:bounds[rank + 1]].contiguous()
+        out = layer.forward(xl).clone()
+        out2 = layer.forward(xl)           # flags and buffers reused
+        torch.cuda.synchronize()
+        layer.check_status()
+        assert torch.equal(out, out2) and out.shape[0] == bounds[rank + 1] - bounds[rank]
+        torch.save(out.cpu(), os.path.join(out_dir, f"u{rank}.pt"))
+        if rank == 0:
+            ref, _ = axm.MoeLayer(w, cfg.tokens, cfg.top_k).forward(x)
+            torch.cuda.synchronize()
+            torch.save(ref.cpu(), os.path.join(out_dir, "uref.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_ranks_with_different_token_counts(tmp_path):
+    """An uneven batch: the ranks hold different numbers of tokens (each at most what the exchange
+    regions were sized for); the gathered output still equals the single-GPU layer's."""
+    mp.start_processes(_uneven_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True,
+                       start_method="spawn")
+    parts = [torch.load(os.path.join(str(tmp_path), f"u{r}.pt")) for r in range(2)]
+    assert torch.equal(torch.cat(parts), torch.load(os.path.join(str(tmp_path), "uref.pt")))
+
+
 @pytest.mark.parametrize("transport", ["c-layer", "c-layer-exact", "nccl", "p2p", "p2p-copy"])
 @pytest.mark.parametrize("name,tokens", [("C1", 64), ("C2", 1024), ("C4", 2048)])
 def test_expert_parallel_equals_single_gpu(tmp_path, name, tokens, transport):
