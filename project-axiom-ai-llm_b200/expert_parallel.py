@@ -526,33 +526,42 @@ class ExpertParallelTrainP2P:
             self.d_shared_up.data_ptr() if g and self.S else None,
             self.d_shared_down.data_ptr() if g and self.S else None)
 
-    def forward(self, x):
-        """Enqueues the forward pass; self.aux then holds this rank's share of the auxiliary loss."""
+    def forward(self, x, tokens_global=None):
+        """Enqueues the forward pass; self.aux then holds this rank's share of the auxiliary loss.
+        A rank may bring fewer tokens than the layer was sized for (an uneven last batch); then
+        tokens_global is this step's token count over all ranks and out / d_x are used up to
+        x.shape[0] rows."""
         self.step_no += 1
         t = self.tensors(x, None)
-        check(self.lib.axm_moe_ep_forward_train(ctypes.byref(self.layouts[0]), ctypes.byref(self.desc),
-                                                ctypes.byref(t), self.tokens_global, ptr(self.workspace),
+        self.step_desc, self.step_tokens = self.desc, self.tokens_global
+        if x.shape[0] != self.Tl or tokens_global is not None:
+            assert x.shape[0] <= self.Tl and tokens_global is not None
+            d = self.desc
+            self.step_desc = make_desc(x.shape[0], self.D, self.F, self.E, self.k, self.S, d.router_dtype, d.flags)
+            self.step_tokens = tokens_global
+        check(self.lib.axm_moe_ep_forward_train(ctypes.byref(self.layouts[0]), ctypes.byref(self.step_desc),
+                                                ctypes.byref(t), self.step_tokens, ptr(self.workspace),
                                                 self.workspace.numel(), self.step_no, current_stream()))
-        return self.out
+        return self.out[:x.shape[0]]
 
     def backward(self, x, d_out, reduce=True):
         """Enqueues the backward pass of the last forward(); reduce=True adds the replicated
         router's gradients (and the auxiliary loss) over the ranks."""
         t = self.tensors(x, d_out)
         check(self.lib.axm_moe_ep_backward(ctypes.byref(self.layouts[0]), ctypes.byref(self.layouts[1]),
-                                           ctypes.byref(self.desc), ctypes.byref(t), self.tokens_global,
+                                           ctypes.byref(self.step_desc), ctypes.byref(t), self.step_tokens,
                                            ptr(self.workspace), self.workspace.numel(), self.step_no,
                                            current_stream()))
         if reduce:
             dist.all_reduce(self.replicated, group=self.group)
             if self.S and self.weight_grads:
                 dist.all_reduce(self.d_shared, group=self.group)
-        return self.d_x
+        return self.d_x[:x.shape[0]]
 
-    def step(self, x, d_out, reduce=True):
-        self.forward(x)
+    def step(self, x, d_out, reduce=True, tokens_global=None):
+        out = self.forward(x, tokens_global=tokens_global)
         self.backward(x, d_out, reduce=reduce)
-        grads = {"d_x": self.d_x, "d_router_w": self.d_router_w}
+        grads = {"d_x": self.d_x[:x.shape[0]], "d_router_w": self.d_router_w}
         if self.d_router_bias is not None:
             grads["d_router_bias"] = self.d_router_bias
         if self.weight_grads:
@@ -560,4 +569,4 @@ class ExpertParallelTrainP2P:
             if self.S:
                 grads.update(d_shared_gate=self.d_shared_gate, d_shared_up=self.d_shared_up,
                              d_shared_down=self.d_shared_down)
-        return self.out, self.aux, grads
+        return out, self.aux, grads

@@ -218,3 +218,59 @@ def test_expert_parallel_training_step_equals_single_gpu(tmp_path, name, tokens)
         assert (p["d_router_w"] - ref["d_router_w"]).abs().max().item() <= 1e-5 * max(scale, 1.0)
         assert (p["d_router_bias"] - ref["d_router_bias"]).abs().max().item() <= 1e-4
         assert abs(p["aux"].item() - ref["aux"].item()) <= 1e-6
+
+
+def _uneven_train_worker(rank, world, port, out_dir):
+    sys.path.insert(0, HERE)
+    import importlib
+    import conftest
+    axm = conftest.load_package()
+    wl = importlib.import_module("project_axiom_ai_llm_b200.workloads")
+    ep = importlib.import_module("project_axiom_ai_llm_b200.expert_parallel")
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        cfg = wl.scaled(wl.CONFIGS["C5"], tokens=512, d_model=512, d_ff=1024)
+        x, w = wl.make_inputs(cfg)
+        d_out = torch.randn(cfg.tokens, cfg.d_model, generator=torch.Generator().manual_seed(99))
+        x, d_out, w = x.to(dev), d_out.to(dev), {k: v.to(dev) for k, v in w.items()}
+        bounds = [0, 300, 512]             # 300 tokens on rank 0, 212 on rank 1; the layer is sized for 320
+        layer = ep.ExpertParallelTrainP2P(ep.shard_weights(w, rank, world), 320, cfg.num_experts, cfg.top_k)
+        xl = x[bounds[rank]:bounds[rank + 1]].contiguous()
+        dl = d_out[bounds[rank]:bounds[rank + 1]].contiguous()
+        for _ in range(2):
+            out, aux, grads = layer.step(xl, dl, tokens_global=cfg.tokens)
+        torch.cuda.synchronize()
+        layer.check_status()
+        assert out.shape[0] == xl.shape[0] and grads["d_x"].shape[0] == xl.shape[0]
+        torch.save({"out": out.cpu(), "aux": aux.cpu(), **{k: v.cpu() for k, v in grads.items()}},
+                   os.path.join(out_dir, f"ut{rank}.pt"))
+        if rank == 0:
+            single = axm.MoeTrainLayer(w, cfg.tokens, cfg.top_k)
+            out, aux, grads = single.step(x, d_out)
+            torch.cuda.synchronize()
+            torch.save({"out": out.cpu(), "aux": aux.cpu(), **{k: v.cpu() for k, v in grads.items()}},
+                       os.path.join(out_dir, "utref.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_training_step_with_different_token_counts_per_rank(tmp_path):
+    """An uneven last batch in training: 300 + 212 tokens on two ranks against the single-GPU step on
+    all 512 (the auxiliary loss and its gradient use the token count over all ranks)."""
+    mp.start_processes(_uneven_train_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True,
+                       start_method="spawn")
+    ref = torch.load(os.path.join(str(tmp_path), "utref.pt"))
+    parts = [torch.load(os.path.join(str(tmp_path), f"ut{r}.pt")) for r in range(2)]
+    assert torch.equal(torch.cat([p["out"] for p in parts]), ref["out"])
+    assert torch.equal(torch.cat([p["d_x"] for p in parts]), ref["d_x"])
+    for k in ("d_w_gate", "d_w_up", "d_w_down"):
+        assert torch.equal(torch.cat([p[k] for p in parts]), ref[k]), k
+    for p in parts:
+        scale = ref["d_router_w"].abs().max().item()
+        assert (p["d_router_w"] - ref["d_router_w"]).abs().max().item() <= 1e-5 * max(scale, 1.0)
+        assert abs(p["aux"].item() - ref["aux"].item()) <= 1e-6
