@@ -117,6 +117,35 @@ def test_configs_on_slices(axm, workloads, oracle, cuda_device, name, tokens, sl
                          exact=run_layer(axm, cfg, x, w, cuda_device, h_exact=True))
 
 
+def test_c3_full_size_properties_and_oracle_slice(axm, workloads, oracle, cuda_device):
+    """The benchmark workload at its full size (8192 tokens, d_model 4096, 8 experts of d_ff 14336,
+    2.8 GB of weights): properties that do not depend on the size, a 64-token slice recomputed by a
+    small call (per-token results do not depend on the batch they are in), and a 32-token slice
+    against the CPU oracle in both modes - routing and permutation of the whole batch bit for bit."""
+    cfg = workloads.CONFIGS["C3"]
+    x, w = workloads.make_inputs(cfg)
+    layer, out = run_layer(axm, cfg, x, w, cuda_device)
+    exact = run_layer(axm, cfg, x, w, cuda_device, h_exact=True)
+    check_against_oracle(oracle, cfg, x, w, layer, out, tok_range=(4000, 4032), exact=exact)
+    n = cfg.tokens * cfg.top_k
+    assert int(layer.histogram.sum()) == n and int(layer.offsets[-1]) == n
+    rs = layer.row_src.long()
+    assert torch.equal(torch.sort(rs).values, torch.arange(n, device=cuda_device))
+    assert torch.equal(rs[layer.slot_dst.long()], torch.arange(n, device=cuda_device))
+    xd = x.to(cuda_device)
+    assert torch.isfinite(out.float()).all()
+    assert torch.equal(out, (xd.float() + layer.y.float()).bfloat16())          # residual identity
+    out1 = out.clone()
+    out2, _ = layer.forward(xd)
+    assert torch.equal(out1, out2)                                              # determinism
+    out3, _ = layer.forward(xd.flip(0).contiguous())
+    assert torch.equal(out3.flip(0), out1)                                      # token-permutation equivariance
+    small = axm.MoeLayer(layer.w, 64, cfg.top_k)
+    out_s, _ = small.forward(xd[5000:5064].contiguous())
+    assert torch.equal(out_s, out1[5000:5064])                                  # batch independence
+    assert layer.status() == 0 and small.status() == 0
+
+
 def test_c2_full_size_properties(axm, workloads, cuda_device):
     cfg = workloads.CONFIGS["C2"]
     x, w = workloads.make_inputs(cfg, device=cuda_device)
