@@ -146,6 +146,23 @@ def test_c3_full_size_properties_and_oracle_slice(axm, workloads, oracle, cuda_d
     assert layer.status() == 0 and small.status() == 0
 
 
+def test_c4_full_size_oracle_slice(axm, workloads, oracle, cuda_device):
+    """The skewed workload at its full size (16384 tokens, 64 experts + 2 shared, top-6, Zipf logit
+    bias): a 32-token slice against the oracle in both modes, the whole batch's routing, permutation
+    and histogram bit for bit, determinism, and the hottest expert holding 10 - 15 % of the slots."""
+    cfg = workloads.CONFIGS["C4"]
+    x, w = workloads.make_inputs(cfg)
+    layer, out = run_layer(axm, cfg, x, w, cuda_device)
+    exact = run_layer(axm, cfg, x, w, cuda_device, h_exact=True)
+    check_against_oracle(oracle, cfg, x, w, layer, out, tok_range=(9000, 9032), exact=exact)
+    hist = layer.histogram.cpu().numpy()
+    assert int(hist.sum()) == cfg.tokens * cfg.top_k
+    assert 0.08 <= hist.max() / hist.sum() <= 0.20, f"hottest expert holds {hist.max() / hist.sum():.3f} of the slots"
+    out1 = out.clone()
+    out2, _ = layer.forward(x.to(cuda_device))
+    assert torch.equal(out1, out2) and layer.status() == 0
+
+
 def test_c2_full_size_properties(axm, workloads, cuda_device):
     cfg = workloads.CONFIGS["C2"]
     x, w = workloads.make_inputs(cfg, device=cuda_device)
