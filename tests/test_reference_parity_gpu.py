@@ -30,11 +30,14 @@ def run_both(axm, workloads, cuda_device, cfg):
     return x, w, wd, ref, r
 
 
-# the reference's own test shape (core/test/test_ai.cpp:944-1015), C1, and C2
+# the reference's own test shape (core/test/test_ai.cpp:944-1015), C1, and C2 - at 512 tokens with
+# the CPU oracle beside it, and at its full 4096 tokens (the largest workload the reference's
+# kernels can launch: about 0.4 s on the GPU) against the reference alone
 CASES = [
     dict(name="C1", tokens=256, d_model=32, d_ff=64),
     dict(name="C1"),
     dict(name="C2", tokens=512),
+    dict(name="C2"),
 ]
 
 
@@ -99,6 +102,8 @@ def test_layer_output_matches_reference(axm, workloads, oracle, cuda_device, cas
                                  what=f"out vs reference ({mode})",
                                  out_step=2.0 ** -8 if exact else 2.0 ** -7, **tail)
     assert torch.equal(r["final"], r["residual_out"])
+    if cfg.tokens > 1024:
+        return   # the oracle leg below is host work in proportion to the tokens; covered at 512
     # the CPU oracle run the reference way agrees with the reference to bf16 rounding
     y_o, out_o = oracle.forward(x, w, ref_idx.cpu().numpy(),
                                 torch.stack([r["w_first"], r["w_second"]], 1).cpu().numpy())
