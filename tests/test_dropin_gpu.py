@@ -56,7 +56,7 @@ def test_dropin_against_oracle(axm, workloads, oracle, cuda_device, kw):
 @pytest.mark.skipif(not reference_binding.available(),
                     reason="parity unpinned: oracle/_ref not built (oracle/build_ref.sh)")
 @pytest.mark.parametrize("name,kw", [("C1", dict(tokens=256, d_model=32, d_ff=64)), ("C1", dict()),
-                                     ("C2", dict(tokens=512))])
+                                     ("C2", dict(tokens=512)), ("C2", dict())])   # the last: C2 at full size
 def test_dropin_against_reference_binary(axm, workloads, cuda_device, name, kw):
     cfg = workloads.scaled(workloads.CONFIGS[name], **kw)
     x, w, m_new, new = drive(axm.DROPIN_PATH, workloads, cuda_device, cfg, axm)
