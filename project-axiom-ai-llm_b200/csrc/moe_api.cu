@@ -4,6 +4,7 @@
 // enqueue router -> dispatch -> expert FFN -> combine on the caller's stream and
 // report only enqueue-time errors.  Unlike the engine it allocates nothing: all
 // scratch comes from the caller's workspace.
+#include <cmath>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -448,6 +449,43 @@ HostPipe* host_pipe() {
 }
 }  // namespace
 
+// Chunk sizes for the host pipeline when every expert holds a handful of 256-row tile pairs per
+// chunk (few experts, routing close to uniform: no logit bias, no shared experts).  A chunk of t
+// tokens gives an expert about t k / E rows, with a binomial spread; it costs the expert
+// pairs(t) = ceil((mean + 2.5 sigma) / 256) tile pairs whether they are full or not.  Even chunks
+// waste pairs (three chunks of 2731 tokens of an 8192-token, 8-expert, top-2 batch need 3 pairs
+// per expert for 683 rows each).  Instead: a first chunk of one pair per expert, so that little
+// copy-in time is exposed, then the remaining pairs in two chunks as full as their pairs allow.
+// Writes the three token counts to `tokens` and returns true, or returns false when the batch
+// does not fit that pattern.  Measured on 8192 tokens, d_model 4096, 8 experts of 14336 with the
+// GPU at its sustained clocks: 5.78 - 5.98 ms per call against 6.09 - 6.24 for three even chunks
+// (5.00 device-resident).
+static bool tile_aware_schedule(int T, int E, int k, int* tokens) {
+  auto pairs = [&](int t) {
+    const double mean = (double)t * k / E;
+    const double sigma = sqrt(mean * (1.0 - 1.0 / E));
+    return (int)ceil((mean + 2.5 * sigma) / 256.0);
+  };
+  auto cap = [&](int p) {  // most tokens (a multiple of 64) that p pairs per expert hold
+    int t = (int)((double)p * 256.0 * E / k) / 64 * 64;
+    while (t > 0 && pairs(t) > p) t -= 64;
+    return t;
+  };
+  const int p_total = pairs(T);
+  if (p_total < 3 || p_total > 24) return false;
+  const int t1 = cap(1);
+  if (t1 < 256 || t1 >= T) return false;
+  const int p_rest = p_total - 1, p2 = (p_rest + 1) / 2, p3 = p_rest - p2;
+  int t2 = cap(p2);
+  if (t2 > T - t1) t2 = T - t1;
+  const int t3 = T - t1 - t2;
+  if (t3 <= 0 || t3 > cap(p3)) return false;
+  tokens[0] = t1;
+  tokens[1] = t2;
+  tokens[2] = t3;
+  return true;
+}
+
 // Tokens are independent, so the batch is cut into chunks and pipelined: while chunk c
 // is computed on the caller's stream, chunk c+1 comes in over PCIe on a copy stream and
 // chunk c-1 goes out on another.  Per-token results do not depend on the chunking.
@@ -474,7 +512,8 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
   // 2:3:3:2 6.55, six 7.04, against 4.6 ms for the layer alone.  Where the copies take as
   // long as the compute (smaller layers), more chunks pay.  So: from 4096 tokens on, three
   // chunks if the estimated compute time is well above the copy-in time, else four; two
-  // from 1024 tokens.  AXM_HOST_CHUNKS = n (1..8) asks for n even chunks,
+  // from 1024 tokens; with few experts and near-uniform routing the three chunks are sized in tile
+  // pairs instead (tile_aware_schedule above).  AXM_HOST_CHUNKS = n (1..8) asks for n even chunks,
   // AXM_HOST_SCHEDULE = "a,b,..." (up to 8 positive integers) for chunks in those
   // proportions; a schedule whose largest chunk does not fit twice into the workspace
   // falls back to even chunks of the same count.
@@ -485,6 +524,12 @@ extern "C" int axm_moe_forward_host(const AxmMoeDesc* desc, const AxmMoeTensors*
     const double compute_s = 6.0 * T * (double)(k + desc->num_shared) * D * (double)desc->d_ff / 1.3e15;
     const double copy_in_s = (double)T * row_bytes / 28e9;
     if (compute_s > 1.5 * copy_in_s) chunks = 3;
+    // Few experts with many rows each: the cost of a chunk is set by how many 256-row tile pairs
+    // each expert needs, so the chunks are sized in tile pairs (see tile_aware_schedule).
+    if (t->router_bias == nullptr && desc->num_shared == 0 && tile_aware_schedule(T, E, k, weights)) {
+      chunks = 3;
+      uneven = true;
+    }
   }
   if (const char* env = getenv("AXM_HOST_CHUNKS")) {
     int v = atoi(env);
