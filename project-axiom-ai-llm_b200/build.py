@@ -16,7 +16,7 @@ LIB = os.path.join(HERE, "libaxm_moe.so")
 DROPIN = os.path.join(HERE, "libaxm_moe_dropin.so")
 
 CORE_SOURCES = ["moe_api.cu", "router.cu", "router_tc.cu", "permute.cu", "grouped_ffn.cu", "noalloc.cu",
-                "ep_exchange.cu", "ep_layer.cu", "ep_train.cu", "decode_ffn.cu", "grouped_bwd.cu", "backward.cu",
+                "ep_exchange.cu", "ep_layer.cu", "ep_train.cu", "grouped_bwd.cu", "backward.cu",
                 "grouped_ffn_2sm.cu", "grouped_bwd_2sm.cu", "checkpoint.cu"]
 DROPIN_SOURCES = ["dropin.cu"]
 

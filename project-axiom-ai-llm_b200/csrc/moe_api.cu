@@ -115,14 +115,6 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                       cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u);
 
-// GEMV-style expert FFN for calls of at most four tokens (decode_ffn.cu).
-size_t decode_partial_bytes(const AxmMoeDesc* d);
-bool decode_path_wanted(const AxmMoeDesc* d);
-int launch_decode_ffn(const AxmMoeDesc* d, const void* x_perm, const void* x_alt, const AxmSegment* segments,
-                      int32_t num_segments, const void* w_gate, const void* w_up, const void* w_down,
-                      const void* shared_gate, const void* shared_up, const void* shared_down, void* h, void* o,
-                      void* partial, int32_t rows_total, cudaStream_t st, cudaEvent_t between);
-
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 // Carves the workspace.  With base == nullptr it only measures.
@@ -142,7 +134,6 @@ struct Workspace {
   void* router_scratch;  // split, transposed router weights of the tensor-core router (may be empty)
   size_t router_scratch_bytes;
   float* rstd;           // [T] per-token 1/rms of the fused pre-norm call
-  void* decode_partial;  // split sums of the decode-sized down projection (empty beyond four tokens)
   size_t bytes;
 };
 
@@ -173,7 +164,6 @@ static Workspace carve(const AxmMoeDesc* d, void* base) {
   axm_moe_router_scratch_bytes(d, &w.router_scratch_bytes);
   w.router_scratch = take(w.router_scratch_bytes);
   w.rstd = static_cast<float*>(take(sizeof(float) * T));
-  w.decode_partial = take(decode_partial_bytes(d));
   w.bytes = off;
   return w;
 }
@@ -210,8 +200,8 @@ extern "C" int axm_moe_forward_launches(const AxmMoeDesc* desc) {
   size_t scratch = 0;
   axm_moe_router_scratch_bytes(desc, &scratch);
   // router (preceded by its weight-preparation kernel on the tensor-core path), permute,
-  // gate/up GEMM, down GEMM (decode-sized calls: gate/up, down in four splits, their sum), combine
-  return (scratch > 0 ? 6 : 5) + (decode_path_wanted(desc) ? 1 : 0);
+  // gate/up GEMM, down GEMM, combine
+  return scratch > 0 ? 6 : 5;
 }
 
 extern "C" int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes) {
@@ -286,14 +276,9 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
                       w.x_perm, w.segments, router_cleared_status ? nullptr : w.status, st, 1, rstd, norm_gamma);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[2], st);
-  if (decode_path_wanted(desc))
-    rc = launch_decode_ffn(desc, w.x_perm, t->x, w.segments, E + S, t->w_gate, t->w_up, t->w_down, t->shared_gate,
-                           t->shared_up, t->shared_down, w.h, w.o, w.decode_partial, T * k + T * S, st,
-                           ev ? ev[3] : nullptr);
-  else
-    rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
-                           t->w_down, t->shared_gate, t->shared_up, t->shared_down, w.h, w.o,
-                           T * k + T * S, w.status, st, ev ? ev[3] : nullptr, nullptr, nullptr, nullptr);
+  rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
+                         t->w_down, t->shared_gate, t->shared_up, t->shared_down, w.h, w.o,
+                         T * k + T * S, w.status, st, ev ? ev[3] : nullptr, nullptr, nullptr, nullptr);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[4], st);
   const float* o_shared =
