@@ -107,6 +107,9 @@ def test_golden_small(axm, cuda_device):
     # decode-sized batches with the full layer dimensions: one token, a small batch, 64 tokens
     # (most experts then hold a handful of rows, some none)
     ("C3", 1, None), ("C3", 16, None), ("C3", 64, None), ("C2", 1, None), ("C2", 16, None), ("C2", 64, None),
+    # a few more of the smallest calls: C4 adds shared experts, top-6 of 64 and a logit bias
+    ("C3", 2, None), ("C3", 4, None), ("C2", 3, None), ("C4", 1, None), ("C4", 4, None), ("C1", 3, None),
+    ("C5", 4, None),
 ])
 def test_configs_on_slices(axm, workloads, oracle, cuda_device, name, tokens, slice_):
     cfg = workloads.scaled(workloads.CONFIGS[name], tokens=tokens)
