@@ -48,6 +48,12 @@ struct Gemm2Args {
   int h_ld;
   int lo_off;
   int two_term;
+  // kModeDown, calls with so few rows that the tile list would leave most CTA pairs idle: the
+  // reduction is cut into k_splits ranges of k-blocks, every (tile, range) is a unit of its own,
+  // and range z stores its partial sums at out + z * split_stride floats (a small kernel adds
+  // them in range order).  1: the whole reduction in one unit, stored at out.
+  int k_splits;
+  long long split_stride;
 };
 
 constexpr int kStagesDh = 5;  // operand stages of kModeDH (one stage's room goes to its epilogue blocks)
@@ -141,7 +147,10 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   const int cluster_id = blockIdx.x >> 1;
   const int num_clusters = gridDim.x >> 1;
   constexpr int BN_OUT = kSwiGLU ? 128 : 256;
-  const int n_tiles = (args.n_total + BN_OUT - 1) / BN_OUT;
+  const int k_splits = (kMode == kModeDown && args.k_splits > 1) ? args.k_splits : 1;
+  // with k_splits > 1 the "column tile" index that orders the units carries the split in its
+  // low part: n_tiles counts (column tile, split) pairs
+  const int n_tiles = ((args.n_total + BN_OUT - 1) / BN_OUT) * k_splits;
   const int kb_half = (args.k_total + BK - 1) / BK;
   const bool two_term = kMode == kModeDown && args.two_term != 0;
   // kModeDX: dG x Wg, then dU x Wu; two-term down: every weight k-block twice (hi rows, lo rows)
@@ -231,8 +240,11 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         const CUtensorMap* mb = kSwiGLU ? (rank == 0 ? (shared_w ? &tm_b0_sh : &tm_b0)
                                                      : (shared_w ? &tm_b1_sh : &tm_b1))
                                         : (shared_w ? &tm_b0_sh : &tm_b0);
-        const int n_col = uc.n_tile * BN_OUT + (kSwiGLU ? 0 : (int)rank * 128);
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        const int n_col = (uc.n_tile / k_splits) * BN_OUT + (kSwiGLU ? 0 : (int)rank * 128);
+        const int kb_per = (k_blocks + k_splits - 1) / k_splits;
+        const int kb0 = (uc.n_tile % k_splits) * kb_per;
+        const int kb1 = kb0 + kb_per < k_blocks ? kb0 + kb_per : k_blocks;
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sh->empty[stage], phase ^ 1u, abort_flag)) {
             raise_abort();
             ok = false;
@@ -280,7 +292,14 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)acc * UMMA_N;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        int kb0 = 0, kb1 = k_blocks;
+        if (k_splits > 1) {
+          const UnitCoord uc = decode_unit(sh, n_tiles, unit, 0);
+          const int kb_per = (k_blocks + k_splits - 1) / k_splits;
+          kb0 = (uc.n_tile % k_splits) * kb_per;
+          kb1 = kb0 + kb_per < k_blocks ? kb0 + kb_per : k_blocks;
+        }
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&sh->full[stage], phase, abort_flag)) {
             raise_abort();
             ok = false;
@@ -295,7 +314,7 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 #pragma unroll
           for (int j = 0; j < BK / UMMA_K; ++j)
             tc_mma2_bf16(d_tmem, da + (uint64_t)(j * 2), db + (uint64_t)(j * (kBKmajor ? 2 : 128)),
-                         kBKmajor ? kInstrDesc2KB : kInstrDesc2, (kb > 0 || j > 0) ? 1u : 0u);
+                         kBKmajor ? kInstrDesc2KB : kInstrDesc2, (kb > kb0 || j > 0) ? 1u : 0u);
           // free this stage in both CTAs once the MMAs that read it are done
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 0));
           tc_commit2(map_to_cta(smem_u32(&sh->empty[stage]), 1));
@@ -349,8 +368,10 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       tc_fence_after();
       const int row_in_seg = uc.m_tile * BM + quad * 32 + lane;
       const bool row_ok = uc.live && row_in_seg < sg.rows;
-      const int n0 = uc.n_tile * BN_OUT;
-      const size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0;
+      const int n0 = (uc.n_tile / k_splits) * BN_OUT;
+      // range z of a split reduction stores into its own copy of the output
+      const size_t out_elem = (size_t)(sg.out_row0 + (row_ok ? row_in_seg : 0)) * args.n_total + n0 +
+                              (k_splits > 1 ? (size_t)(uc.n_tile % k_splits) * (size_t)args.split_stride : 0);
       const uint32_t t_addr = tmem_base + ((uint32_t)(quad * 32) << 16) + (uint32_t)acc * UMMA_N;
       if constexpr (kDH) {
         // The SwiGLU derivative with the saved g, u: dG = dH u s (1 + g (1 - s)), dU = dH g s,
@@ -536,6 +557,44 @@ grouped_gemm_2sm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   }
 }
 
+// o[i] = sum over the ranges of a split down projection, in range order.
+__global__ void __launch_bounds__(256)
+down_split_reduce_kernel(const float* __restrict__ partial, float* __restrict__ o, long long n, int splits) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  float s = 0.0f;
+  for (int z = 0; z < splits; ++z) s += partial[(size_t)z * n + i];
+  o[i] = s;
+}
+
+// Scratch for the partial sums of a split down projection, lent for the duration of one layer
+// call by a caller that owns a workspace (axm_moe_forward); other callers run unsplit.
+constexpr int kSplitTokensMax = 8;
+constexpr int kSplitsMax = 4;
+static thread_local void* g_split_scratch = nullptr;
+static thread_local size_t g_split_scratch_bytes = 0;
+void set_down_split_scratch(void* p, size_t bytes) {
+  g_split_scratch = p;
+  g_split_scratch_bytes = bytes;
+}
+// Ranges the down projection of this call is cut into on `pairs` CTA pairs (1: not split).
+int down_splits_for(const AxmMoeDesc* d, int pairs) {
+  const int D = d->d_model, F = d->d_ff, E = d->num_experts, S = d->num_shared;
+  if ((d->flags & AXM_FLAG_H_EXACT) || d->tokens <= 0 || d->tokens > kSplitTokensMax || pairs <= 0) return 1;
+  const long long rows_max = (long long)d->tokens * (d->top_k + S);
+  const int n_tiles = (D + 255) / 256, k_blocks = (F + BK - 1) / BK;
+  const long long units_max = (rows_max < E + S ? rows_max : (long long)(E + S)) * n_tiles;
+  if (units_max <= 0) return 1;
+  int splits = (int)((2LL * pairs + units_max - 1) / units_max);  // about two units per CTA pair
+  if (splits > kSplitsMax) splits = kSplitsMax;
+  while (splits > 1 && (splits - 1) * ((k_blocks + splits - 1) / splits) >= k_blocks) --splits;  // no empty range
+  return splits < 1 ? 1 : splits;
+}
+size_t down_split_scratch_bytes(const AxmMoeDesc* d) {
+  if (d->tokens <= 0 || d->tokens > kSplitTokensMax) return 0;
+  return sizeof(float) * kSplitsMax * (size_t)d->tokens * (d->top_k + d->num_shared) * d->d_model;
+}
+
 // Row-major bf16 matrix of `rows` x `cols` whose rows are `ld` elements apart (0: cols).
 static int map2_rows(CUtensorMap* m, const void* base, uint64_t rows, uint64_t cols, uint64_t ld = 0) {
   const uint64_t dims[2] = {cols, rows};
@@ -627,6 +686,8 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.h_ld = (int)h_ld;
   ga.lo_off = exact ? F : 0;
   ga.two_term = 0;
+  ga.k_splits = 1;
+  ga.split_stride = 0;
   ga.segments = segments;
   ga.num_segments = num_segments;
   ga.routed_experts = E;
@@ -650,9 +711,30 @@ int launch_expert_ffn_2sm(const AxmMoeDesc* d, const void* x_perm, int32_t a_row
   ga.save_u = nullptr;
   ga.out1 = nullptr;
   ga.two_term = exact ? 1 : 0;
+  ga.k_splits = 1;
+  ga.split_stride = 0;
+  // A call with a handful of tokens touches few experts, each with one tile pair: fewer units than
+  // CTA pairs (one token, top-2, D = 4096: 32 units for 74 pairs).  The reduction is then cut
+  // into up to four ranges that run as units of their own and are added afterwards, if the
+  // caller has lent the scratch for their partial sums.
+  int splits = down_splits_for(d, grid / 2);
+  const size_t split_bytes = sizeof(float) * (size_t)splits * rows_total * D;
+  if (splits > 1 && (g_split_scratch == nullptr || g_split_scratch_bytes < split_bytes)) splits = 1;
+  if (splits > 1) {
+    ga.k_splits = splits;
+    ga.split_stride = (long long)rows_total * D;
+    ga.out = g_split_scratch;
+  }
   grouped_gemm_2sm_kernel<kModeDown><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(a2, a2_lo, dn, dn, dn_sh, dn_sh, a2,
                                                                                   a2, a2, a2, ga);
-  return check_launch("grouped_gemm_2sm_kernel<down>");
+  if (int rc2 = check_launch("grouped_gemm_2sm_kernel<down>")) return rc2;
+  if (splits > 1) {
+    const long long n = (long long)rows_total * D;
+    down_split_reduce_kernel<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(static_cast<const float*>(g_split_scratch),
+                                                                         static_cast<float*>(o), n, splits);
+    return check_launch("down_split_reduce_kernel");
+  }
+  return AXM_OK;
 }
 
 // Weights [experts][n_rows][k_cols] read K-major by a CTA pair: box = 64 k x 128 n x 1 expert.
@@ -709,6 +791,8 @@ int launch_bwd_dh_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.h_ld = F;
   ga.lo_off = 0;
   ga.two_term = 0;
+  ga.k_splits = 1;
+  ga.split_stride = 0;
   grouped_gemm_2sm_kernel<kModeDH><<<grid, kGemmThreads, kGemm2DhSmemBytes, st>>>(m_do, m_do, m_wd, m_wd, m_wd,
                                                                                   m_wd, m_g, m_u, m_dg, m_du, ga);
   return check_launch("grouped_gemm_2sm_kernel<dH>");
@@ -747,6 +831,8 @@ int launch_bwd_dx_2sm(const AxmMoeDesc* d, const AxmSegment* segments, int32_t n
   ga.h_ld = D;
   ga.lo_off = 0;
   ga.two_term = 0;
+  ga.k_splits = 1;
+  ga.split_stride = 0;
   grouped_gemm_2sm_kernel<kModeDX><<<grid, kGemmThreads, kGemm2SmemBytes, st>>>(m_dg, m_du, m_wg, m_wu, m_wg,
                                                                                 m_wu, m_dg, m_dg, m_dg, m_dg, ga);
   return check_launch("grouped_gemm_2sm_kernel<dX>");

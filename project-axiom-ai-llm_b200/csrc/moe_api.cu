@@ -115,6 +115,12 @@ int launch_expert_ffn(const AxmMoeDesc* d, const void* x_perm, int32_t a_rows, c
                       void* h, void* o, int32_t rows_total, int32_t* status, cudaStream_t st,
                       cudaEvent_t between, const AxmRemoteOut* remote, void* save_g, void* save_u);
 
+// Scratch of the split down projection of calls with a handful of tokens (grouped_ffn_2sm.cu).
+void set_down_split_scratch(void* p, size_t bytes);
+size_t down_split_scratch_bytes(const AxmMoeDesc* d);
+int down_splits_for(const AxmMoeDesc* d, int pairs);
+bool use_2sm_kernels();
+
 static size_t align256(size_t v) { return (v + 255) & ~static_cast<size_t>(255); }
 
 // Carves the workspace.  With base == nullptr it only measures.
@@ -134,6 +140,8 @@ struct Workspace {
   void* router_scratch;  // split, transposed router weights of the tensor-core router (may be empty)
   size_t router_scratch_bytes;
   float* rstd;           // [T] per-token 1/rms of the fused pre-norm call
+  void* down_split;      // partial sums of the split down projection (empty beyond eight tokens)
+  size_t down_split_bytes;
   size_t bytes;
 };
 
@@ -164,6 +172,8 @@ static Workspace carve(const AxmMoeDesc* d, void* base) {
   axm_moe_router_scratch_bytes(d, &w.router_scratch_bytes);
   w.router_scratch = take(w.router_scratch_bytes);
   w.rstd = static_cast<float*>(take(sizeof(float) * T));
+  w.down_split_bytes = down_split_scratch_bytes(d);
+  w.down_split = take(w.down_split_bytes);
   w.bytes = off;
   return w;
 }
@@ -200,8 +210,10 @@ extern "C" int axm_moe_forward_launches(const AxmMoeDesc* desc) {
   size_t scratch = 0;
   axm_moe_router_scratch_bytes(desc, &scratch);
   // router (preceded by its weight-preparation kernel on the tensor-core path), permute,
-  // gate/up GEMM, down GEMM, combine
-  return scratch > 0 ? 6 : 5;
+  // gate/up GEMM, down GEMM (plus the sum of its ranges when a handful of tokens makes it split
+  // the reduction; counted for the 74 CTA pairs of a B200), combine
+  const int split = (use_2sm_kernels() && down_splits_for(desc, 74) > 1) ? 1 : 0;
+  return (scratch > 0 ? 6 : 5) + split;
 }
 
 extern "C" int axm_moe_workspace_bytes(const AxmMoeDesc* desc, size_t* bytes) {
@@ -276,9 +288,11 @@ static int forward_impl(const AxmMoeDesc* desc, const AxmMoeTensors* t, void* wo
                       w.x_perm, w.segments, router_cleared_status ? nullptr : w.status, st, 1, rstd, norm_gamma);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[2], st);
+  set_down_split_scratch(w.down_split, w.down_split_bytes);
   rc = launch_expert_ffn(desc, w.x_perm, T * k, t->x, T, w.segments, E + S, t->w_gate, t->w_up,
                          t->w_down, t->shared_gate, t->shared_up, t->shared_down, w.h, w.o,
                          T * k + T * S, w.status, st, ev ? ev[3] : nullptr, nullptr, nullptr, nullptr);
+  set_down_split_scratch(nullptr, 0);
   if (rc) return rc;
   if (ev) cudaEventRecord(ev[4], st);
   const float* o_shared =
