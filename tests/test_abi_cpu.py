@@ -63,6 +63,14 @@ def test_workspace_size_and_launch_count(axm):
     assert axm.load().axm_moe_forward_launches(ctypes.byref(wide)) == 5
     d0 = axm.make_desc(0, 2048, 5632, 8, 2)
     assert axm.load().axm_moe_forward_launches(ctypes.byref(d0)) == 0
+    # up to eight tokens the down projection splits its reduction (one more launch: the sum of the
+    # ranges) and the workspace holds the ranges' partial sums; not in the strict-tolerance mode
+    few = axm.make_desc(1, 4096, 14336, 8, 2)
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(few)) == 7
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(axm.make_desc(16, 4096, 14336, 8, 2))) == 6
+    few_x = axm.make_desc(1, 4096, 14336, 8, 2, flags=axm.FLAG_RESIDUAL | axm.FLAG_H_EXACT)
+    assert axm.load().axm_moe_forward_launches(ctypes.byref(few_x)) == 6
+    assert axm.workspace_bytes(few) >= 4 * 2 * 4096 * 4
 
 
 @pytest.mark.parametrize("kw", [
